@@ -1,0 +1,202 @@
+/*
+ * vtlb.h -- C ABI of libvtlb200.so: the B200 (sm_100a) device layer for the
+ * dense-contraction hot path of vlang/vtl.
+ *
+ * This is the boundary a V build of vtl binds with `fn C.vtlb_*` declarations in
+ * `*_d_b200.v` files.  It takes the place of the calls vtl makes today into the
+ * VSL CUDA wrappers; each entry point names the reference interface it replaces
+ * (paths inside vlang/vtl).
+ *
+ * Conventions
+ *  - every function returns 0 (VTLB_OK) or a negative VTLB_E* code and never
+ *    throws or aborts; vtlb_last_error(ctx) gives the message of the last failure;
+ *  - one vtlb_ctx per GPU; calls on one ctx are issued from one thread at a time
+ *    (the reference is single-threaded) and are ordered on the ctx's stream;
+ *    they are asynchronous unless stated, vtlb_sync() and vtlb_d2h() block;
+ *  - `const void* d_*` / `void* d_*` arguments are DEVICE pointers obtained from
+ *    vtlb_alloc (offsets into such allocations are fine, 16-byte aligned);
+ *    `h_*` arguments are HOST pointers borrowed for the duration of the call;
+ *  - matrices are dense row-major with the stated shape; there is no CPU
+ *    fallback anywhere: without a usable GPU every call fails with VTLB_ECUDA.
+ */
+#ifndef VTLB_H
+#define VTLB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VTLB_OK 0
+#define VTLB_EINVAL (-1)   /* bad argument (shape, alignment, null pointer) */
+#define VTLB_ECUDA (-2)    /* a CUDA runtime/driver call failed */
+#define VTLB_ENOMEM (-3)   /* device allocation failed */
+#define VTLB_ETIMEOUT (-4) /* a bounded device-side wait gave up; see vtlb_check_status */
+#define VTLB_ENCCL (-5)    /* NCCL missing or a collective failed */
+#define VTLB_ESTATE (-6)   /* call not valid in the ctx's current state */
+
+typedef struct vtlb_ctx vtlb_ctx;
+
+/* ---- context ------------------------------------------------------------
+ * Replaces: cuda.get_default_device()/cuda.get_device(id) as used by
+ * storage/cuda_d_cuda.v:32-47 and DeviceSession.init_device
+ * (autograd_cuda/device_session_d_cuda.v:9-15); the session pointer kept in
+ * Context.device_session (autograd/context.v:23). */
+int vtlb_device_count(int* count);
+int vtlb_ctx_create(int device, vtlb_ctx** out);
+int vtlb_ctx_destroy(vtlb_ctx* ctx);
+int vtlb_sync(vtlb_ctx* ctx);
+const char* vtlb_last_error(vtlb_ctx* ctx); /* ctx may be NULL: process-wide last error */
+/* Reads and clears the device status word written by kernels whose bounded
+ * waits ran out (0 = none).  Blocks until the stream is idle. */
+int vtlb_check_status(vtlb_ctx* ctx, uint32_t* status);
+/* Number of kernels this library launched on ctx since creation. */
+uint64_t vtlb_launch_count(vtlb_ctx* ctx);
+/* cudaStream_t of the ctx (as void*), for callers that time with CUDA events. */
+void* vtlb_stream(vtlb_ctx* ctx);
+
+/* Device-side timing with CUDA events on the ctx's compute stream (measurement
+ * helper; no counterpart in the reference, which times with time.ticks()). */
+int vtlb_event_create(vtlb_ctx* ctx, void** ev_out);
+int vtlb_event_record(vtlb_ctx* ctx, void* ev);
+int vtlb_event_elapsed_ms(vtlb_ctx* ctx, void* ev_start, void* ev_stop, float* ms); /* blocks */
+int vtlb_event_destroy(vtlb_ctx* ctx, void* ev);
+
+/* ---- memory ---------------------------------------------------------------
+ * Replaces: CpuStorage.cuda()/CudaStorage.cpu()/to_array()/release()
+ * (storage/cuda_d_cuda.v:32-107), the raw C.cudaMalloc/cudaMemcpy/cudaFree of
+ * autograd_cuda/device_session_gpu_d_cuda.v:24-45,118-152 and
+ * compute.GpuBufF64{ensure,upload,download,release}
+ * (autograd_cuda/device_session_optimizer_d_cuda.v:7-59). */
+int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out);
+int vtlb_free(vtlb_ctx* ctx, void* d_ptr);
+int vtlb_h2d(vtlb_ctx* ctx, void* d_dst, const void* h_src, size_t bytes);
+int vtlb_d2h(vtlb_ctx* ctx, void* h_dst, const void* d_src, size_t bytes); /* blocks */
+int vtlb_d2d(vtlb_ctx* ctx, void* d_dst, const void* d_src, size_t bytes);
+int vtlb_memset0(vtlb_ctx* ctx, void* d_dst, size_t bytes);
+/* Pinned host staging memory for fast h2d/d2h (optional; any host memory works). */
+int vtlb_host_alloc(size_t bytes, void** h_out);
+int vtlb_host_free(void* h_ptr);
+/* Grows the ctx's internal scratch (operand-split buffers, partial sums) to at
+ * least `bytes` ahead of time, so that later calls allocate nothing. */
+int vtlb_reserve_scratch(vtlb_ctx* ctx, size_t bytes);
+
+/* ---- f32 GEMM -------------------------------------------------------------
+ * C[M,N] = op(A).op(B) (+ bias[N]) (ReLU).  op(A) is [M,K]: A is [M,K] row-major
+ * when transA == 0, [K,M] when transA != 0; likewise B is [K,N] or, with transB,
+ * [N,K].  Computed on tcgen05 tensor cores as a 3-pass TF32 split (hi.hi +
+ * hi.lo + lo.hi) with f32 accumulation in tensor memory.
+ * Replaces: la.matmul[f32] (la/la.v:38-55), gate_matmul
+ * (autograd/gates_blas.v:6-23), compute.gemm_cuda as called from
+ * autograd_cuda/device_session_d_cuda.v:43 and tensor_cuda_d_cuda.v:169, and
+ * C.cublasDgemm_v2 (autograd_cuda/device_session_gpu_d_cuda.v:143). */
+int vtlb_gemm_f32(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const void* d_A,
+                  const void* d_B, void* d_C, const void* d_bias_or_null, int relu);
+
+/* ---- Linear layer ---------------------------------------------------------
+ * Y[M,N] = X[M,K].W[N,K]^T + b[N]; with relu != 0, Y = relu(.) and, when
+ * d_pre_or_null is given, the pre-activation is stored there as well (it is
+ * the cache the ReLU gate needs).
+ * Replaces: linear_forward_f32 (nn/layers/linear_forward_f32.v:7-18),
+ * DeviceSession.linear_forward_f64 (autograd_cuda/device_session_d_cuda.v:17-57)
+ * and linear_forward_gpu_chain (device_session_gpu_d_cuda.v:88-181). */
+int vtlb_linear_fwd_f32(vtlb_ctx* ctx, const void* d_X, const void* d_W, const void* d_b_or_null,
+                        void* d_Y, int M, int N, int K, int relu, void* d_pre_or_null);
+/* dX[M,K] = G.W, dW[N,K] = G^T.X, db[N] = column sums of G; any of the three
+ * outputs may be NULL.  Outputs are overwritten (the first accumulation onto a
+ * zero gradient in Variable.backprop, autograd/variable.v:105).
+ * Replaces: LinearGate.backward (nn/gates/layers/linear.v:25-95),
+ * linear_backward_f64 (autograd_cuda/linear_backward_cuda_d_cuda.v:9-34),
+ * linear_gate_backward_f32_try (nn/gates/layers/linear_gate_backward_f32_try_*.v:6). */
+int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X, const void* d_W,
+                        void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N,
+                        int K);
+
+/* ---- ReLU -----------------------------------------------------------------
+ * y = x < 0 ? 0 : x;   dx = cached_x < 0 ? 0 : g   (gradient passes at exactly 0).
+ * Replaces: relu_forward_f32_try (nn/layers/activation_relu_forward_f32_try_*.v:6),
+ * compute.relu_cuda (tensor_cuda_d_cuda.v:208), internal.relu / deriv_relu
+ * (nn/internal/activation.v:63-87). */
+int vtlb_relu_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, size_t n);
+int vtlb_relu_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_cached_x, void* d_dx, size_t n);
+
+/* ---- losses ---------------------------------------------------------------
+ * MSE as the reference computes it: loss = sum((p-t)^2)/n, dP = (p - t) * g with
+ * no 2/n factor (nn/internal/activation.v:365-373, nn/internal/loss.v:7-12).
+ * d_loss receives one f32 (`loss_scale` multiplies it: pass 1, or 1/ranks ... as
+ * needed by the caller); d_dP may be NULL.  `n_div` is the divisor n (the global
+ * element count when rows are sharded over ranks). */
+int vtlb_mse_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_P, const void* d_T, size_t n, size_t n_div,
+                         void* d_loss, void* d_dP_or_null);
+/* Softmax cross-entropy over rows of X[B,C] against targets T[B,C]
+ * (nn/internal/activation.v:392-420, nn/internal/loss.v:39-65): f64 inside,
+ * loss = sum_i(lse_i - t_i.x_i)/batch_div, dX = (softmax - t)/batch_div. */
+int vtlb_softmax_ce_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_X, const void* d_T, int B, int C,
+                                int batch_div, void* d_loss, void* d_dX_or_null);
+
+/* ---- Adam / AdamW ---------------------------------------------------------
+ * One fused multi-tensor launch per call.  Scalars are the f64 values of
+ * AdamStepParams (nn/optimizers/adam_step_f64.v:6-12); lr_t is computed by the
+ * caller as AdamOptimizer.update does (nn/optimizers/adam.v:88-91).
+ * zero_grad != 0 also clears the gradients (adam.v:142).
+ * Adam  : f32 arithmetic of adam_step_f32_cpu (nn/optimizers/adam_step_f32.v:6-21).
+ * AdamW : f64 arithmetic on f32 state of AdamWOptimizer.update (adamw.v:84-104).
+ * Replaces: adam_update_f64_cuda / adam_step_f64 and their 14 BLAS-1 launches
+ * (nn/optimizers/adam_f64_d_cuda.v:8-20, adam_step_cuda_d_cuda.v:8-121),
+ * try_adam_update_f32_vulkan (adam_f32_vulkan_d_vulkan.v:23). */
+typedef struct vtlb_adam_tensor {
+  void* d_grad;
+  void* d_theta;
+  void* d_m;
+  void* d_v;
+  size_t n;
+} vtlb_adam_tensor;
+int vtlb_adam_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors, double beta1,
+                       double beta2, double lr_t, double epsilon, int zero_grad);
+int vtlb_adamw_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors,
+                        double beta1, double beta2, double lr_t, double epsilon,
+                        double weight_decay, int zero_grad);
+
+/* ---- INT8 quantised linear ------------------------------------------------
+ * No counterpart in the reference (it has no quantisation code); defined here:
+ *   amax_r = max_k |a_rk|;  inv = amax_r > 0 ? 127/amax_r : 0;
+ *   q_rk = clamp(rint(a_rk * inv), -127, 127);  scale_r = amax_r / 127     (all f32)
+ * Code matrices are row-major int8 with leading dimension vtlb_i8_ld(K)
+ * (K rounded up to a multiple of 16; the padding bytes are never read).
+ * vtlb_quant_rows_i8 serves activations (rows of A[M,K]) and weights (rows of
+ * W[N,K], i.e. output channels).  With d_amax_in_or_null the row maxima are
+ * taken from there instead of being computed (column-sharded layers). */
+int vtlb_i8_ld(int K);
+int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_Q, void* d_scale,
+                       const void* d_amax_in_or_null);
+int vtlb_row_absmax_f32(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_amax);
+/* acc[M,N] (int32) = Aq[M,K].Wq[N,K]^T, exact (tcgen05 kind::i8). */
+int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq, int M, int N, int K,
+                     void* d_acc);
+/* Y[M,N] = relu?( (float)acc * (sa[m]*sw[n]) + bias[n] ), the dequantisation
+ * fused into the GEMM epilogue; every f32 operation rounds on its own. */
+int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa, const void* d_Wq,
+                       const void* d_sw, const void* d_bias_or_null, void* d_Y, int M, int N,
+                       int K, int relu);
+
+/* ---- collectives (NCCL over NVLink) ---------------------------------------
+ * No counterpart in the reference (single device).  One ctx per rank/process.
+ * vtlb_comm_unique_id fills a 128-byte id on one rank; the caller ships it to
+ * the others (any host channel) and every rank calls vtlb_comm_init_rank. */
+int vtlb_comm_unique_id(void* h_id128);
+int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void* h_id128);
+int vtlb_comm_destroy(vtlb_ctx* ctx);
+/* In-place sum over ranks, enqueued on the ctx's communication stream after the
+ * work already enqueued on the compute stream; returns at once. */
+int vtlb_allreduce_sum_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
+int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
+int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_recv, size_t bytes_per_rank);
+/* Makes the compute stream wait for every collective enqueued so far. */
+int vtlb_comm_wait(vtlb_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VTLB_H */

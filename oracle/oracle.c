@@ -1,0 +1,499 @@
+/*
+ * CPU oracle for the dense-contraction hot path of vlang/vtl.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file restates, in plain C, the arithmetic the
+ * reference performs on its CPU path, so that the CUDA kernels can be checked
+ * against it.  It is never linked into, imported by, or called from the product
+ * library; only the tests, the smoke check and the CPU-baseline leg of the
+ * benchmark load it.
+ *
+ * Parity status: the f32/f64 functions are pinned against the known-answer
+ * tests the reference ships for this path (identity matmul, MSE 0 / 4.0 / grad
+ * 2.0, the Adam and Linear vectors of its CUDA-vs-CPU tests, the 1x1x4x4 conv
+ * case).  The f64 GEMM itself lives in the un-vendored VSL module
+ * (vsl@v0.2.0-beta.1, BLAS dgemm), whose summation order is unspecified: it is
+ * restated as "accumulate in f64, round once".  The INT8 functions have no
+ * counterpart in the reference: PARITY UNPINNED for them; their definition is
+ * the one written in the comments below and both sides implement exactly it.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC (see Makefile).
+ * -ffp-contract=off matters: every f32 expression below is meant to round after
+ * each operation, as the reference's V-to-C output does on x86-64.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ matmul */
+
+/* la.matmul[T] (la/la.v:38-55) and gate_matmul (autograd/gates_blas.v:6-23):
+ * operands are cast to f64, multiplied by VSL's matrix_matrix_mul (dgemm) and
+ * the result is cast back to T once.  ta/tb select op(A)=A^T / op(B)=B^T with
+ * true-transpose semantics (the math nn/layers/linear.v:10 documents and
+ * autograd_cuda/device_session.v:38-46 implements with an explicit W^T).
+ * A is [M,K] (or [K,M] when ta), B is [K,N] (or [N,K] when tb), C is [M,N]. */
+ORC_API void orc_matmul_f32(const float *A, const float *B, float *C, int M, int N, int K,
+                            int ta, int tb) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    for (int j = 0; j < N; ++j) {
+      double acc = 0.0;
+      for (int k = 0; k < K; ++k) {
+        double a = ta ? (double)A[(size_t)k * M + i] : (double)A[(size_t)i * K + k];
+        double b = tb ? (double)B[(size_t)j * K + k] : (double)B[(size_t)k * N + j];
+        acc += a * b;
+      }
+      C[(size_t)i * N + j] = (float)acc;
+    }
+  }
+}
+
+ORC_API void orc_matmul_f64(const double *A, const double *B, double *C, int M, int N, int K,
+                            int ta, int tb) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    for (int j = 0; j < N; ++j) {
+      double acc = 0.0;
+      for (int k = 0; k < K; ++k) {
+        double a = ta ? A[(size_t)k * M + i] : A[(size_t)i * K + k];
+        double b = tb ? B[(size_t)j * K + k] : B[(size_t)k * N + j];
+        acc += a * b;
+      }
+      C[(size_t)i * N + j] = acc;
+    }
+  }
+}
+
+/* The as-written behaviour of la.matmul on a transposed VIEW: Tensor.copy()
+ * (a_tensor.v:162-174) clones the flat buffer and re-derives row-major strides
+ * from the view's shape, so matmul(x, w.t()) multiplies by reshape(W_buf,[K,N]).
+ * Kept for forensic comparison only; no parity test uses it. */
+ORC_API void orc_matmul_f32_copy_quirk(const float *X, const float *Wbuf, float *C, int M, int N,
+                                       int K) {
+  orc_matmul_f32(X, Wbuf, C, M, N, K, 0, 0);
+}
+
+/* ------------------------------------------------------------------ linear */
+
+/* LinearLayer.forward -> linear_forward_f32_cpu (nn/layers/linear_forward_f32.v:16-18):
+ * Y = matmul(X, W^T) + b, the add being an f32 broadcast add.  X[M,K], W[N,K], b[N]. */
+ORC_API void orc_linear_fwd_f32(const float *X, const float *W, const float *b, float *Y, int M,
+                                int N, int K) {
+  orc_matmul_f32(X, W, Y, M, N, K, 0, 1);
+  if (b)
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) Y[(size_t)i * N + j] = Y[(size_t)i * N + j] + b[j];
+}
+
+/* linear_forward_f64_cpu (autograd_cuda/device_session.v) */
+ORC_API void orc_linear_fwd_f64(const double *X, const double *W, const double *b, double *Y,
+                                int M, int N, int K) {
+  orc_matmul_f64(X, W, Y, M, N, K, 0, 1);
+  if (b)
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) Y[(size_t)i * N + j] += b[j];
+}
+
+/* LinearGate.backward (nn/gates/layers/linear.v:69-79):
+ * dX = G.W, dW = G^T.X, db = ones[1,M].G, each through la.matmul. */
+ORC_API void orc_linear_bwd_f32(const float *G, const float *X, const float *W, float *dX,
+                                float *dW, float *db, int M, int N, int K) {
+  if (dX) orc_matmul_f32(G, W, dX, M, K, N, 0, 0);
+  if (dW) orc_matmul_f32(G, X, dW, N, K, M, 1, 0);
+  if (db) {
+    float *ones = (float *)malloc(sizeof(float) * (size_t)M);
+    for (int i = 0; i < M; ++i) ones[i] = 1.0f;
+    orc_matmul_f32(ones, G, db, 1, N, M, 0, 0);
+    free(ones);
+  }
+}
+
+/* linear_backward_f64_cpu (autograd_cuda/linear_backward_f64.v:7-18) */
+ORC_API void orc_linear_bwd_f64(const double *G, const double *X, const double *W, double *dX,
+                                double *dW, double *db, int M, int N, int K) {
+  if (dX) orc_matmul_f64(G, W, dX, M, K, N, 0, 0);
+  if (dW) orc_matmul_f64(G, X, dW, N, K, M, 1, 0);
+  if (db)
+    for (int j = 0; j < N; ++j) {
+      double s = 0.0;
+      for (int i = 0; i < M; ++i) s += 1.0 * G[(size_t)i * N + j];
+      db[j] = s;
+    }
+}
+
+/* -------------------------------------------------------------------- relu */
+
+/* internal.relu (nn/internal/activation.v:63-70): val < 0 -> 0 else val. */
+ORC_API void orc_relu_f32(const float *x, float *y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] < 0 ? 0.0f : x[i];
+}
+
+/* internal.deriv_relu (nn/internal/activation.v:78-87): cached < 0 -> 0 else g.
+ * `cached` is the pre-activation input (nn/layers/relu.v:34-49). */
+ORC_API void orc_relu_bwd_f32(const float *g, const float *cached, float *dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) dx[i] = cached[i] < 0 ? 0.0f : g[i];
+}
+
+/* ------------------------------------------------------------------ losses */
+
+/* internal.mse (nn/internal/activation.v:365-373): sequential f32 sum, in
+ * row-major order, of (f32)pow((f64)(p - t), 2), divided by (f32)size. */
+ORC_API float orc_mse_f32(const float *p, const float *t, size_t n) {
+  float acc = 0.0f;
+  for (size_t i = 0; i < n; ++i) {
+    float d = p[i] - t[i];
+    float next = (float)pow((double)d, 2.0);
+    acc = acc + next;
+  }
+  return acc / (float)n;
+}
+
+ORC_API double orc_mse_f64(const double *p, const double *t, size_t n) {
+  double acc = 0.0;
+  for (size_t i = 0; i < n; ++i) acc += pow(p[i] - t[i], 2.0);
+  return acc / (double)n;
+}
+
+/* internal.mse_backward (nn/internal/loss.v:7-12): g * (p - t) / g.size, where
+ * the upstream gradient g is the [1] tensor of ones set by backprop()
+ * (autograd/variable.v:87-109), so g.size == 1 and there is no 2/N factor. */
+ORC_API void orc_mse_bwd_f32(const float *p, const float *t, float *dp, size_t n, float g) {
+  for (size_t i = 0; i < n; ++i) dp[i] = g * (p[i] - t[i]) / 1.0f;
+}
+
+/* internal.softmax_cross_entropy (nn/internal/activation.v:392-420): f64 inside,
+ * max-subtracted log-sum-exp, mean over the batch, cast to T at the end. */
+ORC_API float orc_softmax_ce_f32(const float *x, const float *t, int B, int C) {
+  double total = 0.0;
+  for (int i = 0; i < B; ++i) {
+    const float *xi = x + (size_t)i * C, *ti = t + (size_t)i * C;
+    double mx = (double)xi[0];
+    for (int c = 1; c < C; ++c)
+      if ((double)xi[c] > mx) mx = (double)xi[c];
+    double se = 0.0;
+    for (int c = 0; c < C; ++c) se += exp((double)xi[c] - mx);
+    double lse = log(se) + mx;
+    double dot = 0.0;
+    for (int c = 0; c < C; ++c) dot += (double)ti[c] * (double)xi[c];
+    total += lse - dot;
+  }
+  return (float)(total / (double)B);
+}
+
+/* softmax_cross_entropy_backward (nn/internal/loss.v:39-65):
+ * upstream * (softmax - target) / batch in f64, cast to T.  `batch_div` is the
+ * divisor (the batch; the global batch when rows are sharded over ranks). */
+ORC_API void orc_softmax_ce_bwd_f32(const float *x, const float *t, float *dx, int B, int C,
+                                    double upstream, int batch_div) {
+  for (int i = 0; i < B; ++i) {
+    const float *xi = x + (size_t)i * C, *ti = t + (size_t)i * C;
+    double mx = (double)xi[0];
+    for (int c = 1; c < C; ++c)
+      if ((double)xi[c] > mx) mx = (double)xi[c];
+    double se = 0.0;
+    for (int c = 0; c < C; ++c) se += exp((double)xi[c] - mx);
+    for (int c = 0; c < C; ++c) {
+      double sm = exp((double)xi[c] - mx) / se;
+      dx[(size_t)i * C + c] = (float)(upstream * (sm - (double)ti[c]) / (double)batch_div);
+    }
+  }
+}
+
+/* -------------------------------------------------------------------- conv */
+
+/* conv2d_forward_cpu_f32 (nn/internal/conv2d_forward_cpu_f32.v:26-62), groups=1,
+ * dilation as given: NCHW direct convolution; the sum starts at 0f and
+ * accumulates in f32 in (ic, kh, kw) order, then + bias. */
+ORC_API void orc_conv2d_fwd_f32(const float *x, const float *w, const float *bias, float *y,
+                                int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
+                                int sh, int sw, int dh, int dw) {
+  int OH = (H + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+  int OW = (W + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int b = 0; b < B; ++b)
+    for (int oc = 0; oc < O; ++oc)
+      for (int oh = 0; oh < OH; ++oh)
+        for (int ow = 0; ow < OW; ++ow) {
+          float sum = 0.0f;
+          for (int ic = 0; ic < C; ++ic)
+            for (int r = 0; r < kh; ++r)
+              for (int s = 0; s < kw; ++s) {
+                int ih = oh * sh - ph + r * dh, iw = ow * sw - pw + s * dw;
+                if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                  float prod = x[(((size_t)b * C + ic) * H + ih) * W + iw] *
+                               w[(((size_t)oc * C + ic) * kh + r) * kw + s];
+                  sum = sum + prod;
+                }
+              }
+          y[(((size_t)b * O + oc) * OH + oh) * OW + ow] = sum + (bias ? bias[oc] : 0.0f);
+        }
+}
+
+/* conv2d_backward_cpu_f32 (nn/internal/conv2d_backward_cpu_f32.v:26-97):
+ * d_input scatter-add in (b, oc, oh, ow, ic, kh, kw) order; d_weight[oc,ic,kh,kw]
+ * = sequential f32 sum over (b, oh, ow); d_bias[oc] = sequential f32 sum. */
+ORC_API void orc_conv2d_bwd_f32(const float *g, const float *x, const float *w, float *dx,
+                                float *dwt, float *db, int B, int C, int H, int W, int O, int kh,
+                                int kw, int ph, int pw, int sh, int sw, int dh, int dw) {
+  int OH = (H + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+  int OW = (W + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+  if (dx) {
+    memset(dx, 0, sizeof(float) * (size_t)B * C * H * W);
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; ++b)
+      for (int oc = 0; oc < O; ++oc)
+        for (int oh = 0; oh < OH; ++oh)
+          for (int ow = 0; ow < OW; ++ow) {
+            float goh = g[(((size_t)b * O + oc) * OH + oh) * OW + ow];
+            for (int ic = 0; ic < C; ++ic)
+              for (int r = 0; r < kh; ++r)
+                for (int s = 0; s < kw; ++s) {
+                  int ih = oh * sh - ph + r * dh, iw = ow * sw - pw + s * dw;
+                  if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                    size_t xi = (((size_t)b * C + ic) * H + ih) * W + iw;
+                    float prod = goh * w[(((size_t)oc * C + ic) * kh + r) * kw + s];
+                    dx[xi] = dx[xi] + prod;
+                  }
+                }
+          }
+  }
+  if (dwt) {
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int oc = 0; oc < O; ++oc)
+      for (int ic = 0; ic < C; ++ic)
+        for (int r = 0; r < kh; ++r)
+          for (int s = 0; s < kw; ++s) {
+            float sum = 0.0f;
+            for (int b = 0; b < B; ++b)
+              for (int oh = 0; oh < OH; ++oh)
+                for (int ow = 0; ow < OW; ++ow) {
+                  int ih = oh * sh - ph + r * dh, iw = ow * sw - pw + s * dw;
+                  if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+                    float prod = x[(((size_t)b * C + ic) * H + ih) * W + iw] *
+                                 g[(((size_t)b * O + oc) * OH + oh) * OW + ow];
+                    sum = sum + prod;
+                  }
+                }
+            dwt[(((size_t)oc * C + ic) * kh + r) * kw + s] = sum;
+          }
+  }
+  if (db) {
+    for (int oc = 0; oc < O; ++oc) {
+      float sum = 0.0f;
+      for (int b = 0; b < B; ++b)
+        for (int oh = 0; oh < OH; ++oh)
+          for (int ow = 0; ow < OW; ++ow) sum = sum + g[(((size_t)b * O + oc) * OH + oh) * OW + ow];
+      db[oc] = sum;
+    }
+  }
+}
+
+/* ----------------------------------------------------------------- maxpool */
+
+/* 2-D max pooling with the window geometry of internal.maxpool2d
+ * (nn/internal/layers.v:21-66) and STANDARD selection semantics: the running
+ * maximum starts at -inf and the first maximum in (i, j) scan order wins.  The
+ * reference as written starts the maximum at +max_f64 and tests `val > max`,
+ * so no element can ever be selected, and scatters plane-local indices into
+ * the whole tensor (:73-83); no reference test pins that behaviour, so it is
+ * not reproduced.  idx holds the flat index into the whole input tensor. */
+ORC_API void orc_maxpool2d_fwd_f32(const float *x, float *y, int32_t *idx, int B, int C, int H,
+                                   int W, int kh, int kw, int ph, int pw, int sh, int sw) {
+  int OH = (H + 2 * ph - kh) / sh + 1, OW = (W + 2 * pw - kw) / sw + 1;
+  for (int n = 0; n < B; ++n)
+    for (int c = 0; c < C; ++c)
+      for (int h = 0; h < OH; ++h)
+        for (int w = 0; w < OW; ++w) {
+          int hs = h * sh - ph, ws = w * sw - pw;
+          int he = hs + kh, we = ws + kw;
+          if (hs < 0) hs = 0;
+          if (ws < 0) ws = 0;
+          if (he > H) he = H;
+          if (we > W) we = W;
+          float best = -INFINITY;
+          int32_t bi = -1;
+          for (int i = hs; i < he; ++i)
+            for (int j = ws; j < we; ++j) {
+              size_t fi = (((size_t)n * C + c) * H + i) * W + j;
+              if (bi < 0 || x[fi] > best) {
+                best = x[fi];
+                bi = (int32_t)fi;
+              }
+            }
+          size_t o = (((size_t)n * C + c) * OH + h) * OW + w;
+          y[o] = best;
+          idx[o] = bi;
+        }
+}
+
+/* maxpool2d_backward (nn/internal/layers.v:69-84) with whole-tensor indices:
+ * zeros, then ret[idx[i]] = g[i] (windows do not overlap when stride == kernel). */
+ORC_API void orc_maxpool2d_bwd_f32(const float *g, const int32_t *idx, float *dx, size_t n_out,
+                                   size_t n_in) {
+  memset(dx, 0, sizeof(float) * n_in);
+  for (size_t i = 0; i < n_out; ++i) dx[idx[i]] = dx[idx[i]] + g[i];
+}
+
+/* -------------------------------------------------------------------- adam */
+
+/* adam_step_f32_cpu (nn/optimizers/adam_step_f32.v:6-21).  Scalars arrive as
+ * f64 (AdamStepParams) and are cast to f32; (1 - beta) is formed in f64 first. */
+ORC_API void orc_adam_step_f32(const float *grad, float *theta, float *m, float *v, size_t n,
+                               double beta1, double beta2, double lr_t, double epsilon) {
+  float b1 = (float)beta1, b2 = (float)beta2, lr = (float)lr_t, eps = (float)epsilon;
+  float omb1 = (float)(1.0 - beta1), omb2 = (float)(1.0 - beta2);
+  for (size_t i = 0; i < n; ++i) {
+    float g = grad[i];
+    float t0 = b1 * m[i];
+    float t1 = omb1 * g;
+    m[i] = t0 + t1;
+    float t2 = b2 * v[i];
+    float t3 = omb2 * g;
+    float t4 = t3 * g;
+    v[i] = t2 + t4;
+    float denom = (float)sqrt((double)v[i]) + eps;
+    float t5 = lr * m[i];
+    float t6 = t5 / denom;
+    theta[i] = theta[i] - t6;
+  }
+}
+
+/* adam_step_f64_cpu (nn/optimizers/adam_step_f64.v:15-23) */
+ORC_API void orc_adam_step_f64(const double *grad, double *theta, double *m, double *v, size_t n,
+                               double beta1, double beta2, double lr_t, double epsilon) {
+  for (size_t i = 0; i < n; ++i) {
+    double g = grad[i];
+    m[i] = beta1 * m[i] + (1.0 - beta1) * g;
+    v[i] = beta2 * v[i] + (1.0 - beta2) * g * g;
+    theta[i] -= lr_t * m[i] / (sqrt(v[i]) + epsilon);
+  }
+}
+
+/* AdamWOptimizer.update for T = f32 (nn/optimizers/adamw.v:84-104): three
+ * passes, each element computed in f64 and cast to f32; the third pass reads
+ * the freshly stored (f32) m and v. */
+ORC_API void orc_adamw_step_f32(const float *grad, float *theta, float *m, float *v, size_t n,
+                                double beta1, double beta2, double lr_t, double epsilon,
+                                double wd) {
+  for (size_t i = 0; i < n; ++i)
+    m[i] = (float)(beta1 * (double)m[i] + (1.0 - beta1) * (double)grad[i]);
+  for (size_t i = 0; i < n; ++i) {
+    double g = (double)grad[i];
+    v[i] = (float)(beta2 * (double)v[i] + (1.0 - beta2) * g * g);
+  }
+  for (size_t i = 0; i < n; ++i) {
+    double th = (double)theta[i], mm = (double)m[i], vv = (double)v[i];
+    theta[i] = (float)(th - lr_t * (mm / (sqrt(vv) + epsilon) + wd * th));
+  }
+}
+
+/* lr_t of AdamOptimizer.update / AdamWOptimizer.update (nn/optimizers/adam.v:88-91):
+ * beta^t starts at beta and is advanced after use. */
+ORC_API double orc_adam_lr_t(double lr, double *beta1_t, double *beta2_t, double beta1,
+                             double beta2) {
+  double lr_t = lr * sqrt(1.0 - *beta2_t) / (1.0 - *beta1_t);
+  *beta1_t *= beta1;
+  *beta2_t *= beta2;
+  return lr_t;
+}
+
+/* -------------------------------------------------------------------- int8 */
+
+/* Symmetric per-row quantisation (not in the reference; definition):
+ *   amax = max_k |a_k| (f32);  inv = amax > 0 ? 127.0f / amax : 0  (IEEE f32 divide)
+ *   q_k  = (int8) clamp(rintf(a_k * inv), -127, 127)   (one f32 multiply, ties-to-even)
+ *   s    = amax / 127.0f
+ * Used for activations (rows of A[M,K]) and weights (rows of W[N,K] = output channels). */
+ORC_API void orc_quant_rows_i8(const float *A, int8_t *Q, float *scale, int M, int K) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    const float *a = A + (size_t)i * K;
+    float amax = 0.0f;
+    for (int k = 0; k < K; ++k) {
+      float v = fabsf(a[k]);
+      if (v > amax) amax = v;
+    }
+    float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    for (int k = 0; k < K; ++k) {
+      float r = rintf(a[k] * inv);
+      if (r > 127.0f) r = 127.0f;
+      if (r < -127.0f) r = -127.0f;
+      Q[(size_t)i * K + k] = (int8_t)r;
+    }
+    scale[i] = amax / 127.0f;
+  }
+}
+
+/* Quantise rows with a scale fixed by the caller (amax given): used when the
+ * row maximum was reduced over several column shards. */
+ORC_API void orc_quant_rows_i8_with_amax(const float *A, const float *amax_in, int8_t *Q,
+                                         float *scale, int M, int K) {
+  for (int i = 0; i < M; ++i) {
+    float amax = amax_in[i];
+    float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    for (int k = 0; k < K; ++k) {
+      float r = rintf(A[(size_t)i * K + k] * inv);
+      if (r > 127.0f) r = 127.0f;
+      if (r < -127.0f) r = -127.0f;
+      Q[(size_t)i * K + k] = (int8_t)r;
+    }
+    scale[i] = amax / 127.0f;
+  }
+}
+
+/* acc[m,n] = sum_k (int32)Aq[m,k] * (int32)Wq[n,k]   (exact) */
+__attribute__((target_clones("arch=skylake-avx512", "avx2", "default")))
+ORC_API void orc_gemm_i8_i32(const int8_t *Aq, const int8_t *Wq, int32_t *acc, int M, int N,
+                             int K) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    const int8_t *a = Aq + (size_t)i * K;
+    for (int j = 0; j < N; ++j) {
+      const int8_t *w = Wq + (size_t)j * K;
+      int32_t s = 0;
+      for (int k = 0; k < K; ++k) s += (int32_t)a[k] * (int32_t)w[k];
+      acc[(size_t)i * N + j] = s;
+    }
+  }
+}
+
+/* y[m,n] = relu?( (float)acc * (sa[m] * sw[n]) + bias[n] ) with separate roundings:
+ *   t = sa*sw;  u = (float)acc * t;  y = u + bias;  relu: y < 0 -> 0. */
+ORC_API void orc_dequant_bias_relu(const int32_t *acc, const float *sa, const float *sw,
+                                   const float *bias, float *Y, int M, int N, int relu) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i)
+    for (int j = 0; j < N; ++j) {
+      float t = sa[i] * sw[j];
+      float u = (float)acc[(size_t)i * N + j] * t;
+      float y = bias ? u + bias[j] : u;
+      if (relu && y < 0) y = 0.0f;
+      Y[(size_t)i * N + j] = y;
+    }
+}
+
+/* Whole quantised linear forward on pre-quantised weights. */
+ORC_API void orc_linear_i8_fwd(const float *A, const int8_t *Wq, const float *sw,
+                               const float *bias, float *Y, int M, int N, int K, int relu) {
+  int8_t *Aq = (int8_t *)malloc((size_t)M * K);
+  float *sa = (float *)malloc(sizeof(float) * (size_t)M);
+  int32_t *acc = (int32_t *)malloc(sizeof(int32_t) * (size_t)M * N);
+  orc_quant_rows_i8(A, Aq, sa, M, K);
+  orc_gemm_i8_i32(Aq, Wq, acc, M, N, K);
+  orc_dequant_bias_relu(acc, sa, sw, bias, Y, M, N, relu);
+  free(Aq);
+  free(sa);
+  free(acc);
+}
+
+ORC_API int orc_max_threads(void) {
+#ifdef _OPENMP
+  extern int omp_get_max_threads(void);
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

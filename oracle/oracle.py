@@ -1,0 +1,413 @@
+"""CPU oracle for the dense-contraction hot path (TEST INFRASTRUCTURE ONLY).
+
+NumPy front end of ``oracle.c`` (loaded through ctypes) plus BLAS-level NumPy
+restatements used where the plain C loops would take too long.  Nothing in the
+product package imports this module; only the tests, the smoke check and the
+CPU-baseline / reference legs of the benchmark do.
+
+Every function names the reference code it follows (paths inside vlang/vtl).
+The INT8 functions have no counterpart in the reference ("parity unpinned"):
+their definition is the one in ``oracle.c``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile oracle.c -> liboracle.so with the Makefile next to it."""
+    src = os.path.join(_HERE, "oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.orc_mse_f32.restype = C.c_float
+        _lib.orc_mse_f64.restype = C.c_double
+        _lib.orc_softmax_ce_f32.restype = C.c_float
+        _lib.orc_adam_lr_t.restype = C.c_double
+        _lib.orc_max_threads.restype = C.c_int
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _f64(a):
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+# ---------------------------------------------------------------- matmul
+def matmul_f32(A, B, ta=False, tb=False):
+    """la.matmul[f32] (la/la.v:38-55): f64 multiply-accumulate, one final rounding."""
+    A, B = _f32(A), _f32(B)
+    M, K = (A.shape[1], A.shape[0]) if ta else A.shape
+    N = B.shape[0] if tb else B.shape[1]
+    out = np.empty((M, N), np.float32)
+    lib().orc_matmul_f32(_p(A), _p(B), _p(out), M, N, K, int(ta), int(tb))
+    return out
+
+
+def matmul_f64(A, B, ta=False, tb=False):
+    A, B = _f64(A), _f64(B)
+    M, K = (A.shape[1], A.shape[0]) if ta else A.shape
+    N = B.shape[0] if tb else B.shape[1]
+    out = np.empty((M, N), np.float64)
+    lib().orc_matmul_f64(_p(A), _p(B), _p(out), M, N, K, int(ta), int(tb))
+    return out
+
+
+def matmul_f32_blas(A, B, ta=False, tb=False):
+    """Same recipe as matmul_f32 with NumPy's OpenBLAS dgemm doing the f64 GEMM
+    (the class of backend VSL uses with -d cblas); for sizes the C loops cannot
+    finish in seconds, and for the timed CPU baseline."""
+    a = np.asarray(A, np.float32).astype(np.float64)
+    b = np.asarray(B, np.float32).astype(np.float64)
+    if ta:
+        a = a.T
+    if tb:
+        b = b.T
+    return (a @ b).astype(np.float32)
+
+
+# ---------------------------------------------------------------- linear
+def linear_fwd_f32(X, W, b=None, blas=False):
+    """linear_forward_f32_cpu (nn/layers/linear_forward_f32.v:16-18): X.W^T + b."""
+    X, W = _f32(X), _f32(W)
+    if blas:
+        Y = matmul_f32_blas(X, W, tb=True)
+        return Y if b is None else (Y + _f32(b).reshape(1, -1)).astype(np.float32)
+    M, K = X.shape
+    N = W.shape[0]
+    Y = np.empty((M, N), np.float32)
+    bb = None if b is None else _f32(b).reshape(-1)
+    lib().orc_linear_fwd_f32(_p(X), _p(W), _p(bb), _p(Y), M, N, K)
+    return Y
+
+
+def linear_bwd_f32(G, X, W, blas=False):
+    """LinearGate.backward (nn/gates/layers/linear.v:69-79) -> (dX, dW, db[1,N])."""
+    G, X, W = _f32(G), _f32(X), _f32(W)
+    M, N = G.shape
+    K = X.shape[1]
+    if blas:
+        dX = matmul_f32_blas(G, W)
+        dW = matmul_f32_blas(G, X, ta=True)
+        db = matmul_f32_blas(np.ones((1, M), np.float32), G)
+        return dX, dW, db
+    dX = np.empty((M, K), np.float32)
+    dW = np.empty((N, K), np.float32)
+    db = np.empty((1, N), np.float32)
+    lib().orc_linear_bwd_f32(_p(G), _p(X), _p(W), _p(dX), _p(dW), _p(db), M, N, K)
+    return dX, dW, db
+
+
+def linear_fwd_f64(X, W, b):
+    X, W, b = _f64(X), _f64(W), _f64(b).reshape(-1)
+    M, K = X.shape
+    N = W.shape[0]
+    Y = np.empty((M, N), np.float64)
+    lib().orc_linear_fwd_f64(_p(X), _p(W), _p(b), _p(Y), M, N, K)
+    return Y
+
+
+def linear_bwd_f64(G, X, W):
+    G, X, W = _f64(G), _f64(X), _f64(W)
+    M, N = G.shape
+    K = X.shape[1]
+    dX = np.empty((M, K))
+    dW = np.empty((N, K))
+    db = np.empty((1, N))
+    lib().orc_linear_bwd_f64(_p(G), _p(X), _p(W), _p(dX), _p(dW), _p(db), M, N, K)
+    return dX, dW, db
+
+
+# ---------------------------------------------------------------- relu / losses
+def relu_f32(x):
+    """internal.relu (nn/internal/activation.v:63-70)."""
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_relu_f32(_p(x), _p(y), C.c_size_t(x.size))
+    return y
+
+
+def relu_bwd_f32(g, cached):
+    """internal.deriv_relu (nn/internal/activation.v:78-87)."""
+    g, cached = _f32(g), _f32(cached)
+    dx = np.empty_like(g)
+    lib().orc_relu_bwd_f32(_p(g), _p(cached), _p(dx), C.c_size_t(g.size))
+    return dx
+
+
+def mse_f32(p, t) -> np.float32:
+    """internal.mse (nn/internal/activation.v:365-373)."""
+    p, t = _f32(p), _f32(t)
+    return np.float32(lib().orc_mse_f32(_p(p), _p(t), C.c_size_t(p.size)))
+
+
+def mse_f64(p, t) -> float:
+    p, t = _f64(p), _f64(t)
+    return float(lib().orc_mse_f64(_p(p), _p(t), C.c_size_t(p.size)))
+
+
+def mse_bwd_f32(p, t, g=1.0):
+    """internal.mse_backward (nn/internal/loss.v:7-12), upstream g of size 1."""
+    p, t = _f32(p), _f32(t)
+    dp = np.empty_like(p)
+    lib().orc_mse_bwd_f32(_p(p), _p(t), _p(dp), C.c_size_t(p.size), C.c_float(g))
+    return dp
+
+
+def softmax_ce_f32(x, t) -> np.float32:
+    """internal.softmax_cross_entropy (nn/internal/activation.v:392-420)."""
+    x, t = _f32(x), _f32(t)
+    return np.float32(lib().orc_softmax_ce_f32(_p(x), _p(t), x.shape[0], x.shape[1]))
+
+
+def softmax_ce_bwd_f32(x, t, upstream=1.0, batch_div=None):
+    """softmax_cross_entropy_backward (nn/internal/loss.v:39-65)."""
+    x, t = _f32(x), _f32(t)
+    dx = np.empty_like(x)
+    bd = x.shape[0] if batch_div is None else int(batch_div)
+    lib().orc_softmax_ce_bwd_f32(_p(x), _p(t), _p(dx), x.shape[0], x.shape[1],
+                                 C.c_double(upstream), bd)
+    return dx
+
+
+# ---------------------------------------------------------------- conv / pool
+def conv_out_hw(H, W, kh, kw, ph, pw, sh, sw, dh=1, dw=1):
+    return (H + 2 * ph - dh * (kh - 1) - 1) // sh + 1, (W + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+
+
+def conv2d_fwd_f32(x, w, bias, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+    """conv2d_forward_cpu_f32 (nn/internal/conv2d_forward_cpu_f32.v:26-62)."""
+    x, w = _f32(x), _f32(w)
+    B, Ci, H, W = x.shape
+    O, _, kh, kw = w.shape
+    OH, OW = conv_out_hw(H, W, kh, kw, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1])
+    y = np.empty((B, O, OH, OW), np.float32)
+    bb = None if bias is None else _f32(bias).reshape(-1)
+    lib().orc_conv2d_fwd_f32(_p(x), _p(w), _p(bb), _p(y), B, Ci, H, W, O, kh, kw, pad[0], pad[1],
+                             stride[0], stride[1], dil[0], dil[1])
+    return y
+
+
+def conv2d_bwd_f32(g, x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1)):
+    """conv2d_backward_cpu_f32 (nn/internal/conv2d_backward_cpu_f32.v:26-97) -> (dx, dw, db[1,O])."""
+    g, x, w = _f32(g), _f32(x), _f32(w)
+    B, Ci, H, W = x.shape
+    O, _, kh, kw = w.shape
+    dx = np.empty_like(x)
+    dw = np.empty_like(w)
+    db = np.empty((1, O), np.float32)
+    lib().orc_conv2d_bwd_f32(_p(g), _p(x), _p(w), _p(dx), _p(dw), _p(db), B, Ci, H, W, O, kh, kw,
+                             pad[0], pad[1], stride[0], stride[1], dil[0], dil[1])
+    return dx, dw, db
+
+
+def maxpool2d_fwd_f32(x, kernel=(2, 2), pad=(0, 0), stride=(2, 2)):
+    """Window geometry of internal.maxpool2d (nn/internal/layers.v:21-66), standard
+    max selection and whole-tensor flat indices (see oracle.c for why)."""
+    x = _f32(x)
+    B, Ci, H, W = x.shape
+    OH = (H + 2 * pad[0] - kernel[0]) // stride[0] + 1
+    OW = (W + 2 * pad[1] - kernel[1]) // stride[1] + 1
+    y = np.empty((B, Ci, OH, OW), np.float32)
+    idx = np.empty((B, Ci, OH, OW), np.int32)
+    lib().orc_maxpool2d_fwd_f32(_p(x), _p(y), _p(idx), B, Ci, H, W, kernel[0], kernel[1], pad[0],
+                                pad[1], stride[0], stride[1])
+    return y, idx
+
+
+def maxpool2d_bwd_f32(g, idx, in_shape):
+    g = _f32(g)
+    idx = np.ascontiguousarray(idx, np.int32)
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_maxpool2d_bwd_f32(_p(g), _p(idx), _p(dx), C.c_size_t(g.size), C.c_size_t(dx.size))
+    return dx
+
+
+# ---------------------------------------------------------------- optimizers
+def adam_lr_t(lr, beta1_t, beta2_t, beta1, beta2):
+    """lr_t and advanced beta^t of AdamOptimizer.update (nn/optimizers/adam.v:88-91)."""
+    b1 = C.c_double(beta1_t)
+    b2 = C.c_double(beta2_t)
+    lr_t = lib().orc_adam_lr_t(C.c_double(lr), C.byref(b1), C.byref(b2), C.c_double(beta1),
+                               C.c_double(beta2))
+    return float(lr_t), b1.value, b2.value
+
+
+def adam_step_f32(grad, theta, m, v, beta1, beta2, lr_t, eps):
+    """adam_step_f32_cpu (nn/optimizers/adam_step_f32.v:6-21); returns new (theta, m, v)."""
+    grad = _f32(grad)
+    theta, m, v = _f32(theta).copy(), _f32(m).copy(), _f32(v).copy()
+    lib().orc_adam_step_f32(_p(grad), _p(theta), _p(m), _p(v), C.c_size_t(grad.size),
+                            C.c_double(beta1), C.c_double(beta2), C.c_double(lr_t), C.c_double(eps))
+    return theta, m, v
+
+
+def adam_step_f64(grad, theta, m, v, beta1, beta2, lr_t, eps):
+    """adam_step_f64_cpu (nn/optimizers/adam_step_f64.v:15-23)."""
+    grad = _f64(grad)
+    theta, m, v = _f64(theta).copy(), _f64(m).copy(), _f64(v).copy()
+    lib().orc_adam_step_f64(_p(grad), _p(theta), _p(m), _p(v), C.c_size_t(grad.size),
+                            C.c_double(beta1), C.c_double(beta2), C.c_double(lr_t), C.c_double(eps))
+    return theta, m, v
+
+
+def adamw_step_f32(grad, theta, m, v, beta1, beta2, lr_t, eps, wd):
+    """AdamWOptimizer.update, T=f32 (nn/optimizers/adamw.v:84-104)."""
+    grad = _f32(grad)
+    theta, m, v = _f32(theta).copy(), _f32(m).copy(), _f32(v).copy()
+    lib().orc_adamw_step_f32(_p(grad), _p(theta), _p(m), _p(v), C.c_size_t(grad.size),
+                             C.c_double(beta1), C.c_double(beta2), C.c_double(lr_t),
+                             C.c_double(eps), C.c_double(wd))
+    return theta, m, v
+
+
+# ---------------------------------------------------------------- int8
+def quant_rows_i8(A):
+    """Symmetric per-row int8 quantisation -> (codes int8 [M,K], scale f32 [M])."""
+    A = _f32(A)
+    M, K = A.shape
+    q = np.empty((M, K), np.int8)
+    s = np.empty((M,), np.float32)
+    lib().orc_quant_rows_i8(_p(A), _p(q), _p(s), M, K)
+    return q, s
+
+
+def quant_rows_i8_with_amax(A, amax):
+    A, amax = _f32(A), _f32(amax)
+    M, K = A.shape
+    q = np.empty((M, K), np.int8)
+    s = np.empty((M,), np.float32)
+    lib().orc_quant_rows_i8_with_amax(_p(A), _p(amax), _p(q), _p(s), M, K)
+    return q, s
+
+
+def gemm_i8_i32(Aq, Wq):
+    """acc[m,n] = sum_k Aq[m,k]*Wq[n,k], exact int32."""
+    Aq = np.ascontiguousarray(Aq, np.int8)
+    Wq = np.ascontiguousarray(Wq, np.int8)
+    M, K = Aq.shape
+    N = Wq.shape[0]
+    acc = np.empty((M, N), np.int32)
+    lib().orc_gemm_i8_i32(_p(Aq), _p(Wq), _p(acc), M, N, K)
+    return acc
+
+
+def dequant_bias_relu(acc, sa, sw, bias, relu):
+    acc = np.ascontiguousarray(acc, np.int32)
+    sa, sw = _f32(sa), _f32(sw)
+    M, N = acc.shape
+    Y = np.empty((M, N), np.float32)
+    bb = None if bias is None else _f32(bias).reshape(-1)
+    lib().orc_dequant_bias_relu(_p(acc), _p(sa), _p(sw), _p(bb), _p(Y), M, N, int(bool(relu)))
+    return Y
+
+
+def linear_i8_fwd(A, Wq, sw, bias, relu):
+    """Quantise rows of A, int8 GEMM against pre-quantised W, dequant + bias (+ReLU)."""
+    A = _f32(A)
+    Wq = np.ascontiguousarray(Wq, np.int8)
+    sw = _f32(sw)
+    M, K = A.shape
+    N = Wq.shape[0]
+    Y = np.empty((M, N), np.float32)
+    bb = None if bias is None else _f32(bias).reshape(-1)
+    lib().orc_linear_i8_fwd(_p(A), _p(Wq), _p(sw), _p(bb), _p(Y), M, N, K, int(bool(relu)))
+    return Y
+
+
+# ---------------------------------------------------------------- training steps
+class MLPOracle:
+    """One f32 training step exactly as the reference CPU path computes it for a
+    Sequential of Linear(+ReLU) layers with MSE loss and Adam or AdamW:
+    Sequential.forward (nn/models/sequential.v:204-215), Variable.backprop
+    (autograd/variable.v:87-109, gradients accumulate onto zeros in f32),
+    AdamOptimizer.update (nn/optimizers/adam.v:87-145) or AdamWOptimizer.update
+    (nn/optimizers/adamw.v:78-106).  ``relu_after[i]`` tells whether a ReLU layer
+    follows Linear i.  ``blas`` switches the GEMMs to OpenBLAS dgemm."""
+
+    def __init__(self, weights, biases, relu_after, lr, beta1=0.9, beta2=0.999, eps=1e-8,
+                 weight_decay=None, blas=False):
+        self.W = [_f32(w).copy() for w in weights]
+        self.b = [_f32(b).reshape(1, -1).copy() for b in biases]
+        self.relu_after = list(relu_after)
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.wd = weight_decay
+        self.beta1_t, self.beta2_t = beta1, beta2
+        self.blas = blas
+        self.mW = [np.zeros_like(w) for w in self.W]
+        self.vW = [np.zeros_like(w) for w in self.W]
+        self.mb = [np.zeros_like(b) for b in self.b]
+        self.vb = [np.zeros_like(b) for b in self.b]
+
+    def forward(self, X):
+        acts, pres = [_f32(X)], []
+        h = acts[0]
+        for W, b, r in zip(self.W, self.b, self.relu_after):
+            pre = linear_fwd_f32(h, W, b, blas=self.blas)
+            pres.append(pre)
+            h = relu_f32(pre) if r else pre
+            acts.append(h)
+        return h, acts, pres
+
+    def grads(self, X, T, grad_scale_rows=None):
+        y, acts, pres = self.forward(X)
+        loss = mse_f32(y, T)
+        g = mse_bwd_f32(y, T)
+        dWs, dbs = [None] * len(self.W), [None] * len(self.W)
+        for i in reversed(range(len(self.W))):
+            if self.relu_after[i]:
+                g = relu_bwd_f32(g, pres[i])
+            dX, dW, db = linear_bwd_f32(g, acts[i], self.W[i], blas=self.blas)
+            dWs[i], dbs[i] = dW, db
+            g = dX
+        return loss, y, dWs, dbs, g
+
+    def apply(self, dWs, dbs):
+        lr_t, self.beta1_t, self.beta2_t = adam_lr_t(self.lr, self.beta1_t, self.beta2_t,
+                                                      self.beta1, self.beta2)
+        for i in range(len(self.W)):
+            for (P, G, Mo, Vo) in ((self.W, dWs, self.mW, self.vW), (self.b, dbs, self.mb, self.vb)):
+                shp = P[i].shape
+                if self.wd is None:
+                    th, m, v = adam_step_f32(G[i].ravel(), P[i].ravel(), Mo[i].ravel(),
+                                             Vo[i].ravel(), self.beta1, self.beta2, lr_t, self.eps)
+                else:
+                    th, m, v = adamw_step_f32(G[i].ravel(), P[i].ravel(), Mo[i].ravel(),
+                                              Vo[i].ravel(), self.beta1, self.beta2, lr_t,
+                                              self.eps, self.wd)
+                P[i], Mo[i], Vo[i] = th.reshape(shp), m.reshape(shp), v.reshape(shp)
+        return lr_t
+
+    def step(self, X, T):
+        loss, y, dWs, dbs, _ = self.grads(X, T)
+        self.apply(dWs, dbs)
+        return loss

@@ -1,0 +1,100 @@
+"""f32 GEMM / Linear forward and backward on the GPU (3xTF32 on tcgen05) against the
+CPU oracle (f64 accumulate, one rounding).  Tolerance is the one the task states:
+max-abs error <= 1e-5 * sqrt(K) * max|A| * max|B|."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def tol(K, A, B):
+    return 1e-5 * np.sqrt(K) * float(np.abs(A).max()) * float(np.abs(B).max())
+
+
+@pytest.mark.parametrize("ta,tb,M,N,K", [
+    (0, 0, 2, 2, 2), (0, 1, 64, 256, 784), (0, 0, 64, 10, 256), (1, 0, 256, 784, 64),
+    (0, 1, 130, 70, 33), (1, 1, 300, 200, 100), (0, 1, 512, 512, 2048), (0, 0, 128, 384, 1000),
+])
+def test_gemm_f32(dev, orc, ta, tb, M, N, K):
+    rng = np.random.default_rng(M + 2 * N + 3 * K + ta + 2 * tb)
+    A = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    dA, dB = dev.to_device(A), dev.to_device(B)
+    dC = dev.zeros((M, N), np.float32)
+    dev.gemm_f32(ta, tb, M, N, K, dA, dB, dC)
+    assert dev.check_status() == 0
+    ref = orc.matmul_f32(A, B, bool(ta), bool(tb))
+    err = np.abs(dC.numpy() - ref).max()
+    assert err <= tol(K, A, B), f"max abs err {err} > {tol(K, A, B)}"
+    for b in (dA, dB, dC):
+        b.free()
+
+
+def test_matmul_identity_kat(dev):
+    """la/la_test.v:30-37: I . B == B exactly."""
+    a = np.array([[1.0, 0], [0.0, 1]], np.float32)
+    b = np.array([[4.0, 1], [2.0, 2]], np.float32)
+    dA, dB, dC = dev.to_device(a), dev.to_device(b), dev.zeros((2, 2), np.float32)
+    dev.gemm_f32(0, 0, 2, 2, 2, dA, dB, dC)
+    assert np.array_equal(dC.numpy(), b)
+
+
+def test_linear_kat_from_reference_session_test(dev, orc):
+    """autograd_cuda/device_session_test.v:25-48 and :60-80 (values in f32)."""
+    x = np.array([[1.0, 2.0, 3.0]], np.float32)
+    w = np.array([[0.1, 0.2, 0.3], [0.4, 0.5, 0.6]], np.float32)
+    b = np.array([0.01, 0.02], np.float32)
+    dx, dw, db = dev.to_device(x), dev.to_device(w), dev.to_device(b)
+    dy = dev.zeros((1, 2), np.float32)
+    dev.linear_fwd_f32(dx, dw, db, dy, 1, 2, 3)
+    assert np.allclose(dy.numpy(), [[1.41, 3.22]], atol=1e-6)
+    g = np.array([[1.0, 0.5]], np.float32)
+    dg = dev.to_device(g)
+    ddx, ddw, ddb = dev.zeros((1, 3)), dev.zeros((2, 3)), dev.zeros((2,))
+    dev.linear_bwd_f32(dg, dx, dw, ddx, ddw, ddb, 1, 2, 3)
+    rdx, rdw, rdb = orc.linear_bwd_f32(g, x, w)
+    assert np.allclose(ddx.numpy(), rdx, atol=1e-6)
+    assert np.allclose(ddw.numpy(), rdw, atol=1e-6)
+    assert np.allclose(ddb.numpy(), rdb.ravel(), atol=1e-6)
+
+
+@pytest.mark.parametrize("M,N,K,relu", [(64, 256, 784, True), (64, 10, 256, False),
+                                        (300, 130, 90, True), (1024, 512, 512, True)])
+def test_linear_fwd_bwd(dev, orc, M, N, K, relu):
+    rng = np.random.default_rng(M + N + K)
+    X = rng.random((M, K), dtype=np.float32)
+    W = (rng.uniform(-1, 1, (N, K)) * np.sqrt(6.0 / K)).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    G = rng.standard_normal((M, N)).astype(np.float32)
+    dX, dW_, db_, dG = (dev.to_device(a) for a in (X, W, b, G))
+    dY, dPre = dev.zeros((M, N)), dev.zeros((M, N))
+    dev.linear_fwd_f32(dX, dW_, db_, dY, M, N, K, relu, dPre if relu else None)
+    assert dev.check_status() == 0
+    pre = orc.linear_fwd_f32(X, W, b)
+    ref = orc.relu_f32(pre) if relu else pre
+    t = tol(K, X, W)
+    assert np.abs(dY.numpy() - ref).max() <= t
+    if relu:
+        assert np.abs(dPre.numpy() - pre).max() <= t
+    gdx, gdw, gdb = dev.zeros((M, K)), dev.zeros((N, K)), dev.zeros((N,))
+    dev.linear_bwd_f32(dG, dX, dW_, gdx, gdw, gdb, M, N, K)
+    assert dev.check_status() == 0
+    rdx, rdw, rdb = orc.linear_bwd_f32(G, X, W)
+    assert np.abs(gdx.numpy() - rdx).max() <= tol(N, G, W)
+    assert np.abs(gdw.numpy() - rdw).max() <= tol(M, G, X)
+    assert np.abs(gdb.numpy() - rdb.ravel()).max() <= tol(M, G, np.ones(1))
+
+
+def test_gemm_f32_large_against_blas(dev, orc):
+    """4096-wide layer at batch 2048: reference recipe with OpenBLAS dgemm."""
+    M, N, K = 2048, 4096, 4096
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.uniform(-1, 1, (N, K)) * np.sqrt(6.0 / K)).astype(np.float32)
+    dX, dW_ = dev.to_device(X), dev.to_device(W)
+    dY = dev.zeros((M, N))
+    dev.linear_fwd_f32(dX, dW_, None, dY, M, N, K)
+    assert dev.check_status() == 0
+    ref = orc.matmul_f32_blas(X, W, tb=True)
+    err = np.abs(dY.numpy() - ref).max()
+    assert err <= tol(K, X, W), f"{err} vs {tol(K, X, W)}"

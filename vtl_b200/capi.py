@@ -1,0 +1,320 @@
+"""ctypes binding of libvtlb200.so (the C ABI declared in include/vtlb.h).
+
+This is the Python stand-in for the `fn C.vtlb_*` declarations a V build of vtl
+would carry.  It adds nothing of its own: `Device` owns one `vtlb_ctx` and
+forwards calls, turning non-zero return codes into `VtlbError`.  There is no
+CPU path: if the library is missing or no B200 is present, creation fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvtlb200.so")
+
+OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ENCCL, ESTATE = 0, -1, -2, -3, -4, -5, -6
+
+
+class VtlbError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"vtlb error {code}: {msg}")
+        self.code = code
+
+
+class AdamTensor(C.Structure):
+    _fields_ = [("d_grad", C.c_void_p), ("d_theta", C.c_void_p), ("d_m", C.c_void_p),
+                ("d_v", C.c_void_p), ("n", C.c_size_t)]
+
+
+_vp, _i, _sz, _d = C.c_void_p, C.c_int, C.c_size_t, C.c_double
+_PROTOS = {
+    "vtlb_device_count": [C.POINTER(C.c_int)],
+    "vtlb_ctx_create": [_i, C.POINTER(_vp)],
+    "vtlb_ctx_destroy": [_vp],
+    "vtlb_sync": [_vp],
+    "vtlb_check_status": [_vp, C.POINTER(C.c_uint32)],
+    "vtlb_event_create": [_vp, C.POINTER(_vp)],
+    "vtlb_event_record": [_vp, _vp],
+    "vtlb_event_elapsed_ms": [_vp, _vp, _vp, C.POINTER(C.c_float)],
+    "vtlb_event_destroy": [_vp, _vp],
+    "vtlb_alloc": [_vp, _sz, C.POINTER(_vp)],
+    "vtlb_free": [_vp, _vp],
+    "vtlb_h2d": [_vp, _vp, _vp, _sz],
+    "vtlb_d2h": [_vp, _vp, _vp, _sz],
+    "vtlb_d2d": [_vp, _vp, _vp, _sz],
+    "vtlb_memset0": [_vp, _vp, _sz],
+    "vtlb_host_alloc": [_sz, C.POINTER(_vp)],
+    "vtlb_host_free": [_vp],
+    "vtlb_reserve_scratch": [_vp, _sz],
+    "vtlb_gemm_f32": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i],
+    "vtlb_linear_fwd_f32": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "vtlb_linear_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "vtlb_relu_fwd_f32": [_vp, _vp, _vp, _sz],
+    "vtlb_relu_bwd_f32": [_vp, _vp, _vp, _vp, _sz],
+    "vtlb_mse_fwd_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp, _vp],
+    "vtlb_softmax_ce_fwd_bwd_f32": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+    "vtlb_adam_step_f32": [_vp, _i, C.POINTER(AdamTensor), _d, _d, _d, _d, _i],
+    "vtlb_adamw_step_f32": [_vp, _i, C.POINTER(AdamTensor), _d, _d, _d, _d, _d, _i],
+    "vtlb_i8_ld": [_i],
+    "vtlb_quant_rows_i8": [_vp, _vp, _i, _i, _vp, _vp, _vp],
+    "vtlb_row_absmax_f32": [_vp, _vp, _i, _i, _vp],
+    "vtlb_gemm_i8_i32": [_vp, _vp, _vp, _i, _i, _i, _vp],
+    "vtlb_linear_i8_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "vtlb_comm_unique_id": [_vp],
+    "vtlb_comm_init_rank": [_vp, _i, _i, _vp],
+    "vtlb_comm_destroy": [_vp],
+    "vtlb_allreduce_sum_f32_async": [_vp, _vp, _sz],
+    "vtlb_allreduce_max_f32_async": [_vp, _vp, _sz],
+    "vtlb_allgather_async": [_vp, _vp, _vp, _sz],
+    "vtlb_comm_wait": [_vp],
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads libvtlb200.so; raises if it has not been built (python -m vtl_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m vtl_b200.build` "
+                              "(there is no CPU fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, args in _PROTOS.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        lib.vtlb_last_error.argtypes = [_vp]
+        lib.vtlb_last_error.restype = C.c_char_p
+        lib.vtlb_launch_count.argtypes = [_vp]
+        lib.vtlb_launch_count.restype = C.c_uint64
+        lib.vtlb_stream.argtypes = [_vp]
+        lib.vtlb_stream.restype = _vp
+        _lib = lib
+    return _lib
+
+
+def device_count() -> int:
+    n = C.c_int(0)
+    load().vtlb_device_count(C.byref(n))
+    return n.value
+
+
+class DBuf:
+    """A device allocation with a shape and dtype attached (host-side bookkeeping only)."""
+
+    def __init__(self, dev: "Device", ptr: int, shape, dtype):
+        self.dev, self.ptr, self.shape, self.dtype = dev, ptr, tuple(shape), np.dtype(dtype)
+
+    @property
+    def nbytes(self) -> int:
+        return int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
+
+    @property
+    def size(self) -> int:
+        return int(np.prod(self.shape, dtype=np.int64))
+
+    def numpy(self) -> np.ndarray:
+        return self.dev.d2h(self)
+
+    def free(self):
+        if self.ptr:
+            self.dev.free(self.ptr)
+            self.ptr = 0
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, DBuf):
+        return x.ptr
+    return x
+
+
+class Device:
+    """One vtlb_ctx (one GPU)."""
+
+    def __init__(self, index: int = 0):
+        self.lib = load()
+        h = _vp()
+        rc = self.lib.vtlb_ctx_create(index, C.byref(h))
+        if rc != OK:
+            raise VtlbError(rc, self.lib.vtlb_last_error(None).decode())
+        self.h = h
+        self.index = index
+
+    # -- plumbing
+    def _ck(self, rc: int):
+        if rc != OK:
+            raise VtlbError(rc, self.lib.vtlb_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.vtlb_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self):
+        self._ck(self.lib.vtlb_sync(self.h))
+
+    def check_status(self) -> int:
+        st = C.c_uint32(0)
+        self._ck(self.lib.vtlb_check_status(self.h, C.byref(st)))
+        return st.value
+
+    def launch_count(self) -> int:
+        return int(self.lib.vtlb_launch_count(self.h))
+
+    # -- events
+    def event(self) -> int:
+        ev = _vp()
+        self._ck(self.lib.vtlb_event_create(self.h, C.byref(ev)))
+        return ev.value
+
+    def record(self, ev: int):
+        self._ck(self.lib.vtlb_event_record(self.h, ev))
+
+    def elapsed_ms(self, e0: int, e1: int) -> float:
+        ms = C.c_float(0)
+        self._ck(self.lib.vtlb_event_elapsed_ms(self.h, e0, e1, C.byref(ms)))
+        return ms.value
+
+    # -- memory
+    def alloc(self, nbytes: int) -> int:
+        p = _vp()
+        self._ck(self.lib.vtlb_alloc(self.h, nbytes, C.byref(p)))
+        return p.value or 0
+
+    def free(self, ptr: int):
+        self._ck(self.lib.vtlb_free(self.h, ptr))
+
+    def empty(self, shape, dtype=np.float32) -> DBuf:
+        shape = (shape,) if np.isscalar(shape) else tuple(shape)
+        nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        return DBuf(self, self.alloc(max(nbytes, 16)), shape, dtype)
+
+    def zeros(self, shape, dtype=np.float32) -> DBuf:
+        b = self.empty(shape, dtype)
+        self._ck(self.lib.vtlb_memset0(self.h, b.ptr, max(b.nbytes, 16)))
+        return b
+
+    def to_device(self, a: np.ndarray) -> DBuf:
+        a = np.ascontiguousarray(a)
+        b = self.empty(a.shape, a.dtype)
+        if a.nbytes:
+            self._ck(self.lib.vtlb_h2d(self.h, b.ptr, a.ctypes.data, a.nbytes))
+            self.sync()  # `a` may be a temporary
+        return b
+
+    def h2d_raw(self, dptr, hptr: int, nbytes: int):
+        self._ck(self.lib.vtlb_h2d(self.h, _ptr(dptr), hptr, nbytes))
+
+    def d2h_raw(self, hptr: int, dptr, nbytes: int):
+        self._ck(self.lib.vtlb_d2h(self.h, hptr, _ptr(dptr), nbytes))
+
+    def d2h(self, b: DBuf) -> np.ndarray:
+        out = np.empty(b.shape, b.dtype)
+        if out.nbytes:
+            self._ck(self.lib.vtlb_d2h(self.h, out.ctypes.data, b.ptr, out.nbytes))
+        return out
+
+    def d2d(self, dst, src, nbytes: int):
+        self._ck(self.lib.vtlb_d2d(self.h, _ptr(dst), _ptr(src), nbytes))
+
+    def memset0(self, dst, nbytes: int):
+        self._ck(self.lib.vtlb_memset0(self.h, _ptr(dst), nbytes))
+
+    def reserve_scratch(self, nbytes: int):
+        self._ck(self.lib.vtlb_reserve_scratch(self.h, nbytes))
+
+    # -- f32
+    def gemm_f32(self, ta, tb, M, N, K, A, B, Cout, bias=None, relu=False):
+        self._ck(self.lib.vtlb_gemm_f32(self.h, int(ta), int(tb), M, N, K, _ptr(A), _ptr(B),
+                                        _ptr(Cout), _ptr(bias), int(relu)))
+
+    def linear_fwd_f32(self, X, W, b, Y, M, N, K, relu=False, pre=None):
+        self._ck(self.lib.vtlb_linear_fwd_f32(self.h, _ptr(X), _ptr(W), _ptr(b), _ptr(Y), M, N, K,
+                                              int(relu), _ptr(pre)))
+
+    def linear_bwd_f32(self, G, X, W, dX, dW, db, M, N, K):
+        self._ck(self.lib.vtlb_linear_bwd_f32(self.h, _ptr(G), _ptr(X), _ptr(W), _ptr(dX),
+                                              _ptr(dW), _ptr(db), M, N, K))
+
+    def relu_fwd_f32(self, x, y, n):
+        self._ck(self.lib.vtlb_relu_fwd_f32(self.h, _ptr(x), _ptr(y), n))
+
+    def relu_bwd_f32(self, g, cached, dx, n):
+        self._ck(self.lib.vtlb_relu_bwd_f32(self.h, _ptr(g), _ptr(cached), _ptr(dx), n))
+
+    def mse_fwd_bwd_f32(self, P, T, n, n_div, loss, dP=None):
+        self._ck(self.lib.vtlb_mse_fwd_bwd_f32(self.h, _ptr(P), _ptr(T), n, n_div, _ptr(loss),
+                                               _ptr(dP)))
+
+    def softmax_ce_fwd_bwd_f32(self, X, T, B, Cc, batch_div, loss, dX=None):
+        self._ck(self.lib.vtlb_softmax_ce_fwd_bwd_f32(self.h, _ptr(X), _ptr(T), B, Cc, batch_div,
+                                                      _ptr(loss), _ptr(dX)))
+
+    # -- optimizers
+    @staticmethod
+    def adam_table(tensors):
+        arr = (AdamTensor * len(tensors))()
+        for i, (g, th, m, v, n) in enumerate(tensors):
+            arr[i] = AdamTensor(_ptr(g), _ptr(th), _ptr(m), _ptr(v), n)
+        return arr
+
+    def adam_step_f32(self, table, beta1, beta2, lr_t, eps, zero_grad=True):
+        self._ck(self.lib.vtlb_adam_step_f32(self.h, len(table), table, beta1, beta2, lr_t, eps,
+                                             int(zero_grad)))
+
+    def adamw_step_f32(self, table, beta1, beta2, lr_t, eps, wd, zero_grad=True):
+        self._ck(self.lib.vtlb_adamw_step_f32(self.h, len(table), table, beta1, beta2, lr_t, eps,
+                                              wd, int(zero_grad)))
+
+    # -- int8
+    def i8_ld(self, K: int) -> int:
+        return int(self.lib.vtlb_i8_ld(K))
+
+    def quant_rows_i8(self, A, M, K, Q, scale, amax_in=None):
+        self._ck(self.lib.vtlb_quant_rows_i8(self.h, _ptr(A), M, K, _ptr(Q), _ptr(scale),
+                                             _ptr(amax_in)))
+
+    def row_absmax_f32(self, A, M, K, amax):
+        self._ck(self.lib.vtlb_row_absmax_f32(self.h, _ptr(A), M, K, _ptr(amax)))
+
+    def gemm_i8_i32(self, Aq, Wq, M, N, K, acc):
+        self._ck(self.lib.vtlb_gemm_i8_i32(self.h, _ptr(Aq), _ptr(Wq), M, N, K, _ptr(acc)))
+
+    def linear_i8_fwd(self, Aq, sa, Wq, sw, bias, Y, M, N, K, relu=False):
+        self._ck(self.lib.vtlb_linear_i8_fwd(self.h, _ptr(Aq), _ptr(sa), _ptr(Wq), _ptr(sw),
+                                             _ptr(bias), _ptr(Y), M, N, K, int(relu)))
+
+    # -- collectives
+    def comm_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        rc = self.lib.vtlb_comm_unique_id(buf)
+        if rc != OK:
+            raise VtlbError(rc, self.lib.vtlb_last_error(None).decode())
+        return buf.raw
+
+    def comm_init_rank(self, nranks: int, rank: int, uid: bytes):
+        self._ck(self.lib.vtlb_comm_init_rank(self.h, nranks, rank, C.c_char_p(uid)))
+
+    def allreduce_sum_f32_async(self, buf, n):
+        self._ck(self.lib.vtlb_allreduce_sum_f32_async(self.h, _ptr(buf), n))
+
+    def allreduce_max_f32_async(self, buf, n):
+        self._ck(self.lib.vtlb_allreduce_max_f32_async(self.h, _ptr(buf), n))
+
+    def allgather_async(self, send, recv, bytes_per_rank):
+        self._ck(self.lib.vtlb_allgather_async(self.h, _ptr(send), _ptr(recv), bytes_per_rank))
+
+    def comm_wait(self):
+        self._ck(self.lib.vtlb_comm_wait(self.h))

@@ -1,0 +1,70 @@
+// Shared host-side plumbing of libvtlb200.so: the context object, error
+// reporting and launch bookkeeping.  Nothing here is visible through the C ABI
+// except the opaque vtlb_ctx pointer.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/vtlb.h"
+
+#define VTLB_API extern "C" __attribute__((visibility("default")))
+
+// Bits of the device status word (vtlb_check_status).
+#define VTLB_ST_GEMM_TIMEOUT 0x1u  // a pipeline wait inside a tcgen05 GEMM ran out
+
+struct vtlb_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;       // compute
+  cudaStream_t comm_stream = nullptr;  // collectives
+  cudaEvent_t ev_compute = nullptr;    // compute -> comm ordering
+  cudaEvent_t ev_comm = nullptr;       // comm -> compute ordering
+  uint32_t* d_status = nullptr;        // device status word
+  void* scratch = nullptr;             // operand-split buffers, partial sums
+  size_t scratch_bytes = 0;
+  void* comm = nullptr;  // ncclComm_t
+  int nranks = 1, rank = 0;
+  uint64_t launches = 0;
+  char err[512] = {0};
+};
+
+extern thread_local char g_vtlb_err[512];
+
+int vtlb_fail(vtlb_ctx* ctx, int code, const char* fmt, ...);
+
+// Makes ctx's device current; every entry point starts with it.
+#define VTLB_ENTER(ctx)                                                         \
+  do {                                                                          \
+    if (!(ctx)) return vtlb_fail(nullptr, VTLB_EINVAL, "%s: null ctx", __func__); \
+    cudaError_t e__ = cudaSetDevice((ctx)->device);                             \
+    if (e__ != cudaSuccess)                                                     \
+      return vtlb_fail((ctx), VTLB_ECUDA, "%s: cudaSetDevice(%d): %s", __func__, \
+                       (ctx)->device, cudaGetErrorString(e__));                 \
+  } while (0)
+
+#define VTLB_CUDA(ctx, call)                                                          \
+  do {                                                                                \
+    cudaError_t e__ = (call);                                                         \
+    if (e__ != cudaSuccess)                                                           \
+      return vtlb_fail((ctx), VTLB_ECUDA, "%s: %s -> %s", __func__, #call,            \
+                       cudaGetErrorString(e__));                                      \
+  } while (0)
+
+// After a kernel launch: count it and surface launch-configuration errors.
+#define VTLB_LAUNCHED(ctx)                                                            \
+  do {                                                                                \
+    (ctx)->launches++;                                                                \
+    cudaError_t e__ = cudaGetLastError();                                             \
+    if (e__ != cudaSuccess)                                                           \
+      return vtlb_fail((ctx), VTLB_ECUDA, "%s: kernel launch: %s", __func__,          \
+                       cudaGetErrorString(e__));                                      \
+  } while (0)
+
+// Returns a scratch region of at least `bytes` (grown on demand; growth
+// synchronises the stream first because earlier kernels may still use the old one).
+int vtlb_scratch(vtlb_ctx* ctx, size_t bytes, void** out);
+
+static inline bool vtlb_aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
+static inline size_t vtlb_round_up(size_t x, size_t m) { return (x + m - 1) / m * m; }

@@ -1,0 +1,246 @@
+// Context, device memory and status: the part of the C ABI that stands where
+// vtl's CudaStorage (storage/cuda_d_cuda.v) and DeviceSession buffers
+// (autograd_cuda/device_session_gpu_d_cuda.v:24-45) stand in the reference.
+#include <stdarg.h>
+
+#include <new>
+
+#include "common.cuh"
+
+thread_local char g_vtlb_err[512] = {0};
+
+int vtlb_fail(vtlb_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  memcpy(g_vtlb_err, buf, sizeof buf);
+  if (ctx) memcpy(ctx->err, buf, sizeof buf);
+  return code;
+}
+
+VTLB_API const char* vtlb_last_error(vtlb_ctx* ctx) { return ctx ? ctx->err : g_vtlb_err; }
+
+VTLB_API int vtlb_device_count(int* count) {
+  if (!count) return vtlb_fail(nullptr, VTLB_EINVAL, "vtlb_device_count: null out");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    *count = 0;
+    return vtlb_fail(nullptr, VTLB_ECUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+  }
+  *count = n;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_ctx_create(int device, vtlb_ctx** out) {
+  if (!out) return vtlb_fail(nullptr, VTLB_EINVAL, "vtlb_ctx_create: null out");
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return vtlb_fail(nullptr, VTLB_ECUDA, "vtlb_ctx_create: no usable CUDA device (%s)",
+                     e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+  if (device < 0 || device >= n)
+    return vtlb_fail(nullptr, VTLB_EINVAL, "vtlb_ctx_create: device %d out of range [0,%d)",
+                     device, n);
+  cudaDeviceProp prop;
+  if ((e = cudaSetDevice(device)) != cudaSuccess ||
+      (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess)
+    return vtlb_fail(nullptr, VTLB_ECUDA, "vtlb_ctx_create: %s", cudaGetErrorString(e));
+  if (prop.major != 10)
+    return vtlb_fail(nullptr, VTLB_ECUDA,
+                     "vtlb_ctx_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                     device, prop.major, prop.minor);
+  vtlb_ctx* ctx = new (std::nothrow) vtlb_ctx();
+  if (!ctx) return vtlb_fail(nullptr, VTLB_ENOMEM, "vtlb_ctx_create: host allocation failed");
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming)) != cudaSuccess ||
+      (e = cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming)) != cudaSuccess ||
+      (e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess ||
+      (e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess) {
+    int rc = vtlb_fail(nullptr, VTLB_ECUDA, "vtlb_ctx_create: %s", cudaGetErrorString(e));
+    vtlb_ctx_destroy(ctx);
+    return rc;
+  }
+  *out = ctx;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
+  if (!ctx) return VTLB_OK;
+  cudaSetDevice(ctx->device);
+  if (ctx->comm) vtlb_comm_destroy(ctx);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
+  if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
+  delete ctx;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_sync(vtlb_ctx* ctx) {
+  VTLB_ENTER(ctx);
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->comm_stream));
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_check_status(vtlb_ctx* ctx, uint32_t* status) {
+  VTLB_ENTER(ctx);
+  if (!status) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_check_status: null out");
+  uint32_t st = 0;
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  VTLB_CUDA(ctx, cudaMemcpy(&st, ctx->d_status, 4, cudaMemcpyDeviceToHost));
+  if (st) VTLB_CUDA(ctx, cudaMemset(ctx->d_status, 0, 4));
+  *status = st;
+  if (st & VTLB_ST_GEMM_TIMEOUT)
+    return vtlb_fail(ctx, VTLB_ETIMEOUT,
+                     "a tcgen05 GEMM pipeline wait ran out (status 0x%x); its output is invalid",
+                     st);
+  return VTLB_OK;
+}
+
+VTLB_API uint64_t vtlb_launch_count(vtlb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+VTLB_API void* vtlb_stream(vtlb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+VTLB_API int vtlb_event_create(vtlb_ctx* ctx, void** ev_out) {
+  VTLB_ENTER(ctx);
+  if (!ev_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_event_create: null out");
+  cudaEvent_t ev;
+  VTLB_CUDA(ctx, cudaEventCreate(&ev));
+  *ev_out = (void*)ev;
+  return VTLB_OK;
+}
+VTLB_API int vtlb_event_record(vtlb_ctx* ctx, void* ev) {
+  VTLB_ENTER(ctx);
+  if (!ev) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_event_record: null event");
+  VTLB_CUDA(ctx, cudaEventRecord((cudaEvent_t)ev, ctx->stream));
+  return VTLB_OK;
+}
+VTLB_API int vtlb_event_elapsed_ms(vtlb_ctx* ctx, void* ev_start, void* ev_stop, float* ms) {
+  VTLB_ENTER(ctx);
+  if (!ev_start || !ev_stop || !ms) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_event_elapsed_ms: null argument");
+  VTLB_CUDA(ctx, cudaEventSynchronize((cudaEvent_t)ev_stop));
+  VTLB_CUDA(ctx, cudaEventElapsedTime(ms, (cudaEvent_t)ev_start, (cudaEvent_t)ev_stop));
+  return VTLB_OK;
+}
+VTLB_API int vtlb_event_destroy(vtlb_ctx* ctx, void* ev) {
+  VTLB_ENTER(ctx);
+  if (ev) VTLB_CUDA(ctx, cudaEventDestroy((cudaEvent_t)ev));
+  return VTLB_OK;
+}
+
+// ---------------------------------------------------------------- memory
+
+VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
+  VTLB_ENTER(ctx);
+  if (!d_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_alloc: null out");
+  *d_out = nullptr;
+  if (bytes == 0) return VTLB_OK;
+  cudaError_t e = cudaMalloc(d_out, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_free(vtlb_ctx* ctx, void* d_ptr) {
+  VTLB_ENTER(ctx);
+  if (!d_ptr) return VTLB_OK;
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  VTLB_CUDA(ctx, cudaFree(d_ptr));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_h2d(vtlb_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!d_dst || !h_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_h2d: null pointer");
+  VTLB_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_d2h(vtlb_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!h_dst || !d_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_d2h: null pointer");
+  VTLB_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_d2d(vtlb_ctx* ctx, void* d_dst, const void* d_src, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!d_dst || !d_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_d2d: null pointer");
+  VTLB_CUDA(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_memset0(vtlb_ctx* ctx, void* d_dst, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!d_dst) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_memset0: null pointer");
+  VTLB_CUDA(ctx, cudaMemsetAsync(d_dst, 0, bytes, ctx->stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_host_alloc(size_t bytes, void** h_out) {
+  if (!h_out) return vtlb_fail(nullptr, VTLB_EINVAL, "vtlb_host_alloc: null out");
+  *h_out = nullptr;
+  if (bytes == 0) return VTLB_OK;
+  cudaError_t e = cudaMallocHost(h_out, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return vtlb_fail(nullptr, VTLB_ENOMEM, "vtlb_host_alloc(%zu): %s", bytes,
+                     cudaGetErrorString(e));
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_host_free(void* h_ptr) {
+  if (!h_ptr) return VTLB_OK;
+  cudaError_t e = cudaFreeHost(h_ptr);
+  if (e != cudaSuccess)
+    return vtlb_fail(nullptr, VTLB_ECUDA, "vtlb_host_free: %s", cudaGetErrorString(e));
+  return VTLB_OK;
+}
+
+int vtlb_scratch(vtlb_ctx* ctx, size_t bytes, void** out) {
+  if (bytes > ctx->scratch_bytes) {
+    VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) VTLB_CUDA(ctx, cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    size_t want = vtlb_round_up(bytes + bytes / 8, (size_t)1 << 20);
+    cudaError_t e = cudaMalloc(&ctx->scratch, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      want = vtlb_round_up(bytes, 256);
+      e = cudaMalloc(&ctx->scratch, want);
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return vtlb_fail(ctx, VTLB_ENOMEM, "scratch of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    }
+    ctx->scratch_bytes = want;
+  }
+  *out = ctx->scratch;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_reserve_scratch(vtlb_ctx* ctx, size_t bytes) {
+  VTLB_ENTER(ctx);
+  void* p;
+  return vtlb_scratch(ctx, bytes, &p);
+}

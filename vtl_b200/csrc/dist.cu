@@ -1,0 +1,141 @@
+// Collectives over NCCL (NVLink / NVSwitch).  The reference is single-device and
+// has nothing here; this file gives the data-parallel trainer its gradient
+// all-reduce and the column-sharded INT8 path its max-reduce and all-gather.
+// libnccl.so.2 is loaded on first use so that the library itself has no link
+// dependency on NCCL; single-GPU users never touch it.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include "common.cuh"
+
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+NcclApi g_nccl;
+
+int load_nccl(vtlb_ctx* ctx) {
+  if (g_nccl.handle) return VTLB_OK;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return vtlb_fail(ctx, VTLB_ENCCL, "cannot load libnccl.so.2: %s", dlerror());
+#define VTLB_SYM(field, name)                                                    \
+  *(void**)(&g_nccl.field) = dlsym(h, name);                                     \
+  if (!g_nccl.field) return vtlb_fail(ctx, VTLB_ENCCL, "libnccl lacks %s", name)
+  VTLB_SYM(GetUniqueId, "ncclGetUniqueId");
+  VTLB_SYM(CommInitRank, "ncclCommInitRank");
+  VTLB_SYM(CommDestroy, "ncclCommDestroy");
+  VTLB_SYM(AllReduce, "ncclAllReduce");
+  VTLB_SYM(AllGather, "ncclAllGather");
+  VTLB_SYM(GetErrorString, "ncclGetErrorString");
+#undef VTLB_SYM
+  g_nccl.handle = h;
+  return VTLB_OK;
+}
+
+#define VTLB_NCCL(ctx, call)                                                      \
+  do {                                                                            \
+    ncclResult_t r__ = (call);                                                    \
+    if (r__ != ncclSuccess)                                                       \
+      return vtlb_fail((ctx), VTLB_ENCCL, "%s: %s -> %s", __func__, #call,        \
+                       g_nccl.GetErrorString(r__));                               \
+  } while (0)
+
+// Orders the communication stream after everything enqueued on the compute stream.
+int comm_after_compute(vtlb_ctx* ctx) {
+  VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_compute, ctx->stream));
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_compute, 0));
+  return VTLB_OK;
+}
+
+int need_comm(vtlb_ctx* ctx, const char* fn) {
+  if (!ctx->comm) return vtlb_fail(ctx, VTLB_ESTATE, "%s: vtlb_comm_init_rank has not been called", fn);
+  return VTLB_OK;
+}
+
+}  // namespace
+
+VTLB_API int vtlb_comm_unique_id(void* h_id128) {
+  if (!h_id128) return vtlb_fail(nullptr, VTLB_EINVAL, "vtlb_comm_unique_id: null out");
+  int rc = load_nccl(nullptr);
+  if (rc) return rc;
+  static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+  ncclUniqueId id;
+  VTLB_NCCL(nullptr, g_nccl.GetUniqueId(&id));
+  memcpy(h_id128, &id, sizeof id);
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void* h_id128) {
+  VTLB_ENTER(ctx);
+  if (nranks < 1 || rank < 0 || rank >= nranks || !h_id128)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_comm_init_rank: bad arguments (nranks %d, rank %d)", nranks, rank);
+  if (ctx->comm) return vtlb_fail(ctx, VTLB_ESTATE, "vtlb_comm_init_rank: communicator already exists");
+  int rc = load_nccl(ctx);
+  if (rc) return rc;
+  ncclUniqueId id;
+  memcpy(&id, h_id128, sizeof id);
+  ncclComm_t comm = nullptr;
+  VTLB_NCCL(ctx, g_nccl.CommInitRank(&comm, nranks, id, rank));
+  ctx->comm = comm;
+  ctx->nranks = nranks;
+  ctx->rank = rank;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_comm_destroy(vtlb_ctx* ctx) {
+  if (!ctx || !ctx->comm) return VTLB_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->comm_stream);
+  g_nccl.CommDestroy((ncclComm_t)ctx->comm);
+  ctx->comm = nullptr;
+  ctx->nranks = 1;
+  ctx->rank = 0;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_allreduce_sum_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n) {
+  VTLB_ENTER(ctx);
+  int rc = need_comm(ctx, __func__);
+  if (rc) return rc;
+  if (n == 0) return VTLB_OK;
+  if ((rc = comm_after_compute(ctx))) return rc;
+  VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclSum, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n) {
+  VTLB_ENTER(ctx);
+  int rc = need_comm(ctx, __func__);
+  if (rc) return rc;
+  if (n == 0) return VTLB_OK;
+  if ((rc = comm_after_compute(ctx))) return rc;
+  VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclMax, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_recv, size_t bytes_per_rank) {
+  VTLB_ENTER(ctx);
+  int rc = need_comm(ctx, __func__);
+  if (rc) return rc;
+  if (bytes_per_rank == 0) return VTLB_OK;
+  if ((rc = comm_after_compute(ctx))) return rc;
+  VTLB_NCCL(ctx, g_nccl.AllGather(d_send, d_recv, bytes_per_rank, ncclInt8, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_comm_wait(vtlb_ctx* ctx) {
+  VTLB_ENTER(ctx);
+  VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  return VTLB_OK;
+}

@@ -1,0 +1,265 @@
+// The tcgen05 GEMM used by both the INT8 path (kind::i8, int32 accumulators) and
+// the f32 path (kind::tf32 issued three times per K step on pre-split hi/lo
+// operands).  D[M,N] = A[M,K] . B[N,K]^T with both operands K-major.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer   (one lane): global -> shared, 128-byte-swizzled tiles
+//   warp 1      MMA issuer     (one lane): tcgen05.mma into tensor memory; owns the
+//                                          tensor-memory allocation
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the fused
+//               epilogue functor, store to global
+// Shared-memory stages form a ring guarded by full/empty mbarriers; the
+// accumulator is double-buffered in tensor memory (2 x BN columns) so the
+// epilogue of tile i overlaps the MMAs of tile i+1.  Every CTA loads its own
+// tiles; there is no cluster and no multicast.
+//
+// Every mbarrier wait is bounded (ptx::mbar_wait_bounded).  If one runs out the
+// CTA raises a shared abort flag, all roles leave their loops, the kernel ORs
+// VTLB_ST_GEMM_TIMEOUT into the status word, waits a bounded time for copies
+// still in flight, frees its tensor memory and returns.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace gemm {
+
+constexpr int BM = 128;           // rows of D per tile = TMEM lanes
+constexpr int ROW_BYTES = 128;    // bytes of K per shared-memory row (= swizzle span)
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+
+enum Kind { KIND_I8 = 0, KIND_TF32X3 = 1 };
+
+template <int KIND>
+struct Traits;
+template <>
+struct Traits<KIND_I8> {
+  static constexpr int ELEM = 1;   // bytes per element
+  static constexpr int NOP = 1;    // operand tiles per side per stage
+  static constexpr uint32_t CFMT = ptx::kCfmtS32, ABFMT = ptx::kFmtS8;
+};
+template <>
+struct Traits<KIND_TF32X3> {
+  static constexpr int ELEM = 4;
+  static constexpr int NOP = 2;    // hi and lo
+  static constexpr uint32_t CFMT = ptx::kCfmtF32, ABFMT = ptx::kFmtTF32;
+};
+
+struct TmapSet {
+  CUtensorMap a[2];  // [0] = A (i8) or A_hi, [1] = A_lo
+  CUtensorMap b[2];
+};
+
+template <int KIND, int BN, int STAGES>
+struct Smem {
+  static constexpr uint32_t A_TILE = BM * ROW_BYTES;
+  static constexpr uint32_t B_TILE = BN * ROW_BYTES;
+  static constexpr uint32_t STAGE = Traits<KIND>::NOP * (A_TILE + B_TILE);
+  static constexpr uint32_t TILES = STAGES * STAGE;
+  static constexpr uint32_t BARS = 8 * (2 * STAGES + 4) + 16;
+  static constexpr uint32_t TOTAL = TILES + BARS + 1024;  // + alignment slack
+};
+
+template <int KIND, int BN, int STAGES, class Epi>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, int K,
+               uint32_t* status) {
+  using T = Traits<KIND>;
+  using S = Smem<KIND, BN, STAGES>;
+  constexpr int NOP = T::NOP;
+  constexpr int BK = ROW_BYTES / T::ELEM;   // elements of K per stage
+  constexpr int KSTEPS = ROW_BYTES / 32;    // MMAs per operand pair per stage (32 B of K each)
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+  constexpr uint32_t IDESC = ptx::umma_idesc(T::CFMT, T::ABFMT, BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = base + S::TILES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 4));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 128);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    for (int i = 0; i < NOP; ++i) {
+      ptx::prefetch_tmap(&tm.a[i]);
+      ptx::prefetch_tmap(&tm.b[i]);
+    }
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(full_bar(stage), S::STAGE);
+          const uint32_t sa = base + stage * S::STAGE;
+          const uint32_t sb = sa + NOP * S::A_TILE;
+#pragma unroll
+          for (int i = 0; i < NOP; ++i)
+            ptx::tma_load_2d(sa + i * S::A_TILE, &tm.a[i], kb * BK, m0, full_bar(stage));
+#pragma unroll
+          for (int i = 0; i < NOP; ++i)
+            ptx::tma_load_2d(sb + i * S::B_TILE, &tm.b[i], kb * BK, n0, full_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS))
+          break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = base + stage * S::STAGE;
+          const uint32_t sb = sa + NOP * S::A_TILE;
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            // advancing 32 bytes along K inside the swizzled row = +2 in the address field
+            if constexpr (KIND == KIND_I8) {
+              const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+              const uint64_t db = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+              ptx::umma_i8(d_tmem, da, db, IDESC, (kb | kk) != 0);
+            } else {
+              const uint64_t a_hi = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+              const uint64_t a_lo = ptx::umma_desc_k_sw128(sa + S::A_TILE) + 2u * kk;
+              const uint64_t b_hi = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+              const uint64_t b_lo = ptx::umma_desc_k_sw128(sb + S::B_TILE) + 2u * kk;
+              // small terms first, then the leading one
+              ptx::umma_tf32(d_tmem, a_lo, b_hi, IDESC, (kb | kk) != 0);
+              ptx::umma_tf32(d_tmem, a_hi, b_lo, IDESC, 1);
+              ptx::umma_tf32(d_tmem, a_hi, b_hi, IDESC, 1);
+            }
+          }
+          ptx::umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t acc = 0, acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32;
+        ptx::tmem_ld_32x32(taddr, v);
+        ptx::tmem_wait_ld();
+        epi(row, n0 + c * 32, v, M, N);
+        __syncwarp();
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(tempty_bar(acc));
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(status, VTLB_ST_GEMM_TIMEOUT);
+    // bounded grace period for TMA copies / MMAs still in flight
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+
+// cuTensorMapEncodeTiled obtained through the runtime (no link against libcuda).
+int encode_tmap_2d(vtlb_ctx* ctx, CUtensorMap* out, bool f32, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                   uint32_t box_outer);
+
+template <int KIND, int BN, int STAGES, class Epi>
+int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K) {
+  using S = Smem<KIND, BN, STAGES>;
+  static_assert(S::TOTAL <= 232448, "shared memory budget");
+  auto kern = gemm_tc_kernel<KIND, BN, STAGES, Epi>;
+  static uint64_t configured = 0;  // one bit per device
+  if (!(configured >> (ctx->device & 63) & 1)) {
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)S::TOTAL));
+    configured |= 1ull << (ctx->device & 63);
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, ctx->d_status);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+}  // namespace gemm

@@ -1,0 +1,385 @@
+// INT8 quantised linear path: per-row symmetric quantisation, int8 x int8 ->
+// int32 GEMM on tcgen05 (kind::i8) and the fused dequant + bias + ReLU epilogue.
+// The reference has no quantisation code; the arithmetic is the one stated in
+// include/vtlb.h and every f32 operation below rounds on its own (__fmul_rn,
+// __fadd_rn, __fdiv_rn) so that results are bit-identical to a plain C loop
+// compiled without FMA contraction.
+#include "gemm_tc.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- quantise rows
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ int quant1(float a, float inv) {
+  int q = __float2int_rn(__fmul_rn(a, inv));  // ties-to-even, like rintf
+  return max(-127, min(127, q));
+}
+
+// One CTA per row.  Pass 1: row max-abs (float4 loads, warp shuffles).  Pass 2
+// re-reads the row (it is still in L1/L2: a row is at most a few tens of KB)
+// and writes 16 codes per thread as one 16-byte store.  Algorithmic HBM traffic:
+// 4K bytes read + K bytes written + 4 bytes of scale per row.
+template <bool HAVE_AMAX>
+__global__ void __launch_bounds__(256) quant_rows_i8_kernel(const float* __restrict__ A, int M,
+                                                            int K, int ldq,
+                                                            int8_t* __restrict__ Q,
+                                                            float* __restrict__ scale,
+                                                            const float* __restrict__ amax_in) {
+  __shared__ float s_part[8];
+  __shared__ float s_amax;
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const float* a = A + (size_t)row * K;
+  const bool vec = ((K & 3) == 0) && ((((uintptr_t)A) & 15u) == 0);
+  float amax;
+  if (HAVE_AMAX) {
+    amax = amax_in[row];
+  } else {
+    float m = 0.0f;
+    if (vec) {
+      const float4* a4 = reinterpret_cast<const float4*>(a);
+      for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+        float4 v = a4[i];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+      }
+    } else {
+      for (int i = threadIdx.x; i < K; i += blockDim.x) m = fmaxf(m, fabsf(a[i]));
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.0f;
+      t = warp_max(t);
+      if (threadIdx.x == 0) s_amax = t;
+    }
+    __syncthreads();
+    amax = s_amax;
+  }
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+  if (threadIdx.x == 0) scale[row] = __fdiv_rn(amax, 127.0f);
+  int8_t* q = Q + (size_t)row * ldq;
+  if (vec && (K & 15) == 0) {
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    int4* q16 = reinterpret_cast<int4*>(q);
+    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) {
+      int w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4 v = a4[i * 4 + j];
+        int b0 = quant1(v.x, inv), b1 = quant1(v.y, inv), b2 = quant1(v.z, inv),
+            b3 = quant1(v.w, inv);
+        w[j] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
+      }
+      q16[i] = make_int4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) q[i] = (int8_t)quant1(a[i], inv);
+  }
+}
+
+__global__ void __launch_bounds__(256) row_absmax_kernel(const float* __restrict__ A, int M, int K,
+                                                         float* __restrict__ amax) {
+  __shared__ float s_part[8];
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const float* a = A + (size_t)row * K;
+  float m = 0.0f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) m = fmaxf(m, fabsf(a[i]));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.0f;
+    t = warp_max(t);
+    if (threadIdx.x == 0) amax[row] = t;
+  }
+}
+
+// ---------------------------------------------------------------- epilogues
+struct EpiStoreI32 {
+  int32_t* C;
+  int ldc;
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
+                                             int N) const {
+    if (row >= M) return;
+    int32_t* c = C + (size_t)row * ldc + col0;
+    if (col0 + 32 <= N && (ldc & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<int4*>(c + j) = make_int4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) c[j] = (int32_t)v[j];
+    }
+  }
+};
+
+__device__ __forceinline__ float dequant1(uint32_t acc, float sa, float sw, float bias,
+                                          bool has_bias, int relu) {
+  float t = __fmul_rn(sa, sw);
+  float u = __fmul_rn(__int2float_rn((int)acc), t);
+  float y = has_bias ? __fadd_rn(u, bias) : u;
+  if (relu && y < 0.0f) y = 0.0f;
+  return y;
+}
+
+struct EpiDequant {
+  float* Y;
+  const float* sa;
+  const float* sw;
+  const float* bias;  // may be null
+  int ldy;
+  int relu;
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
+                                             int N) const {
+    if (row >= M) return;
+    const float s = sa[row];
+    float* y = Y + (size_t)row * ldy + col0;
+    const bool hb = bias != nullptr;
+    if (col0 + 32 <= N && (ldy & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 w4 = __ldg(reinterpret_cast<const float4*>(sw + col0 + j));
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (hb) b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+        float4 o;
+        o.x = dequant1(v[j], s, w4.x, b4.x, hb, relu);
+        o.y = dequant1(v[j + 1], s, w4.y, b4.y, hb, relu);
+        o.z = dequant1(v[j + 2], s, w4.z, b4.z, hb, relu);
+        o.w = dequant1(v[j + 3], s, w4.w, b4.w, hb, relu);
+        *reinterpret_cast<float4*>(y + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N)
+          y[j] = dequant1(v[j], s, sw[col0 + j], hb ? bias[col0 + j] : 0.0f, hb, relu);
+    }
+  }
+};
+
+// ---------------------------------------------------------------- small M (GEMV-like)
+// For M <= 16 the 128-row tensor-core tile would be mostly padding and the
+// problem is bound by streaming W once from HBM (N*K bytes).  Each warp owns
+// NPW output channels at a time and walks K in 512-byte steps (16 bytes per
+// lane), accumulating with dp4a against up to MT rows of A (exact int32).
+template <int MT, int NPW, bool FUSED>
+__global__ void __launch_bounds__(256) gemv_i8_kernel(const int8_t* __restrict__ Aq,
+                                                      const int8_t* __restrict__ Wq, int M, int N,
+                                                      int K, int ldk, int32_t* __restrict__ acc_out,
+                                                      float* __restrict__ Y,
+                                                      const float* __restrict__ sa,
+                                                      const float* __restrict__ sw,
+                                                      const float* __restrict__ bias, int relu) {
+  const int lane = threadIdx.x & 31;
+  const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int n0 = gwarp * NPW; n0 < N; n0 += nwarps * NPW) {
+    int acc[NPW][MT];
+#pragma unroll
+    for (int p = 0; p < NPW; ++p)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[p][m] = 0;
+    for (int k = lane * 16; k < ldk; k += 32 * 16) {
+      int4 w[NPW];
+#pragma unroll
+      for (int p = 0; p < NPW; ++p) {
+        w[p] = make_int4(0, 0, 0, 0);
+        if (n0 + p < N) w[p] = *reinterpret_cast<const int4*>(Wq + (size_t)(n0 + p) * ldk + k);
+      }
+      // bytes at k >= K inside the padded leading dimension are never used: mask them
+      int4 mask = make_int4(-1, -1, -1, -1);
+      if (k + 16 > K) {
+        int valid = K - k;  // 1..15 valid bytes (ldk is K rounded up to 16)
+        int mm[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int vb = valid - 4 * j;
+          mm[j] = vb >= 4 ? -1 : (vb <= 0 ? 0 : (int)((1u << (8 * vb)) - 1u));
+        }
+        mask = make_int4(mm[0], mm[1], mm[2], mm[3]);
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m < M) {
+          int4 a = __ldg(reinterpret_cast<const int4*>(Aq + (size_t)m * ldk + k));
+          a.x &= mask.x; a.y &= mask.y; a.z &= mask.z; a.w &= mask.w;
+#pragma unroll
+          for (int p = 0; p < NPW; ++p) {
+            int s = acc[p][m];
+            s = __dp4a(a.x, w[p].x, s);
+            s = __dp4a(a.y, w[p].y, s);
+            s = __dp4a(a.z, w[p].z, s);
+            s = __dp4a(a.w, w[p].w, s);
+            acc[p][m] = s;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < NPW; ++p)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        int s = acc[p][m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        acc[p][m] = s;
+      }
+    if (lane == 0) {
+#pragma unroll
+      for (int p = 0; p < NPW; ++p) {
+        const int n = n0 + p;
+        if (n >= N) continue;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          if (m >= M) continue;
+          if (FUSED)
+            Y[(size_t)m * N + n] = dequant1((uint32_t)acc[p][m], sa[m], sw[n],
+                                            bias ? bias[n] : 0.0f, bias != nullptr, relu);
+          else
+            acc_out[(size_t)m * N + n] = acc[p][m];
+        }
+      }
+    }
+  }
+}
+
+template <bool FUSED>
+int launch_gemv(vtlb_ctx* ctx, const int8_t* Aq, const int8_t* Wq, int M, int N, int K,
+                int32_t* acc, float* Y, const float* sa, const float* sw, const float* bias,
+                int relu) {
+  const int ldk = vtlb_i8_ld(K);
+  constexpr int NPW = 4;
+  const int warps_needed = (N + NPW - 1) / NPW;
+  int blocks = (warps_needed + 7) / 8;
+  if (blocks > ctx->sm_count * 4) blocks = ctx->sm_count * 4;
+  if (blocks < 1) blocks = 1;
+#define VTLB_GEMV(MT)                                                                          \
+  gemv_i8_kernel<MT, NPW, FUSED><<<blocks, 256, 0, ctx->stream>>>(Aq, Wq, M, N, K, ldk, acc, Y, \
+                                                                  sa, sw, bias, relu)
+  if (M <= 1) VTLB_GEMV(1);
+  else if (M <= 2) VTLB_GEMV(2);
+  else if (M <= 4) VTLB_GEMV(4);
+  else if (M <= 8) VTLB_GEMV(8);
+  else VTLB_GEMV(16);
+#undef VTLB_GEMV
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+int make_i8_tmaps(vtlb_ctx* ctx, gemm::TmapSet* tm, const void* Aq, const void* Wq, int M, int N,
+                  int K, int bn) {
+  const int ldk = vtlb_i8_ld(K);
+  int rc = gemm::encode_tmap_2d(ctx, &tm->a[0], false, Aq, (uint64_t)K, (uint64_t)M, (uint64_t)ldk,
+                                128, gemm::BM);
+  if (rc) return rc;
+  rc = gemm::encode_tmap_2d(ctx, &tm->b[0], false, Wq, (uint64_t)K, (uint64_t)N, (uint64_t)ldk, 128,
+                            bn);
+  if (rc) return rc;
+  tm->a[1] = tm->a[0];
+  tm->b[1] = tm->b[0];
+  return VTLB_OK;
+}
+
+// Tile width: 256 columns when that still gives every SM a tile, else narrower
+// so that small problems spread over more CTAs.
+int pick_bn(vtlb_ctx* ctx, int M, int N) {
+  const int tm = (M + gemm::BM - 1) / gemm::BM;
+  if (tm * ((N + 255) / 256) >= ctx->sm_count) return 256;
+  if (tm * ((N + 127) / 128) >= ctx->sm_count / 2) return 128;
+  return 64;
+}
+
+template <class Epi>
+int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, const Epi& epi) {
+  gemm::TmapSet tm;
+  const int bn = pick_bn(ctx, M, N);
+  int rc = make_i8_tmaps(ctx, &tm, Aq, Wq, M, N, K, bn);
+  if (rc) return rc;
+  if (bn == 256) return gemm::launch<gemm::KIND_I8, 256, 4, Epi>(ctx, tm, epi, M, N, K);
+  if (bn == 128) return gemm::launch<gemm::KIND_I8, 128, 6, Epi>(ctx, tm, epi, M, N, K);
+  return gemm::launch<gemm::KIND_I8, 64, 8, Epi>(ctx, tm, epi, M, N, K);
+}
+
+int check_i8_args(vtlb_ctx* ctx, const char* fn, int M, int N, int K) {
+  if (M < 0 || N < 0 || K <= 0)
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: bad shape M=%d N=%d K=%d (K must be > 0)", fn, M, N, K);
+  return VTLB_OK;
+}
+
+}  // namespace
+
+VTLB_API int vtlb_i8_ld(int K) { return (K + 15) / 16 * 16; }
+
+VTLB_API int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_Q,
+                                void* d_scale, const void* d_amax_in_or_null) {
+  VTLB_ENTER(ctx);
+  if (M < 0 || K <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: bad shape %dx%d", M, K);
+  if (M == 0) return VTLB_OK;
+  if (!d_A || !d_Q || !d_scale) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: null pointer");
+  if (!vtlb_aligned16(d_Q)) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: Q not 16-byte aligned");
+  const int ldq = vtlb_i8_ld(K);
+  if (d_amax_in_or_null)
+    quant_rows_i8_kernel<true><<<M, 256, 0, ctx->stream>>>((const float*)d_A, M, K, ldq,
+                                                           (int8_t*)d_Q, (float*)d_scale,
+                                                           (const float*)d_amax_in_or_null);
+  else
+    quant_rows_i8_kernel<false><<<M, 256, 0, ctx->stream>>>((const float*)d_A, M, K, ldq,
+                                                            (int8_t*)d_Q, (float*)d_scale, nullptr);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_row_absmax_f32(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_amax) {
+  VTLB_ENTER(ctx);
+  if (M < 0 || K <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_row_absmax_f32: bad shape %dx%d", M, K);
+  if (M == 0) return VTLB_OK;
+  if (!d_A || !d_amax) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_row_absmax_f32: null pointer");
+  row_absmax_kernel<<<M, 256, 0, ctx->stream>>>((const float*)d_A, M, K, (float*)d_amax);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq, int M, int N,
+                              int K, void* d_acc) {
+  VTLB_ENTER(ctx);
+  int rc = check_i8_args(ctx, "vtlb_gemm_i8_i32", M, N, K);
+  if (rc) return rc;
+  if (M == 0 || N == 0) return VTLB_OK;
+  if (!d_Aq || !d_Wq || !d_acc) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: null pointer");
+  if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_acc))
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: pointers must be 16-byte aligned");
+  if (M <= 16)
+    return launch_gemv<false>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K,
+                              (int32_t*)d_acc, nullptr, nullptr, nullptr, nullptr, 0);
+  EpiStoreI32 epi{(int32_t*)d_acc, N};
+  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi);
+}
+
+VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa,
+                                const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
+                                void* d_Y, int M, int N, int K, int relu) {
+  VTLB_ENTER(ctx);
+  int rc = check_i8_args(ctx, "vtlb_linear_i8_fwd", M, N, K);
+  if (rc) return rc;
+  if (M == 0 || N == 0) return VTLB_OK;
+  if (!d_Aq || !d_Wq || !d_sa || !d_sw || !d_Y)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd: null pointer");
+  if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) ||
+      !vtlb_aligned16(d_sw) || (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd: pointers must be 16-byte aligned");
+  if (M <= 16)
+    return launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr,
+                             (float*)d_Y, (const float*)d_sa, (const float*)d_sw,
+                             (const float*)d_bias_or_null, relu);
+  EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null,
+                 N, relu};
+  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi);
+}
