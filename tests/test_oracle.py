@@ -1,0 +1,172 @@
+"""The CPU oracle against the reference's own known-answer vectors
+(tests/golden/reference_kats.json) and against independent NumPy restatements."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def kats():
+    with open(os.path.join(HERE, "golden", "reference_kats.json")) as f:
+        return json.load(f)
+
+
+def test_matmul_identity(orc, kats):
+    k = kats["matmul_identity"]
+    for fn, dt in ((orc.matmul_f32, np.float32), (orc.matmul_f64, np.float64), (orc.matmul_f32_blas, np.float32)):
+        assert np.array_equal(fn(np.array(k["a"], dt), np.array(k["b"], dt)), np.array(k["expected"], dt))
+
+
+def test_linear_forward_backward_f64(orc, kats):
+    k = kats["linear_forward_f64"]
+    y = orc.linear_fwd_f64(k["x"], k["w"], k["b"])
+    assert np.abs(y - np.array(k["expected"])).max() < k["tol"]
+    k = kats["linear_backward_f64"]
+    dx, dw, db = orc.linear_bwd_f64(k["grad"], k["x"], k["w"])
+    assert np.abs(dx - np.array(k["dx"])).max() < k["tol"]
+    assert np.abs(dw - np.array(k["dw"])).max() < k["tol"]
+    assert np.abs(db - np.array(k["db"])).max() < k["tol"]
+    # f32 twin within f32 rounding
+    dx32, dw32, db32 = orc.linear_bwd_f32(k["grad"], k["x"], k["w"])
+    assert np.abs(dx32 - np.array(k["dx"])).max() < 1e-6
+    assert dw32.shape == (2, 3) and db32.shape == (1, 2)
+
+
+def test_mse_kats(orc, kats):
+    c = kats["mse"]["cases"]
+    assert orc.mse_f64(c[0]["pred"], c[0]["target"]) < c[0]["tol"]
+    assert abs(orc.mse_f64(c[1]["pred"], c[1]["target"]) - c[1]["loss"]) < c[1]["tol"]
+    assert abs(float(orc.mse_f32(c[1]["pred"], c[1]["target"])) - c[1]["loss"]) < c[1]["tol"]
+    assert abs(orc.mse_bwd_f32(c[2]["pred"], c[2]["target"])[0] - c[2]["grad0"]) < c[2]["tol"]
+
+
+def test_adam_kats(orc, kats):
+    k = kats["adam_one_step_f64"]
+    p = k["params"]
+    th, m, v = orc.adam_step_f64(k["grad"], k["theta"], k["m"], k["v"], p["b1"], p["b2"], p["lr_t"], p["eps"])
+    assert np.abs(th - np.array(k["theta_out"])).max() < 1e-15
+    assert np.abs(m - np.array(k["m_out"])).max() < 1e-15
+    assert np.abs(v - np.array(k["v_out"])).max() < 1e-15
+    th32, m32, v32 = orc.adam_step_f32(k["grad"], k["theta"], k["m"], k["v"], p["b1"], p["b2"], p["lr_t"], p["eps"])
+    assert np.abs(th32 - np.array(k["theta_out"])).max() < k["tol"]
+    assert np.abs(m32 - np.array(k["m_out"])).max() < k["tol"]
+    k = kats["adam_two_steps_f64"]
+    th, m, v = np.array(k["theta"]), np.zeros(2), np.zeros(2)
+    for _ in range(2):
+        th, m, v = orc.adam_step_f64(k["grad"], th, m, v, p["b1"], p["b2"], p["lr_t"], p["eps"])
+    assert np.abs(th - np.array(k["theta_out"])).max() < 1e-15
+
+
+def test_conv2d_kats(orc, kats):
+    k = kats["conv2d_4x4"]
+    x = np.array(k["input"], np.float32).reshape(1, 1, 4, 4)
+    w = np.array(k["weight"], np.float32).reshape(1, 1, 3, 3)
+    y = orc.conv2d_fwd_f32(x, w, np.zeros((1, 1), np.float32), pad=k["pad"], stride=k["stride"])
+    assert np.abs(y.reshape(4, 4) - np.array(k["forward"])).max() < k["tol_fwd"]
+    g = np.array(k["grad_out"], np.float32).reshape(1, 1, 4, 4)
+    dx, dw, db = orc.conv2d_bwd_f32(g, x, w, pad=k["pad"], stride=k["stride"])
+    assert np.abs(dx.reshape(4, 4) - np.array(k["d_input"])).max() < k["tol_bwd"]
+    assert np.abs(dw.reshape(3, 3) - np.array(k["d_weight"])).max() < k["tol_bwd"]
+    assert abs(float(db[0, 0]) - k["d_bias"]) < k["tol_bwd"]
+    s = kats["conv2d_shape"]
+    y = orc.conv2d_fwd_f32(np.zeros(s["in"], np.float32), np.zeros((1, 1, 2, 2), np.float32), None)
+    assert list(y.shape) == s["out"]
+
+
+def test_matmul_c_vs_blas_and_transposes(orc):
+    rng = np.random.default_rng(0)
+    A = rng.standard_normal((37, 53)).astype(np.float32)
+    B = rng.standard_normal((53, 29)).astype(np.float32)
+    ref = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)
+    for ta, tb, a, b in ((0, 0, A, B), (1, 0, A.T.copy(), B), (0, 1, A, B.T.copy()), (1, 1, A.T.copy(), B.T.copy())):
+        got = orc.matmul_f32(a, b, bool(ta), bool(tb))
+        # f64 summation order differs between the C loop and dgemm: at most 1 ulp of f32 after rounding
+        assert np.abs(got - ref).max() <= 2 * np.spacing(np.abs(ref).max())
+        assert np.abs(orc.matmul_f32_blas(a, b, bool(ta), bool(tb)) - ref).max() <= 2 * np.spacing(np.abs(ref).max())
+
+
+def test_relu_semantics(orc):
+    x = np.array([-1.0, -0.0, 0.0, 2.0, np.float32(-1e-45)], np.float32)
+    assert np.array_equal(orc.relu_f32(x), np.array([0, -0.0, 0, 2, 0], np.float32))
+    g = np.ones(5, np.float32)
+    assert np.array_equal(orc.relu_bwd_f32(g, x), np.array([0, 1, 1, 1, 0], np.float32))  # passes at exactly 0
+
+
+def test_softmax_ce_against_numpy(orc):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((9, 10)).astype(np.float32) * 4
+    t = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 9)]
+    xs = x.astype(np.float64)
+    lse = np.log(np.exp(xs - xs.max(1, keepdims=True)).sum(1)) + xs.max(1)
+    ref = np.mean(lse - (t * xs).sum(1))
+    assert abs(float(orc.softmax_ce_f32(x, t)) - ref) < 1e-6
+    sm = np.exp(xs - xs.max(1, keepdims=True))
+    sm /= sm.sum(1, keepdims=True)
+    assert np.abs(orc.softmax_ce_bwd_f32(x, t) - (sm - t) / 9).max() < 1e-7
+
+
+def test_maxpool_standard_semantics(orc):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 3, 6, 8)).astype(np.float32)
+    y, idx = orc.maxpool2d_fwd_f32(x)
+    ref = x.reshape(2, 3, 3, 2, 4, 2).max(axis=(3, 5))
+    assert np.array_equal(y, ref)
+    assert np.array_equal(x.ravel()[idx.ravel()], y.ravel())
+    g = rng.standard_normal(y.shape).astype(np.float32)
+    dx = orc.maxpool2d_bwd_f32(g, idx, x.shape)
+    assert np.isclose(dx.sum(), g.sum(), rtol=1e-5) and np.count_nonzero(dx) == g.size
+
+
+def test_adamw_matches_numpy_f64(orc):
+    rng = np.random.default_rng(3)
+    g, th, m = (rng.standard_normal(1000).astype(np.float32) for _ in range(3))
+    v = rng.random(1000).astype(np.float32)
+    b1, b2, lr_t, eps, wd = 0.9, 0.999, 1e-4, 1e-8, 0.01
+    m2 = (b1 * m.astype(np.float64) + (1 - b1) * g.astype(np.float64)).astype(np.float32)
+    v2 = (b2 * v.astype(np.float64) + (1 - b2) * g.astype(np.float64) * g.astype(np.float64)).astype(np.float32)
+    t64 = th.astype(np.float64)
+    th2 = (t64 - lr_t * (m2.astype(np.float64) / (np.sqrt(v2.astype(np.float64)) + eps) + wd * t64)).astype(np.float32)
+    oth, om, ov = orc.adamw_step_f32(g, th, m, v, b1, b2, lr_t, eps, wd)
+    assert np.array_equal(om, m2) and np.array_equal(ov, v2) and np.array_equal(oth, th2)
+
+
+def test_adam_lr_t_schedule(orc):
+    lr_t, b1t, b2t = orc.adam_lr_t(1e-3, 0.9, 0.999, 0.9, 0.999)
+    assert abs(lr_t - 1e-3 * np.sqrt(1 - 0.999) / (1 - 0.9)) < 1e-18
+    assert abs(b1t - 0.81) < 1e-15 and abs(b2t - 0.998001) < 1e-15
+
+
+def test_int8_definition(orc):
+    A = np.array([[0.0, 0.0, 0.0, 0.0], [1.0, -2.0, 0.5, 0.25], [127.0, -127.0, 63.5, 0.5]], np.float32)
+    q, s = orc.quant_rows_i8(A)
+    assert np.array_equal(q[0], [0, 0, 0, 0]) and s[0] == 0
+    assert np.array_equal(q[1], [64, -127, 32, 16])  # 63.5 -> 64 and 31.75 -> 32, 15.875 -> 16
+    assert np.array_equal(q[2], [127, -127, 64, 0])  # ties to even: 63.5 -> 64, 0.5 -> 0
+    assert s[1] == np.float32(2.0) / np.float32(127.0)
+    rng = np.random.default_rng(5)
+    a = rng.integers(-127, 128, (7, 33), dtype=np.int8)
+    w = rng.integers(-127, 128, (5, 33), dtype=np.int8)
+    acc = orc.gemm_i8_i32(a, w)
+    assert np.array_equal(acc, a.astype(np.int32) @ w.astype(np.int32).T)
+    sa, sw = rng.random(7, dtype=np.float32), rng.random(5, dtype=np.float32)
+    b = rng.standard_normal(5).astype(np.float32)
+    y = orc.dequant_bias_relu(acc, sa, sw, b, True)
+    ref = np.maximum(acc.astype(np.float32) * (sa[:, None] * sw[None, :]) + b[None, :], 0).astype(np.float32)
+    assert np.array_equal(y, ref)
+
+
+def test_mlp_oracle_step_decreases_loss(orc):
+    rng = np.random.default_rng(1)
+    W1 = (rng.uniform(-1, 1, (16, 8)) * np.sqrt(6 / 8)).astype(np.float32)
+    W2 = (rng.uniform(-1, 1, (4, 16)) * np.sqrt(6 / 16)).astype(np.float32)
+    net = orc.MLPOracle([W1, W2], [np.zeros(16), np.zeros(4)], [True, False], lr=1e-2)
+    X = rng.random((32, 8), dtype=np.float32)
+    T = np.eye(4, dtype=np.float32)[rng.integers(0, 4, 32)]
+    losses = [float(net.step(X, T)) for _ in range(30)]
+    assert losses[-1] < losses[0]
+    blas = orc.MLPOracle([W1, W2], [np.zeros(16), np.zeros(4)], [True, False], lr=1e-2, blas=True)
+    assert abs(float(blas.step(X, T)) - losses[0]) < 1e-6

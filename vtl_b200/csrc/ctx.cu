@@ -57,6 +57,12 @@ VTLB_API int vtlb_ctx_create(int device, vtlb_ctx** out) {
   if (!ctx) return vtlb_fail(nullptr, VTLB_ENOMEM, "vtlb_ctx_create: host allocation failed");
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
+  {  // keep freed blocks in the pool instead of returning them to the driver at every sync
+    cudaMemPool_t pool;
+    unsigned long long keep = ~0ull;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess)
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming)) != cudaSuccess ||
@@ -146,7 +152,9 @@ VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
   if (!d_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_alloc: null out");
   *d_out = nullptr;
   if (bytes == 0) return VTLB_OK;
-  cudaError_t e = cudaMalloc(d_out, bytes);
+  // Stream-ordered allocation from the device's pool: no device-wide synchronisation,
+  // and freed blocks are reused by later allocations on the same stream.
+  cudaError_t e = cudaMallocAsync(d_out, bytes, ctx->stream);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
@@ -157,8 +165,13 @@ VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
 VTLB_API int vtlb_free(vtlb_ctx* ctx, void* d_ptr) {
   VTLB_ENTER(ctx);
   if (!d_ptr) return VTLB_OK;
-  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  VTLB_CUDA(ctx, cudaFree(d_ptr));
+  // ordered after the work already enqueued on the compute stream; collectives still in
+  // flight on the communication stream are waited for first
+  if (ctx->comm) {
+    VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+    VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  }
+  VTLB_CUDA(ctx, cudaFreeAsync(d_ptr, ctx->stream));
   return VTLB_OK;
 }
 

@@ -212,7 +212,7 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
   if ((rc = split_operand(ctx, B, N, K, transB == 0, ld, b_hi, b_lo))) return rc;
 
   int bn = f32_bn_override();
-  if (bn != 64 && bn != 128 && bn != 256) {
+  if (bn != 64 && bn != 128) {
     const int tm = (M + gemm::BM - 1) / gemm::BM;
     bn = (tm * ((N + 127) / 128) >= ctx->sm_count / 2) ? 128 : 64;
   }
@@ -223,7 +223,6 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, b_hi, K, N, stride, 32, bn))) return rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, b_lo, K, N, stride, 32, bn))) return rc;
   EpiBiasRelu epi{C, bias, pre, N, relu};
-  if (bn == 256) return gemm::launch<gemm::KIND_TF32X3, 256, 2, EpiBiasRelu>(ctx, tm, epi, M, N, K);
   if (bn == 128) return gemm::launch<gemm::KIND_TF32X3, 128, 3, EpiBiasRelu>(ctx, tm, epi, M, N, K);
   return gemm::launch<gemm::KIND_TF32X3, 64, 4, EpiBiasRelu>(ctx, tm, epi, M, N, K);
 }

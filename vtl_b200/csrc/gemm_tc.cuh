@@ -9,8 +9,8 @@
 //   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the fused
 //               epilogue functor, store to global
 // Shared-memory stages form a ring guarded by full/empty mbarriers; the
-// accumulator is double-buffered in tensor memory (2 x BN columns) so the
-// epilogue of tile i overlaps the MMAs of tile i+1.  Every CTA loads its own
+// accumulator is double-buffered in tensor memory so the epilogue of one
+// accumulator overlaps the MMAs that fill the other.  Every CTA loads its own
 // tiles; there is no cluster and no multicast.
 //
 // Every mbarrier wait is bounded (ptx::mbar_wait_bounded).  If one runs out the
@@ -72,7 +72,15 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
   constexpr int NOP = T::NOP;
   constexpr int BK = ROW_BYTES / T::ELEM;   // elements of K per stage
   constexpr int KSTEPS = ROW_BYTES / 32;    // MMAs per operand pair per stage (32 B of K each)
-  constexpr uint32_t TMEM_COLS = 2 * BN;
+  // Tensor-memory accumulators.  INT8 is exact, so one accumulator per buffer takes the
+  // whole K loop.  The f32 accumulator of tcgen05 truncates on every add, a bias that
+  // grows with the number of MMAs; the TF32x3 path therefore (a) keeps the small
+  // cross terms (lo.hi + hi.lo) in an accumulator of their own, so they never cost
+  // the leading sum an ulp, and (b) closes an accumulator every CHUNK_KB stages; the
+  // epilogue warps sum the chunks in registers with round-to-nearest adds.
+  constexpr int NACC = (KIND == KIND_TF32X3) ? 2 : 1;
+  constexpr int CHUNK_KB = (KIND == KIND_TF32X3) ? 4 : 0;  // 0 = the whole K loop
+  constexpr uint32_t TMEM_COLS = 2 * NACC * BN;
   static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
   constexpr uint32_t IDESC = ptx::umma_idesc(T::CFMT, T::ABFMT, BM, BN);
 
@@ -91,6 +99,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int chunk_kb = CHUNK_KB ? CHUNK_KB : num_kb;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -152,72 +161,116 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS))
-          break;
-        ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
+          const int kb1 = kb0 + chunk_kb < num_kb ? kb0 + chunk_kb : num_kb;
+          if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag,
+                                      WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t sa = base + stage * S::STAGE;
-          const uint32_t sb = sa + NOP * S::A_TILE;
+          const uint32_t d_main = tmem_base + acc * BN;
+          const uint32_t d_small = tmem_base + (2 + acc) * BN;  // TF32x3 only
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t sa = base + stage * S::STAGE;
+            const uint32_t sb = sa + NOP * S::A_TILE;
 #pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {
-            // advancing 32 bytes along K inside the swizzled row = +2 in the address field
-            if constexpr (KIND == KIND_I8) {
-              const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
-              const uint64_t db = ptx::umma_desc_k_sw128(sb) + 2u * kk;
-              ptx::umma_i8(d_tmem, da, db, IDESC, (kb | kk) != 0);
-            } else {
-              const uint64_t a_hi = ptx::umma_desc_k_sw128(sa) + 2u * kk;
-              const uint64_t a_lo = ptx::umma_desc_k_sw128(sa + S::A_TILE) + 2u * kk;
-              const uint64_t b_hi = ptx::umma_desc_k_sw128(sb) + 2u * kk;
-              const uint64_t b_lo = ptx::umma_desc_k_sw128(sb + S::B_TILE) + 2u * kk;
-              // small terms first, then the leading one
-              ptx::umma_tf32(d_tmem, a_lo, b_hi, IDESC, (kb | kk) != 0);
-              ptx::umma_tf32(d_tmem, a_hi, b_lo, IDESC, 1);
-              ptx::umma_tf32(d_tmem, a_hi, b_hi, IDESC, 1);
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+              const uint32_t first = (kb == kb0 && kk == 0) ? 0u : 1u;
+              // advancing 32 bytes along K inside the swizzled row = +2 in the address field
+              if constexpr (KIND == KIND_I8) {
+                const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+                const uint64_t db = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+                ptx::umma_i8(d_main, da, db, IDESC, first);
+              } else {
+                const uint64_t a_hi = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+                const uint64_t a_lo = ptx::umma_desc_k_sw128(sa + S::A_TILE) + 2u * kk;
+                const uint64_t b_hi = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+                const uint64_t b_lo = ptx::umma_desc_k_sw128(sb + S::B_TILE) + 2u * kk;
+                ptx::umma_tf32(d_small, a_lo, b_hi, IDESC, first);
+                ptx::umma_tf32(d_small, a_hi, b_lo, IDESC, 1);
+                ptx::umma_tf32(d_main, a_hi, b_hi, IDESC, first);
+              }
+            }
+            ptx::umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
-          ptx::umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (!ok) break;
+          ptx::umma_commit(tfull_bar(acc));  // this chunk's accumulators are complete
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        if (!ok) break;
-        ptx::umma_commit(tfull_bar(acc));  // accumulator complete
-        acc ^= 1u;
-        if (acc == 0) acc_phase ^= 1u;
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-      bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      ptx::tc_fence_after();
       const int row = m0 + q * 32 + lane;
+      if constexpr (KIND == KIND_I8) {
+        ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ptx::tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32;
-        ptx::tmem_ld_32x32(taddr, v);
-        ptx::tmem_wait_ld();
-        epi(row, n0 + c * 32, v, M, N);
-        __syncwarp();
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
+          ptx::tmem_wait_ld();
+          epi(row, n0 + c * 32, v, M, N);
+          __syncwarp();
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(tempty_bar(acc));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      } else {
+        float sum[BN];
+#pragma unroll
+        for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
+        for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+          ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32], w[32];
+            ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
+            ptx::tmem_ld_32x32(lane_base + (2 + acc) * BN + c * 32, w);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              sum[c * 32 + j] = __fadd_rn(
+                  sum[c * 32 + j], __fadd_rn(__uint_as_float(v[j]), __uint_as_float(w[j])));
+          }
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(tempty_bar(acc));
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
+          epi(row, n0 + c * 32, v, M, N);
+          __syncwarp();
+        }
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(tempty_bar(acc));
-      acc ^= 1u;
-      if (acc == 0) acc_phase ^= 1u;
     }
   }
 

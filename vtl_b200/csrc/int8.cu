@@ -251,6 +251,9 @@ __global__ void __launch_bounds__(256) gemv_i8_kernel(const int8_t* __restrict__
   }
 }
 
+// Above this many rows the tensor-core kernel (narrow tiles) is faster than dp4a.
+constexpr int kGemvMaxM = 4;
+
 template <bool FUSED>
 int launch_gemv(vtlb_ctx* ctx, const int8_t* Aq, const int8_t* Wq, int M, int N, int K,
                 int32_t* acc, float* Y, const float* sa, const float* sw, const float* bias,
@@ -356,7 +359,7 @@ VTLB_API int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq,
   if (!d_Aq || !d_Wq || !d_acc) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: null pointer");
   if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_acc))
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: pointers must be 16-byte aligned");
-  if (M <= 16)
+  if (M <= kGemvMaxM)
     return launch_gemv<false>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K,
                               (int32_t*)d_acc, nullptr, nullptr, nullptr, nullptr, 0);
   EpiStoreI32 epi{(int32_t*)d_acc, N};
@@ -375,7 +378,7 @@ VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_s
   if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) ||
       !vtlb_aligned16(d_sw) || (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd: pointers must be 16-byte aligned");
-  if (M <= 16)
+  if (M <= kGemvMaxM)
     return launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr,
                              (float*)d_Y, (const float*)d_sa, (const float*)d_sw,
                              (const float*)d_bias_or_null, relu);
