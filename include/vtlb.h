@@ -114,6 +114,19 @@ int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X, const v
                         void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N,
                         int K);
 
+/* db[N] = column sums of G[M,N] (the bias gradient of vtlb_linear_bwd_f32) for callers
+ * that cannot let the library allocate device memory: a host that has already given all of
+ * HBM to its own pools, or a loop whose latency budget an allocation's implicit
+ * synchronisation would break.  No counterpart in the reference.  The partial sums live in
+ * a fixed 2 MiB array inside the library image (held on every GPU that loads the library
+ * until exit) instead of the ctx scratch, so the call never allocates; the limit is
+ * N <= 4096 columns (any M), larger N is refused with VTLB_EINVAL.  The first call on a
+ * device looks up the array's device address: make that call before any stream capture.
+ * All calls on a GPU share the one array (each call overwrites what it reads, nothing is
+ * carried over), so calls that overlap on the same GPU - two contexts, two streams - race;
+ * issue them one after the other. */
+int vtlb_bias_grad_f32_noalloc(vtlb_ctx* ctx, const void* d_G, int M, int N, void* d_db);
+
 /* ---- ReLU -----------------------------------------------------------------
  * y = x < 0 ? 0 : x;   dx = cached_x < 0 ? 0 : g   (gradient passes at exactly 0).
  * Replaces: relu_forward_f32_try (nn/layers/activation_relu_forward_f32_try_*.v:6),

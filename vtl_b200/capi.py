@@ -52,6 +52,7 @@ _PROTOS = {
     "vtlb_gemm_f32": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i],
     "vtlb_linear_fwd_f32": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "vtlb_linear_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
+    "vtlb_bias_grad_f32_noalloc": [_vp, _vp, _i, _i, _vp],
     "vtlb_relu_fwd_f32": [_vp, _vp, _vp, _sz],
     "vtlb_relu_bwd_f32": [_vp, _vp, _vp, _vp, _sz],
     "vtlb_mse_fwd_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp, _vp],
@@ -247,6 +248,9 @@ class Device:
     def linear_bwd_f32(self, G, X, W, dX, dW, db, M, N, K):
         self._ck(self.lib.vtlb_linear_bwd_f32(self.h, _ptr(G), _ptr(X), _ptr(W), _ptr(dX),
                                               _ptr(dW), _ptr(db), M, N, K))
+
+    def bias_grad_f32_noalloc(self, G, M, N, db):
+        self._ck(self.lib.vtlb_bias_grad_f32_noalloc(self.h, _ptr(G), M, N, _ptr(db)))
 
     def relu_fwd_f32(self, x, y, n):
         self._ck(self.lib.vtlb_relu_fwd_f32(self.h, _ptr(x), _ptr(y), n))

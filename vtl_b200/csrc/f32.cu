@@ -304,3 +304,49 @@ VTLB_API int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X
   }
   return VTLB_OK;
 }
+
+// ---------------------------------------------------------------- bias gradient without allocation
+// Some hosts cannot let this library allocate device memory while they run: a
+// serving process that handed every byte of HBM to its own pools at start-up
+// (so a cudaMalloc here would simply fail), or a control loop with a latency
+// budget that the implicit synchronisation of an allocation would break.  For
+// them the bias gradient (column sums of G) is offered with its partial-sum
+// scratch in a fixed array that is part of the library image: every GPU that
+// loads the library holds these 2 MiB until the process exits.
+constexpr int kNoAllocMaxN = 4096;  // widest G supported by the fixed scratch
+constexpr int kNoAllocMaxS = 64;    // row slices (same cap as the allocating path)
+static __device__ __align__(256) double g_bias_grad_scratch[(size_t)kNoAllocMaxS * kNoAllocMaxN];
+
+// In host code the array's name is only a handle; the device address has to be
+// asked for, once per device, with that device current.
+static double* g_bias_grad_scratch_addr[64] = {nullptr};
+
+VTLB_API int vtlb_bias_grad_f32_noalloc(vtlb_ctx* ctx, const void* d_G, int M, int N, void* d_db) {
+  VTLB_ENTER(ctx);
+  if (M <= 0 || N <= 0)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_bias_grad_f32_noalloc: bad shape M=%d N=%d", M, N);
+  if (N > kNoAllocMaxN)
+    return vtlb_fail(ctx, VTLB_EINVAL,
+                     "vtlb_bias_grad_f32_noalloc: N=%d exceeds the fixed scratch (at most %d "
+                     "columns); use vtlb_linear_bwd_f32, which allocates",
+                     N, kNoAllocMaxN);
+  if (!d_G || !d_db) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_bias_grad_f32_noalloc: null pointer");
+  if (ctx->device < 0 || ctx->device >= 64)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_bias_grad_f32_noalloc: device index %d not supported", ctx->device);
+  double* scratch = g_bias_grad_scratch_addr[ctx->device];
+  if (!scratch) {  // first call on this device: resolve the array's device address
+    void* p = nullptr;
+    VTLB_CUDA(ctx, cudaGetSymbolAddress(&p, g_bias_grad_scratch));
+    scratch = g_bias_grad_scratch_addr[ctx->device] = (double*)p;
+  }
+  int S = (M + 63) / 64;
+  if (S > kNoAllocMaxS) S = kNoAllocMaxS;
+  // every partial[s][n] with s < S, n < N is written by the first kernel before the second
+  // reads it, so nothing left over from an earlier call is ever used and nothing needs clearing
+  dim3 grid((N + 127) / 128, S);
+  colsum_partial_kernel<<<grid, 128, 0, ctx->stream>>>((const float*)d_G, M, N, scratch);
+  VTLB_LAUNCHED(ctx);
+  colsum_final_kernel<<<(N + 127) / 128, 128, 0, ctx->stream>>>(scratch, S, N, (float*)d_db);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
