@@ -135,6 +135,34 @@ int vtlb_bias_grad_f32_noalloc(vtlb_ctx* ctx, const void* d_G, int M, int N, voi
 int vtlb_relu_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, size_t n);
 int vtlb_relu_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_cached_x, void* d_dx, size_t n);
 
+/* dst += src (Variable.backprop's parent.grad.add(diff), autograd/variable.v:105) and
+ * dst[i] = value (ones_like for the backprop seed, autograd/variable.v:88). */
+int vtlb_add_inplace_f32(vtlb_ctx* ctx, void* d_dst, const void* d_src, size_t n);
+int vtlb_fill_f32(vtlb_ctx* ctx, void* d_dst, float value, size_t n);
+
+/* ---- Conv2D / max pooling (NCHW, groups = 1, dilation = 1) ------------------
+ * y[B,O,OH,OW] = conv(x[B,C,H,W], w[O,C,kh,kw]) + bias[O], OH = (H+2ph-kh)/sh+1; with
+ * relu != 0 the output is activated and d_pre_or_null receives the pre-activation.
+ * Lowered to the 3xTF32 tcgen05 GEMM with K = C*kh*kw in (ic,kh,kw) order.
+ * Backward: d_input, d_weight[O,C,kh,kw], d_bias[O]; any output may be NULL.
+ * Replaces: conv2d_forward_f32 / conv2d_backward_f32 (nn/internal/conv2d_forward_f32.v:6,
+ * conv2d_backward_f32.v:6, CPU loops conv2d_forward_cpu_f32.v:26-62,
+ * conv2d_backward_cpu_f32.v:26-97) and compute.conv2d_cuda / conv2d_backward_cuda
+ * (nn/internal/conv2d_cuda_d_cuda.v:28-71, conv2d_backward_cuda_d_cuda.v:9-46). */
+int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                        void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
+                        int sh, int sw, int relu, void* d_pre_or_null);
+int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
+                        void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
+                        int W, int O, int kh, int kw, int ph, int pw, int sh, int sw);
+/* 2-D max pooling with the window geometry of internal.maxpool2d
+ * (nn/internal/layers.v:21-66); the first maximum in scan order wins; d_idx (int32) holds
+ * the flat index into the whole input.  Backward scatters g onto zeros (layers.v:69-84). */
+int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, void* d_idx, int B, int C, int H,
+                           int W, int kh, int kw, int ph, int pw, int sh, int sw);
+int vtlb_maxpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, void* d_dx, size_t n_out,
+                           size_t n_in);
+
 /* ---- losses ---------------------------------------------------------------
  * MSE as the reference computes it: loss = sum((p-t)^2)/n, dP = (p - t) * g with
  * no 2/n factor (nn/internal/activation.v:365-373, nn/internal/loss.v:7-12).

@@ -411,3 +411,85 @@ class MLPOracle:
         loss, y, dWs, dbs, _ = self.grads(X, T)
         self.apply(dWs, dbs)
         return loss
+
+
+class SequentialOracle:
+    """A Sequential of conv2d / relu / maxpool2d / flatten / linear layers with an MSE or
+    softmax-cross-entropy loss and Adam, stepped exactly as the reference CPU path does
+    (Sequential.forward nn/models/sequential.v:204-215; backprop autograd/variable.v:87-109;
+    AdamOptimizer.update nn/optimizers/adam.v:87-145).  `spec` is a list of tuples:
+    ("conv2d", W[O,C,kh,kw], b[O], pad, stride) | ("linear", W[N,K], b[N]) | ("relu",) |
+    ("maxpool2d", kernel, pad, stride) | ("flatten",)."""
+
+    def __init__(self, spec, loss="mse", lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, blas=False):
+        self.spec = [list(s) for s in spec]
+        self.loss_kind, self.lr, self.beta1, self.beta2, self.eps = loss, lr, beta1, beta2, eps
+        self.beta1_t, self.beta2_t, self.blas = beta1, beta2, blas
+        self.params = []  # (layer index, slot) in the order layers declare them (weight, bias)
+        for li, s in enumerate(self.spec):
+            if s[0] in ("conv2d", "linear"):
+                s[1] = _f32(s[1]).copy()
+                s[2] = _f32(s[2]).reshape(1, -1).copy()
+                self.params += [(li, 1), (li, 2)]
+        self.m = [np.zeros_like(self.spec[li][k]) for li, k in self.params]
+        self.v = [np.zeros_like(self.spec[li][k]) for li, k in self.params]
+
+    def param(self, i):
+        li, k = self.params[i]
+        return self.spec[li][k]
+
+    def forward(self, x):
+        caches = []
+        h = _f32(x)
+        for s in self.spec:
+            if s[0] == "conv2d":
+                caches.append(h)
+                h = conv2d_fwd_f32(h, s[1], s[2], pad=s[3], stride=s[4])
+            elif s[0] == "linear":
+                caches.append(h)
+                h = linear_fwd_f32(h, s[1], s[2], blas=self.blas)
+            elif s[0] == "relu":
+                caches.append(h)
+                h = relu_f32(h)
+            elif s[0] == "maxpool2d":
+                y, idx = maxpool2d_fwd_f32(h, s[1], s[2], s[3])
+                caches.append((idx, h.shape))
+                h = y
+            elif s[0] == "flatten":
+                caches.append(h.shape)
+                h = h.reshape(h.shape[0], -1)
+        return h, caches
+
+    def grads(self, x, t):
+        y, caches = self.forward(x)
+        if self.loss_kind == "mse":
+            loss, g = mse_f32(y, t), mse_bwd_f32(y, t)
+        else:
+            loss, g = softmax_ce_f32(y, t), softmax_ce_bwd_f32(y, t)
+        grads = {}
+        for li in reversed(range(len(self.spec))):
+            s, c = self.spec[li], caches[li]
+            if s[0] == "conv2d":
+                g, dw, db = conv2d_bwd_f32(g, c, s[1], pad=s[3], stride=s[4])
+                grads[(li, 1)], grads[(li, 2)] = dw, db
+            elif s[0] == "linear":
+                g, dw, db = linear_bwd_f32(g, c, s[1], blas=self.blas)
+                grads[(li, 1)], grads[(li, 2)] = dw, db
+            elif s[0] == "relu":
+                g = relu_bwd_f32(g, c)
+            elif s[0] == "maxpool2d":
+                g = maxpool2d_bwd_f32(g, c[0], c[1])
+            elif s[0] == "flatten":
+                g = g.reshape(c)
+        return loss, y, [grads[p] for p in self.params], g
+
+    def step(self, x, t):
+        loss, _, grads, _ = self.grads(x, t)
+        lr_t, self.beta1_t, self.beta2_t = adam_lr_t(self.lr, self.beta1_t, self.beta2_t, self.beta1,
+                                                      self.beta2)
+        for i, (li, k) in enumerate(self.params):
+            shp = self.spec[li][k].shape
+            th, m, v = adam_step_f32(grads[i].ravel(), self.spec[li][k].ravel(), self.m[i].ravel(),
+                                     self.v[i].ravel(), self.beta1, self.beta2, lr_t, self.eps)
+            self.spec[li][k], self.m[i], self.v[i] = th.reshape(shp), m.reshape(shp), v.reshape(shp)
+        return loss

@@ -1,0 +1,119 @@
+"""Conv2D forward/backward and max pooling on the GPU against the CPU oracle.  The oracle
+accumulates in f32 in (ic,kh,kw) order as the reference does; the GPU runs the lowered 3xTF32
+GEMM, so the comparison uses the stated bound 1e-5*sqrt(K)*max|A|*max|B| with K the
+contraction length of each product."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def tol(K, A, B):
+    return 1e-5 * np.sqrt(K) * float(np.abs(A).max()) * float(np.abs(B).max())
+
+
+def run_conv(dev, x, w, b, pad, stride, relu=False):
+    B, C, H, W = x.shape
+    O, _, kh, kw = w.shape
+    OH = (H + 2 * pad[0] - kh) // stride[0] + 1
+    OW = (W + 2 * pad[1] - kw) // stride[1] + 1
+    dx, dw = dev.to_device(x), dev.to_device(w)
+    db = dev.to_device(b) if b is not None else None
+    dy, dpre = dev.zeros((B, O, OH, OW)), dev.zeros((B, O, OH, OW))
+    dev.conv2d_fwd_f32(dx, dw, db, dy, B, C, H, W, O, kh, kw, pad[0], pad[1], stride[0], stride[1], relu,
+                       dpre if relu else None)
+    assert dev.check_status() == 0
+    return dy.numpy(), dpre.numpy()
+
+
+def run_conv_bwd(dev, g, x, w, pad, stride):
+    B, C, H, W = x.shape
+    O, _, kh, kw = w.shape
+    dg, dx, dw = dev.to_device(g), dev.to_device(x), dev.to_device(w)
+    gdx, gdw, gdb = dev.zeros(x.shape), dev.zeros(w.shape), dev.zeros(O)
+    dev.conv2d_bwd_f32(dg, dx, dw, gdx, gdw, gdb, B, C, H, W, O, kh, kw, pad[0], pad[1], stride[0], stride[1])
+    assert dev.check_status() == 0
+    return gdx.numpy(), gdw.numpy(), gdb.numpy()
+
+
+def test_conv2d_reference_kat(dev):
+    """nn/internal/conv2d_cuda_test.v:32-59, 85-122 (1x1x4x4 input 1..16, 3x3 kernel, pad 1)."""
+    k = json.load(open(os.path.join(HERE, "golden", "reference_kats.json")))["conv2d_4x4"]
+    x = np.array(k["input"], np.float32).reshape(1, 1, 4, 4)
+    w = np.array(k["weight"], np.float32).reshape(1, 1, 3, 3)
+    y, _ = run_conv(dev, x, w, np.zeros(1, np.float32), k["pad"], k["stride"])
+    assert np.abs(y.reshape(4, 4) - np.array(k["forward"])).max() < k["tol_fwd"]
+    g = np.array(k["grad_out"], np.float32).reshape(1, 1, 4, 4)
+    dx, dw, db = run_conv_bwd(dev, g, x, w, k["pad"], k["stride"])
+    assert np.abs(dx.reshape(4, 4) - np.array(k["d_input"])).max() < k["tol_bwd"]
+    assert np.abs(dw.reshape(3, 3) - np.array(k["d_weight"])).max() < k["tol_bwd"]
+    assert abs(float(db[0]) - k["d_bias"]) < k["tol_bwd"]
+
+
+@pytest.mark.parametrize("B,C,H,W,O,k,pad,stride", [
+    (2, 3, 32, 32, 32, 3, 1, 1),      # conv1 of the CNN configuration (small batch)
+    (2, 32, 32, 32, 64, 3, 1, 1),     # conv2
+    (3, 5, 9, 11, 7, 3, 0, 1),        # ragged everything, no padding
+    (2, 4, 12, 10, 6, 2, 1, 2),       # even kernel, stride 2
+    (1, 1, 4, 4, 1, 2, 0, 1),         # conv2d_cuda_test.v:7-19 shape case -> [1,1,3,3]
+])
+def test_conv2d_fwd_bwd_vs_oracle(dev, orc, B, C, H, W, O, k, pad, stride):
+    rng = np.random.default_rng(B * 100 + C * 10 + O)
+    x = rng.standard_normal((B, C, H, W)).astype(np.float32)
+    w = (rng.uniform(-1, 1, (O, C, k, k)) * np.sqrt(6.0 / (C * k * k))).astype(np.float32)
+    b = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    y, pre = run_conv(dev, x, w, b, (pad, pad), (stride, stride), relu=True)
+    ref = orc.conv2d_fwd_f32(x, w, b, pad=(pad, pad), stride=(stride, stride))
+    Kc = C * k * k
+    assert y.shape == ref.shape
+    assert np.abs(pre - ref).max() <= tol(Kc, x, w)
+    assert np.abs(y - orc.relu_f32(ref)).max() <= tol(Kc, x, w)
+    g = rng.standard_normal(ref.shape).astype(np.float32)
+    dx, dw, db = run_conv_bwd(dev, g, x, w, (pad, pad), (stride, stride))
+    rdx, rdw, rdb = orc.conv2d_bwd_f32(g, x, w, pad=(pad, pad), stride=(stride, stride))
+    Mc = B * ref.shape[2] * ref.shape[3]
+    assert np.abs(dx - rdx).max() <= tol(O * k * k, g, w)
+    assert np.abs(dw - rdw).max() <= tol(Mc, g, x)
+    assert np.abs(db - rdb.ravel()).max() <= tol(Mc, g, np.ones(1))
+
+
+def test_conv2d_split_k_path(dev, orc):
+    """A batch large enough for the d_weight GEMM to split its contraction over CTAs."""
+    rng = np.random.default_rng(9)
+    B, C, H, W, O = 16, 8, 32, 32, 16
+    x = rng.standard_normal((B, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((O, C, 3, 3)) * 0.1).astype(np.float32)
+    g = rng.standard_normal((B, O, H, W)).astype(np.float32)
+    dx, dw, db = run_conv_bwd(dev, g, x, w, (1, 1), (1, 1))
+    rdx, rdw, rdb = orc.conv2d_bwd_f32(g, x, w, pad=(1, 1), stride=(1, 1))
+    assert np.abs(dw - rdw).max() <= tol(B * H * W, g, x)
+    assert np.abs(dx - rdx).max() <= tol(O * 9, g, w)
+    assert np.abs(db - rdb.ravel()).max() <= tol(B * H * W, g, np.ones(1))
+
+
+@pytest.mark.parametrize("shape,kernel,pad,stride", [((2, 3, 6, 8), (2, 2), (0, 0), (2, 2)),
+                                                      ((4, 64, 32, 32), (2, 2), (0, 0), (2, 2)),
+                                                      ((1, 2, 7, 7), (3, 3), (1, 1), (2, 2))])
+def test_maxpool_bit_exact(dev, orc, shape, kernel, pad, stride):
+    rng = np.random.default_rng(sum(shape))
+    x = rng.standard_normal(shape).astype(np.float32)
+    x[0, 0, 0, :2] = 5.0  # a tie inside the first window: the first maximum must win
+    ry, ridx = orc.maxpool2d_fwd_f32(x, kernel, pad, stride)
+    dx = dev.to_device(x)
+    dy, didx = dev.zeros(ry.shape), dev.zeros(ry.shape, np.int32)
+    B, C, H, W = shape
+    dev.maxpool2d_fwd_f32(dx, dy, didx, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1])
+    assert np.array_equal(dy.numpy(), ry)
+    assert np.array_equal(didx.numpy(), ridx)
+    g = rng.standard_normal(ry.shape).astype(np.float32)
+    dg, dgx = dev.to_device(g), dev.zeros(shape)
+    dev.maxpool2d_bwd_f32(dg, didx, dgx, g.size, x.size)
+    ref = orc.maxpool2d_bwd_f32(g, ridx, shape)
+    if stride[0] >= kernel[0]:
+        assert np.array_equal(dgx.numpy(), ref)
+    else:  # overlapping windows add in a different order
+        assert np.abs(dgx.numpy() - ref).max() <= 1e-6

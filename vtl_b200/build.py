@@ -79,7 +79,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
+    _build_host(force or bool(jobs), verbose)
     return LIB
+
+
+HOST_LIB = os.path.join(HERE, "libvtl_host.so")
+
+
+def _build_host(force: bool, verbose: bool) -> str:
+    """The C++ host mirror (csrc/host): plain g++, linked against libvtlb200.so only."""
+    hdir = os.path.join(CSRC, "host")
+    srcs = sorted(glob.glob(os.path.join(hdir, "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(hdir, "*.h*")) + [os.path.join(HERE, "..", "include", "vtlb.h")]
+    if not force and os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(map(os.path.getmtime, deps)):
+        return HOST_LIB
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-fvisibility=default", "-o", HOST_LIB, *srcs,
+           "-L", HERE, "-lvtlb200", "-Wl,-rpath,$ORIGIN"]
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    if p.returncode != 0:
+        raise RuntimeError(f"host library build failed:\n{p.stdout}\n{p.stderr}")
+    if verbose:
+        print(p.stdout, p.stderr)
+    return HOST_LIB
 
 
 if __name__ == "__main__":

@@ -55,6 +55,12 @@ _PROTOS = {
     "vtlb_bias_grad_f32_noalloc": [_vp, _vp, _i, _i, _vp],
     "vtlb_relu_fwd_f32": [_vp, _vp, _vp, _sz],
     "vtlb_relu_bwd_f32": [_vp, _vp, _vp, _vp, _sz],
+    "vtlb_add_inplace_f32": [_vp, _vp, _vp, _sz],
+    "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
+    "vtlb_conv2d_fwd_f32": [_vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_vp],
+    "vtlb_conv2d_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 11,
+    "vtlb_maxpool2d_fwd_f32": [_vp, _vp, _vp, _vp] + [_i] * 10,
+    "vtlb_maxpool2d_bwd_f32": [_vp, _vp, _vp, _vp, _sz, _sz],
     "vtlb_mse_fwd_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp, _vp],
     "vtlb_softmax_ce_fwd_bwd_f32": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "vtlb_adam_step_f32": [_vp, _i, C.POINTER(AdamTensor), _d, _d, _d, _d, _i],
@@ -257,6 +263,27 @@ class Device:
 
     def relu_bwd_f32(self, g, cached, dx, n):
         self._ck(self.lib.vtlb_relu_bwd_f32(self.h, _ptr(g), _ptr(cached), _ptr(dx), n))
+
+    def add_inplace_f32(self, dst, src, n):
+        self._ck(self.lib.vtlb_add_inplace_f32(self.h, _ptr(dst), _ptr(src), n))
+
+    def fill_f32(self, dst, value, n):
+        self._ck(self.lib.vtlb_fill_f32(self.h, _ptr(dst), value, n))
+
+    def conv2d_fwd_f32(self, x, w, bias, y, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, relu=False, pre=None):
+        self._ck(self.lib.vtlb_conv2d_fwd_f32(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), B, Cc, H, W, O,
+                                              kh, kw, ph, pw, sh, sw, int(relu), _ptr(pre)))
+
+    def conv2d_bwd_f32(self, g, x, w, dx, dw, db, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw):
+        self._ck(self.lib.vtlb_conv2d_bwd_f32(self.h, _ptr(g), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db),
+                                              B, Cc, H, W, O, kh, kw, ph, pw, sh, sw))
+
+    def maxpool2d_fwd_f32(self, x, y, idx, B, Cc, H, W, kh, kw, ph, pw, sh, sw):
+        self._ck(self.lib.vtlb_maxpool2d_fwd_f32(self.h, _ptr(x), _ptr(y), _ptr(idx), B, Cc, H, W, kh, kw,
+                                                 ph, pw, sh, sw))
+
+    def maxpool2d_bwd_f32(self, g, idx, dx, n_out, n_in):
+        self._ck(self.lib.vtlb_maxpool2d_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(dx), n_out, n_in))
 
     def mse_fwd_bwd_f32(self, P, T, n, n_div, loss, dP=None):
         self._ck(self.lib.vtlb_mse_fwd_bwd_f32(self.h, _ptr(P), _ptr(T), n, n_div, _ptr(loss),

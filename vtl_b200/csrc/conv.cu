@@ -1,0 +1,393 @@
+// Conv2D forward/backward (NCHW, groups = 1, dilation = 1) and 2-D max pooling.
+// Reference: nn/internal/conv2d_forward_cpu_f32.v:26-62, conv2d_backward_cpu_f32.v:26-97,
+// nn/internal/layers.v:21-84; replaces compute.conv2d_cuda / conv2d_backward_cuda
+// (nn/internal/conv2d_cuda_d_cuda.v:51, conv2d_backward_cuda_d_cuda.v:25).
+//
+// The convolution runs as GEMMs on the same 3xTF32 tcgen05 kernel as Linear.  A
+// memory-bound pass lowers the operands into K-major TF32 planes in the context
+// scratch (im2col for the input, permutes for the gradient), with K = C*kh*kw in the
+// weight tensor's own (ic, kh, kw) order so the weights need no re-layout:
+//   forward : y[(b,oh,ow), oc] = col[(b,oh,ow), k] . W[oc, k]^T + bias[oc]
+//   d_weight: dW[oc, k]        = gT[oc, m] . colT[k, m]^T      (split-K over m = (b,oh,ow))
+//   d_input : dcol[m, k]       = gM[m, oc] . Wt[k, oc]^T, then a col2im gather
+//   d_bias  : per-channel sums of g (f64 partials)
+#include "f32_common.cuh"
+
+namespace {
+
+using f32::split1;
+
+struct ConvDims {
+  int B, C, H, W, O, kh, kw, ph, pw, sh, sw, OH, OW;
+  __host__ __device__ int P() const { return OH * OW; }
+  __host__ __device__ int K() const { return C * kh * kw; }
+  __host__ __device__ long long M() const { return (long long)B * OH * OW; }
+};
+
+// value of the im2col matrix at (m, k); zero in the padding
+__device__ __forceinline__ float im2col_at(const float* __restrict__ x, const ConvDims& d, long long m, int k) {
+  const int P = d.OH * d.OW;
+  const int b = (int)(m / P), p = (int)(m - (long long)b * P);
+  const int oh = p / d.OW, ow = p - oh * d.OW;
+  const int ic = k / (d.kh * d.kw), r = k - ic * d.kh * d.kw;
+  const int kh = r / d.kw, kw = r - kh * d.kw;
+  const int ih = oh * d.sh - d.ph + kh, iw = ow * d.sw - d.pw + kw;
+  if (ih < 0 || ih >= d.H || iw < 0 || iw >= d.W) return 0.0f;
+  return x[(((size_t)b * d.C + ic) * d.H + ih) * d.W + iw];
+}
+
+// colT planes [K, ld >= M]: consecutive threads take consecutive m, so the reads of x and the
+// writes are both (nearly) contiguous.
+__global__ void __launch_bounds__(256) im2colT_split_kernel(const float* __restrict__ x, ConvDims d, int ld,
+                                                            float* __restrict__ hi, float* __restrict__ lo) {
+  const long long M = d.M();
+  const long long n = M * d.K();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i / M);
+    const long long m = i - (long long)k * M;
+    float h, l;
+    split1(im2col_at(x, d, m, k), h, l);
+    hi[(size_t)k * ld + m] = h;
+    lo[(size_t)k * ld + m] = l;
+  }
+}
+
+// col planes [M, ld >= K]: 32x32 tiles through shared memory (read along m, write along k).
+__global__ void __launch_bounds__(256) im2col_split_kernel(const float* __restrict__ x, ConvDims d, int ld,
+                                                           float* __restrict__ hi, float* __restrict__ lo) {
+  __shared__ float tile[32][33];
+  const long long M = d.M();
+  const int K = d.K();
+  const long long tiles_m = (M + 31) / 32;
+  const int tiles_k = (K + 31) / 32;
+  const long long ntiles = tiles_m * tiles_k;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long m0 = (t / tiles_k) * 32;
+    const int k0 = (int)(t % tiles_k) * 32;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int k = k0 + ty + j;
+      const long long m = m0 + tx;
+      tile[ty + j][tx] = (k < K && m < M) ? im2col_at(x, d, m, k) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const long long m = m0 + ty + j;
+      const int k = k0 + tx;
+      if (m < M && k < K) {
+        float h, l;
+        split1(tile[tx][ty + j], h, l);
+        hi[(size_t)m * ld + k] = h;
+        lo[(size_t)m * ld + k] = l;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// g is NCHW [B, O, P].  gT planes [O, ld >= M]: gT[oc][b*P + p] = g[b][oc][p] (rows of P copied).
+__global__ void __launch_bounds__(256) grad_to_OM_split_kernel(const float* __restrict__ g, int B, int O, int P,
+                                                               int ld, float* __restrict__ hi,
+                                                               float* __restrict__ lo) {
+  const long long n = (long long)B * O * P;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i % P);
+    const long long bo = i / P;
+    const int oc = (int)(bo % O), b = (int)(bo / O);
+    float h, l;
+    split1(g[i], h, l);
+    const size_t o = (size_t)oc * ld + (size_t)b * P + p;
+    hi[o] = h;
+    lo[o] = l;
+  }
+}
+
+// gM planes [M, ld >= O]: gM[b*P + p][oc] = g[b][oc][p]: a [O, P] -> [P, O] transpose per image.
+__global__ void __launch_bounds__(256) grad_to_MO_split_kernel(const float* __restrict__ g, int B, int O, int P,
+                                                               int ld, float* __restrict__ hi,
+                                                               float* __restrict__ lo) {
+  __shared__ float tile[32][33];
+  const int tiles_o = (O + 31) / 32, tiles_p = (P + 31) / 32;
+  const long long ntiles = (long long)B * tiles_o * tiles_p;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int b = (int)(t / (tiles_o * tiles_p));
+    const int r = (int)(t % (tiles_o * tiles_p));
+    const int o0 = (r / tiles_p) * 32, p0 = (r % tiles_p) * 32;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int oc = o0 + ty + j, p = p0 + tx;
+      tile[ty + j][tx] = (oc < O && p < P) ? g[((size_t)b * O + oc) * P + p] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      const int p = p0 + ty + j, oc = o0 + tx;
+      if (p < P && oc < O) {
+        float h, l;
+        split1(tile[tx][ty + j], h, l);
+        const size_t o = ((size_t)b * P + p) * ld + oc;
+        hi[o] = h;
+        lo[o] = l;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// dx[b, ic, ih, iw] = sum over (kh, kw) of dcol[(b, oh, ow), (ic, kh, kw)] where the window
+// position maps back onto (ih, iw); a gather, so no atomics and a fixed summation order.
+__global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restrict__ dcol, ConvDims d, int ldc,
+                                                            float* __restrict__ dx) {
+  const long long n = (long long)d.B * d.C * d.H * d.W;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int iw = (int)(i % d.W);
+    long long r = i / d.W;
+    const int ih = (int)(r % d.H);
+    r /= d.H;
+    const int ic = (int)(r % d.C), b = (int)(r / d.C);
+    float s = 0.0f;
+    for (int kh = 0; kh < d.kh; ++kh) {
+      const int th = ih + d.ph - kh;
+      if (th < 0 || th % d.sh) continue;
+      const int oh = th / d.sh;
+      if (oh >= d.OH) continue;
+      for (int kw = 0; kw < d.kw; ++kw) {
+        const int tw = iw + d.pw - kw;
+        if (tw < 0 || tw % d.sw) continue;
+        const int ow = tw / d.sw;
+        if (ow >= d.OW) continue;
+        const size_t m = ((size_t)b * d.OH + oh) * d.OW + ow;
+        s = __fadd_rn(s, dcol[m * ldc + (ic * d.kh + kh) * d.kw + kw]);
+      }
+    }
+    dx[i] = s;
+  }
+}
+
+// per-channel sums of g [B, O, P] in f64: partial[s][oc] over images b == s (mod S)
+__global__ void __launch_bounds__(256) chan_sum_partial_kernel(const float* __restrict__ g, int B, int O, int P,
+                                                               double* __restrict__ partial) {
+  __shared__ double sm[8];
+  const int oc = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+  double acc = 0.0;
+  for (int b = s; b < B; b += S) {
+    const float* row = g + ((size_t)b * O + oc) * P;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) acc += (double)row[p];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sm[w];
+    partial[(size_t)s * O + oc] = t;
+  }
+}
+__global__ void chan_sum_final_kernel(const double* __restrict__ partial, int S, int O, float* __restrict__ out) {
+  const int oc = blockIdx.x * blockDim.x + threadIdx.x;
+  if (oc >= O) return;
+  double t = 0.0;
+  for (int s = 0; s < S; ++s) t += partial[(size_t)s * O + oc];
+  out[oc] = (float)t;
+}
+
+// Forward epilogue: D[m, oc] -> y[b, oc, oh, ow] (+ bias[oc], optional pre-activation copy and
+// ReLU).  For each output channel the 32 lanes of a warp hold 32 consecutive pixels, so every
+// store instruction writes one contiguous 128-byte run.
+struct EpiConvOut {
+  float* Y;
+  const float* bias;
+  float* pre;
+  int O, P, relu;
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
+                                             int /*split*/) const {
+    if (row >= M) return;
+    const int b = row / P, p = row - b * P;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int oc = col0 + j;
+      if (oc < N) {
+        float o = __uint_as_float(v[j]);
+        if (bias) o = __fadd_rn(o, __ldg(bias + oc));
+        const size_t idx = ((size_t)b * O + oc) * P + p;
+        if (pre) pre[idx] = o;
+        if (relu && o < 0.f) o = 0.f;
+        Y[idx] = o;
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------- max pooling
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                          int32_t* __restrict__ idx, int B, int C, int H, int W,
+                                                          int kh, int kw, int ph, int pw, int sh, int sw,
+                                                          int OH, int OW) {
+  const long long n = (long long)B * C * OH * OW;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int w = (int)(i % OW);
+    long long r = i / OW;
+    const int h = (int)(r % OH);
+    const long long nc = r / OH;
+    int hs = h * sh - ph, ws = w * sw - pw;
+    int he = hs + kh, we = ws + kw;
+    hs = max(hs, 0);
+    ws = max(ws, 0);
+    he = min(he, H);
+    we = min(we, W);
+    float best = -INFINITY;
+    long long bi = -1;
+    for (int a = hs; a < he; ++a)
+      for (int c = ws; c < we; ++c) {
+        const long long fi = (nc * H + a) * W + c;
+        const float val = x[fi];
+        if (bi < 0 || val > best) {
+          best = val;
+          bi = fi;
+        }
+      }
+    y[i] = best;
+    idx[i] = (int32_t)bi;
+  }
+}
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx,
+                                                          float* __restrict__ dx, size_t n_out) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_out; i += (size_t)gridDim.x * blockDim.x) {
+    const int32_t t = idx[i];
+    if (t >= 0) atomicAdd(dx + t, g[i]);  // windows overlap only when stride < kernel
+  }
+}
+
+int check_conv(vtlb_ctx* ctx, const char* fn, ConvDims& d) {
+  if (d.B <= 0 || d.C <= 0 || d.H <= 0 || d.W <= 0 || d.O <= 0 || d.kh <= 0 || d.kw <= 0 || d.ph < 0 ||
+      d.pw < 0 || d.sh <= 0 || d.sw <= 0)
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: bad convolution geometry", fn);
+  d.OH = (d.H + 2 * d.ph - (d.kh - 1) - 1) / d.sh + 1;
+  d.OW = (d.W + 2 * d.pw - (d.kw - 1) - 1) / d.sw + 1;
+  if (d.OH <= 0 || d.OW <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "%s: empty output", fn);
+  if (d.M() > 0x7fffffffLL || d.M() * d.K() > (1LL << 40))
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: problem too large for the lowered GEMM", fn);
+  return VTLB_OK;
+}
+
+}  // namespace
+
+VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                                 void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
+                                 int sh, int sw, int relu, void* d_pre_or_null) {
+  VTLB_ENTER(ctx);
+  ConvDims d{B, C, H, W, O, kh, kw, ph, pw, sh, sw, 0, 0};
+  int rc = check_conv(ctx, "vtlb_conv2d_fwd_f32", d);
+  if (rc) return rc;
+  if (!d_x || !d_w || !d_y) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_fwd_f32: null pointer");
+  const int M = (int)d.M(), K = d.K();
+  f32::Planes p;
+  if ((rc = f32::alloc_planes(ctx, M, O, K, 0, &p))) return rc;
+  const long long tiles = ((long long)(M + 31) / 32) * ((K + 31) / 32);
+  im2col_split_kernel<<<f32::grid_for(ctx, (size_t)tiles, 1), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld,
+                                                                                    p.a_hi, p.a_lo);
+  VTLB_LAUNCHED(ctx);
+  if ((rc = f32::split_operand(ctx, (const float*)d_w, O, K, false, p.ld, p.b_hi, p.b_lo))) return rc;
+  EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
+  return f32::launch_tf32x3(ctx, p, M, O, K, epi);
+}
+
+VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
+                                 void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
+                                 int W, int O, int kh, int kw, int ph, int pw, int sh, int sw) {
+  VTLB_ENTER(ctx);
+  ConvDims d{B, C, H, W, O, kh, kw, ph, pw, sh, sw, 0, 0};
+  int rc = check_conv(ctx, "vtlb_conv2d_bwd_f32", d);
+  if (rc) return rc;
+  if (!d_g) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: null gradient");
+  const int M = (int)d.M(), K = d.K(), P = d.P();
+  const float* g = (const float*)d_g;
+  if (d_dw_or_null) {  // dW[oc, k] = sum_m g[m, oc] * col[m, k]
+    if (!d_x) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_weight needs x");
+    const int mn_tiles = ((O + 127) / 128) * ((K + 63) / 64);
+    int want = (2 * ctx->sm_count + mn_tiles - 1) / mn_tiles;
+    const int max_by_len = (M + 1023) / 1024;  // at least 1024 rows of the contraction per range
+    if (want > max_by_len) want = max_by_len;
+    const int S = f32::effective_splits(M, want);
+    f32::Planes p;
+    if ((rc = f32::alloc_planes(ctx, O, K, M, (size_t)S * O * K * sizeof(float), &p))) return rc;
+    grad_to_OM_split_kernel<<<f32::grid_for(ctx, (size_t)B * O * P, 1024), 256, 0, ctx->stream>>>(g, B, O, P, p.ld,
+                                                                                                 p.a_hi, p.a_lo);
+    VTLB_LAUNCHED(ctx);
+    im2colT_split_kernel<<<f32::grid_for(ctx, (size_t)M * K, 1024), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld,
+                                                                                          p.b_hi, p.b_lo);
+    VTLB_LAUNCHED(ctx);
+    if (S == 1) {
+      f32::EpiBiasRelu epi{(float*)d_dw_or_null, nullptr, nullptr, K, 0};
+      if (!vtlb_aligned16(d_dw_or_null)) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: dW not 16-byte aligned");
+      if ((rc = f32::launch_tf32x3(ctx, p, O, K, M, epi, 1))) return rc;
+    } else {
+      f32::EpiPartial epi{(float*)p.extra, K, (size_t)O * K};
+      if ((rc = f32::launch_tf32x3(ctx, p, O, K, M, epi, S))) return rc;
+      if ((rc = f32::reduce_splits(ctx, (const float*)p.extra, S, (size_t)O * K, (float*)d_dw_or_null))) return rc;
+    }
+  }
+  if (d_dx_or_null) {  // dcol[m, k] = sum_oc g[m, oc] * W[oc, k]; dx = col2im(dcol)
+    if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
+    const int ldc = (int)vtlb_round_up((size_t)K, 4);
+    f32::Planes p;
+    if ((rc = f32::alloc_planes(ctx, M, K, O, (size_t)M * ldc * sizeof(float), &p))) return rc;
+    const long long tiles = (long long)B * ((O + 31) / 32) * ((P + 31) / 32);
+    grad_to_MO_split_kernel<<<f32::grid_for(ctx, (size_t)tiles, 1), 256, 0, ctx->stream>>>(g, B, O, P, p.ld, p.a_hi,
+                                                                                          p.a_lo);
+    VTLB_LAUNCHED(ctx);
+    if ((rc = f32::split_operand(ctx, (const float*)d_w, K, O, true, p.ld, p.b_hi, p.b_lo))) return rc;
+    f32::EpiBiasRelu epi{(float*)p.extra, nullptr, nullptr, ldc, 0};
+    if ((rc = f32::launch_tf32x3(ctx, p, M, K, O, epi))) return rc;
+    col2im_gather_kernel<<<f32::grid_for(ctx, (size_t)B * C * H * W, 1024), 256, 0, ctx->stream>>>(
+        (const float*)p.extra, d, ldc, (float*)d_dx_or_null);
+    VTLB_LAUNCHED(ctx);
+  }
+  if (d_db_or_null) {
+    int S = B < 32 ? B : 32;
+    void* scr = nullptr;
+    if ((rc = vtlb_scratch(ctx, (size_t)S * O * sizeof(double), &scr))) return rc;
+    chan_sum_partial_kernel<<<dim3(O, S), 256, 0, ctx->stream>>>(g, B, O, P, (double*)scr);
+    VTLB_LAUNCHED(ctx);
+    chan_sum_final_kernel<<<(O + 127) / 128, 128, 0, ctx->stream>>>((const double*)scr, S, O, (float*)d_db_or_null);
+    VTLB_LAUNCHED(ctx);
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, void* d_idx, int B, int C, int H,
+                                    int W, int kh, int kw, int ph, int pw, int sh, int sw) {
+  VTLB_ENTER(ctx);
+  if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: bad geometry");
+  const int OH = (H + 2 * ph - kh) / sh + 1, OW = (W + 2 * pw - kw) / sw + 1;
+  if (OH <= 0 || OW <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: empty output");
+  if ((long long)B * C * H * W > 0x7fffffffLL)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: input too large for 32-bit indices");
+  if (!d_x || !d_y || !d_idx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: null pointer");
+  const size_t n = (size_t)B * C * OH * OW;
+  maxpool_fwd_kernel<<<f32::grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(
+      (const float*)d_x, (float*)d_y, (int32_t*)d_idx, B, C, H, W, kh, kw, ph, pw, sh, sw, OH, OW);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_maxpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, void* d_dx, size_t n_out,
+                                    size_t n_in) {
+  VTLB_ENTER(ctx);
+  if (!d_g || !d_idx || !d_dx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_bwd_f32: null pointer");
+  VTLB_CUDA(ctx, cudaMemsetAsync(d_dx, 0, n_in * sizeof(float), ctx->stream));
+  if (n_out == 0) return VTLB_OK;
+  maxpool_bwd_kernel<<<f32::grid_for(ctx, n_out, 1024), 256, 0, ctx->stream>>>((const float*)d_g, (const int32_t*)d_idx,
+                                                                              (float*)d_dx, n_out);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}

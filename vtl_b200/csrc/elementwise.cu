@@ -53,6 +53,18 @@ __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__
   for (size_t i = done + tid; i < n; i += stride) dx[i] = c[i] < 0.f ? 0.f : g[i];
 }
 
+__global__ void __launch_bounds__(256) add_inplace_kernel(float* __restrict__ dst,
+                                                          const float* __restrict__ src, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = __fadd_rn(dst[i], src[i]);
+}
+__global__ void __launch_bounds__(256) fill_kernel(float* __restrict__ dst, float value, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = value;
+}
+
 __device__ __forceinline__ double block_sum(double v, double* smem) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -128,6 +140,24 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float* __restrict
 }
 
 }  // namespace
+
+VTLB_API int vtlb_add_inplace_f32(vtlb_ctx* ctx, void* d_dst, const void* d_src, size_t n) {
+  VTLB_ENTER(ctx);
+  if (n == 0) return VTLB_OK;
+  if (!d_dst || !d_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_add_inplace_f32: null pointer");
+  add_inplace_kernel<<<ew_grid(ctx, n, 1024), 256, 0, ctx->stream>>>((float*)d_dst, (const float*)d_src, n);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_fill_f32(vtlb_ctx* ctx, void* d_dst, float value, size_t n) {
+  VTLB_ENTER(ctx);
+  if (n == 0) return VTLB_OK;
+  if (!d_dst) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_fill_f32: null pointer");
+  fill_kernel<<<ew_grid(ctx, n, 1024), 256, 0, ctx->stream>>>((float*)d_dst, value, n);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
 
 VTLB_API int vtlb_relu_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, size_t n) {
   VTLB_ENTER(ctx);

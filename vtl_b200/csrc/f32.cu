@@ -6,24 +6,14 @@
 // split into two TF32 numbers, hi = tf32(x) and lo = tf32(x - hi), by a
 // memory-bound pass that also lays the operand out K-major (transposing when
 // the caller's layout is the other way round), and the GEMM issues three
-// kind::tf32 MMAs per K step (lo.hi + hi.lo + hi.hi) into one f32 accumulator.
-// The dropped lo.lo term and the rounding of lo are ~2^-22 relative per
-// product, well inside the 1e-5*sqrt(K)*max|A|*max|B| bound.
-#include <stdlib.h>
-
-#include "gemm_tc.cuh"
+// kind::tf32 MMAs per K step (lo.hi + hi.lo + hi.hi).  The dropped lo.lo term
+// and the rounding of lo are ~2^-22 relative per product, well inside the
+// 1e-5*sqrt(K)*max|A|*max|B| bound.
+#include "f32_common.cuh"
 
 namespace {
 
-__device__ __forceinline__ float tf32_rna(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-__device__ __forceinline__ void split1(float x, float& hi, float& lo) {
-  hi = tf32_rna(x);
-  lo = tf32_rna(x - hi);
-}
+using f32::split1;
 
 // src [R, C] row-major (C % 4 == 0, 16-byte aligned) -> hi/lo [R, C].  12 bytes/element.
 __global__ void __launch_bounds__(256) split_rows_vec_kernel(const float4* __restrict__ src,
@@ -106,125 +96,58 @@ __global__ void __launch_bounds__(128) colsum_final_kernel(const double* __restr
   out[n] = (float)s;
 }
 
-// Epilogue: y = acc + bias (one f32 add, as the reference's broadcast add on the
-// rounded matmul result), optional store of the pre-activation, optional ReLU.
-struct EpiBiasRelu {
-  float* Y;
-  const float* bias;  // may be null
-  float* pre;         // may be null
-  int ldy;
-  int relu;
-  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
-                                             int N) const {
-    if (row >= M) return;
-    float* y = Y + (size_t)row * ldy + col0;
-    float* p = pre ? pre + (size_t)row * ldy + col0 : nullptr;
-    if (col0 + 32 <= N && (ldy & 3) == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                               __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-        if (bias) {
-          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
-          o.x = __fadd_rn(o.x, b4.x);
-          o.y = __fadd_rn(o.y, b4.y);
-          o.z = __fadd_rn(o.z, b4.z);
-          o.w = __fadd_rn(o.w, b4.w);
-        }
-        if (p) *reinterpret_cast<float4*>(p + j) = o;
-        if (relu) {
-          o.x = o.x < 0.f ? 0.f : o.x;
-          o.y = o.y < 0.f ? 0.f : o.y;
-          o.z = o.z < 0.f ? 0.f : o.z;
-          o.w = o.w < 0.f ? 0.f : o.w;
-        }
-        *reinterpret_cast<float4*>(y + j) = o;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < N) {
-          float o = __uint_as_float(v[j]);
-          if (bias) o = __fadd_rn(o, bias[col0 + j]);
-          if (p) p[j] = o;
-          if (relu && o < 0.f) o = 0.f;
-          y[j] = o;
-        }
-    }
+__global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial,
+                                                            int splits, size_t n,
+                                                            float* __restrict__ out) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float s = partial[i];
+    for (int k = 1; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * n + i]);
+    out[i] = s;
   }
-};
-
-int grid_for(vtlb_ctx* ctx, size_t work_items, int per_block) {
-  size_t b = (work_items + per_block - 1) / per_block;
-  size_t cap = (size_t)ctx->sm_count * 16;
-  if (b > cap) b = cap;
-  if (b < 1) b = 1;
-  return (int)b;
 }
+
+}  // namespace
 
 // Writes op(src) as K-major hi/lo [rows, ld] where rows x kdim is the logical
 // operand.  `transposed` says src is stored [kdim, rows].
-int split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool transposed, int ld,
+int f32::split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool transposed, int ld,
                   float* hi, float* lo) {
   if (!transposed) {
     if ((kdim & 3) == 0 && ld == kdim && vtlb_aligned16(src)) {
       const size_t n4 = (size_t)rows * kdim / 4;
-      split_rows_vec_kernel<<<grid_for(ctx, n4, 256 * 4), 256, 0, ctx->stream>>>(
+      split_rows_vec_kernel<<<f32::grid_for(ctx, n4, 256 * 4), 256, 0, ctx->stream>>>(
           (const float4*)src, (float4*)hi, (float4*)lo, n4);
     } else {
-      split_rows_kernel<<<grid_for(ctx, (size_t)rows * kdim, 256 * 4), 256, 0, ctx->stream>>>(
+      split_rows_kernel<<<f32::grid_for(ctx, (size_t)rows * kdim, 256 * 4), 256, 0, ctx->stream>>>(
           src, rows, kdim, ld, hi, lo);
     }
   } else {
     const size_t tiles = (size_t)((rows + 31) / 32) * ((kdim + 31) / 32);
-    split_transpose_kernel<<<grid_for(ctx, tiles, 1), 256, 0, ctx->stream>>>(src, kdim, rows, ld,
-                                                                            hi, lo);
+    split_transpose_kernel<<<f32::grid_for(ctx, tiles, 1), 256, 0, ctx->stream>>>(src, kdim, rows, ld,
+                                                                                 hi, lo);
   }
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
 
-int f32_bn_override() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("VTLB_F32_BN");
-    v = e ? atoi(e) : 0;
-  }
-  return v;
-}
+namespace {
+
+using f32::split_operand;
 
 int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
                   const float* B, float* C, const float* bias, int relu, float* pre) {
   if (!vtlb_aligned16(C) || (pre && !vtlb_aligned16(pre)) || (bias && !vtlb_aligned16(bias)))
     return vtlb_fail(ctx, VTLB_EINVAL, "f32 GEMM: output and bias pointers must be 16-byte aligned");
-  const int ld = (int)vtlb_round_up((size_t)K, 4);
-  const size_t a_elems = (size_t)M * ld, b_elems = (size_t)N * ld;
-  void* scr = nullptr;
-  int rc = vtlb_scratch(ctx, (2 * a_elems + 2 * b_elems) * sizeof(float) + 1024, &scr);
+  f32::Planes p;
+  int rc = f32::alloc_planes(ctx, M, N, K, 0, &p);
   if (rc) return rc;
-  float* a_hi = (float*)scr;
-  float* a_lo = a_hi + vtlb_round_up(a_elems, 64);
-  float* b_hi = a_lo + vtlb_round_up(a_elems, 64);
-  float* b_lo = b_hi + vtlb_round_up(b_elems, 64);
   // op(A) is [M,K]: stored [K,M] when transA.  The B operand of the kernel is
   // [N,K] K-major: B stored [K,N] (transB == 0) must be transposed.
-  if ((rc = split_operand(ctx, A, M, K, transA != 0, ld, a_hi, a_lo))) return rc;
-  if ((rc = split_operand(ctx, B, N, K, transB == 0, ld, b_hi, b_lo))) return rc;
-
-  int bn = f32_bn_override();
-  if (bn != 64 && bn != 128) {
-    const int tm = (M + gemm::BM - 1) / gemm::BM;
-    bn = (tm * ((N + 127) / 128) >= ctx->sm_count / 2) ? 128 : 64;
-  }
-  gemm::TmapSet tm;
-  const uint64_t stride = (uint64_t)ld * 4;
-  if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[0], true, a_hi, K, M, stride, 32, gemm::BM))) return rc;
-  if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[1], true, a_lo, K, M, stride, 32, gemm::BM))) return rc;
-  if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, b_hi, K, N, stride, 32, bn))) return rc;
-  if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, b_lo, K, N, stride, 32, bn))) return rc;
-  EpiBiasRelu epi{C, bias, pre, N, relu};
-  if (bn == 128) return gemm::launch<gemm::KIND_TF32X3, 128, 3, EpiBiasRelu>(ctx, tm, epi, M, N, K);
-  return gemm::launch<gemm::KIND_TF32X3, 64, 4, EpiBiasRelu>(ctx, tm, epi, M, N, K);
+  if ((rc = split_operand(ctx, A, M, K, transA != 0, p.ld, p.a_hi, p.a_lo))) return rc;
+  if ((rc = split_operand(ctx, B, N, K, transB == 0, p.ld, p.b_hi, p.b_lo))) return rc;
+  f32::EpiBiasRelu epi{C, bias, pre, N, relu};
+  return f32::launch_tf32x3(ctx, p, M, N, K, epi);
 }
 
 int colsum(vtlb_ctx* ctx, const float* G, int M, int N, float* out) {
@@ -250,6 +173,12 @@ int check_f32(vtlb_ctx* ctx, const char* fn, int M, int N, int K) {
 
 }  // namespace
 
+int f32::reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out) {
+  reduce_splits_kernel<<<f32::grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(partial, splits, n, out);
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
 VTLB_API int vtlb_gemm_f32(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
                            const void* d_A, const void* d_B, void* d_C,
                            const void* d_bias_or_null, int relu) {
@@ -258,8 +187,6 @@ VTLB_API int vtlb_gemm_f32(vtlb_ctx* ctx, int transA, int transB, int M, int N, 
   if (rc) return rc;
   if (M == 0 || N == 0) return VTLB_OK;
   if (!d_A || !d_B || !d_C) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_f32: null pointer");
-  if (!vtlb_aligned16(d_C) || (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_f32: C and bias must be 16-byte aligned");
   return gemm_f32_impl(ctx, transA, transB, M, N, K, (const float*)d_A, (const float*)d_B,
                        (float*)d_C, (const float*)d_bias_or_null, relu, nullptr);
 }
@@ -272,9 +199,6 @@ VTLB_API int vtlb_linear_fwd_f32(vtlb_ctx* ctx, const void* d_X, const void* d_W
   if (rc) return rc;
   if (M == 0 || N == 0) return VTLB_OK;
   if (!d_X || !d_W || !d_Y) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_fwd_f32: null pointer");
-  if (!vtlb_aligned16(d_Y) || (d_b_or_null && !vtlb_aligned16(d_b_or_null)) ||
-      (d_pre_or_null && !vtlb_aligned16(d_pre_or_null)))
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_fwd_f32: outputs and bias must be 16-byte aligned");
   return gemm_f32_impl(ctx, 0, 1, M, N, K, (const float*)d_X, (const float*)d_W, (float*)d_Y,
                        (const float*)d_b_or_null, relu, (float*)d_pre_or_null);
 }

@@ -1,0 +1,158 @@
+// Pieces shared by the f32 GEMM users (f32.cu, conv.cu): the TF32 hi/lo split, the
+// operand planes in the context scratch, and the launcher of the 3xTF32 tcgen05 GEMM.
+#pragma once
+#include <stdlib.h>
+
+#include "gemm_tc.cuh"
+
+namespace f32 {
+
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+// x = hi + lo + O(2^-22 |x|), both representable in TF32 (10-bit mantissa)
+__device__ __forceinline__ void split1(float x, float& hi, float& lo) {
+  hi = tf32_rna(x);
+  lo = tf32_rna(x - hi);
+}
+
+inline int grid_for(vtlb_ctx* ctx, size_t work_items, int per_block) {
+  size_t b = (work_items + per_block - 1) / per_block;
+  size_t cap = (size_t)ctx->sm_count * 16;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+// Two K-major operands, each as a pair of TF32 planes [rows, ld] in the context scratch.
+struct Planes {
+  float *a_hi, *a_lo, *b_hi, *b_lo;
+  int ld;       // row stride in elements: K rounded up to 4 (TMA wants 16-byte strides)
+  void* extra;  // `extra_bytes` of additional scratch behind the planes
+};
+inline int alloc_planes(vtlb_ctx* ctx, int rows_a, int rows_b, int K, size_t extra_bytes, Planes* p) {
+  p->ld = (int)vtlb_round_up((size_t)K, 4);
+  const size_t a = vtlb_round_up((size_t)rows_a * p->ld, 64), b = vtlb_round_up((size_t)rows_b * p->ld, 64);
+  void* scr = nullptr;
+  int rc = vtlb_scratch(ctx, (2 * a + 2 * b) * sizeof(float) + vtlb_round_up(extra_bytes, 256) + 256, &scr);
+  if (rc) return rc;
+  p->a_hi = (float*)scr;
+  p->a_lo = p->a_hi + a;
+  p->b_hi = p->a_lo + a;
+  p->b_lo = p->b_hi + b;
+  p->extra = p->b_lo + b;
+  return VTLB_OK;
+}
+
+inline int bn_override() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("VTLB_F32_BN");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
+// How many K ranges a launch with `want` splits really gets (empty ranges are dropped).
+inline int effective_splits(int K, int want) {
+  const int total_kb = (K + 31) / 32;
+  if (want < 1) want = 1;
+  if (want > total_kb) want = total_kb;
+  const int per = (total_kb + want - 1) / want;
+  return (total_kb + per - 1) / per;
+}
+
+// D[M,N] = A[M,K] . B[N,K]^T on the planes, epilogue functor `epi`.
+template <class Epi>
+int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, const Epi& epi, int splits = 1) {
+  int bn = bn_override();
+  if (bn != 64 && bn != 128) {
+    const int tm = (M + gemm::BM - 1) / gemm::BM;
+    bn = (tm * ((N + 127) / 128) * splits >= ctx->sm_count / 2) ? 128 : 64;
+    if (N <= 64) bn = 64;
+  }
+  gemm::TmapSet tm;
+  const uint64_t stride = (uint64_t)p.ld * 4;
+  int rc;
+  if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[0], true, p.a_hi, K, M, stride, 32, gemm::BM))) return rc;
+  if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[1], true, p.a_lo, K, M, stride, 32, gemm::BM))) return rc;
+  if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, p.b_hi, K, N, stride, 32, bn))) return rc;
+  if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, p.b_lo, K, N, stride, 32, bn))) return rc;
+  if (bn == 128) return gemm::launch<gemm::KIND_TF32X3, 128, 3, Epi>(ctx, tm, epi, M, N, K, splits);
+  return gemm::launch<gemm::KIND_TF32X3, 64, 4, Epi>(ctx, tm, epi, M, N, K, splits);
+}
+
+// Epilogue: y = acc + bias[col] (one f32 add, as the reference's broadcast add on the
+// rounded matmul result), optional store of the pre-activation, optional ReLU.
+struct EpiBiasRelu {
+  float* Y;
+  const float* bias;  // may be null
+  float* pre;         // may be null
+  int ldy;
+  int relu;
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
+                                             int /*split*/) const {
+    if (row >= M) return;
+    float* y = Y + (size_t)row * ldy + col0;
+    float* p = pre ? pre + (size_t)row * ldy + col0 : nullptr;
+    if (col0 + 32 <= N && (ldy & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                               __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        if (bias) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+          o.x = __fadd_rn(o.x, b4.x);
+          o.y = __fadd_rn(o.y, b4.y);
+          o.z = __fadd_rn(o.z, b4.z);
+          o.w = __fadd_rn(o.w, b4.w);
+        }
+        if (p) *reinterpret_cast<float4*>(p + j) = o;
+        if (relu) {
+          o.x = o.x < 0.f ? 0.f : o.x;
+          o.y = o.y < 0.f ? 0.f : o.y;
+          o.z = o.z < 0.f ? 0.f : o.z;
+          o.w = o.w < 0.f ? 0.f : o.w;
+        }
+        *reinterpret_cast<float4*>(y + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) {
+          float o = __uint_as_float(v[j]);
+          if (bias) o = __fadd_rn(o, bias[col0 + j]);
+          if (p) p[j] = o;
+          if (relu && o < 0.f) o = 0.f;
+          y[j] = o;
+        }
+    }
+  }
+};
+
+// Epilogue of a split-K launch: partial[split][row][col] = acc.
+struct EpiPartial {
+  float* P;
+  int ldp;
+  size_t split_stride;
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
+                                             int split) const {
+    if (row >= M) return;
+    float* y = P + split * split_stride + (size_t)row * ldp + col0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < N) y[j] = __uint_as_float(v[j]);
+  }
+};
+
+// Writes op(src) as K-major TF32 planes hi/lo [rows, ld]; rows x kdim is the logical operand
+// and `transposed` says src is stored [kdim, rows].
+int split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool transposed, int ld,
+                  float* hi, float* lo);
+
+// out[i] = sum_s partial[s][i] (fixed order, f32 round-to-nearest), n elements.
+int reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out);
+
+}  // namespace f32

@@ -65,7 +65,7 @@ struct Smem {
 
 template <int KIND, int BN, int STAGES, class Epi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, int K,
+gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, int K, int splits,
                uint32_t* status) {
   using T = Traits<KIND>;
   using S = Smem<KIND, BN, STAGES>;
@@ -97,9 +97,13 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + BK - 1) / BK;
-  const int chunk_kb = CHUNK_KB ? CHUNK_KB : num_kb;
+  // Split-K: the K loop is cut into `splits` ranges and every (m, n, range) is a tile of its
+  // own; the epilogue functor receives the range index and stores a partial result.
+  const int mn_tiles = tiles_m * tiles_n;
+  const int num_tiles = mn_tiles * splits;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_per_split = (total_kb + splits - 1) / splits;
+  const int chunk_kb = CHUNK_KB ? CHUNK_KB : kb_per_split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -133,8 +137,11 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int mn = tile % mn_tiles, split = tile / mn_tiles;
+        const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * BN;
+        const int kb_begin = split * kb_per_split;
+        const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
@@ -161,8 +168,10 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
-          const int kb1 = kb0 + chunk_kb < num_kb ? kb0 + chunk_kb : num_kb;
+        const int kb_begin = (tile / mn_tiles) * kb_per_split;
+        const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
+        for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += chunk_kb) {
+          const int kb1 = kb0 + chunk_kb < kb_end ? kb0 + chunk_kb : kb_end;
           if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag,
                                       WAIT_LIMIT_NS)) {
             ok = false;
@@ -217,7 +226,10 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int mn = tile % mn_tiles, split = tile / mn_tiles;
+      const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * BN;
+      const int kb_begin = split * kb_per_split;
+      const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
       const int row = m0 + q * 32 + lane;
       if constexpr (KIND == KIND_I8) {
         ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
@@ -229,7 +241,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           uint32_t v[32];
           ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
           ptx::tmem_wait_ld();
-          epi(row, n0 + c * 32, v, M, N);
+          epi(row, n0 + c * 32, v, M, N, split);
           __syncwarp();
         }
         ptx::tc_fence_before();
@@ -240,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
         float sum[BN];
 #pragma unroll
         for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
-        for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+        for (int kb0 = kb_begin; kb0 < kb_end; kb0 += chunk_kb) {
           ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -267,7 +279,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           uint32_t v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
-          epi(row, n0 + c * 32, v, M, N);
+          epi(row, n0 + c * 32, v, M, N, split);
           __syncwarp();
         }
       }
@@ -298,7 +310,7 @@ int encode_tmap_2d(vtlb_ctx* ctx, CUtensorMap* out, bool f32, const void* base, 
                    uint32_t box_outer);
 
 template <int KIND, int BN, int STAGES, class Epi>
-int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K) {
+int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K, int splits = 1) {
   using S = Smem<KIND, BN, STAGES>;
   static_assert(S::TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_tc_kernel<KIND, BN, STAGES, Epi>;
@@ -308,9 +320,17 @@ int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K
                                         (int)S::TOTAL));
     configured |= 1ull << (ctx->device & 63);
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  {  // drop ranges that would be empty
+    constexpr int BKE = ROW_BYTES / Traits<KIND>::ELEM;
+    const int total_kb = (K + BKE - 1) / BKE;
+    if (splits < 1) splits = 1;
+    if (splits > total_kb) splits = total_kb;
+    const int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, ctx->d_status);
+  kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, splits, ctx->d_status);
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }

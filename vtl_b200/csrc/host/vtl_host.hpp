@@ -1,0 +1,248 @@
+// C++ mirror of the part of vtl's V API that sits above the device boundary:
+// Tensor / Variable / Context (tape) / Layer / Sequential / Loss / Optimizer.
+// It is the host side a V build of vtl would keep; here it is written in C++
+// because no V compiler is available.  Names, argument meaning and error
+// behaviour follow the reference (paths inside vlang/vtl are cited per class).
+// It talks to the GPU only through the C ABI of include/vtlb.h.
+//
+// Difference from the reference, on purpose: tensors are device-resident
+// (`value` and `grad` are device buffers, as Variable.gpu_activation hints at in
+// autograd/variable.v:36), so a training step never round-trips through host
+// arrays.  There is no CPU path: every operation needs a session.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../../include/vtlb.h"
+
+namespace vtl {
+
+struct Error : std::runtime_error {
+  int code;
+  Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+// autograd_cuda.DeviceSession (autograd_cuda/device_session.v:13-36): owns the device
+// context; attached to a Context through Context.device_session.
+struct Session {
+  vtlb_ctx* ctx = nullptr;
+  int nranks = 1, rank = 0;
+  bool owns_ctx = true;
+  explicit Session(int device);
+  ~Session();
+  void check(int rc) const;  // throws Error with vtlb_last_error on rc != 0
+  void comm_init(int nranks_, int rank_, const void* id128);
+  void sync() const { check(vtlb_sync(ctx)); }
+};
+
+struct DeviceBuf {  // one vtlb_alloc; freed (stream-ordered) when the last Tensor view dies
+  Session* s;
+  void* ptr;
+  size_t bytes;
+  bool owned;
+  DeviceBuf(Session* s_, size_t bytes_);
+  DeviceBuf(Session* s_, void* borrowed) : s(s_), ptr(borrowed), bytes(0), owned(false) {}  // caller's memory
+  virtual ~DeviceBuf();
+};
+
+// vtl.Tensor[f32] (a_tensor.v): shape + storage; row-major, contiguous.  Several tensors
+// may view one allocation (a layer's dW and db share a buffer so that data-parallel
+// training reduces them with one collective).
+class Tensor {
+ public:
+  Tensor() = default;
+  static Tensor empty(Session* s, std::vector<int> shape);
+  static Tensor zeros(Session* s, std::vector<int> shape);
+  static Tensor ones(Session* s, std::vector<int> shape);
+  static Tensor from_array(Session* s, const float* host, std::vector<int> shape);  // vtl.from_array
+  static Tensor view(const std::shared_ptr<DeviceBuf>& buf, size_t offset_elems, std::vector<int> shape);
+  void to_array(float* host) const;  // Tensor.to_array()
+  Tensor reshape(std::vector<int> new_shape) const;
+  size_t size() const;
+  float* data() const { return buf_ ? reinterpret_cast<float*>(static_cast<char*>(buf_->ptr)) + off_ : nullptr; }
+  Session* session() const { return buf_ ? buf_->s : nullptr; }
+  const std::vector<int>& shape() const { return shape_; }
+  const std::shared_ptr<DeviceBuf>& buffer() const { return buf_; }
+  size_t offset() const { return off_; }
+  bool defined() const { return (bool)buf_; }
+
+ private:
+  std::shared_ptr<DeviceBuf> buf_;
+  size_t off_ = 0;
+  std::vector<int> shape_;
+};
+
+struct Context;
+struct Gate;
+
+// autograd.Variable (autograd/variable.v:17-57)
+struct Variable {
+  Tensor value, grad;
+  Context* context = nullptr;
+  bool requires_grad = true;
+  bool grad_is_zero = true;  // grad holds zeros_like(value): the first accumulation may alias
+  void backprop();           // autograd/variable.v:87-109
+};
+using VarPtr = std::shared_ptr<Variable>;
+
+// autograd.Gate + Node + Payload (autograd/gate.v, node.v, payload.v): backward returns one
+// gradient per parent, in parent order; an undefined Tensor means "no gradient".
+struct Gate {
+  virtual ~Gate() = default;
+  virtual std::vector<Tensor> backward(const Tensor& upstream) = 0;
+};
+struct Node {
+  std::unique_ptr<Gate> gate;
+  std::vector<VarPtr> parents;
+  VarPtr result;  // payload.variable
+  std::string name;
+};
+
+// autograd.Context (autograd/context.v:14-107): the tape.
+struct Context {
+  std::vector<Node> nodes;
+  bool no_grad = false;
+  Session* device_session = nullptr;
+  explicit Context(Session* s) : device_session(s) {}
+  VarPtr variable(const Tensor& value, bool requires_grad = true);  // ctx.variable(...)
+  void register_node(std::string name, std::unique_ptr<Gate> gate, VarPtr result, std::vector<VarPtr> parents);
+};
+
+// nn/types/layer.v:6-60
+struct Layer {
+  virtual ~Layer() = default;
+  virtual VarPtr forward(const VarPtr& input) = 0;
+  virtual std::vector<VarPtr> variables() { return {}; }
+  virtual std::vector<int> output_shape() const = 0;  // without the batch dimension
+  virtual const char* kind() const = 0;
+};
+
+// nn/layers/input.v
+struct InputLayer : Layer {
+  std::vector<int> shape;
+  explicit InputLayer(std::vector<int> s) : shape(std::move(s)) {}
+  VarPtr forward(const VarPtr& input) override { return input; }
+  std::vector<int> output_shape() const override { return shape; }
+  const char* kind() const override { return "input"; }
+};
+
+// nn/layers/linear.v:17-74 -- weights [out,in], bias [1,out]
+struct LinearLayer : Layer {
+  VarPtr weights, bias;
+  int in_features, out_features;
+  LinearLayer(Context* ctx, int in, int out);
+  VarPtr forward(const VarPtr& input) override;
+  // Linear followed by ReLU in one launch: returns the activated output and registers both
+  // gates (the ReLU gate caches the pre-activation, as nn/layers/relu.v:34-49 does).
+  VarPtr forward_with_relu(const VarPtr& input);
+  std::vector<VarPtr> variables() override { return {weights, bias}; }
+  std::vector<int> output_shape() const override { return {out_features}; }
+  const char* kind() const override { return "linear"; }
+};
+
+// nn/layers/relu.v
+struct ReLULayer : Layer {
+  std::vector<int> shape;
+  explicit ReLULayer(std::vector<int> s) : shape(std::move(s)) {}
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override { return shape; }
+  const char* kind() const override { return "relu"; }
+};
+
+// nn/layers/flatten.v:38-48
+struct FlattenLayer : Layer {
+  std::vector<int> in_shape;
+  explicit FlattenLayer(std::vector<int> s) : in_shape(std::move(s)) {}
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override;
+  const char* kind() const override { return "flatten"; }
+};
+
+// nn/layers/conv2d.v:15-105 -- weight [oc, ic, kh, kw], bias [1, oc]; groups = 1, dilation = 1
+struct Conv2DConfig {
+  int pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1;
+};
+struct Conv2DLayer : Layer {
+  VarPtr weight, bias;
+  int in_ch, out_ch, kh, kw;
+  Conv2DConfig cfg;
+  std::vector<int> in_shape;  // [C, H, W]
+  Conv2DLayer(Context* ctx, std::vector<int> in_shape, int out_ch, int kh, int kw, Conv2DConfig cfg);
+  VarPtr forward(const VarPtr& input) override;
+  VarPtr forward_with_relu(const VarPtr& input);
+  std::vector<VarPtr> variables() override { return {weight, bias}; }
+  std::vector<int> output_shape() const override;
+  const char* kind() const override { return "conv2d"; }
+
+ private:
+  VarPtr run(const VarPtr& input, bool relu);
+};
+
+// nn/layers/maxpool.v
+struct MaxPool2DLayer : Layer {
+  std::vector<int> in_shape;  // [C, H, W]
+  int kh, kw, ph, pw, sh, sw;
+  MaxPool2DLayer(std::vector<int> in_shape, int kh, int kw, int ph, int pw, int sh, int sw);
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override;
+  const char* kind() const override { return "maxpool2d"; }
+};
+
+// nn/types/loss.v:7-27, nn/loss/mse.v:30-41, nn/loss/softmax_cross_entropy.v
+struct Loss {
+  virtual ~Loss() = default;
+  // `global_rows` = rows of the whole (unsharded) batch; equals output rows on one GPU
+  virtual VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows) = 0;
+};
+struct MSELoss : Loss {
+  VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows) override;
+};
+struct SoftmaxCrossEntropyLoss : Loss {
+  VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows) override;
+};
+
+// nn/models/sequential.v:11-220 + sequential_info.v
+class Sequential {
+ public:
+  explicit Sequential(Session* s);
+  Context* ctx() { return &ctx_; }
+  void input(std::vector<int> shape);
+  void linear(int output_size);
+  void relu();
+  void flatten();
+  void conv2d(int in_channels, int out_channels, int kh, int kw, Conv2DConfig cfg);
+  void maxpool2d(int kh, int kw, int ph, int pw, int sh, int sw);
+  void mse_loss();
+  void softmax_cross_entropy_loss();
+  VarPtr forward(const VarPtr& train);                                  // sequential.v:204-215
+  VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows = -1);  // :218-220
+  std::vector<std::unique_ptr<Layer>> layers;
+  std::unique_ptr<Loss> loss_fn;
+  bool fuse_relu = true;  // run Linear/Conv + ReLU pairs as one launch
+
+ private:
+  Context ctx_;
+  std::vector<int> cur_shape() const;
+};
+
+// nn/optimizers/adam.v:19-145 and adamw.v:17-106.  With a data-parallel session the
+// gradient all-reduces started during backprop are awaited before the update.
+struct AdamConfig {
+  double learning_rate = 0.001, beta1 = 0.9, beta2 = 0.999, epsilon = 1e-8, weight_decay = 0.01;
+};
+class AdamOptimizer {
+ public:
+  AdamOptimizer(AdamConfig c, bool decoupled_weight_decay);
+  void build_params(const std::vector<std::unique_ptr<Layer>>& layers);
+  void update();
+  double learning_rate, beta1, beta2, epsilon, weight_decay, beta1_t, beta2_t;
+  bool adamw;
+  std::vector<VarPtr> params;
+  std::vector<Tensor> first_moments, second_moments;
+};
+
+}  // namespace vtl

@@ -1,0 +1,57 @@
+/* C entry points of libvtl_host.so: a thin driver around the C++ host mirror
+ * (vtl_host.hpp: Tensor / Variable / Context / Sequential / optimizers), so that the
+ * Python tests and the benchmark can build a model the way a vtl program does
+ * (input, linear, relu, ..., mse_loss; adam) and run training steps.  Not part of the
+ * device boundary (that is include/vtlb.h); every function returns 0 or a negative
+ * VTLB_E* code, vtlh_last_error() gives the message. */
+#ifndef VTLH_H
+#define VTLH_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+typedef struct vtlh_session vtlh_session;
+typedef struct vtlh_model vtlh_model;
+
+const char* vtlh_last_error(void);
+int vtlh_session_create(int device, vtlh_session** out);
+int vtlh_session_destroy(vtlh_session* s);
+void* vtlh_session_ctx(vtlh_session* s); /* the vtlb_ctx* the session owns */
+int vtlh_session_comm_init(vtlh_session* s, int nranks, int rank, const void* id128);
+
+int vtlh_model_create(vtlh_session* s, vtlh_model** out);
+int vtlh_model_destroy(vtlh_model* m);
+int vtlh_model_input(vtlh_model* m, int ndim, const int* shape);
+int vtlh_model_linear(vtlh_model* m, int output_size);
+int vtlh_model_relu(vtlh_model* m);
+int vtlh_model_flatten(vtlh_model* m);
+int vtlh_model_conv2d(vtlh_model* m, int in_ch, int out_ch, int kh, int kw, int ph, int pw, int sh, int sw);
+int vtlh_model_maxpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw);
+int vtlh_model_mse_loss(vtlh_model* m);
+int vtlh_model_softmax_cross_entropy_loss(vtlh_model* m);
+int vtlh_model_set_fuse_relu(vtlh_model* m, int on);
+int vtlh_model_adam(vtlh_model* m, double lr, double beta1, double beta2, double eps);
+int vtlh_model_adamw(vtlh_model* m, double lr, double beta1, double beta2, double eps, double wd);
+
+int vtlh_model_num_params(vtlh_model* m);
+int vtlh_model_param_size(vtlh_model* m, int i, size_t* n);
+int vtlh_model_set_param(vtlh_model* m, int i, const float* host);
+int vtlh_model_get_param(vtlh_model* m, int i, float* host);
+int vtlh_model_get_grad(vtlh_model* m, int i, float* host);           /* after a step with do_update == 0 */
+int vtlh_model_get_moment(vtlh_model* m, int i, int second, float* host);
+
+/* forward only; copies the output into d_y (device) when non-null */
+int vtlh_model_forward(vtlh_model* m, const void* d_x, int ndim, const int* xshape, void* d_y);
+/* forward, loss, backprop and (do_update != 0) optimizer update on device-resident x and
+ * target; global_rows = rows of the whole batch when rows are sharded over ranks (0: local);
+ * h_loss (may be null) receives the loss value, which makes the call synchronous */
+int vtlh_model_train_step(vtlh_model* m, const void* d_x, int ndim, const int* xshape, const void* d_t,
+                          int tdim, const int* tshape, int global_rows, int do_update, float* h_loss);
+/* resets every parameter gradient to zero (what AdamOptimizer.update does after stepping) */
+int vtlh_model_zero_grad(vtlh_model* m);
+/* gradient of the loss w.r.t. the input of the last train_step (device -> host) */
+int vtlh_model_get_input_grad(vtlh_model* m, float* host);
+#ifdef __cplusplus
+}
+#endif
+#endif

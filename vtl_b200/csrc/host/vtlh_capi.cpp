@@ -1,0 +1,213 @@
+// C driver around the host mirror (see vtlh.h).
+#include "vtlh.h"
+
+#include <cstring>
+#include <memory>
+#include <string>
+
+#include "vtl_host.hpp"
+
+using namespace vtl;
+
+struct vtlh_session {
+  std::unique_ptr<Session> s;
+};
+struct vtlh_model {
+  Session* s;
+  std::unique_ptr<Sequential> seq;
+  std::unique_ptr<AdamOptimizer> opt;
+  std::vector<VarPtr> params;
+  VarPtr last_input;
+};
+
+static thread_local std::string g_err;
+const char* vtlh_last_error(void) { return g_err.c_str(); }
+
+template <class F>
+static int guard(F&& f) {
+  try {
+    f();
+    return VTLB_OK;
+  } catch (const Error& e) {
+    g_err = e.what();
+    return e.code;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return VTLB_EINVAL;
+  }
+}
+
+// a Tensor over memory the caller owns
+static Tensor borrow(Session* s, const void* d_ptr, int ndim, const int* shape) {
+  struct NoFree : DeviceBuf {
+    NoFree(Session* s_, void* p) : DeviceBuf(s_, p) {}
+  };
+  std::vector<int> sh(shape, shape + ndim);
+  return Tensor::view(std::make_shared<NoFree>(s, const_cast<void*>(d_ptr)), 0, sh);
+}
+
+int vtlh_session_create(int device, vtlh_session** out) {
+  return guard([&] {
+    auto p = new vtlh_session;
+    p->s = std::make_unique<Session>(device);
+    *out = p;
+  });
+}
+int vtlh_session_destroy(vtlh_session* s) {
+  delete s;
+  return VTLB_OK;
+}
+void* vtlh_session_ctx(vtlh_session* s) { return s->s->ctx; }
+int vtlh_session_comm_init(vtlh_session* s, int nranks, int rank, const void* id128) {
+  return guard([&] { s->s->comm_init(nranks, rank, id128); });
+}
+
+int vtlh_model_create(vtlh_session* s, vtlh_model** out) {
+  return guard([&] {
+    auto m = new vtlh_model;
+    m->s = s->s.get();
+    m->seq = std::make_unique<Sequential>(m->s);
+    *out = m;
+  });
+}
+int vtlh_model_destroy(vtlh_model* m) {
+  delete m;
+  return VTLB_OK;
+}
+int vtlh_model_input(vtlh_model* m, int ndim, const int* shape) {
+  return guard([&] { m->seq->input(std::vector<int>(shape, shape + ndim)); });
+}
+int vtlh_model_linear(vtlh_model* m, int n) { return guard([&] { m->seq->linear(n); }); }
+int vtlh_model_relu(vtlh_model* m) { return guard([&] { m->seq->relu(); }); }
+int vtlh_model_flatten(vtlh_model* m) { return guard([&] { m->seq->flatten(); }); }
+int vtlh_model_conv2d(vtlh_model* m, int ic, int oc, int kh, int kw, int ph, int pw, int sh, int sw) {
+  return guard([&] { m->seq->conv2d(ic, oc, kh, kw, Conv2DConfig{ph, pw, sh, sw}); });
+}
+int vtlh_model_maxpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw) {
+  return guard([&] { m->seq->maxpool2d(kh, kw, ph, pw, sh, sw); });
+}
+int vtlh_model_mse_loss(vtlh_model* m) { return guard([&] { m->seq->mse_loss(); }); }
+int vtlh_model_softmax_cross_entropy_loss(vtlh_model* m) {
+  return guard([&] { m->seq->softmax_cross_entropy_loss(); });
+}
+int vtlh_model_set_fuse_relu(vtlh_model* m, int on) {
+  m->seq->fuse_relu = on != 0;
+  return VTLB_OK;
+}
+
+static void collect_params(vtlh_model* m) {
+  m->params.clear();
+  for (auto& l : m->seq->layers)
+    for (auto& v : l->variables()) m->params.push_back(v);
+}
+int vtlh_model_adam(vtlh_model* m, double lr, double b1, double b2, double eps) {
+  return guard([&] {
+    m->opt = std::make_unique<AdamOptimizer>(AdamConfig{lr, b1, b2, eps, 0.0}, false);
+    m->opt->build_params(m->seq->layers);
+    collect_params(m);
+  });
+}
+int vtlh_model_adamw(vtlh_model* m, double lr, double b1, double b2, double eps, double wd) {
+  return guard([&] {
+    m->opt = std::make_unique<AdamOptimizer>(AdamConfig{lr, b1, b2, eps, wd}, true);
+    m->opt->build_params(m->seq->layers);
+    collect_params(m);
+  });
+}
+
+int vtlh_model_num_params(vtlh_model* m) {
+  if (m->params.empty()) collect_params(m);
+  return (int)m->params.size();
+}
+static Variable& param(vtlh_model* m, int i) {
+  if (m->params.empty()) collect_params(m);
+  if (i < 0 || i >= (int)m->params.size()) throw Error(VTLB_EINVAL, "parameter index out of range");
+  return *m->params[i];
+}
+int vtlh_model_param_size(vtlh_model* m, int i, size_t* n) {
+  return guard([&] { *n = param(m, i).value.size(); });
+}
+int vtlh_model_set_param(vtlh_model* m, int i, const float* host) {
+  return guard([&] {
+    Variable& v = param(m, i);
+    m->s->check(vtlb_h2d(m->s->ctx, v.value.data(), host, v.value.size() * sizeof(float)));
+    m->s->sync();
+  });
+}
+int vtlh_model_get_param(vtlh_model* m, int i, float* host) {
+  return guard([&] { param(m, i).value.to_array(host); });
+}
+int vtlh_model_get_grad(vtlh_model* m, int i, float* host) {
+  return guard([&] {
+    Variable& v = param(m, i);
+    if (v.grad_is_zero || !v.grad.defined())
+      std::memset(host, 0, v.value.size() * sizeof(float));
+    else
+      v.grad.to_array(host);
+  });
+}
+int vtlh_model_get_moment(vtlh_model* m, int i, int second, float* host) {
+  return guard([&] {
+    if (!m->opt || i < 0 || i >= (int)m->opt->params.size()) throw Error(VTLB_EINVAL, "no optimizer or bad index");
+    (second ? m->opt->second_moments[i] : m->opt->first_moments[i]).to_array(host);
+  });
+}
+
+int vtlh_model_forward(vtlh_model* m, const void* d_x, int ndim, const int* xshape, void* d_y) {
+  return guard([&] {
+    Context* ctx = m->seq->ctx();
+    ctx->nodes.clear();
+    const bool ng = ctx->no_grad;
+    ctx->no_grad = true;
+    VarPtr x = ctx->variable(borrow(m->s, d_x, ndim, xshape), false);
+    VarPtr y;
+    try {
+      y = m->seq->forward(x);
+    } catch (...) {
+      ctx->no_grad = ng;
+      throw;
+    }
+    ctx->no_grad = ng;
+    if (d_y) m->s->check(vtlb_d2d(m->s->ctx, d_y, y->value.data(), y->value.size() * sizeof(float)));
+  });
+}
+
+int vtlh_model_train_step(vtlh_model* m, const void* d_x, int ndim, const int* xshape, const void* d_t, int tdim,
+                          const int* tshape, int global_rows, int do_update, float* h_loss) {
+  return guard([&] {
+    Context* ctx = m->seq->ctx();
+    ctx->nodes.clear();
+    // the reference's ctx.variable(x) defaults to requires_grad = true (autograd/context.v:61-65),
+    // so the gradient w.r.t. the network input is computed as well
+    VarPtr x = ctx->variable(borrow(m->s, d_x, ndim, xshape), true);
+    m->last_input = x;
+    VarPtr y = m->seq->forward(x);
+    Tensor t = borrow(m->s, d_t, tdim, tshape);
+    VarPtr l = m->seq->loss(y, t, global_rows > 0 ? global_rows : -1);
+    l->backprop();
+    if (do_update) {
+      if (!m->opt) throw Error(VTLB_ESTATE, "train_step: no optimizer configured");
+      m->opt->update();
+    } else if (m->s->nranks > 1) {
+      m->s->check(vtlb_comm_wait(m->s->ctx));
+    }
+    if (h_loss) l->value.to_array(h_loss);
+  });
+}
+
+int vtlh_model_zero_grad(vtlh_model* m) {
+  return guard([&] {
+    if (m->params.empty()) collect_params(m);
+    for (auto& p : m->params) {
+      p->grad = Tensor();
+      p->grad_is_zero = true;
+    }
+  });
+}
+
+int vtlh_model_get_input_grad(vtlh_model* m, float* host) {
+  return guard([&] {
+    if (!m->last_input || m->last_input->grad_is_zero) throw Error(VTLB_ESTATE, "no input gradient available");
+    m->last_input->grad.to_array(host);
+  });
+}

@@ -106,7 +106,7 @@ struct EpiStoreI32 {
   int32_t* C;
   int ldc;
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
-                                             int N) const {
+                                             int N, int /*split*/) const {
     if (row >= M) return;
     int32_t* c = C + (size_t)row * ldc + col0;
     if (col0 + 32 <= N && (ldc & 3) == 0) {
@@ -138,7 +138,7 @@ struct EpiDequant {
   int ldy;
   int relu;
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
-                                             int N) const {
+                                             int N, int /*split*/) const {
     if (row >= M) return;
     const float s = sa[row];
     float* y = Y + (size_t)row * ldy + col0;

@@ -1,0 +1,191 @@
+"""ctypes binding of libvtl_host.so: the C++ mirror of vtl's Sequential / autograd /
+optimizer API (vtl_b200/csrc/host).  A model is built the way a vtl program builds it:
+
+    s = Session(0)
+    m = Model(s)
+    m.input([784]); m.linear(256); m.relu(); m.linear(10); m.mse_loss()
+    m.adam(1e-3)
+    loss = m.train_step(d_x, (64, 784), d_t, (64, 10))
+
+Inputs and targets are device buffers (vtl_b200.capi.DBuf or raw device pointers)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import capi
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvtl_host.so")
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        capi.load()  # libvtlb200.so first (the host library links against it)
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m vtl_b200.build`")
+        lib = C.CDLL(LIB_PATH)
+        lib.vtlh_last_error.restype = C.c_char_p
+        lib.vtlh_session_ctx.restype = C.c_void_p
+        lib.vtlh_session_ctx.argtypes = [C.c_void_p]
+        vp, i, d = C.c_void_p, C.c_int, C.c_double
+        ip = C.POINTER(C.c_int)
+        protos = {
+            "vtlh_session_create": [i, C.POINTER(vp)], "vtlh_session_destroy": [vp],
+            "vtlh_session_comm_init": [vp, i, i, vp],
+            "vtlh_model_create": [vp, C.POINTER(vp)], "vtlh_model_destroy": [vp],
+            "vtlh_model_input": [vp, i, ip], "vtlh_model_linear": [vp, i], "vtlh_model_relu": [vp],
+            "vtlh_model_flatten": [vp], "vtlh_model_conv2d": [vp] + [i] * 8,
+            "vtlh_model_maxpool2d": [vp] + [i] * 6, "vtlh_model_mse_loss": [vp],
+            "vtlh_model_softmax_cross_entropy_loss": [vp], "vtlh_model_set_fuse_relu": [vp, i],
+            "vtlh_model_adam": [vp, d, d, d, d], "vtlh_model_adamw": [vp, d, d, d, d, d],
+            "vtlh_model_num_params": [vp], "vtlh_model_param_size": [vp, i, C.POINTER(C.c_size_t)],
+            "vtlh_model_set_param": [vp, i, vp], "vtlh_model_get_param": [vp, i, vp],
+            "vtlh_model_get_grad": [vp, i, vp], "vtlh_model_get_moment": [vp, i, i, vp],
+            "vtlh_model_forward": [vp, vp, i, ip, vp],
+            "vtlh_model_train_step": [vp, vp, i, ip, vp, i, ip, i, i, C.POINTER(C.c_float)],
+            "vtlh_model_get_input_grad": [vp, vp], "vtlh_model_zero_grad": [vp],
+        }
+        for name, args in protos.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _lib = lib
+    return _lib
+
+
+def _ck(rc: int):
+    if rc != 0:
+        raise capi.VtlbError(rc, load().vtlh_last_error().decode())
+
+
+def _shape(shape):
+    arr = (C.c_int * len(shape))(*[int(x) for x in shape])
+    return len(shape), arr
+
+
+class Session:
+    """autograd_cuda.DeviceSession: owns the device context of one GPU."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load()
+        h = C.c_void_p()
+        _ck(self.lib.vtlh_session_create(device, C.byref(h)))
+        self.h = h
+        # a capi.Device view of the same vtlb_ctx, for allocations and copies
+        self.dev = capi.Device.__new__(capi.Device)
+        self.dev.lib = capi.load()
+        self.dev.h = C.c_void_p(self.lib.vtlh_session_ctx(h))
+        self.dev.index = device
+        self.dev.close = lambda: None  # the session owns the context
+
+    def comm_init(self, nranks: int, rank: int, uid: bytes):
+        _ck(self.lib.vtlh_session_comm_init(self.h, nranks, rank, C.c_char_p(uid)))
+
+    def close(self):
+        if self.h:
+            self.dev.h = None
+            self.lib.vtlh_session_destroy(self.h)
+            self.h = None
+
+
+class Model:
+    """nn/models/sequential.v Sequential plus its optimizer."""
+
+    def __init__(self, session: Session):
+        self.s, self.lib = session, session.lib
+        h = C.c_void_p()
+        _ck(self.lib.vtlh_model_create(session.h, C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.lib.vtlh_model_destroy(self.h)
+            self.h = None
+
+    # -- builder (same names as the reference)
+    def input(self, shape):
+        _ck(self.lib.vtlh_model_input(self.h, *_shape(shape)))
+
+    def linear(self, n):
+        _ck(self.lib.vtlh_model_linear(self.h, n))
+
+    def relu(self):
+        _ck(self.lib.vtlh_model_relu(self.h))
+
+    def flatten(self):
+        _ck(self.lib.vtlh_model_flatten(self.h))
+
+    def conv2d(self, in_ch, out_ch, kernel, padding=(0, 0), stride=(1, 1)):
+        _ck(self.lib.vtlh_model_conv2d(self.h, in_ch, out_ch, kernel[0], kernel[1], padding[0], padding[1],
+                                       stride[0], stride[1]))
+
+    def maxpool2d(self, kernel, padding, stride):
+        _ck(self.lib.vtlh_model_maxpool2d(self.h, kernel[0], kernel[1], padding[0], padding[1], stride[0],
+                                          stride[1]))
+
+    def mse_loss(self):
+        _ck(self.lib.vtlh_model_mse_loss(self.h))
+
+    def softmax_cross_entropy_loss(self):
+        _ck(self.lib.vtlh_model_softmax_cross_entropy_loss(self.h))
+
+    def set_fuse_relu(self, on: bool):
+        _ck(self.lib.vtlh_model_set_fuse_relu(self.h, int(on)))
+
+    def adam(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8):
+        _ck(self.lib.vtlh_model_adam(self.h, lr, beta1, beta2, eps))
+
+    def adamw(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01):
+        _ck(self.lib.vtlh_model_adamw(self.h, lr, beta1, beta2, eps, weight_decay))
+
+    # -- parameters
+    def num_params(self) -> int:
+        return int(self.lib.vtlh_model_num_params(self.h))
+
+    def param_size(self, i) -> int:
+        n = C.c_size_t(0)
+        _ck(self.lib.vtlh_model_param_size(self.h, i, C.byref(n)))
+        return n.value
+
+    def set_param(self, i, a):
+        a = np.ascontiguousarray(a, np.float32)
+        assert a.size == self.param_size(i), (a.size, self.param_size(i))
+        _ck(self.lib.vtlh_model_set_param(self.h, i, a.ctypes.data))
+
+    def _get(self, fn, i, *extra):
+        out = np.empty(self.param_size(i), np.float32)
+        _ck(fn(self.h, i, *extra, out.ctypes.data))
+        return out
+
+    def get_param(self, i):
+        return self._get(self.lib.vtlh_model_get_param, i)
+
+    def get_grad(self, i):
+        return self._get(self.lib.vtlh_model_get_grad, i)
+
+    def get_moment(self, i, second=False):
+        return self._get(self.lib.vtlh_model_get_moment, i, int(second))
+
+    # -- running
+    def forward(self, d_x, xshape, d_y=None):
+        _ck(self.lib.vtlh_model_forward(self.h, capi._ptr(d_x), *_shape(xshape), capi._ptr(d_y)))
+
+    def train_step(self, d_x, xshape, d_t, tshape, global_rows=0, update=True, want_loss=True):
+        loss = C.c_float(0)
+        _ck(self.lib.vtlh_model_train_step(self.h, capi._ptr(d_x), *_shape(xshape), capi._ptr(d_t),
+                                           *_shape(tshape), int(global_rows), int(update),
+                                           C.byref(loss) if want_loss else None))
+        return loss.value if want_loss else None
+
+    def zero_grad(self):
+        _ck(self.lib.vtlh_model_zero_grad(self.h))
+
+    def input_grad(self, shape):
+        out = np.empty(shape, np.float32)
+        _ck(self.lib.vtlh_model_get_input_grad(self.h, out.ctypes.data))
+        return out
