@@ -1,0 +1,285 @@
+"""f32 training workloads of bench.py (`--workload mlp_c1 | mlp_c4 | cnn_c3`), run through
+the C++ host mirror of vtl's Sequential / autograd / optimizer API (vtl_b200.host).
+
+mlp_c1  baseline config 1: Sequential 784 -> 256 -> 10 (Linear, ReLU, Linear), batch 64,
+        MSE vs one-hot targets, Adam lr 1e-3.  With N ranks every rank trains on 64 rows
+        of a 64*N batch (weak scaling).
+mlp_c4  baseline config 4: 8 Linear layers of width 4096 (ReLU after the first seven),
+        global batch 65536 split evenly over the ranks (strong scaling), MSE vs N(0,1)
+        targets, AdamW lr 1e-4 wd 0.01, gradient all-reduce (sum) per layer over NCCL,
+        started during backprop and awaited before the optimizer step.
+cnn_c3  baseline config 3: conv3x3 3->32 +ReLU, conv3x3 32->64 +ReLU, 2x2 max-pool,
+        Linear 16384->10, softmax cross-entropy, Adam lr 1e-3, batch 256 split over ranks.
+
+The metric is training samples per second (whole job).  `e2e` copies the step's batch and
+targets from pinned host memory and reads the loss back every step."""
+from __future__ import annotations
+
+import ctypes as C
+import statistics
+import time
+
+import numpy as np
+
+
+def kaiming_uniform(rng, shape, fan_in):
+    return (rng.uniform(-1.0, 1.0, shape) * np.sqrt(6.0 / fan_in)).astype(np.float32)
+
+
+class Workload:
+    def __init__(self, name, world, rank):
+        self.name, self.world, self.rank = name, world, rank
+        if name == "mlp_c1":
+            self.dims, self.relu = [784, 256, 10], [True, False]
+            self.local_rows, self.global_rows = 64, 64 * world
+            self.scaling, self.opt, self.loss = "weak", ("adam", dict(lr=1e-3)), "mse"
+            self.seed, self.default_steps = 1, 100
+        elif name == "mlp_c4":
+            self.dims, self.relu = [4096] * 9, [True] * 7 + [False]
+            self.global_rows = 65536
+            self.local_rows = self.global_rows // world
+            self.scaling, self.loss = "strong", "mse"
+            self.opt = ("adamw", dict(lr=1e-4, weight_decay=0.01))
+            self.seed, self.default_steps = 4, 20
+        elif name == "cnn_c3":
+            self.global_rows = 256
+            self.local_rows = self.global_rows // world
+            self.scaling, self.opt, self.loss = "strong", ("adam", dict(lr=1e-3)), "sce"
+            self.seed, self.default_steps = 3, 50
+        else:
+            raise SystemExit(f"unknown workload {name}")
+
+    # ---- parameters: same seed on every rank => identical replicas
+    def params(self):
+        rng = np.random.default_rng(self.seed)
+        if self.name == "cnn_c3":
+            return [kaiming_uniform(rng, (32, 3, 3, 3), 27), np.zeros(32, np.float32),
+                    kaiming_uniform(rng, (64, 32, 3, 3), 288), np.zeros(64, np.float32),
+                    kaiming_uniform(rng, (10, 16384), 16384), np.zeros(10, np.float32)]
+        out = []
+        for i in range(len(self.dims) - 1):
+            out += [kaiming_uniform(rng, (self.dims[i + 1], self.dims[i]), self.dims[i]),
+                    np.zeros(self.dims[i + 1], np.float32)]
+        return out
+
+    def batch(self, rows=None):
+        """This rank's shard of the synthetic batch (one fixed batch, reused every step)."""
+        rows = self.local_rows if rows is None else rows
+        rng = np.random.default_rng(self.seed * 1000 + 17 + self.rank)
+        if self.name == "mlp_c1":
+            X = rng.random((rows, 784), dtype=np.float32)
+            T = np.eye(10, dtype=np.float32)[rng.integers(0, 10, rows)]
+        elif self.name == "mlp_c4":
+            X = rng.standard_normal((rows, 4096), dtype=np.float32)
+            T = rng.standard_normal((rows, 4096), dtype=np.float32)
+        else:
+            X = rng.standard_normal((rows, 3, 32, 32), dtype=np.float32)
+            T = np.eye(10, dtype=np.float32)[rng.integers(0, 10, rows)]
+        return X, T
+
+    def build(self, session):
+        from vtl_b200 import host
+        m = host.Model(session)
+        if self.name == "cnn_c3":
+            m.input([3, 32, 32])
+            m.conv2d(3, 32, (3, 3), padding=(1, 1)); m.relu()
+            m.conv2d(32, 64, (3, 3), padding=(1, 1)); m.relu()
+            m.maxpool2d((2, 2), (0, 0), (2, 2))
+            m.flatten()
+            m.linear(10)
+            m.softmax_cross_entropy_loss()
+        else:
+            m.input([self.dims[0]])
+            for i, d in enumerate(self.dims[1:]):
+                m.linear(d)
+                if self.relu[i]:
+                    m.relu()
+            m.mse_loss()
+        kind, kw = self.opt
+        (m.adam if kind == "adam" else m.adamw)(**kw)
+        for i, p in enumerate(self.params()):
+            m.set_param(i, p)
+        return m
+
+    def flops_per_step(self, rows):
+        """Algorithmic FLOPs of forward + backward for `rows` samples (2*M*N*K per GEMM; dX of
+        the first layer included, as the reference computes it)."""
+        if self.name == "cnn_c3":
+            conv = lambda C_, O: 2.0 * rows * 32 * 32 * O * C_ * 9
+            lin = 2.0 * rows * 16384 * 10
+            return 3.0 * (conv(3, 32) + conv(32, 64) + lin)
+        return 3.0 * sum(2.0 * rows * self.dims[i] * self.dims[i + 1] for i in range(len(self.dims) - 1))
+
+    def describe(self):
+        if self.name == "mlp_c1":
+            return ("f32 Sequential MLP 784->256->10 (Linear, ReLU, Linear), batch 64 per GPU, MSE vs "
+                    "one-hot targets, Adam lr=1e-3 (baseline config 1)")
+        if self.name == "mlp_c4":
+            return ("f32 deep MLP, 8 Linear layers of width 4096 with ReLU (none after the last), global "
+                    "batch 65536, MSE vs N(0,1) targets, AdamW lr=1e-4 wd=0.01 (baseline config 4)")
+        return ("f32 CNN on CIFAR-shaped synthetic data: conv3x3 3->32+ReLU, conv3x3 32->64+ReLU, 2x2 "
+                "max-pool, Linear 16384->10, softmax-CE, Adam lr=1e-3, batch 256 (baseline config 3)")
+
+    # ---- the CPU oracle for this workload (reference arm / cpu_baseline)
+    def oracle_model(self, blas=True):
+        from oracle import oracle
+        p = self.params()
+        if self.name == "cnn_c3":
+            return oracle.SequentialOracle(
+                [("conv2d", p[0], p[1], (1, 1), (1, 1)), ("relu",), ("conv2d", p[2], p[3], (1, 1), (1, 1)),
+                 ("relu",), ("maxpool2d", (2, 2), (0, 0), (2, 2)), ("flatten",), ("linear", p[4], p[5])],
+                loss="sce", lr=1e-3, blas=blas)
+        kind, kw = self.opt
+        return oracle.MLPOracle(p[0::2], p[1::2], self.relu, lr=kw["lr"],
+                                weight_decay=kw.get("weight_decay") if kind == "adamw" else None, blas=blas)
+
+    def cpu_sample_rows(self):
+        return {"mlp_c1": 64, "mlp_c4": 512, "cnn_c3": 8}[self.name]
+
+
+def cpu_baseline(wl, steps=None, budget_s=15.0):
+    """Times the CPU oracle (f32->f64 OpenBLAS dgemm GEMMs, scalar optimizer loops, direct conv
+    loops) on a bounded sample of the workload; returns the cpu_baseline object."""
+    from oracle import oracle
+    oracle.build()
+    rows = wl.cpu_sample_rows()
+    X, T = wl.batch(rows)
+    net = wl.oracle_model(blas=True)
+    net.step(X, T)  # warm-up (BLAS threads, page faults)
+    n, t0 = 0, time.perf_counter()
+    while n < (steps or 10 ** 9) and (n == 0 or time.perf_counter() - t0 < budget_s):
+        net.step(X, T)
+        n += 1
+        if steps is None and wl.name == "mlp_c1" and n >= 100:
+            break
+    dt = (time.perf_counter() - t0) / n
+    import os
+    return {"value": rows / dt, "unit": "samples/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{n} full training steps on a batch of {rows} rows (of {wl.global_rows}); GEMMs as "
+                      f"f32->f64 OpenBLAS dgemm on all cores, optimizer and conv loops single-threaded C",
+            "ms_per_step": dt * 1e3}, rows, dt
+
+
+def run_reference(args, ranks):
+    if ranks.rank != 0:
+        ranks.close()
+        return None
+    wl = Workload(args.workload, 1, 0)
+    cb, rows, dt = cpu_baseline(wl, steps=max(1, args.steps), budget_s=120.0)
+    out = {"impl": "reference", "metric": "f32_train_samples_per_s", "value": cb["value"], "unit": "samples/s",
+           "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+           "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
+           "data": "synthetic", "config": {"workload": wl.describe(), "rows_per_step": rows},
+           "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+           "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    ranks.close()
+    return out
+
+
+def run(args, ranks, ClockSampler, peaks, cuda_sync):
+    from vtl_b200 import host
+    wl = Workload(args.workload, ranks.world, ranks.rank)
+    session = host.Session(ranks.local_rank)
+    dev = session.dev
+    ranks.attach(dev, session)  # the session creates the communicator, so its gates know the world size
+    model = wl.build(session)
+    X, T = wl.batch()
+    dX, dT = dev.to_device(X), dev.to_device(T)
+    xs, ts, G = X.shape, T.shape, wl.global_rows
+
+    def step(want_loss=False):
+        return model.train_step(dX, xs, dT, ts, global_rows=G, update=True, want_loss=want_loss)
+
+    cuda_sync(dev)  # also pays the one-off import costs now, not between warm-up and timing
+    sampler = ClockSampler(ranks.local_rank)
+    if ranks.rank == 0:
+        sampler.start()
+    ranks.barrier()
+    for _ in range(args.warmup):  # directly before the timed region: the GPU must not idle
+        step()                    # (and drop its clocks) between warm-up and timing
+    dev.sync()
+    ranks.barrier()
+    l0 = dev.launch_count()
+    e0, e1 = dev.event(), dev.event()
+    dev.record(e0)
+    for _ in range(args.steps):
+        step()
+    dev.record(e1)
+    ms_total = dev.elapsed_ms(e0, e1)
+    launches = dev.launch_count() - l0
+    cuda_sync(dev)
+    ranks.barrier()
+    ms_total = ranks.max_f32(ms_total)
+    last_loss = step(want_loss=True)
+
+    # the tensor-core GEMM launches alone, timed with event pairs around each launch
+    prof_steps = max(1, min(args.steps, 2048 // 64))
+    dev.profile_gemm(True)
+    for _ in range(prof_steps):
+        step()
+    gemm_ms, gemm_n, gemm_ops = dev.profile_gemm_read()
+    dev.profile_gemm(False)
+
+    # end to end: batch and targets come from pinned host memory, the loss goes back, every step
+    hX, hT = C.c_void_p(), C.c_void_p()
+    assert dev.lib.vtlb_host_alloc(X.nbytes, C.byref(hX)) == 0
+    assert dev.lib.vtlb_host_alloc(T.nbytes, C.byref(hT)) == 0
+    C.memmove(hX.value, X.ctypes.data, X.nbytes)
+    C.memmove(hT.value, T.ctypes.data, T.nbytes)
+
+    def e2e_step():
+        dev.h2d_raw(dX, hX.value, X.nbytes)
+        dev.h2d_raw(dT, hT.value, T.nbytes)
+        return step(want_loss=True)
+
+    e2e_step()
+    cuda_sync(dev)
+    ranks.barrier()
+    e2e_steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    cuda_sync(dev)
+    e2e_ms = ranks.max_f32((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if ranks.rank == 0 else None
+    assert dev.check_status() == 0
+    dev.lib.vtlb_host_free(hX)
+    dev.lib.vtlb_host_free(hT)
+
+    out = None
+    if ranks.rank == 0:
+        pk = peaks()
+        ms_step = ms_total / args.steps
+        tf32x3_peak = pk["bf16_tflops"] / 2.0 / 3.0
+        gemm_tflops = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        out = {
+            "metric": "f32_train_samples_per_s", "value": G / (ms_step * 1e-3), "unit": "samples/s",
+            "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None,
+            "dtype": "f32 (3xTF32 tensor-core products, f32 accumulate)", "data": "synthetic",
+            "config": {"workload": wl.describe(), "global_batch": G, "rows_per_gpu": wl.local_rows,
+                       "parallelism": f"dp{ranks.world}: batch rows sharded, per-layer NCCL all-reduce(sum) of "
+                                      "gradients overlapped with backprop" if ranks.world > 1 else "single GPU",
+                       "l2": "activations and gradients of a step exceed the 126 MB L2" if wl.name != "mlp_c1"
+                             else "working set (1.7 MB) fits in L2: the step is launch-latency bound; no flush",
+                       "final_loss": last_loss,
+                       "algorithmic_tflops_per_s": wl.flops_per_step(G) / (ms_step * 1e-3) / 1e12},
+            "e2e": {"value": G / (e2e_ms / e2e_steps * 1e-3), "unit": "samples/s",
+                    "h2d_bytes_per_step": int(X.nbytes + T.nbytes), "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<tf32 x3> (all GEMM launches of a step)",
+                         "achieved": gemm_tflops, "peak": tf32x3_peak, "unit": "TFLOP/s",
+                         "frac": (gemm_tflops / tf32x3_peak) if gemm_tflops else None, "traffic": None,
+                         "peak_source": f"bf16_tflops of {pk['_source']} / 2 (TF32 rate) / 3 (three MMAs per "
+                                        "algorithmic product)",
+                         "kernel_ms_per_step": gemm_ms / prof_steps, "launches_per_step": gemm_n / prof_steps},
+        }
+        if ranks.world == 1:
+            cb, _, _ = cpu_baseline(wl)
+            out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    model.close()
+    ranks.close()
+    session.close()
+    return out

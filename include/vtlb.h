@@ -64,6 +64,13 @@ int vtlb_event_record(vtlb_ctx* ctx, void* ev);
 int vtlb_event_elapsed_ms(vtlb_ctx* ctx, void* ev_start, void* ev_stop, float* ms); /* blocks */
 int vtlb_event_destroy(vtlb_ctx* ctx, void* ev);
 
+/* Optional timing of the tensor-core GEMM launches alone (measurement helper, off by
+ * default): while enabled, a CUDA event pair brackets each of the next 2048 GEMM launches on
+ * the compute stream; _read blocks, returns their summed duration, their count and their
+ * algorithmic work (2*M*N*K each) and resets the counters. */
+int vtlb_profile_gemm(vtlb_ctx* ctx, int enable);
+int vtlb_profile_gemm_read(vtlb_ctx* ctx, double* total_ms, uint64_t* launches, double* total_ops);
+
 /* ---- memory ---------------------------------------------------------------
  * Replaces: CpuStorage.cuda()/CudaStorage.cpu()/to_array()/release()
  * (storage/cuda_d_cuda.v:32-107), the raw C.cudaMalloc/cudaMemcpy/cudaFree of

@@ -40,6 +40,8 @@ _PROTOS = {
     "vtlb_event_record": [_vp, _vp],
     "vtlb_event_elapsed_ms": [_vp, _vp, _vp, C.POINTER(C.c_float)],
     "vtlb_event_destroy": [_vp, _vp],
+    "vtlb_profile_gemm": [_vp, _i],
+    "vtlb_profile_gemm_read": [_vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)],
     "vtlb_alloc": [_vp, _sz, C.POINTER(_vp)],
     "vtlb_free": [_vp, _vp],
     "vtlb_h2d": [_vp, _vp, _vp, _sz],
@@ -179,6 +181,15 @@ class Device:
 
     def launch_count(self) -> int:
         return int(self.lib.vtlb_launch_count(self.h))
+
+    def profile_gemm(self, enable: bool):
+        self._ck(self.lib.vtlb_profile_gemm(self.h, int(enable)))
+
+    def profile_gemm_read(self):
+        """-> (summed GEMM kernel ms, launches, algorithmic operations) since the last read."""
+        ms, n, ops = C.c_double(0), C.c_uint64(0), C.c_double(0)
+        self._ck(self.lib.vtlb_profile_gemm_read(self.h, C.byref(ms), C.byref(n), C.byref(ops)))
+        return ms.value, int(n.value), ops.value
 
     # -- events
     def event(self) -> int:

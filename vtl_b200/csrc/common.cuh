@@ -27,6 +27,13 @@ struct vtlb_ctx {
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
   uint64_t launches = 0;
+  // Optional timing of the tensor-core GEMM launches (vtlb_profile_gemm): a ring of event
+  // pairs recorded around each launch plus the algorithmic work of the launches timed.
+  bool prof_on = false;
+  static constexpr int kProfSlots = 2048;
+  cudaEvent_t* prof_ev = nullptr;  // 2 * kProfSlots events, created on first enable
+  int prof_n = 0;
+  double prof_flops = 0.0;
   char err[512] = {0};
 };
 

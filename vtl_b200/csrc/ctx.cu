@@ -118,6 +118,39 @@ VTLB_API int vtlb_check_status(vtlb_ctx* ctx, uint32_t* status) {
 VTLB_API uint64_t vtlb_launch_count(vtlb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 VTLB_API void* vtlb_stream(vtlb_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
+VTLB_API int vtlb_profile_gemm(vtlb_ctx* ctx, int enable) {
+  VTLB_ENTER(ctx);
+  if (enable && !ctx->prof_ev) {
+    ctx->prof_ev = new (std::nothrow) cudaEvent_t[2 * vtlb_ctx::kProfSlots];
+    if (!ctx->prof_ev) return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_profile_gemm: host allocation failed");
+    for (int i = 0; i < 2 * vtlb_ctx::kProfSlots; ++i) VTLB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[i]));
+  }
+  ctx->prof_on = enable != 0;
+  if (enable) {
+    ctx->prof_n = 0;
+    ctx->prof_flops = 0.0;
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_profile_gemm_read(vtlb_ctx* ctx, double* total_ms, uint64_t* launches, double* total_ops) {
+  VTLB_ENTER(ctx);
+  if (!total_ms || !launches || !total_ops) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_profile_gemm_read: null out");
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  double ms = 0.0;
+  for (int i = 0; i < ctx->prof_n; ++i) {
+    float t = 0.f;
+    VTLB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+    ms += t;
+  }
+  *total_ms = ms;
+  *launches = (uint64_t)ctx->prof_n;
+  *total_ops = ctx->prof_flops;
+  ctx->prof_n = 0;
+  ctx->prof_flops = 0.0;
+  return VTLB_OK;
+}
+
 VTLB_API int vtlb_event_create(vtlb_ctx* ctx, void** ev_out) {
   VTLB_ENTER(ctx);
   if (!ev_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_event_create: null out");

@@ -2,11 +2,11 @@
 // the f32 path (kind::tf32 issued three times per K step on pre-split hi/lo
 // operands).  D[M,N] = A[M,K] . B[N,K]^T with both operands K-major.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer   (one lane): global -> shared, 128-byte-swizzled tiles
 //   warp 1      MMA issuer     (one lane): tcgen05.mma into tensor memory; owns the
 //                                          tensor-memory allocation
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the fused
+//   warps 2..9  epilogue: tcgen05.ld the finished accumulator, apply the fused
 //               epilogue functor, store to global
 // Shared-memory stages form a ring guarded by full/empty mbarriers; the
 // accumulator is double-buffered in tensor memory so the epilogue of one
@@ -28,7 +28,8 @@ namespace gemm {
 
 constexpr int BM = 128;           // rows of D per tile = TMEM lanes
 constexpr int ROW_BYTES = 128;    // bytes of K per shared-memory row (= swizzle span)
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;       // two warps per tensor-memory lane quarter, alternate column chunks
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 
 enum Kind { KIND_I8 = 0, KIND_TF32X3 = 1 };
@@ -112,7 +113,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), 128);
+      ptx::mbar_init(tempty_bar(a), 32 * EPI_WARPS);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -221,7 +222,8 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;  // which of the quarter's two warps: even or odd column chunks
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
@@ -237,7 +239,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
         if (!ok) break;
         ptx::tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half; c < BN / 32; c += 2) {
           uint32_t v[32];
           ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
           ptx::tmem_wait_ld();
@@ -249,24 +251,25 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       } else {
-        float sum[BN];
+        float sum[BN / 2];
 #pragma unroll
-        for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
+        for (int j = 0; j < BN / 2; ++j) sum[j] = 0.0f;
         for (int kb0 = kb_begin; kb0 < kb_end; kb0 += chunk_kb) {
           ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ptx::tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int cc = 0; cc < BN / 64; ++cc) {
+            const int c = 2 * cc + half;
             uint32_t v[32], w[32];
             ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
             ptx::tmem_ld_32x32(lane_base + (2 + acc) * BN + c * 32, w);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              sum[c * 32 + j] = __fadd_rn(
-                  sum[c * 32 + j], __fadd_rn(__uint_as_float(v[j]), __uint_as_float(w[j])));
+              sum[cc * 32 + j] = __fadd_rn(
+                  sum[cc * 32 + j], __fadd_rn(__uint_as_float(v[j]), __uint_as_float(w[j])));
           }
           ptx::tc_fence_before();
           ptx::mbar_arrive(tempty_bar(acc));
@@ -275,11 +278,11 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
         }
         if (!ok) break;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int cc = 0; cc < BN / 64; ++cc) {
           uint32_t v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
-          epi(row, n0 + c * 32, v, M, N, split);
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[cc * 32 + j]);
+          epi(row, n0 + (2 * cc + half) * 32, v, M, N, split);
           __syncwarp();
         }
       }
@@ -330,7 +333,14 @@ int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
+  if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
   kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, splits, ctx->d_status);
+  if (timed) {
+    cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
+    ctx->prof_n++;
+    ctx->prof_flops += 2.0 * M * N * K;
+  }
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }

@@ -1,0 +1,275 @@
+// INT8 GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 tile of D per pair.
+//
+// Why a pair: with one CTA per 128 x 256 tile every SM has to land 48 KB of operands in
+// shared memory per 512 tensor-core cycles while the MMA reads 96 B/clk from the same
+// shared memory, and the tensor pipe idles waiting for data.  A pair shares the B operand:
+// each CTA loads its own 128 rows of A and HALF of the 256 B rows (32 KB per stage), the MMA
+// of the leader CTA reads both halves, and each CTA ends up with its own 128 x 256 slice of
+// D in its tensor memory.
+//
+// Roles per CTA (320 threads) as in gemm_tc.cuh: warp 0 TMA producer, warp 1 MMA issuer
+// (only in the leader CTA) and tensor-memory owner, warps 2..9 epilogue.  Cross-CTA
+// signalling:
+//   full[s]    lives in the leader; both CTAs' TMA loads complete their bytes on it
+//   empty[s]   one per CTA; the leader's tcgen05.commit multicasts the arrive to both
+//   tfull[a]   one per CTA; commit multicast
+//   tempty[a]  lives in the leader; the 16 epilogue warps of the pair arrive on it
+// No TMA multicast is used: every CTA issues plain loads into its own shared memory.
+// All waits are bounded (see gemm_tc.cuh); the two cluster barriers are reached by every
+// thread on every path.
+#pragma once
+#include "gemm_tc.cuh"
+
+namespace gemm2 {
+
+using gemm::BM;
+using gemm::NUM_THREADS;
+using gemm::ROW_BYTES;
+using gemm::WAIT_LIMIT_NS;
+
+constexpr int BN2 = 256;      // columns of D per pair tile
+constexpr int STAGES2 = 6;
+constexpr uint32_t A_TILE = BM * ROW_BYTES;          // 16 KB: this CTA's 128 rows of A
+constexpr uint32_t B_HALF = (BN2 / 2) * ROW_BYTES;   // 16 KB: this CTA's 128 rows of B
+constexpr uint32_t STAGE = A_TILE + B_HALF;
+constexpr uint32_t TILES = STAGES2 * STAGE;
+constexpr uint32_t SMEM_TOTAL = TILES + 8 * (2 * STAGES2 + 4) + 16 + 1024;
+constexpr uint32_t TMEM_COLS = 2 * BN2;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose byte count completes on an mbarrier that may
+// live in the peer CTA (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tmap, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the mbarrier at this shared-memory offset in both CTAs of the pair once every
+// tcgen05 operation issued so far has completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(mask)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M, int N, int K,
+                    uint32_t* status) {
+  constexpr int BK = ROW_BYTES;          // int8: 128 elements of K per stage
+  constexpr int KSTEPS = ROW_BYTES / 32;
+  constexpr uint32_t IDESC = ptx::umma_idesc(ptx::kCfmtS32, ptx::kFmtS8, 2 * BM, BN2);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bars = base + TILES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES2 + 4));
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN2 - 1) / BN2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      ptx::mbar_init(full_bar(s), 1);   // the leader's expect_tx arrive; bytes from both CTAs
+      ptx::mbar_init(empty_bar(s), 1);  // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 2 * gemm::EPI_WARPS);  // the epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tmap(&tm.a[0]);
+    ptx::prefetch_tmap(&tm.b[0]);
+  }
+  if (warp == 1) {
+    tmem_alloc2(ptx::smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish2();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * 2 * BM + (int)rank * BM;
+        const int n0 = (tile / tiles_m) * BN2 + (int)rank * (BN2 / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = mapa(full_bar(stage), 0);
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE);
+          const uint32_t sa = base + stage * STAGE;
+          tma_load_2d_pair(sa, &tm.a[0], kb * BK, m0, leader_full);
+          tma_load_2d_pair(sa + A_TILE, &tm.b[0], kb * BK, n0, leader_full);
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = base + stage * STAGE;
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+            const uint64_t db = ptx::umma_desc_k_sw128(sa + A_TILE) + 2u * kk;
+            umma_i8_pair(d_tmem, da, db, IDESC, (kb | kk) != 0);
+          }
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;  // even or odd 32-column chunks
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint32_t acc = 0, acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      const int m0 = (tile % tiles_m) * 2 * BM + (int)rank * BM, n0 = (tile / tiles_m) * BN2;
+      bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = half; c < BN2 / 32; c += 2) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
+        ptx::tmem_wait_ld();
+        epi(row, n0 + c * 32, v, M, N, 0);
+        __syncwarp();
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(status, VTLB_ST_GEMM_TIMEOUT);
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // the peer may still signal this CTA's barriers until it gets here
+  ptx::tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
+template <class Epi>
+int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, int N, int K) {
+  static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
+  auto kern = gemm_i8_pair_kernel<Epi>;
+  static uint64_t configured = 0;
+  if (!(configured >> (ctx->device & 63) & 1)) {
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_TOTAL));
+    configured |= 1ull << (ctx->device & 63);
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN2 - 1) / BN2);
+  int pairs = ctx->sm_count / 2;
+  if (tiles < pairs) pairs = tiles;
+  const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
+  if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
+  kern<<<2 * pairs, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, ctx->d_status);
+  if (timed) {
+    cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
+    ctx->prof_n++;
+    ctx->prof_flops += 2.0 * M * N * K;
+  }
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
+}
+
+}  // namespace gemm2

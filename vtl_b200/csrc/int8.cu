@@ -4,7 +4,9 @@
 // include/vtlb.h and every f32 operation below rounds on its own (__fmul_rn,
 // __fadd_rn, __fdiv_rn) so that results are bit-identical to a plain C loop
 // compiled without FMA contraction.
-#include "gemm_tc.cuh"
+#include <stdlib.h>
+
+#include "gemm_tc2.cuh"
 
 namespace {
 
@@ -300,9 +302,28 @@ int pick_bn(vtlb_ctx* ctx, int M, int N) {
   return 64;
 }
 
+// CTA pairs (256 x 256 tiles) pay off once there are enough such tiles to occupy the pairs;
+// VTLB_I8_PAIR=0/1 forces the choice (for measurements).
+bool use_pair_kernel(vtlb_ctx* ctx, int M, int N) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = getenv("VTLB_I8_PAIR");
+    forced = e ? atoi(e) : -1;
+  }
+  if (forced == 0) return false;
+  if (forced == 1) return true;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return M >= 512 && N >= 256 && tiles >= ctx->sm_count / 4;
+}
+
 template <class Epi>
 int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, const Epi& epi) {
   gemm::TmapSet tm;
+  if (use_pair_kernel(ctx, M, N)) {
+    int rc = make_i8_tmaps(ctx, &tm, Aq, Wq, M, N, K, 128);  // each CTA loads 128 rows of B
+    if (rc) return rc;
+    return gemm2::launch_pair<Epi>(ctx, tm, epi, M, N, K);
+  }
   const int bn = pick_bn(ctx, M, N);
   int rc = make_i8_tmaps(ctx, &tm, Aq, Wq, M, N, K, bn);
   if (rc) return rc;
