@@ -365,7 +365,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="int8_linear")
     args = ap.parse_args()
-    defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5)}
+    defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5),
+                "int8_mlp_c5": (20, 3)}
     if args.workload not in defaults:
         raise SystemExit(f"unknown workload {args.workload}; choose from {sorted(defaults)}")
     if args.steps is None:
@@ -377,6 +378,12 @@ def main():
     ranks = Ranks(args.gpus)
     if args.workload == "int8_linear":
         out = run_int8_reference(args, ranks) if args.impl == "reference" else run_int8(args, ranks)
+    elif args.workload == "int8_mlp_c5":
+        import bench_infer
+        if args.impl == "reference":
+            out = bench_infer.run_reference(args, ranks)
+        else:
+            out = bench_infer.run(args, ranks, ClockSampler, peaks, cuda_sync)
     else:
         import bench_train
         if args.impl == "reference":

@@ -1,0 +1,210 @@
+"""INT8 weight-quantised MLP inference workload of bench.py (`--workload int8_mlp_c5`),
+baseline config 5: 4 layers 8192 -> 28672 -> 8192 -> 28672 -> 8192, weights ~N(0,0.02)
+quantised per output channel, activations quantised per row on the fly, a batch of 16384
+tokens ~N(0,1), ReLU between layers.
+
+With N ranks every layer is sharded by output columns (rank r owns N_l/N channels and their
+scales) and the activations are exchanged between layers:
+    local f32 slab [M, N_l/N]  ->  row max-abs  ->  NCCL all-reduce(max) over ranks
+    ->  quantise the slab with the global row scale  ->  NCCL all-gather of the int8 codes
+The next layer's GEMM reads the gathered shards in place (vtlb_linear_i8_fwd_sharded_a).
+The last layer's output stays sharded.  Strong scaling: the total work is fixed."""
+from __future__ import annotations
+
+import ctypes as C
+import time
+
+import numpy as np
+
+DIMS = [8192, 28672, 8192, 28672, 8192]
+TOKENS = 16384
+
+
+def total_ops(tokens=TOKENS):
+    return sum(2.0 * tokens * DIMS[i] * DIMS[i + 1] for i in range(len(DIMS) - 1))
+
+
+class ShardedInt8MLP:
+    """One rank's part of the model and its activation buffers."""
+
+    def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5):
+        self.dev, self.R, self.rank, self.M, self.dims = dev, world, rank, tokens, dims
+        self.layers = []
+        for li in range(len(dims) - 1):
+            K, N = dims[li], dims[li + 1]
+            n = N // world
+            rng = np.random.default_rng(seed * 100 + li * 10 + 1)
+            # the rank's rows of W: generated shard by shard so no rank ever holds the full matrix
+            rng = np.random.default_rng([seed, li, rank])
+            W = rng.standard_normal((n, K), dtype=np.float32) * np.float32(0.02)
+            b = rng.standard_normal(n, dtype=np.float32) * np.float32(0.01)
+            dW = dev.to_device(W)
+            dQ, dS = dev.zeros((n, K), np.int8), dev.zeros(n)
+            dev.quant_rows_i8(dW, n, K, dQ, dS)
+            dev.sync()
+            dW.free()
+            self.layers.append(dict(K=K, N=N, n=n, Wq=dQ, sw=dS, bias=dev.to_device(b),
+                                    Y=dev.zeros((tokens, n)), amax=dev.zeros(tokens),
+                                    q_local=dev.zeros((tokens, n), np.int8),
+                                    q_all=dev.zeros((world, tokens, n), np.int8), sa=dev.zeros(tokens)))
+        self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
+
+    def forward(self, dX):
+        dev, M, R = self.dev, self.M, self.R
+        dev.quant_rows_i8(dX, M, self.dims[0], self.q_in, self.sa_in)  # replicated input
+        aq, sa, shards = self.q_in, self.sa_in, 1
+        for li, L in enumerate(self.layers):
+            last = li + 1 == len(self.layers)
+            dev.linear_i8_fwd_sharded_a(aq, shards, sa, L["Wq"], L["sw"], L["bias"], L["Y"], M, L["n"], L["K"],
+                                        relu=not last)
+            if last:
+                break
+            dev.row_absmax_f32(L["Y"], M, L["n"], L["amax"])
+            if R > 1:
+                dev.allreduce_max_f32_async(L["amax"], M)
+                dev.comm_wait()
+                dev.quant_rows_i8(L["Y"], M, L["n"], L["q_local"], L["sa"], L["amax"])
+                dev.allgather_async(L["q_local"], L["q_all"], M * L["n"])
+                dev.comm_wait()
+            else:
+                dev.quant_rows_i8(L["Y"], M, L["n"], L["q_all"], L["sa"], L["amax"])
+            aq, sa, shards = L["q_all"], L["sa"], R
+        return self.layers[-1]["Y"]
+
+
+def cpu_sample(tokens=64, budget_s=15.0):
+    """The oracle's unsharded forward on a few tokens, all host threads."""
+    from oracle import oracle
+    oracle.build()
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((tokens, DIMS[0]), dtype=np.float32)
+    Ws = []
+    for li in range(len(DIMS) - 1):
+        W = rng.standard_normal((DIMS[li + 1], DIMS[li]), dtype=np.float32) * np.float32(0.02)
+        Ws.append(oracle.quant_rows_i8(W) + ((rng.standard_normal(DIMS[li + 1]) * 0.01).astype(np.float32),))
+
+    def fwd():
+        A = X
+        for i, (wq, sw, b) in enumerate(Ws):
+            A = oracle.linear_i8_fwd(A, wq, sw, b, relu=(i + 1 < len(Ws)))
+        return A
+
+    fwd()
+    n, t0 = 0, time.perf_counter()
+    while n == 0 or time.perf_counter() - t0 < budget_s:
+        fwd()
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    return {"value": total_ops(tokens) / dt / 1e12, "unit": "TOPS", "cores": oracle.max_threads(), "kind": "port",
+            "sample": f"{n} forward passes of {tokens} tokens (of {TOKENS}) through all four layers",
+            "tokens_per_s": tokens / dt}, dt
+
+
+def run_reference(args, ranks):
+    if ranks.rank != 0:
+        ranks.close()
+        return None
+    cb, dt = cpu_sample(budget_s=max(5.0, 20.0 * max(1, args.steps)))
+    out = {"impl": "reference", "metric": "int8_mlp_inference_tops", "value": cb["value"], "unit": "TOPS",
+           "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+           "config": {"workload": "INT8 MLP inference 8192-28672-8192-28672-8192 (baseline config 5), CPU oracle"},
+           "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+           "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    ranks.close()
+    return out
+
+
+def run(args, ranks, ClockSampler, peaks, cuda_sync):
+    from vtl_b200 import capi
+    dev = capi.Device(ranks.local_rank)
+    ranks.attach(dev)
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank)
+    X = np.random.default_rng(5).standard_normal((TOKENS, DIMS[0]), dtype=np.float32)
+    dX = dev.to_device(X)
+    cuda_sync(dev)
+    sampler = ClockSampler(ranks.local_rank)
+    if ranks.rank == 0:
+        sampler.start()
+    ranks.barrier()
+    for _ in range(args.warmup):
+        model.forward(dX)
+    dev.sync()
+    ranks.barrier()
+    l0 = dev.launch_count()
+    e0, e1 = dev.event(), dev.event()
+    dev.record(e0)
+    for _ in range(args.steps):
+        model.forward(dX)
+    dev.record(e1)
+    ms_total = dev.elapsed_ms(e0, e1)
+    launches = dev.launch_count() - l0
+    cuda_sync(dev)
+    ranks.barrier()
+    ms_total = ranks.max_f32(ms_total)
+    # GEMM launches alone
+    dev.profile_gemm(True)
+    psteps = max(1, min(args.steps, 8))
+    for _ in range(psteps):
+        model.forward(dX)
+    gemm_ms, gemm_n, gemm_ops = dev.profile_gemm_read()
+    dev.profile_gemm(False)
+    # end to end: tokens from pinned host memory in, this rank's slab of the output back
+    last = model.layers[-1]
+    hX, hY = C.c_void_p(), C.c_void_p()
+    out_bytes = TOKENS * last["n"] * 4
+    assert dev.lib.vtlb_host_alloc(X.nbytes, C.byref(hX)) == 0
+    assert dev.lib.vtlb_host_alloc(out_bytes, C.byref(hY)) == 0
+    C.memmove(hX.value, X.ctypes.data, X.nbytes)
+
+    def e2e_step():
+        dev.h2d_raw(dX, hX.value, X.nbytes)
+        y = model.forward(dX)
+        dev.d2h_raw(hY.value, y, out_bytes)
+
+    e2e_step()
+    cuda_sync(dev)
+    ranks.barrier()
+    esteps = max(1, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(esteps):
+        e2e_step()
+    cuda_sync(dev)
+    e2e_ms = ranks.max_f32((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if ranks.rank == 0 else None
+    assert dev.check_status() == 0
+    out = None
+    if ranks.rank == 0:
+        pk = peaks()
+        ms_step = ms_total / args.steps
+        int8_peak = 2.0 * pk["bf16_tflops"]
+        gemm_tops = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        out = {"metric": "int8_mlp_inference_tops", "value": total_ops() / (ms_step * 1e-3) / 1e12, "unit": "TOPS",
+               "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+               "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
+               "config": {"workload": "INT8 weight-quantised MLP inference, 4 layers 8192->28672->8192->28672->8192, "
+                                      "16384 tokens ~N(0,1), per-row dynamic activation quantisation, ReLU between "
+                                      "layers (baseline config 5)",
+                          "tokens": TOKENS, "tokens_per_s": TOKENS / (ms_step * 1e-3),
+                          "parallelism": f"output columns sharded x{ranks.world}; per layer all-reduce(max) of row "
+                                         "maxima and all-gather of int8 codes over NCCL" if ranks.world > 1
+                          else "single GPU",
+                          "l2": "weights (4 x 235 MB int8) and activations exceed the 126 MB L2"},
+               "e2e": {"value": total_ops() / (e2e_ms / esteps * 1e-3) / 1e12, "unit": "TOPS",
+                       "h2d_bytes_per_step": int(X.nbytes), "d2h_bytes_per_step": int(out_bytes),
+                       "ms_per_step": e2e_ms / esteps},
+               "gpu_launches": int(launches), "clocks": clocks,
+               "roofline": {"bound": "tensor", "kernel": "INT8 GEMM launches of a forward pass (fused epilogue)",
+                            "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
+                            "frac": gemm_tops / int8_peak if gemm_tops else None, "traffic": None,
+                            "peak_source": f"2 x bf16_tflops of {pk['_source']}",
+                            "kernel_ms_per_step": gemm_ms / psteps, "launches_per_step": gemm_n / psteps}}
+        if ranks.world == 1:
+            cb, _ = cpu_sample()
+            out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    ranks.close()
+    dev.close()
+    return out

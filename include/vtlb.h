@@ -229,6 +229,15 @@ int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa, const 
                        const void* d_sw, const void* d_bias_or_null, void* d_Y, int M, int N,
                        int K, int relu);
 
+/* Same as vtlb_linear_i8_fwd with the activation codes stored as `shards` column shards one
+ * after another: shard s is a dense [M, K/shards] int8 matrix holding columns
+ * [s*K/shards, (s+1)*K/shards) - the layout an all-gather of per-rank column slabs of the
+ * previous layer leaves behind, read in place through a 3-D tensor map (no re-layout pass).
+ * K/shards must be a multiple of 128.  Used by output-column-sharded INT8 inference. */
+int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards, const void* d_sa,
+                                 const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
+                                 void* d_Y, int M, int N, int K, int relu);
+
 /* ---- collectives (NCCL over NVLink) ---------------------------------------
  * No counterpart in the reference (single device).  One ctx per rank/process.
  * vtlb_comm_unique_id fills a 128-byte id on one rank; the caller ships it to

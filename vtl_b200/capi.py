@@ -72,6 +72,7 @@ _PROTOS = {
     "vtlb_row_absmax_f32": [_vp, _vp, _i, _i, _vp],
     "vtlb_gemm_i8_i32": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "vtlb_linear_i8_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
+    "vtlb_linear_i8_fwd_sharded_a": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "vtlb_comm_unique_id": [_vp],
     "vtlb_comm_init_rank": [_vp, _i, _i, _vp],
     "vtlb_comm_destroy": [_vp],
@@ -337,6 +338,10 @@ class Device:
     def linear_i8_fwd(self, Aq, sa, Wq, sw, bias, Y, M, N, K, relu=False):
         self._ck(self.lib.vtlb_linear_i8_fwd(self.h, _ptr(Aq), _ptr(sa), _ptr(Wq), _ptr(sw),
                                              _ptr(bias), _ptr(Y), M, N, K, int(relu)))
+
+    def linear_i8_fwd_sharded_a(self, Aq_shards, shards, sa, Wq, sw, bias, Y, M, N, K, relu=False):
+        self._ck(self.lib.vtlb_linear_i8_fwd_sharded_a(self.h, _ptr(Aq_shards), shards, _ptr(sa), _ptr(Wq),
+                                                       _ptr(sw), _ptr(bias), _ptr(Y), M, N, K, int(relu)))
 
     # -- collectives
     def comm_unique_id(self) -> bytes:

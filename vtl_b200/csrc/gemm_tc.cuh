@@ -64,10 +64,32 @@ struct Smem {
   static constexpr uint32_t TOTAL = TILES + BARS + 1024;  // + alignment slack
 };
 
+// Tile order.  Tiles are walked in groups of `group_m` rows of tiles: inside a group the m
+// index runs fastest, then n.  The CTAs resident at one time then share `group_m` blocks of A
+// (which stay in L2 for the whole sweep over n) and a few blocks of B, instead of touching
+// every block of A for each handful of B blocks.
+__device__ __forceinline__ void decode_tile(int mn, int tiles_m, int tiles_n, int group_m, int& tm,
+                                            int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = mn / per_group;
+  const int first_m = g * group_m;
+  const int gsz = tiles_m - first_m < group_m ? tiles_m - first_m : group_m;
+  const int r = mn - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+// Rows of tiles per group such that the group's A blocks take about `budget` bytes of L2.
+inline int pick_group_m(int tiles_m, size_t a_bytes_per_tile_row, size_t budget = (size_t)40 << 20) {
+  size_t g = budget / (a_bytes_per_tile_row ? a_bytes_per_tile_row : 1);
+  if (g < 1) g = 1;
+  if (g > (size_t)tiles_m) g = tiles_m;
+  return (int)g;
+}
+
 template <int KIND, int BN, int STAGES, class Epi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, int K, int splits,
-               uint32_t* status) {
+               int group_m, int a_chunk_k, uint32_t* status) {
   using T = Traits<KIND>;
   using S = Smem<KIND, BN, STAGES>;
   constexpr int NOP = T::NOP;
@@ -139,7 +161,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int mn = tile % mn_tiles, split = tile / mn_tiles;
-        const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * BN;
+        int tmi, tni;
+      decode_tile(mn, tiles_m, tiles_n, group_m, tmi, tni);
+      const int m0 = tmi * BM, n0 = tni * BN;
         const int kb_begin = split * kb_per_split;
         const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -152,7 +176,11 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           const uint32_t sb = sa + NOP * S::A_TILE;
 #pragma unroll
           for (int i = 0; i < NOP; ++i)
-            ptx::tma_load_2d(sa + i * S::A_TILE, &tm.a[i], kb * BK, m0, full_bar(stage));
+            if (a_chunk_k)  // A stored as [chunk][M][a_chunk_k] (gathered column shards)
+              ptx::tma_load_3d(sa + i * S::A_TILE, &tm.a[i], (kb * BK) % a_chunk_k, m0,
+                               (kb * BK) / a_chunk_k, full_bar(stage));
+            else
+              ptx::tma_load_2d(sa + i * S::A_TILE, &tm.a[i], kb * BK, m0, full_bar(stage));
 #pragma unroll
           for (int i = 0; i < NOP; ++i)
             ptx::tma_load_2d(sb + i * S::B_TILE, &tm.b[i], kb * BK, n0, full_bar(stage));
@@ -229,7 +257,9 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int mn = tile % mn_tiles, split = tile / mn_tiles;
-      const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * BN;
+      int tmi, tni;
+      decode_tile(mn, tiles_m, tiles_n, group_m, tmi, tni);
+      const int m0 = tmi * BM, n0 = tni * BN;
       const int kb_begin = split * kb_per_split;
       const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
       const int row = m0 + q * 32 + lane;
@@ -308,12 +338,16 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
 // ---------------------------------------------------------------- host side
 
 // cuTensorMapEncodeTiled obtained through the runtime (no link against libcuda).
+int encode_tmap_3d_u8(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows,
+                      uint64_t planes, uint64_t row_stride_bytes, uint64_t plane_stride_bytes,
+                      uint32_t box_inner, uint32_t box_rows);
 int encode_tmap_2d(vtlb_ctx* ctx, CUtensorMap* out, bool f32, const void* base, uint64_t inner,
                    uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
                    uint32_t box_outer);
 
 template <int KIND, int BN, int STAGES, class Epi>
-int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K, int splits = 1) {
+int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K, int splits = 1,
+           int a_chunk_k = 0) {
   using S = Smem<KIND, BN, STAGES>;
   static_assert(S::TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_tc_kernel<KIND, BN, STAGES, Epi>;
@@ -335,7 +369,9 @@ int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, splits, ctx->d_status);
+  const int group_m = pick_group_m((M + BM - 1) / BM, (size_t)BM * K * Traits<KIND>::ELEM * Traits<KIND>::NOP);
+  kern<<<grid, NUM_THREADS, S::TOTAL, ctx->stream>>>(tm, epi, M, N, K, splits, group_m, a_chunk_k,
+                                                     ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;

@@ -63,6 +63,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* tmap, int x, int y, int z,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
                : "memory");
@@ -97,7 +105,7 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
 template <class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M, int N, int K,
-                    uint32_t* status) {
+                    int group_m, int a_chunk_k, uint32_t* status) {
   constexpr int BK = ROW_BYTES;          // int8: 128 elements of K per stage
   constexpr int KSTEPS = ROW_BYTES / 32;
   constexpr uint32_t IDESC = ptx::umma_idesc(ptx::kCfmtS32, ptx::kFmtS8, 2 * BM, BN2);
@@ -151,8 +159,10 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % tiles_m) * 2 * BM + (int)rank * BM;
-        const int n0 = (tile / tiles_m) * BN2 + (int)rank * (BN2 / 2);
+        int tmi, tni;
+        gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
+        const int m0 = tmi * 2 * BM + (int)rank * BM;
+        const int n0 = tni * BN2 + (int)rank * (BN2 / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
@@ -161,7 +171,10 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
           const uint32_t leader_full = mapa(full_bar(stage), 0);
           if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE);
           const uint32_t sa = base + stage * STAGE;
-          tma_load_2d_pair(sa, &tm.a[0], kb * BK, m0, leader_full);
+          if (a_chunk_k)  // A stored as [chunk][M][a_chunk_k] (gathered column shards)
+            tma_load_3d_pair(sa, &tm.a[0], (kb * BK) % a_chunk_k, m0, (kb * BK) / a_chunk_k, leader_full);
+          else
+            tma_load_2d_pair(sa, &tm.a[0], kb * BK, m0, leader_full);
           tma_load_2d_pair(sa + A_TILE, &tm.b[0], kb * BK, n0, leader_full);
           if (++stage == STAGES2) {
             stage = 0;
@@ -211,7 +224,9 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-      const int m0 = (tile % tiles_m) * 2 * BM + (int)rank * BM, n0 = (tile / tiles_m) * BN2;
+      int tmi, tni;
+      gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
+      const int m0 = tmi * 2 * BM + (int)rank * BM, n0 = tni * BN2;
       bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -249,7 +264,8 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
 }
 
 template <class Epi>
-int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, int N, int K) {
+int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, int N, int K,
+                int a_chunk_k = 0) {
   static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_i8_pair_kernel<Epi>;
   static uint64_t configured = 0;
@@ -262,7 +278,9 @@ int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, i
   if (tiles < pairs) pairs = tiles;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  kern<<<2 * pairs, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, ctx->d_status);
+  const int group_m = gemm::pick_group_m((M + 2 * BM - 1) / (2 * BM), (size_t)2 * BM * K);
+  kern<<<2 * pairs, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k,
+                                                            ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;

@@ -316,20 +316,28 @@ bool use_pair_kernel(vtlb_ctx* ctx, int M, int N) {
   return M >= 512 && N >= 256 && tiles >= ctx->sm_count / 4;
 }
 
+// `chunks` > 1: Aq is stored as that many column shards one after another, each a dense
+// [M, K/chunks] matrix (the layout an all-gather of per-rank column slabs leaves behind); the
+// A operand is then read through a 3-D tensor map (k within shard, row, shard).
 template <class Epi>
-int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, const Epi& epi) {
+int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, const Epi& epi,
+           int chunks = 1) {
   gemm::TmapSet tm;
-  if (use_pair_kernel(ctx, M, N)) {
-    int rc = make_i8_tmaps(ctx, &tm, Aq, Wq, M, N, K, 128);  // each CTA loads 128 rows of B
-    if (rc) return rc;
-    return gemm2::launch_pair<Epi>(ctx, tm, epi, M, N, K);
-  }
-  const int bn = pick_bn(ctx, M, N);
+  const int chunk_k = chunks > 1 ? K / chunks : 0;
+  const bool pair = use_pair_kernel(ctx, M, N);
+  const int bn = pair ? 128 : pick_bn(ctx, M, N);  // a CTA of a pair loads 128 rows of B
   int rc = make_i8_tmaps(ctx, &tm, Aq, Wq, M, N, K, bn);
   if (rc) return rc;
-  if (bn == 256) return gemm::launch<gemm::KIND_I8, 256, 4, Epi>(ctx, tm, epi, M, N, K);
-  if (bn == 128) return gemm::launch<gemm::KIND_I8, 128, 6, Epi>(ctx, tm, epi, M, N, K);
-  return gemm::launch<gemm::KIND_I8, 64, 8, Epi>(ctx, tm, epi, M, N, K);
+  if (chunk_k) {
+    if ((rc = gemm::encode_tmap_3d_u8(ctx, &tm.a[0], Aq, (uint64_t)chunk_k, (uint64_t)M, (uint64_t)chunks,
+                                      (uint64_t)chunk_k, (uint64_t)M * chunk_k, 128, gemm::BM)))
+      return rc;
+    tm.a[1] = tm.a[0];
+  }
+  if (pair) return gemm2::launch_pair<Epi>(ctx, tm, epi, M, N, K, chunk_k);
+  if (bn == 256) return gemm::launch<gemm::KIND_I8, 256, 4, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
+  if (bn == 128) return gemm::launch<gemm::KIND_I8, 128, 6, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
+  return gemm::launch<gemm::KIND_I8, 64, 8, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
 }
 
 int check_i8_args(vtlb_ctx* ctx, const char* fn, int M, int N, int K) {
@@ -406,4 +414,25 @@ VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_s
   EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null,
                  N, relu};
   return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi);
+}
+
+VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards,
+                                          const void* d_sa, const void* d_Wq, const void* d_sw,
+                                          const void* d_bias_or_null, void* d_Y, int M, int N, int K,
+                                          int relu) {
+  VTLB_ENTER(ctx);
+  int rc = check_i8_args(ctx, "vtlb_linear_i8_fwd_sharded_a", M, N, K);
+  if (rc) return rc;
+  if (shards < 1 || K % shards || (K / shards) % 128)
+    return vtlb_fail(ctx, VTLB_EINVAL,
+                     "vtlb_linear_i8_fwd_sharded_a: K=%d must split into %d shards of a multiple of 128 columns",
+                     K, shards);
+  if (M == 0 || N == 0) return VTLB_OK;
+  if (!d_Aq_shards || !d_Wq || !d_sa || !d_sw || !d_Y)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_sharded_a: null pointer");
+  if (!vtlb_aligned16(d_Aq_shards) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) || !vtlb_aligned16(d_sw) ||
+      (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_sharded_a: pointers must be 16-byte aligned");
+  EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, N, relu};
+  return run_i8(ctx, d_Aq_shards, d_Wq, M, N, K, epi, shards);
 }

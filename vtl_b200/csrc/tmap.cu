@@ -47,4 +47,27 @@ int encode_tmap_2d(vtlb_ctx* ctx, CUtensorMap* out, bool f32, const void* base, 
   return VTLB_OK;
 }
 
+// 3-D byte operand: `planes` dense [rows, inner] matrices one after another; box =
+// box_inner x box_rows x 1 with the 128-byte swizzle.
+int encode_tmap_3d_u8(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows,
+                      uint64_t planes, uint64_t row_stride_bytes, uint64_t plane_stride_bytes,
+                      uint32_t box_inner, uint32_t box_rows) {
+  CUtensorMap probe;
+  int rc = encode_tmap_2d(ctx, &probe, false, base, inner, rows, row_stride_bytes, box_inner, box_rows);
+  if (rc) return rc;  // also resolves the driver entry point and checks alignment
+  if (plane_stride_bytes & 15u)
+    return vtlb_fail(ctx, VTLB_EINVAL, "GEMM operand shard stride %llu is not a multiple of 16 bytes",
+                     (unsigned long long)plane_stride_bytes);
+  cuuint64_t dims[3] = {inner, rows, planes};
+  cuuint64_t strides[2] = {row_stride_bytes, plane_stride_bytes};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return vtlb_fail(ctx, VTLB_ECUDA, "cuTensorMapEncodeTiled (3-D) failed (%d)", (int)r);
+  return VTLB_OK;
+}
+
 }  // namespace gemm
