@@ -45,7 +45,8 @@ def _headers():
 
 
 def _compile(src: str, obj: str, verbose: bool) -> str:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-ccbin", "g++", "-I", os.path.join(HERE, "..", "include"),
+    extra = os.environ.get("VTLB_NVCC_EXTRA", "").split()  # e.g. -DVTLB_PAIR_STAGES=7 for tuning runs
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-ccbin", "g++", "-I", os.path.join(HERE, "..", "include"),
            "-c", src, "-o", obj]
     p = subprocess.run(cmd, capture_output=True, text=True)
     if p.returncode != 0:

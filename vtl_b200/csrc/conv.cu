@@ -202,6 +202,7 @@ __global__ void chan_sum_final_kernel(const double* __restrict__ partial, int S,
 // ReLU).  For each output channel the 32 lanes of a warp hold 32 consecutive pixels, so every
 // store instruction writes one contiguous 128-byte run.
 struct EpiConvOut {
+  static constexpr bool kTmaCapable = false;  // NCHW scatter: its own per-channel coalesced stores
   float* Y;
   const float* bias;
   float* pre;

@@ -66,14 +66,27 @@ inline int effective_splits(int K, int want) {
 
 // D[M,N] = A[M,K] . B[N,K]^T on the planes, epilogue functor `epi`.
 template <class Epi>
-int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, const Epi& epi, int splits = 1) {
+int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, int splits = 1) {
+  gemm::TmapSet tm;
+  if constexpr (Epi::kTmaCapable) {
+    // outputs with a 16-byte-multiple row pitch go out through TMA stores
+    epi.tma = (epi.ldy % 4 == 0) && vtlb_aligned16(epi.Y) && (!epi.pre || vtlb_aligned16(epi.pre)) &&
+              (!epi.bias || N % 4 == 0);
+    if (epi.tma) {
+      int rc0 = gemm::encode_tmap_2d(ctx, &tm.out[0], true, epi.Y, N, M, (uint64_t)epi.ldy * 4, 32, 32);
+      if (rc0) return rc0;
+      tm.out[1] = tm.out[0];
+      if (epi.pre &&
+          (rc0 = gemm::encode_tmap_2d(ctx, &tm.out[1], true, epi.pre, N, M, (uint64_t)epi.ldy * 4, 32, 32)))
+        return rc0;
+    }
+  }
   int bn = bn_override();
   if (bn != 64 && bn != 128) {
-    const int tm = (M + gemm::BM - 1) / gemm::BM;
-    bn = (tm * ((N + 127) / 128) * splits >= ctx->sm_count / 2) ? 128 : 64;
+    const int tiles_m = (M + gemm::BM - 1) / gemm::BM;
+    bn = (tiles_m * ((N + 127) / 128) * splits >= ctx->sm_count / 2) ? 128 : 64;
     if (N <= 64) bn = 64;
   }
-  gemm::TmapSet tm;
   const uint64_t stride = (uint64_t)p.ld * 4;
   int rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[0], true, p.a_hi, K, M, stride, 32, gemm::BM))) return rc;
@@ -87,11 +100,39 @@ int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, const Epi
 // Epilogue: y = acc + bias[col] (one f32 add, as the reference's broadcast add on the
 // rounded matmul result), optional store of the pre-activation, optional ReLU.
 struct EpiBiasRelu {
+  static constexpr bool kTmaCapable = true;
   float* Y;
   const float* bias;  // may be null
   float* pre;         // may be null
   int ldy;
   int relu;
+  int tma;  // store through tm.out[0] (and tm.out[1] for the pre-activation)
+  // adds the bias in registers; returns true when the pre-activation has to be stored
+  // separately before activate() applies the ReLU
+  __device__ __forceinline__ bool transform(int, int col0, uint32_t (&v)[32], int, int N) const {
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (col0 + j < N) {
+          const float4 b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+          v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), b4.x));
+          v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), b4.y));
+          v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), b4.z));
+          v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), b4.w));
+        }
+      }
+    }
+    if (pre) return true;
+    activate(v);
+    return false;
+  }
+  __device__ __forceinline__ void activate(uint32_t (&v)[32]) const {
+    if (relu) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (__uint_as_float(v[j]) < 0.f) v[j] = 0u;
+    }
+  }
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
                                              int /*split*/) const {
     if (row >= M) return;
@@ -134,6 +175,7 @@ struct EpiBiasRelu {
 
 // Epilogue of a split-K launch: partial[split][row][col] = acc.
 struct EpiPartial {
+  static constexpr bool kTmaCapable = false;
   float* P;
   int ldp;
   size_t split_stride;

@@ -50,9 +50,14 @@ struct Traits<KIND_TF32X3> {
 };
 
 struct TmapSet {
-  CUtensorMap a[2];  // [0] = A (i8) or A_hi, [1] = A_lo
+  CUtensorMap a[2];    // [0] = A (i8) or A_hi, [1] = A_lo
   CUtensorMap b[2];
+  CUtensorMap out[2];  // output (and pre-activation output) for epilogues that store through TMA
 };
+
+// One 32-row x 32-column staging tile (128-byte rows, 128-byte swizzle) per epilogue warp.
+constexpr uint32_t STAGING_PER_WARP = 32 * 128;
+constexpr uint32_t STAGING = EPI_WARPS * STAGING_PER_WARP;
 
 template <int KIND, int BN, int STAGES>
 struct Smem {
@@ -60,9 +65,52 @@ struct Smem {
   static constexpr uint32_t B_TILE = BN * ROW_BYTES;
   static constexpr uint32_t STAGE = Traits<KIND>::NOP * (A_TILE + B_TILE);
   static constexpr uint32_t TILES = STAGES * STAGE;
+  static constexpr uint32_t BARS_OFF = TILES + STAGING;
   static constexpr uint32_t BARS = 8 * (2 * STAGES + 4) + 16;
-  static constexpr uint32_t TOTAL = TILES + BARS + 1024;  // + alignment slack
+  static constexpr uint32_t TOTAL = BARS_OFF + BARS + 1024;  // + alignment slack
 };
+
+// Epilogue of one 32 x 32 chunk held one row per lane in v[32].
+//
+// Functors that declare kTmaCapable and have `tma` set transform the values in registers and
+// hand them to a TMA store: the warp writes its chunk into a swizzled staging tile in shared
+// memory and one lane issues cp.async.bulk.tensor, so global memory sees whole 128-byte rows
+// instead of 32 scattered 16-byte pieces per store instruction (measured: the scattered stores,
+// not the MMAs, bounded the 4096^3 INT8 GEMM).  Edges need no care: the store clips at the
+// tensor's extent.  Everything else goes through the functor's own direct stores.
+__device__ __forceinline__ void stage_and_store(uint32_t stg, const CUtensorMap* tmap, int lane, int row0,
+                                                int col0, const uint32_t (&v)[32], int M, int N) {
+  if (lane == 0) ptx::bulk_wait_read_all();  // the previous store has finished reading the tile
+  __syncwarp();
+  const uint32_t rowaddr = stg + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    ptx::st_shared_v4(rowaddr + (((uint32_t)j ^ ((uint32_t)lane & 7u)) << 4), v[4 * j], v[4 * j + 1],
+                      v[4 * j + 2], v[4 * j + 3]);
+  ptx::fence_proxy_async();
+  __syncwarp();
+  if (lane == 0 && row0 < M && col0 < N) {
+    ptx::tma_store_2d(tmap, col0, row0, stg);
+    ptx::bulk_commit_group();
+  }
+}
+
+template <class Epi>
+__device__ __forceinline__ void epilogue_chunk(const Epi& epi, const TmapSet& tm, uint32_t stg, int lane,
+                                               int row0, int col0, uint32_t (&v)[32], int M, int N,
+                                               int split) {
+  if constexpr (Epi::kTmaCapable) {
+    if (epi.tma) {
+      if (epi.transform(row0 + lane, col0, v, M, N)) {  // true: v now holds the pre-activation
+        stage_and_store(stg, &tm.out[1], lane, row0, col0, v, M, N);
+        epi.activate(v);
+      }
+      stage_and_store(stg, &tm.out[0], lane, row0, col0, v, M, N);
+      return;
+    }
+  }
+  epi(row0 + lane, col0, v, M, N, split);
+}
 
 // Tile order.  Tiles are walked in groups of `group_m` rows of tiles: inside a group the m
 // index runs fastest, then n.  The CTAs resident at one time then share `group_m` blocks of A
@@ -110,7 +158,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + S::TILES;
+  const uint32_t bars = base + S::BARS_OFF;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
@@ -252,6 +300,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;            // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;  // which of the quarter's two warps: even or odd column chunks
+    const uint32_t stg = base + S::TILES + (uint32_t)(warp - 2) * STAGING_PER_WARP;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
@@ -262,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
       const int m0 = tmi * BM, n0 = tni * BN;
       const int kb_begin = split * kb_per_split;
       const int kb_end = kb_begin + kb_per_split < total_kb ? kb_begin + kb_per_split : total_kb;
-      const int row = m0 + q * 32 + lane;
+      const int row0 = m0 + q * 32;
       if constexpr (KIND == KIND_I8) {
         ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
         ok = __all_sync(0xffffffffu, ok);
@@ -273,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           uint32_t v[32];
           ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, v);
           ptx::tmem_wait_ld();
-          epi(row, n0 + c * 32, v, M, N, split);
+          epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, split);
           __syncwarp();
         }
         ptx::tc_fence_before();
@@ -312,7 +361,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           uint32_t v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[cc * 32 + j]);
-          epi(row, n0 + (2 * cc + half) * 32, v, M, N, split);
+          epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, split);
           __syncwarp();
         }
       }
@@ -320,6 +369,7 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
   }
 
   // ------------------------------------------------------------ teardown
+  if (warp >= 2 && lane == 0) ptx::bulk_wait_read_all();  // staged TMA stores have left shared memory
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();

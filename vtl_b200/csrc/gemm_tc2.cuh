@@ -28,12 +28,16 @@ using gemm::ROW_BYTES;
 using gemm::WAIT_LIMIT_NS;
 
 constexpr int BN2 = 256;      // columns of D per pair tile
-constexpr int STAGES2 = 6;
+#ifndef VTLB_PAIR_STAGES
+#define VTLB_PAIR_STAGES 6  // shared-memory ring depth of the pair kernel (tuning knob)
+#endif
+constexpr int STAGES2 = VTLB_PAIR_STAGES;
 constexpr uint32_t A_TILE = BM * ROW_BYTES;          // 16 KB: this CTA's 128 rows of A
 constexpr uint32_t B_HALF = (BN2 / 2) * ROW_BYTES;   // 16 KB: this CTA's 128 rows of B
 constexpr uint32_t STAGE = A_TILE + B_HALF;
 constexpr uint32_t TILES = STAGES2 * STAGE;
-constexpr uint32_t SMEM_TOTAL = TILES + 8 * (2 * STAGES2 + 4) + 16 + 1024;
+constexpr uint32_t BARS_OFF = TILES + gemm::STAGING;  // staging tiles of the epilogue warps sit between
+constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES2 + 4) + 16 + 1024;
 constexpr uint32_t TMEM_COLS = 2 * BN2;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -113,7 +117,7 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + TILES;
+  const uint32_t bars = base + BARS_OFF;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + a); };
@@ -221,6 +225,7 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;  // even or odd 32-column chunks
+    const uint32_t stg = base + TILES + (uint32_t)(warp - 2) * gemm::STAGING_PER_WARP;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
@@ -231,13 +236,13 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
-      const int row = m0 + q * 32 + lane;
+      const int row0 = m0 + q * 32;
 #pragma unroll 1
       for (int c = half; c < BN2 / 32; c += 2) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
         ptx::tmem_wait_ld();
-        epi(row, n0 + c * 32, v, M, N, 0);
+        gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
         __syncwarp();
       }
       ptx::tc_fence_before();
@@ -249,6 +254,7 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
   }
 
   // ------------------------------------------------------------ teardown
+  if (warp >= 2 && lane == 0) ptx::bulk_wait_read_all();  // staged TMA stores have left shared memory
   ptx::tc_fence_before();
   __syncthreads();
   if (*abort_flag) {

@@ -105,11 +105,18 @@ __global__ void __launch_bounds__(256) row_absmax_kernel(const float* __restrict
 
 // ---------------------------------------------------------------- epilogues
 struct EpiStoreI32 {
+  static constexpr bool kTmaCapable = true;
   int32_t* C;
   int ldc;
+  int tma;  // store through the output tensor map (tm.out[0]) instead of per-thread stores
+  __device__ __forceinline__ bool transform(int, int, uint32_t (&)[32], int, int) const { return false; }
+  __device__ __forceinline__ void activate(uint32_t (&)[32]) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
+#ifdef VTLB_DEBUG_SKIP_STORES  // measurement only: how long does the GEMM take without its stores
+    if (v[0] != 0x7fffffffu) return;
+#endif
     int32_t* c = C + (size_t)row * ldc + col0;
     if (col0 + 32 <= N && (ldc & 3) == 0) {
 #pragma unroll
@@ -133,12 +140,34 @@ __device__ __forceinline__ float dequant1(uint32_t acc, float sa, float sw, floa
 }
 
 struct EpiDequant {
+  static constexpr bool kTmaCapable = true;
   float* Y;
   const float* sa;
   const float* sw;
   const float* bias;  // may be null
   int ldy;
   int relu;
+  int tma;  // store through the output tensor map (needs N % 4 == 0)
+  // dequantises the chunk in registers; rows and columns past the edge yield values the
+  // clipped TMA store never writes
+  __device__ __forceinline__ bool transform(int row, int col0, uint32_t (&v)[32], int M, int N) const {
+    const float s = row < M ? sa[row] : 0.0f;
+    const bool hb = bias != nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = w4;
+      if (col0 + j < N) {
+        w4 = __ldg(reinterpret_cast<const float4*>(sw + col0 + j));
+        if (hb) b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
+      }
+      v[j] = __float_as_uint(dequant1(v[j], s, w4.x, b4.x, hb, relu));
+      v[j + 1] = __float_as_uint(dequant1(v[j + 1], s, w4.y, b4.y, hb, relu));
+      v[j + 2] = __float_as_uint(dequant1(v[j + 2], s, w4.z, b4.z, hb, relu));
+      v[j + 3] = __float_as_uint(dequant1(v[j + 3], s, w4.w, b4.w, hb, relu));
+    }
+    return false;
+  }
+  __device__ __forceinline__ void activate(uint32_t (&)[32]) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
@@ -320,9 +349,16 @@ bool use_pair_kernel(vtlb_ctx* ctx, int M, int N) {
 // [M, K/chunks] matrix (the layout an all-gather of per-rank column slabs leaves behind); the
 // A operand is then read through a 3-D tensor map (k within shard, row, shard).
 template <class Epi>
-int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, const Epi& epi,
+int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, Epi epi, void* out,
            int chunks = 1) {
   gemm::TmapSet tm;
+  // 4-byte outputs with a 16-byte-multiple row pitch go out through TMA stores
+  epi.tma = (N % 4 == 0) && vtlb_aligned16(out);
+  if (epi.tma) {
+    int rc0 = gemm::encode_tmap_2d(ctx, &tm.out[0], true, out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 4, 32, 32);
+    if (rc0) return rc0;
+    tm.out[1] = tm.out[0];
+  }
   const int chunk_k = chunks > 1 ? K / chunks : 0;
   const bool pair = use_pair_kernel(ctx, M, N);
   const int bn = pair ? 128 : pick_bn(ctx, M, N);  // a CTA of a pair loads 128 rows of B
@@ -392,7 +428,7 @@ VTLB_API int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq,
     return launch_gemv<false>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K,
                               (int32_t*)d_acc, nullptr, nullptr, nullptr, nullptr, 0);
   EpiStoreI32 epi{(int32_t*)d_acc, N};
-  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi);
+  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_acc);
 }
 
 VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa,
@@ -413,7 +449,7 @@ VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_s
                              (const float*)d_bias_or_null, relu);
   EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null,
                  N, relu};
-  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi);
+  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_Y);
 }
 
 VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards,
@@ -434,5 +470,5 @@ VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards
       (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_sharded_a: pointers must be 16-byte aligned");
   EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, N, relu};
-  return run_i8(ctx, d_Aq_shards, d_Wq, M, N, K, epi, shards);
+  return run_i8(ctx, d_Aq_shards, d_Wq, M, N, K, epi, d_Y, shards);
 }

@@ -92,6 +92,21 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tma
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// 2-D tiled store shared -> global through a tensor map; the part of the box that lies
+// beyond the tensor's extent is not written.  Completion is tracked by bulk async-groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until every committed bulk store of this thread has finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
