@@ -310,9 +310,16 @@ def run_int8(args, ranks):
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<int8, fused dequant+bias+ReLU>",
+            "roofline": {"bound": "tensor",
+                         "kernel": "gemm2::gemm_i8_pair_kernel<EpiDequant> (tcgen05 kind::i8, cta_group::2, "
+                                   "fused dequant+bias+ReLU, TMA-store epilogue)",
                          "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
-                         "frac": gemm_tops / int8_peak, "traffic": None,
+                         "frac": gemm_tops / int8_peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on
+                         # this workload, from the ncu capture summarised in
+                         # profiles/gemm_i8_pair_fused_4096.md (algorithmic operand bytes: 33.6 MB read)
+                         "traffic": 54.2e6, "traffic_unit": "bytes per launch (ncu, 34.0 MB read + 20.2 MB written)",
+                         "algorithmic_ops_per_launch": 2.0 * M * N * K,
                          "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
                                         "dense INT8 issues at twice the bf16 rate)",
                          "kernel_ms": gemm_ms},
@@ -364,6 +371,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="int8_linear")
+    ap.add_argument("--rows", type=int, default=None,
+                    help="training workloads only: global batch override, for small profiling captures")
     args = ap.parse_args()
     defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5),
                 "int8_mlp_c5": (20, 3)}

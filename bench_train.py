@@ -27,8 +27,16 @@ def kaiming_uniform(rng, shape, fan_in):
 
 
 class Workload:
-    def __init__(self, name, world, rank):
+    def __init__(self, name, world, rank, rows=None):
+        """`rows` (global batch) replaces the configuration's batch: only for small profiling
+        captures, the result then says so in config.global_batch."""
         self.name, self.world, self.rank = name, world, rank
+        self._init(name, world)
+        if rows:
+            self.global_rows = int(rows)
+            self.local_rows = self.global_rows // world
+
+    def _init(self, name, world):
         if name == "mlp_c1":
             self.dims, self.relu = [784, 256, 10], [True, False]
             self.local_rows, self.global_rows = 64, 64 * world
@@ -179,7 +187,7 @@ def run_reference(args, ranks):
 
 def run(args, ranks, ClockSampler, peaks, cuda_sync):
     from vtl_b200 import host
-    wl = Workload(args.workload, ranks.world, ranks.rank)
+    wl = Workload(args.workload, ranks.world, ranks.rank, getattr(args, "rows", None))
     session = host.Session(ranks.local_rank)
     dev = session.dev
     ranks.attach(dev, session)  # the session creates the communicator, so its gates know the world size
