@@ -259,7 +259,11 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
     if ranks.rank == 0:
         pk = peaks()
         ms_step = ms_total / args.steps
-        tf32x3_peak = pk["bf16_tflops"] / 2.0 / 3.0
+        # GEMMs timed inside a step that keeps the GPU busy for hundreds of ms run under the power
+        # cap: the sustained figure is the yardstick there, the burst figure for short steps
+        long_step = ms_step > 50.0
+        bf16_peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) if long_step else pk["bf16_tflops"]
+        tf32x3_peak = bf16_peak / 2.0 / 3.0
         gemm_tflops = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         out = {
             "metric": "f32_train_samples_per_s", "value": G / (ms_step * 1e-3), "unit": "samples/s",
@@ -280,8 +284,8 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
             "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<tf32 x3> (all GEMM launches of a step)",
                          "achieved": gemm_tflops, "peak": tf32x3_peak, "unit": "TFLOP/s",
                          "frac": (gemm_tflops / tf32x3_peak) if gemm_tflops else None, "traffic": None,
-                         "peak_source": f"bf16_tflops of {pk['_source']} / 2 (TF32 rate) / 3 (three MMAs per "
-                                        "algorithmic product)",
+                         "peak_source": f"{'bf16_tflops_sustained' if long_step else 'bf16_tflops'} of "
+                                        f"{pk['_source']} / 2 (TF32 rate) / 3 (three MMAs per algorithmic product)",
                          "kernel_ms_per_step": gemm_ms / prof_steps, "launches_per_step": gemm_n / prof_steps},
         }
         if ranks.world == 1:

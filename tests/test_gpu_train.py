@@ -168,3 +168,21 @@ def test_host_api_errors(sess):
     with pytest.raises(capi.VtlbError):
         m.train_step(x, (2, 7), t, (2, 4), update=False)  # wrong input width
     m.close()
+
+
+@pytest.mark.parametrize("M,K,N", [(2, 2, 2), (96, 130, 50), (512, 300, 256)])
+def test_variable_matmul_gate(sess, orc, M, K, N):
+    """Variable.matmul / MatMulGate (autograd/variable_ops.v:82-94, gates_blas.v:41-46):
+    C = A.B, dA = G.B^T, dB = A^T.G with G = C - T from the MSE loss."""
+    rng = np.random.default_rng(M + K + N)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    T = rng.standard_normal((M, N)).astype(np.float32)
+    dA_, dB_, dT_ = (sess.dev.to_device(a) for a in (A, B, T))
+    loss, C, dA, dB = sess.matmul_mse_backprop(dA_, M, K, dB_, N, dT_)
+    rC = orc.matmul_f32(A, B)
+    G = orc.mse_bwd_f32(rC, T)
+    assert np.abs(C - rC).max() <= bound(K, A, B)
+    assert abs(loss - float(orc.mse_f32(rC, T))) <= 1e-4 * float(orc.mse_f32(rC, T))
+    assert np.abs(dA - orc.matmul_f32(G, B, tb=True)).max() <= bound(N, G, B) * 2
+    assert np.abs(dB - orc.matmul_f32(A, G, ta=True)).max() <= bound(M, A, G) * 2

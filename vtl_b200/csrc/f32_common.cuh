@@ -3,7 +3,7 @@
 #pragma once
 #include <stdlib.h>
 
-#include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 
 namespace f32 {
 
@@ -89,6 +89,19 @@ int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, 
   }
   const uint64_t stride = (uint64_t)p.ld * 4;
   int rc;
+  // large problems: CTA pairs, 256 x 256 tiles (VTLB_F32_PAIR=0 keeps them on single CTAs)
+  static int pair_env = -2;
+  if (pair_env == -2) {
+    const char* e = getenv("VTLB_F32_PAIR");
+    pair_env = e ? atoi(e) : -1;
+  }
+  if (splits == 1 && pair_env != 0 && gemm2::pair_worthwhile(ctx, M, N)) {
+    if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[0], true, p.a_hi, K, M, stride, 32, gemm::BM))) return rc;
+    if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[1], true, p.a_lo, K, M, stride, 32, gemm::BM))) return rc;
+    if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, p.b_hi, K, N, stride, 32, 128))) return rc;
+    if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, p.b_lo, K, N, stride, 32, 128))) return rc;
+    return gemm2::launch_pair<gemm::KIND_TF32X3, Epi>(ctx, tm, epi, M, N, K);
+  }
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[0], true, p.a_hi, K, M, stride, 32, gemm::BM))) return rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.a[1], true, p.a_lo, K, M, stride, 32, gemm::BM))) return rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, p.b_hi, K, N, stride, 32, bn))) return rc;

@@ -1,4 +1,5 @@
-// INT8 GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 tile of D per pair.
+// GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 tile of D per pair; INT8 (kind::i8)
+// and f32 as 3xTF32 (kind::tf32 on hi/lo planes).
 //
 // Why a pair: with one CTA per 128 x 256 tile every SM has to land 48 KB of operands in
 // shared memory per 512 tensor-core cycles while the MMA reads 96 B/clk from the same
@@ -29,15 +30,25 @@ using gemm::WAIT_LIMIT_NS;
 
 constexpr int BN2 = 256;      // columns of D per pair tile
 #ifndef VTLB_PAIR_STAGES
-#define VTLB_PAIR_STAGES 6  // shared-memory ring depth of the pair kernel (tuning knob)
+#define VTLB_PAIR_STAGES 6  // shared-memory ring depth of the INT8 pair kernel (tuning knob)
 #endif
-constexpr int STAGES2 = VTLB_PAIR_STAGES;
-constexpr uint32_t A_TILE = BM * ROW_BYTES;          // 16 KB: this CTA's 128 rows of A
-constexpr uint32_t B_HALF = (BN2 / 2) * ROW_BYTES;   // 16 KB: this CTA's 128 rows of B
-constexpr uint32_t STAGE = A_TILE + B_HALF;
-constexpr uint32_t TILES = STAGES2 * STAGE;
-constexpr uint32_t BARS_OFF = TILES + gemm::STAGING;  // staging tiles of the epilogue warps sit between
-constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES2 + 4) + 16 + 1024;
+
+template <int KIND>
+struct Cfg {
+  static constexpr int NOP = gemm::Traits<KIND>::NOP;                 // operand planes per side
+  static constexpr int STAGES = KIND == gemm::KIND_I8 ? VTLB_PAIR_STAGES : 3;
+  static constexpr uint32_t A_TILE = BM * ROW_BYTES;                  // this CTA's 128 rows of A
+  static constexpr uint32_t B_HALF = (BN2 / 2) * ROW_BYTES;           // this CTA's 128 rows of B
+  static constexpr uint32_t STAGE = NOP * (A_TILE + B_HALF);          // 32 KB (INT8) / 64 KB (TF32x3)
+  static constexpr uint32_t TILES = STAGES * STAGE;
+  static constexpr uint32_t BARS_OFF = TILES + gemm::STAGING;         // epilogue staging tiles in between
+  static constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES + 4) + 16 + 1024;
+  // TF32x3 closes its accumulator every CHUNK_KB stages (the f32 accumulate of tcgen05 truncates;
+  // see gemm_tc.cuh).  With 256 columns per accumulator and two buffers there is no room in tensor
+  // memory for a separate accumulator of the small cross terms: here they share the main one, which
+  // costs three truncations per K step instead of one, still two orders inside the error bound.
+  static constexpr int CHUNK_KB = KIND == gemm::KIND_TF32X3 ? 4 : 0;
+};
 constexpr uint32_t TMEM_COLS = 2 * BN2;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -94,6 +105,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
       "h"(mask)
       : "memory");
 }
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
   asm volatile(
@@ -106,23 +128,26 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
       : "memory");
 }
 
-template <class Epi>
+template <int KIND, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M, int N, int K,
-                    int group_m, int a_chunk_k, uint32_t* status) {
-  constexpr int BK = ROW_BYTES;          // int8: 128 elements of K per stage
+gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M, int N, int K,
+                 int group_m, int a_chunk_k, uint32_t* status) {
+  using T = gemm::Traits<KIND>;
+  using C = Cfg<KIND>;
+  constexpr int NOP = C::NOP, STAGES = C::STAGES;
+  constexpr int BK = ROW_BYTES / T::ELEM;  // elements of K per stage
   constexpr int KSTEPS = ROW_BYTES / 32;
-  constexpr uint32_t IDESC = ptx::umma_idesc(ptx::kCfmtS32, ptx::kFmtS8, 2 * BM, BN2);
+  constexpr uint32_t IDESC = ptx::umma_idesc(T::CFMT, T::ABFMT, 2 * BM, BN2);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + BARS_OFF;
+  const uint32_t bars = base + C::BARS_OFF;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (STAGES2 + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES2 + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES2 + 4));
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 4));
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,9 +156,10 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN2 - 1) / BN2;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int chunk_kb = C::CHUNK_KB ? C::CHUNK_KB : num_kb;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES2; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(full_bar(s), 1);   // the leader's expect_tx arrive; bytes from both CTAs
       ptx::mbar_init(empty_bar(s), 1);  // one multicast commit
     }
@@ -144,8 +170,10 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
-    ptx::prefetch_tmap(&tm.a[0]);
-    ptx::prefetch_tmap(&tm.b[0]);
+    for (int i = 0; i < NOP; ++i) {
+      ptx::prefetch_tmap(&tm.a[i]);
+      ptx::prefetch_tmap(&tm.b[i]);
+    }
   }
   if (warp == 1) {
     tmem_alloc2(ptx::smem_u32(tmem_slot), TMEM_COLS);
@@ -173,14 +201,21 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
             break;
           }
           const uint32_t leader_full = mapa(full_bar(stage), 0);
-          if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE);
-          const uint32_t sa = base + stage * STAGE;
-          if (a_chunk_k)  // A stored as [chunk][M][a_chunk_k] (gathered column shards)
-            tma_load_3d_pair(sa, &tm.a[0], (kb * BK) % a_chunk_k, m0, (kb * BK) / a_chunk_k, leader_full);
-          else
-            tma_load_2d_pair(sa, &tm.a[0], kb * BK, m0, leader_full);
-          tma_load_2d_pair(sa + A_TILE, &tm.b[0], kb * BK, n0, leader_full);
-          if (++stage == STAGES2) {
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE);
+          const uint32_t sa = base + stage * C::STAGE;
+          const uint32_t sb = sa + NOP * C::A_TILE;
+#pragma unroll
+          for (int i = 0; i < NOP; ++i) {
+            if (a_chunk_k)  // A stored as [chunk][M][a_chunk_k] (gathered column shards)
+              tma_load_3d_pair(sa + i * C::A_TILE, &tm.a[i], (kb * BK) % a_chunk_k, m0, (kb * BK) / a_chunk_k,
+                               leader_full);
+            else
+              tma_load_2d_pair(sa + i * C::A_TILE, &tm.a[i], kb * BK, m0, leader_full);
+          }
+#pragma unroll
+          for (int i = 0; i < NOP; ++i)
+            tma_load_2d_pair(sb + i * C::B_HALF, &tm.b[i], kb * BK, n0, leader_full);
+          if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
@@ -193,63 +228,116 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) break;
-        ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
+          const int kb1 = kb0 + chunk_kb < num_kb ? kb0 + chunk_kb : num_kb;
+          if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t sa = base + stage * STAGE;
+          const uint32_t d_tmem = tmem_base + acc * BN2;
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t sa = base + stage * C::STAGE;
+            const uint32_t sb = sa + NOP * C::A_TILE;
 #pragma unroll
-          for (int kk = 0; kk < KSTEPS; ++kk) {
-            const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
-            const uint64_t db = ptx::umma_desc_k_sw128(sa + A_TILE) + 2u * kk;
-            umma_i8_pair(d_tmem, da, db, IDESC, (kb | kk) != 0);
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+              const uint32_t first = (kb == kb0 && kk == 0) ? 0u : 1u;
+              if constexpr (KIND == gemm::KIND_I8) {
+                const uint64_t da = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+                const uint64_t db = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+                umma_i8_pair(d_tmem, da, db, IDESC, first);
+              } else {
+                const uint64_t a_hi = ptx::umma_desc_k_sw128(sa) + 2u * kk;
+                const uint64_t a_lo = ptx::umma_desc_k_sw128(sa + C::A_TILE) + 2u * kk;
+                const uint64_t b_hi = ptx::umma_desc_k_sw128(sb) + 2u * kk;
+                const uint64_t b_lo = ptx::umma_desc_k_sw128(sb + C::B_HALF) + 2u * kk;
+                umma_tf32_pair(d_tmem, a_lo, b_hi, IDESC, first);  // small terms first
+                umma_tf32_pair(d_tmem, a_hi, b_lo, IDESC, 1);
+                umma_tf32_pair(d_tmem, a_hi, b_hi, IDESC, 1);
+              }
+            }
+            umma_commit_pair(empty_bar(stage));
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
-          umma_commit_pair(empty_bar(stage));
-          if (++stage == STAGES2) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          if (!ok) break;
+          umma_commit_pair(tfull_bar(acc));
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        if (!ok) break;
-        umma_commit_pair(tfull_bar(acc));
-        acc ^= 1u;
-        if (acc == 0) acc_phase ^= 1u;
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;  // even or odd 32-column chunks
-    const uint32_t stg = base + TILES + (uint32_t)(warp - 2) * gemm::STAGING_PER_WARP;
+    const uint32_t stg = base + C::TILES + (uint32_t)(warp - 2) * gemm::STAGING_PER_WARP;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int tmi, tni;
       gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
       const int m0 = tmi * 2 * BM + (int)rank * BM, n0 = tni * BN2;
-      bool ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      ptx::tc_fence_after();
       const int row0 = m0 + q * 32;
+      if constexpr (KIND == gemm::KIND_I8) {
+        ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        ptx::tc_fence_after();
 #pragma unroll 1
-      for (int c = half; c < BN2 / 32; c += 2) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
-        ptx::tmem_wait_ld();
-        gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
+        for (int c = half; c < BN2 / 32; c += 2) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
+          ptx::tmem_wait_ld();
+          gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
+          __syncwarp();
+        }
+        ptx::tc_fence_before();
         __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      } else {
+        float sum[BN2 / 2];  // this warp's four 32-column chunks
+#pragma unroll
+        for (int j = 0; j < BN2 / 2; ++j) sum[j] = 0.0f;
+        for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+          ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < BN2 / 64; ++cc) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(lane_base + acc * BN2 + (2 * cc + half) * 32, v);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[cc * 32 + j] = __fadd_rn(sum[cc * 32 + j], __uint_as_float(v[j]));
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int cc = 0; cc < BN2 / 64; ++cc) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[cc * 32 + j]);
+          gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, 0);
+          __syncwarp();
+        }
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
-      acc ^= 1u;
-      if (acc == 0) acc_phase ^= 1u;
     }
   }
 
@@ -269,14 +357,21 @@ gemm_i8_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int
   }
 }
 
-template <class Epi>
+// True when the problem has enough 256 x 256 tiles for the CTA pairs to pay off.
+inline bool pair_worthwhile(vtlb_ctx* ctx, int M, int N) {
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return M >= 512 && N >= 256 && tiles >= ctx->sm_count / 4;
+}
+
+template <int KIND, class Epi>
 int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, int N, int K,
                 int a_chunk_k = 0) {
-  static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
-  auto kern = gemm_i8_pair_kernel<Epi>;
+  using C = Cfg<KIND>;
+  static_assert(C::SMEM_TOTAL <= 232448, "shared memory budget");
+  auto kern = gemm_pair_kernel<KIND, Epi>;
   static uint64_t configured = 0;
   if (!(configured >> (ctx->device & 63) & 1)) {
-    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_TOTAL));
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_TOTAL));
     configured |= 1ull << (ctx->device & 63);
   }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN2 - 1) / BN2);
@@ -284,9 +379,10 @@ int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, i
   if (tiles < pairs) pairs = tiles;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  const int group_m = gemm::pick_group_m((M + 2 * BM - 1) / (2 * BM), (size_t)2 * BM * K);
-  kern<<<2 * pairs, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k,
-                                                            ctx->d_status);
+  const int group_m = gemm::pick_group_m((M + 2 * BM - 1) / (2 * BM),
+                                         (size_t)2 * BM * K * gemm::Traits<KIND>::ELEM * C::NOP);
+  kern<<<2 * pairs, NUM_THREADS, C::SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k,
+                                                               ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;

@@ -231,6 +231,45 @@ struct LossGate : Gate {
 
 }  // namespace
 
+// ---------------------------------------------------------------- Variable.matmul
+namespace {
+// autograd/gates_blas.v:25-46
+struct MatMulGate : Gate {
+  VarPtr a, b;
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Session* s = g.session();
+    const int M = a->value.shape()[0], K = a->value.shape()[1], N = b->value.shape()[1];
+    Tensor dA, dB;
+    if (a->requires_grad) {  // dA[M,K] = G[M,N] . B^T  (B is [K,N]: the B operand is "transposed")
+      dA = Tensor::empty(s, {M, K});
+      s->check(vtlb_gemm_f32(s->ctx, 0, 1, M, K, N, g.data(), b->value.data(), dA.data(), nullptr, 0));
+    }
+    if (b->requires_grad) {  // dB[K,N] = A^T . G
+      dB = Tensor::empty(s, {K, N});
+      s->check(vtlb_gemm_f32(s->ctx, 1, 0, K, N, M, a->value.data(), g.data(), dB.data(), nullptr, 0));
+    }
+    return {dA, dB};
+  }
+};
+}  // namespace
+
+VarPtr matmul(const VarPtr& a, const VarPtr& b) {
+  Context* ctx = a->context;
+  Session* s = ctx->device_session;
+  const auto& as = a->value.shape();
+  const auto& bs = b->value.shape();
+  if (as.size() != 2 || bs.size() != 2) throw Error(VTLB_EINVAL, "matmul: both operands must be 2-D");
+  if (as[1] != bs[0]) throw Error(VTLB_EINVAL, "matmul: inner dimensions differ");
+  Tensor c = Tensor::empty(s, {as[0], bs[1]});
+  s->check(vtlb_gemm_f32(s->ctx, 0, 0, as[0], bs[1], as[1], a->value.data(), b->value.data(), c.data(), nullptr, 0));
+  VarPtr out = ctx->variable(c);
+  auto g = std::make_unique<MatMulGate>();
+  g->a = a;
+  g->b = b;
+  ctx->register_node("MatMul", std::move(g), out, {a, b});
+  return out;
+}
+
 // ---------------------------------------------------------------- layers
 LinearLayer::LinearLayer(Context* ctx, int in, int out) : in_features(in), out_features(out) {
   Session* s = ctx->device_session;

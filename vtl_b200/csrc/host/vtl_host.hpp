@@ -112,6 +112,10 @@ struct Context {
   void register_node(std::string name, std::unique_ptr<Gate> gate, VarPtr result, std::vector<VarPtr> parents);
 };
 
+// Variable.matmul (autograd/variable_ops.v:82-94): C = A.B for 2-D variables, registered with
+// a MatMulGate whose backward is dA = G.B^T, dB = A^T.G (autograd/gates_blas.v:41-46).
+VarPtr matmul(const VarPtr& a, const VarPtr& b);
+
 // nn/types/layer.v:6-60
 struct Layer {
   virtual ~Layer() = default;

@@ -51,6 +51,10 @@ int vtlh_model_train_step(vtlh_model* m, const void* d_x, int ndim, const int* x
 int vtlh_model_zero_grad(vtlh_model* m);
 /* gradient of the loss w.r.t. the input of the last train_step (device -> host) */
 int vtlh_model_get_input_grad(vtlh_model* m, float* host);
+/* Variable.matmul on its own tape: C = A[M,K].B[K,N], loss = MSE(C, T), backprop; copies the loss,
+ * C and the gradients of A and B to the host (any of the outputs may be null) */
+int vtlh_matmul_mse_backprop(vtlh_session* s, const void* d_A, int M, int K, const void* d_B, int N,
+                             const void* d_T, float* h_loss, float* h_C, float* h_dA, float* h_dB);
 #ifdef __cplusplus
 }
 #endif

@@ -205,6 +205,24 @@ int vtlh_model_zero_grad(vtlh_model* m) {
   });
 }
 
+int vtlh_matmul_mse_backprop(vtlh_session* hs, const void* d_A, int M, int K, const void* d_B, int N,
+                             const void* d_T, float* h_loss, float* h_C, float* h_dA, float* h_dB) {
+  return guard([&] {
+    Session* s = hs->s.get();
+    Context ctx(s);
+    const int as[2] = {M, K}, bs[2] = {K, N}, ts[2] = {M, N};
+    VarPtr a = ctx.variable(borrow(s, d_A, 2, as)), b = ctx.variable(borrow(s, d_B, 2, bs));
+    VarPtr c = matmul(a, b);
+    MSELoss mse;
+    VarPtr l = mse.loss(c, borrow(s, d_T, 2, ts), -1);
+    l->backprop();
+    if (h_loss) l->value.to_array(h_loss);
+    if (h_C) c->value.to_array(h_C);
+    if (h_dA) a->grad.to_array(h_dA);
+    if (h_dB) b->grad.to_array(h_dB);
+  });
+}
+
 int vtlh_model_get_input_grad(vtlh_model* m, float* host) {
   return guard([&] {
     if (!m->last_input || m->last_input->grad_is_zero) throw Error(VTLB_ESTATE, "no input gradient available");

@@ -341,8 +341,7 @@ bool use_pair_kernel(vtlb_ctx* ctx, int M, int N) {
   }
   if (forced == 0) return false;
   if (forced == 1) return true;
-  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  return M >= 512 && N >= 256 && tiles >= ctx->sm_count / 4;
+  return gemm2::pair_worthwhile(ctx, M, N);
 }
 
 // `chunks` > 1: Aq is stored as that many column shards one after another, each a dense
@@ -370,7 +369,7 @@ int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, E
       return rc;
     tm.a[1] = tm.a[0];
   }
-  if (pair) return gemm2::launch_pair<Epi>(ctx, tm, epi, M, N, K, chunk_k);
+  if (pair) return gemm2::launch_pair<gemm::KIND_I8, Epi>(ctx, tm, epi, M, N, K, chunk_k);
   if (bn == 256) return gemm::launch<gemm::KIND_I8, 256, 4, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
   if (bn == 128) return gemm::launch<gemm::KIND_I8, 128, 6, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
   return gemm::launch<gemm::KIND_I8, 64, 8, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);

@@ -49,6 +49,7 @@ def load() -> C.CDLL:
             "vtlh_model_forward": [vp, vp, i, ip, vp],
             "vtlh_model_train_step": [vp, vp, i, ip, vp, i, ip, i, i, C.POINTER(C.c_float)],
             "vtlh_model_get_input_grad": [vp, vp], "vtlh_model_zero_grad": [vp],
+            "vtlh_matmul_mse_backprop": [vp, vp, i, i, vp, i, vp, vp, vp, vp, vp],
         }
         for name, args in protos.items():
             fn = getattr(lib, name)
@@ -85,6 +86,14 @@ class Session:
 
     def comm_init(self, nranks: int, rank: int, uid: bytes):
         _ck(self.lib.vtlh_session_comm_init(self.h, nranks, rank, C.c_char_p(uid)))
+
+    def matmul_mse_backprop(self, d_A, M, K, d_B, N, d_T):
+        """Variable.matmul + MSE loss + backprop on a fresh tape -> (loss, C, dA, dB) on the host."""
+        loss = np.zeros(1, np.float32)
+        Cm, dA, dB = np.empty((M, N), np.float32), np.empty((M, K), np.float32), np.empty((K, N), np.float32)
+        _ck(self.lib.vtlh_matmul_mse_backprop(self.h, capi._ptr(d_A), M, K, capi._ptr(d_B), N, capi._ptr(d_T),
+                                              loss.ctypes.data, Cm.ctypes.data, dA.ctypes.data, dB.ctypes.data))
+        return float(loss[0]), Cm, dA, dB
 
     def close(self):
         if self.h:
