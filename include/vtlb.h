@@ -102,6 +102,12 @@ int vtlb_reserve_scratch(vtlb_ctx* ctx, size_t bytes);
 int vtlb_gemm_f32(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const void* d_A,
                   const void* d_B, void* d_C, const void* d_bias_or_null, int relu);
 
+/* f32 products of at most `max_flops` (2*M*N*K) run as one FFMA kernel on CUDA cores straight
+ * from the caller's operands instead of the tensor-core path: at the size of a 784->256->10
+ * MLP on a batch of 64 the call is bound by launch latency, not arithmetic.  Default 1.4e8;
+ * 0 sends every product to the tensor cores.  Both paths meet the same error bound. */
+int vtlb_set_small_gemm_limit(vtlb_ctx* ctx, double max_flops);
+
 /* ---- Linear layer ---------------------------------------------------------
  * Y[M,N] = X[M,K].W[N,K]^T + b[N]; with relu != 0, Y = relu(.) and, when
  * d_pre_or_null is given, the pre-activation is stored there as well (it is

@@ -27,6 +27,15 @@ def dev():
     d.close()
 
 
+@pytest.fixture(params=["tensor_cores_only", "small_products_on_cuda_cores"])
+def gemm_path(request, dev):
+    """Runs a test twice: with every f32 product forced onto the tcgen05 path, and with the
+    library's default routing of small products to the CUDA-core kernel."""
+    dev.set_small_gemm_limit(0.0 if request.param == "tensor_cores_only" else 1.4e8)
+    yield request.param
+    dev.set_small_gemm_limit(1.4e8)
+
+
 @pytest.fixture(scope="session")
 def orc():
     from oracle import oracle

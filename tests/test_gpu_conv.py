@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gemm_path")]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

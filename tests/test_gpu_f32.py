@@ -4,7 +4,7 @@ max-abs error <= 1e-5 * sqrt(K) * max|A| * max|B|."""
 import numpy as np
 import pytest
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("gemm_path")]
 
 
 def tol(K, A, B):

@@ -18,6 +18,14 @@ def sess():
     s.close()
 
 
+@pytest.fixture(params=["tensor_cores_only", "small_products_on_cuda_cores"], autouse=True)
+def session_gemm_path(request, sess):
+    """Every training test runs with all f32 products on tcgen05 and with the default routing."""
+    sess.dev.set_small_gemm_limit(0.0 if request.param == "tensor_cores_only" else 1.4e8)
+    yield
+    sess.dev.set_small_gemm_limit(1.4e8)
+
+
 def kaiming_uniform(rng, out_f, in_f):
     return (rng.uniform(-1, 1, (out_f, in_f)) * np.sqrt(6.0 / in_f)).astype(np.float32)
 

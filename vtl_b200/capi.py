@@ -51,6 +51,7 @@ _PROTOS = {
     "vtlb_host_alloc": [_sz, C.POINTER(_vp)],
     "vtlb_host_free": [_vp],
     "vtlb_reserve_scratch": [_vp, _sz],
+    "vtlb_set_small_gemm_limit": [_vp, _d],
     "vtlb_gemm_f32": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i],
     "vtlb_linear_fwd_f32": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "vtlb_linear_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
@@ -255,6 +256,9 @@ class Device:
         self._ck(self.lib.vtlb_reserve_scratch(self.h, nbytes))
 
     # -- f32
+    def set_small_gemm_limit(self, max_flops: float):
+        self._ck(self.lib.vtlb_set_small_gemm_limit(self.h, float(max_flops)))
+
     def gemm_f32(self, ta, tb, M, N, K, A, B, Cout, bias=None, relu=False):
         self._ck(self.lib.vtlb_gemm_f32(self.h, int(ta), int(tb), M, N, K, _ptr(A), _ptr(B),
                                         _ptr(Cout), _ptr(bias), int(relu)))

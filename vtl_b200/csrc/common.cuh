@@ -27,6 +27,9 @@ struct vtlb_ctx {
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
   uint64_t launches = 0;
+  // f32 GEMMs of at most this many flops (2*M*N*K) run on the CUDA-core kernel of
+  // f32_small.cu instead of the tensor-core path (vtlb_set_small_gemm_limit; 0 = never).
+  double small_gemm_flops = 1.4e8;
   // Optional timing of the tensor-core GEMM launches (vtlb_profile_gemm): a ring of event
   // pairs recorded around each launch plus the algorithmic work of the launches timed.
   bool prof_on = false;

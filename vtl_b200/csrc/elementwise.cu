@@ -98,6 +98,22 @@ __global__ void __launch_bounds__(256) mse_partial_kernel(const float* __restric
   const double s = block_sum(acc, sm);
   if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
+// Short inputs: one CTA does both stages in a single launch.
+__global__ void __launch_bounds__(256) mse_short_kernel(const float* __restrict__ p, const float* __restrict__ t,
+                                                        size_t n, double divisor, float* __restrict__ dp,
+                                                        float* __restrict__ loss) {
+  __shared__ double sm[8];
+  double acc = 0.0;
+  for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const float d = __fsub_rn(p[i], t[i]);
+    if (dp) dp[i] = d;
+    const double dd = (double)d;
+    acc += (double)(float)(dd * dd);
+  }
+  const double s = block_sum(acc, sm);
+  if (threadIdx.x == 0) *loss = __fdiv_rn((float)s, (float)divisor);
+}
+
 __global__ void __launch_bounds__(256) loss_final_kernel(const double* __restrict__ partial,
                                                          int nparts, double divisor,
                                                          int divide_in_f32,
@@ -186,6 +202,12 @@ VTLB_API int vtlb_mse_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_P, const void* d_
   VTLB_ENTER(ctx);
   if (n == 0 || n_div == 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: empty input");
   if (!d_P || !d_T || !d_loss) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: null pointer");
+  if (n <= 8192) {
+    mse_short_kernel<<<1, 256, 0, ctx->stream>>>((const float*)d_P, (const float*)d_T, n, (double)n_div,
+                                                 (float*)d_dP_or_null, (float*)d_loss);
+    VTLB_LAUNCHED(ctx);
+    return VTLB_OK;
+  }
   const int blocks = ew_grid(ctx, n, 2048);
   void* scr = nullptr;
   int rc = vtlb_scratch(ctx, (size_t)blocks * sizeof(double), &scr);

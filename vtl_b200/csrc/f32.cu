@@ -96,6 +96,26 @@ __global__ void __launch_bounds__(128) colsum_final_kernel(const double* __restr
   out[n] = (float)s;
 }
 
+// Column sums for short matrices in one launch: 32 columns per CTA, 8 row slices summed in f64
+// and combined through shared memory in a fixed order.
+__global__ void __launch_bounds__(256) colsum_short_kernel(const float* __restrict__ G, int M, int N,
+                                                           float* __restrict__ out) {
+  __shared__ double part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int n = blockIdx.x * 32 + tx;
+  double s = 0.0;
+  if (n < N)
+    for (int r = ty; r < M; r += 8) s += (double)G[(size_t)r * N + n];
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && n < N) {
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += part[i][tx];
+    out[n] = (float)t;
+  }
+}
+
 __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial,
                                                             int splits, size_t n,
                                                             float* __restrict__ out) {
@@ -139,6 +159,8 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
                   const float* B, float* C, const float* bias, int relu, float* pre) {
   if (!vtlb_aligned16(C) || (pre && !vtlb_aligned16(pre)) || (bias && !vtlb_aligned16(bias)))
     return vtlb_fail(ctx, VTLB_EINVAL, "f32 GEMM: output and bias pointers must be 16-byte aligned");
+  if (2.0 * M * N * K <= ctx->small_gemm_flops)  // launch-latency-bound sizes: CUDA cores, no split passes
+    return f32::sgemm_small(ctx, transA, transB, M, N, K, A, B, C, bias, relu, pre);
   f32::Planes p;
   int rc = f32::alloc_planes(ctx, M, N, K, 0, &p);
   if (rc) return rc;
@@ -151,6 +173,11 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
 }
 
 int colsum(vtlb_ctx* ctx, const float* G, int M, int N, float* out) {
+  if (M <= 1024) {
+    colsum_short_kernel<<<(N + 31) / 32, 256, 0, ctx->stream>>>(G, M, N, out);
+    VTLB_LAUNCHED(ctx);
+    return VTLB_OK;
+  }
   int S = (M + 63) / 64;
   if (S > 64) S = 64;
   if (S < 1) S = 1;

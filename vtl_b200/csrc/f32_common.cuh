@@ -207,6 +207,10 @@ struct EpiPartial {
 int split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool transposed, int ld,
                   float* hi, float* lo);
 
+// C[M,N] = op(A).op(B) (+bias, pre-activation copy, ReLU) on CUDA cores, for small products.
+int sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
+                const float* B, float* C, const float* bias, int relu, float* pre);
+
 // out[i] = sum_s partial[s][i] (fixed order, f32 round-to-nearest), n elements.
 int reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out);
 
