@@ -25,15 +25,22 @@ def total_ops(tokens=TOKENS):
 
 
 class ShardedInt8MLP:
-    """One rank's part of the model and its activation buffers."""
+    """One rank's part of the model and its activation buffers.
 
-    def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5):
+    With more than one rank the tokens are processed as `chunks` independent row blocks (rows
+    are quantised independently, so a block can run ahead through the layers): while the codes
+    of one block are all-gathered on the communication stream, the GEMM of the next block runs
+    on the compute stream."""
+
+    def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5, chunks=None):
         self.dev, self.R, self.rank, self.M, self.dims = dev, world, rank, tokens, dims
+        self.C = chunks if chunks else (4 if world > 1 else 1)
+        assert tokens % self.C == 0
+        self.Mc = tokens // self.C
         self.layers = []
         for li in range(len(dims) - 1):
             K, N = dims[li], dims[li + 1]
             n = N // world
-            rng = np.random.default_rng(seed * 100 + li * 10 + 1)
             # the rank's rows of W: generated shard by shard so no rank ever holds the full matrix
             rng = np.random.default_rng([seed, li, rank])
             W = rng.standard_normal((n, K), dtype=np.float32) * np.float32(0.02)
@@ -46,29 +53,51 @@ class ShardedInt8MLP:
             self.layers.append(dict(K=K, N=N, n=n, Wq=dQ, sw=dS, bias=dev.to_device(b),
                                     Y=dev.zeros((tokens, n)), amax=dev.zeros(tokens),
                                     q_local=dev.zeros((tokens, n), np.int8),
-                                    q_all=dev.zeros((world, tokens, n), np.int8), sa=dev.zeros(tokens)))
+                                    # per row block: the gathered shards [world][Mc][n]
+                                    q_all=dev.zeros((self.C, world, self.Mc, n), np.int8), sa=dev.zeros(tokens)))
         self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
 
     def forward(self, dX):
-        dev, M, R = self.dev, self.M, self.R
+        dev, M, R, C, Mc = self.dev, self.M, self.R, self.C, self.Mc
         dev.quant_rows_i8(dX, M, self.dims[0], self.q_in, self.sa_in)  # replicated input
-        aq, sa, shards = self.q_in, self.sa_in, 1
+        # per row block: where its quantised activations live and in how many column shards
+        aq = [self.q_in.ptr + c * Mc * self.dims[0] for c in range(C)]
+        sa = [self.sa_in.ptr + 4 * c * Mc for c in range(C)]
+        shards = 1
+        issued = waited = 0          # collectives enqueued / covered by a comm_wait so far
+        gathered_at = [0] * C        # sequence number of the block's last all-gather
         for li, L in enumerate(self.layers):
             last = li + 1 == len(self.layers)
-            dev.linear_i8_fwd_sharded_a(aq, shards, sa, L["Wq"], L["sw"], L["bias"], L["Y"], M, L["n"], L["K"],
-                                        relu=not last)
-            if last:
-                break
-            dev.row_absmax_f32(L["Y"], M, L["n"], L["amax"])
-            if R > 1:
-                dev.allreduce_max_f32_async(L["amax"], M)
-                dev.comm_wait()
-                dev.quant_rows_i8(L["Y"], M, L["n"], L["q_local"], L["sa"], L["amax"])
-                dev.allgather_async(L["q_local"], L["q_all"], M * L["n"])
-                dev.comm_wait()
-            else:
-                dev.quant_rows_i8(L["Y"], M, L["n"], L["q_all"], L["sa"], L["amax"])
-            aq, sa, shards = L["q_all"], L["sa"], R
+            n, K = L["n"], L["K"]
+            for c in range(C):
+                if gathered_at[c] > waited:  # the block's codes must have arrived
+                    dev.comm_wait()
+                    waited = issued
+                y = L["Y"].ptr + 4 * c * Mc * n
+                dev.linear_i8_fwd_sharded_a(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K,
+                                            relu=not last)
+                if last:
+                    continue
+                amax = L["amax"].ptr + 4 * c * Mc
+                sa_out = L["sa"].ptr + 4 * c * Mc
+                q_all = L["q_all"].ptr + c * R * Mc * n
+                dev.row_absmax_f32(y, Mc, n, amax)
+                if R > 1:
+                    q_loc = L["q_local"].ptr + c * Mc * n
+                    dev.allreduce_max_f32_async(amax, Mc)
+                    issued += 1
+                    dev.comm_wait()
+                    waited = issued
+                    dev.quant_rows_i8(y, Mc, n, q_loc, sa_out, amax)
+                    dev.allgather_async(q_loc, q_all, Mc * n)
+                    issued += 1
+                    gathered_at[c] = issued
+                else:
+                    dev.quant_rows_i8(y, Mc, n, q_all, sa_out, amax)
+                aq[c], sa[c] = q_all, sa_out
+            shards = R
+        if issued > waited:
+            dev.comm_wait()
         return self.layers[-1]["Y"]
 
 

@@ -79,3 +79,24 @@ def test_sharded_a_argument_errors(dev):
         dev.linear_i8_fwd_sharded_a(q, 3, s, q, s, None, y, 64, 64, 256)   # 256 does not split in 3
     with pytest.raises(VtlbError):
         dev.linear_i8_fwd_sharded_a(q, 4, s, q, s, None, y, 64, 64, 256)   # shards of 64 columns
+
+
+def test_row_block_pipeline_of_the_benchmark_model(dev, orc):
+    """bench_infer.ShardedInt8MLP walks the tokens as independent row blocks (that is what lets
+    the all-gather of one block overlap the GEMM of the next on several GPUs).  One rank, four
+    blocks: same result as the oracle run on all rows at once."""
+    import bench_infer
+    dims, tokens, seed = [256, 512, 256], 512, 5
+    model = bench_infer.ShardedInt8MLP(dev, 1, 0, tokens=tokens, dims=dims, seed=seed, chunks=4)
+    X = np.random.default_rng(9).standard_normal((tokens, dims[0])).astype(np.float32)
+    dX = dev.to_device(X)
+    y = model.forward(dX)
+    dev.sync()
+    assert dev.check_status() == 0
+    Ws, bs = [], []
+    for li in range(len(dims) - 1):
+        rng = np.random.default_rng([seed, li, 0])
+        Ws.append(rng.standard_normal((dims[li + 1], dims[li]), dtype=np.float32) * np.float32(0.02))
+        bs.append(rng.standard_normal(dims[li + 1], dtype=np.float32) * np.float32(0.01))
+    ref = oracle_mlp(orc, X, Ws, bs)
+    assert np.array_equal(y.numpy().view(np.uint32), ref.view(np.uint32))
