@@ -12,6 +12,7 @@ The last layer's output stays sharded.  Strong scaling: the total work is fixed.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import time
 
 import numpy as np
@@ -34,7 +35,7 @@ class ShardedInt8MLP:
 
     def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5, chunks=None):
         self.dev, self.R, self.rank, self.M, self.dims = dev, world, rank, tokens, dims
-        self.C = chunks if chunks else (4 if world > 1 else 1)
+        self.C = chunks if chunks else (int(os.environ.get("VTLB_C5_ROW_BLOCKS", "2")) if world > 1 else 1)
         assert tokens % self.C == 0
         self.Mc = tokens // self.C
         self.layers = []
