@@ -85,6 +85,58 @@ __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const float* __restr
   }
 }
 
+// Rows of at most 1024 * VPT elements with K % 4 == 0: every thread keeps its part of the row
+// in registers (VPT coalesced float4 loads issued back to back), so the row is read exactly
+// once from memory and the quantising pass costs no memory reads at all.
+template <int VPT, bool HAVE_AMAX>
+__global__ void __launch_bounds__(256) quant_rows_i8_reg_kernel(const float* __restrict__ A, int M, int K,
+                                                                int ldq, int8_t* __restrict__ Q,
+                                                                float* __restrict__ scale,
+                                                                const float* __restrict__ amax_in) {
+  __shared__ float s_part[8];
+  __shared__ float s_amax;
+  const int row = blockIdx.x;
+  const float4* a4 = reinterpret_cast<const float4*>(A + (size_t)row * K);
+  const int n4 = K >> 2;
+  float4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + 256 * i;
+    v[i] = idx < n4 ? __ldcs(a4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float amax;
+  if (HAVE_AMAX) {
+    amax = amax_in[row];
+  } else {
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < 8 ? s_part[threadIdx.x] : 0.0f;
+      t = warp_max(t);
+      if (threadIdx.x == 0) s_amax = t;
+    }
+    __syncthreads();
+    amax = s_amax;
+  }
+  const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+  if (threadIdx.x == 0) scale[row] = __fdiv_rn(amax, 127.0f);
+  int* q4 = reinterpret_cast<int*>(Q + (size_t)row * ldq);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + 256 * i;
+    if (idx < n4) {
+      const int b0 = quant1(v[i].x, inv), b1 = quant1(v[i].y, inv), b2 = quant1(v[i].z, inv),
+                b3 = quant1(v[i].w, inv);
+      q4[idx] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | ((b3 & 0xff) << 24);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) row_absmax_kernel(const float* __restrict__ A, int M, int K,
                                                          float* __restrict__ amax) {
   __shared__ float s_part[8];
@@ -393,6 +445,24 @@ VTLB_API int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, vo
   if (!d_A || !d_Q || !d_scale) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: null pointer");
   if (!vtlb_aligned16(d_Q)) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: Q not 16-byte aligned");
   const int ldq = vtlb_i8_ld(K);
+  if ((K & 3) == 0 && K <= 8192 && vtlb_aligned16(d_A)) {  // register-resident rows
+    const float* A = (const float*)d_A;
+    int8_t* Q = (int8_t*)d_Q;
+    float* sc = (float*)d_scale;
+    const float* am = (const float*)d_amax_in_or_null;
+#define VTLB_QREG(VPT)                                                                            \
+  do {                                                                                            \
+    if (am) quant_rows_i8_reg_kernel<VPT, true><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);  \
+    else quant_rows_i8_reg_kernel<VPT, false><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);    \
+  } while (0)
+    if (K <= 1024) VTLB_QREG(1);
+    else if (K <= 2048) VTLB_QREG(2);
+    else if (K <= 4096) VTLB_QREG(4);
+    else VTLB_QREG(8);
+#undef VTLB_QREG
+    VTLB_LAUNCHED(ctx);
+    return VTLB_OK;
+  }
   if (d_amax_in_or_null)
     quant_rows_i8_kernel<true><<<M, 256, 0, ctx->stream>>>((const float*)d_A, M, K, ldq,
                                                            (int8_t*)d_Q, (float*)d_scale,
