@@ -63,6 +63,9 @@ SHAPES = [
     (17, 64, 32), (128, 256, 128), (128, 64, 4096),        # one tile, each tile width
     (200, 328, 400), (129, 257, 144),                      # ragged M, N, K
     (512, 1024, 512), (1024, 4096, 1024),
+    # more 256 x 256 tiles than CTA pairs with a short final wave: its tiles are cut along K
+    # between two pairs (90 tiles and 256 tiles on 74 pairs)
+    (2500, 2100, 1100), (4096, 4096, 1024), (2304, 2302, 1024),
 ]
 
 
@@ -86,6 +89,7 @@ def test_gemm_i8_i32_bit_exact(dev, orc, M, N, K):
 @pytest.mark.parametrize("M,N,K,relu,bias", [
     (1, 256, 512, True, True), (16, 300, 128, False, True),
     (128, 256, 256, True, True), (300, 500, 272, True, False), (512, 512, 1024, False, True),
+    (2304, 2300, 1024, True, True),  # K-split final wave through the fused epilogue
 ])
 def test_linear_i8_fwd_matches_oracle(dev, orc, M, N, K, relu, bias):
     rng = np.random.default_rng(M + N + K)

@@ -24,6 +24,10 @@ struct vtlb_ctx {
   uint32_t* d_status = nullptr;        // device status word
   void* scratch = nullptr;             // operand-split buffers, partial sums
   size_t scratch_bytes = 0;
+  // INT8 pair GEMM, K-split final wave: flags + parked accumulators (allocated on first use);
+  // every launch that splits stamps its flags with a fresh epoch, so nothing is ever reset.
+  void* ksplit_buf = nullptr;
+  uint32_t ksplit_epoch = 0;
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
   uint64_t launches = 0;

@@ -84,6 +84,7 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->ksplit_buf) cudaFree(ctx->ksplit_buf);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->ev_compute) cudaEventDestroy(ctx->ev_compute);
   if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);

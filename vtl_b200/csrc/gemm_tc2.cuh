@@ -128,10 +128,54 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
       : "memory");
 }
 
+// Scratch of the K-split tiles (see the kernel): flags first, then the parked accumulators.
+constexpr int KSPLIT_MAX_TILES = 64;  // at most half of the CTA pairs of a device
+constexpr int KSPLIT_FLAG_WORDS = KSPLIT_MAX_TILES * 2 * gemm::EPI_WARPS;  // [tile][rank][warp]
+constexpr size_t KSPLIT_BYTES = (size_t)KSPLIT_FLAG_WORDS * 4 + (size_t)KSPLIT_MAX_TILES * 2 * BM * BN2 * 4;
+
+__device__ __forceinline__ void flag_release(uint32_t* flag, uint32_t value) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+// Spins until *flag == value; gives up after limit_ns or when the CTA's abort flag is raised
+// (and raises it), like the mbarrier waits.
+__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t value,
+                                                  volatile uint32_t* abort_flag, uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (seen == value) return true;
+    if ((spins & 63u) == 63u) {
+      if (*abort_flag) return false;
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+#ifdef VTLB_PAIR_TRACE
+// Tuning aid: cycles each role of a CTA spent waiting, [cta][slot]
+//   0 producer total, 1 producer waiting for empty slots, 2 MMA total, 3 MMA waiting for operands,
+//   4 MMA waiting for a free accumulator, 5 epilogue warp 2 total, 6 its wait for accumulators,
+//   7 cycle at which epilogue warp 2 finished the CTA's first unit
+//   8.. cycle (since the MMA thread started) at which its i-th unit had all MMAs issued
+static __device__ long long g_pair_trace[160][16];
+#define VTLB_TR(...) __VA_ARGS__
+#else
+#define VTLB_TR(...)
+#endif
+
 template <int KIND, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M, int N, int K,
-                 int group_m, int a_chunk_k, uint32_t* status) {
+                 int group_m, int a_chunk_k, int split_tiles, uint32_t* ksplit_buf, uint32_t ksplit_epoch,
+                 uint32_t* status) {
   using T = gemm::Traits<KIND>;
   using C = Cfg<KIND>;
   constexpr int NOP = C::NOP, STAGES = C::STAGES;
@@ -157,6 +201,52 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
   const int chunk_kb = C::CHUNK_KB ? C::CHUNK_KB : num_kb;
+  // Work units.  When the tiles do not fill the last wave of CTA pairs, `split_tiles` tiles (the
+  // first ones) are cut along K into two units each, which evens out the work per pair (4096^3:
+  // 256 tiles on 74 pairs = 3.46 waves; with 34 tiles cut, 68 pairs run 3.5 tiles' worth and 6
+  // pairs run 3).  Pair 2s runs the first K half of cut tile s as its FIRST unit, parks the raw
+  // int32 accumulators in `ksplit_buf` and publishes one flag per epilogue warp; pair 2s+1 runs
+  // the second half as its SECOND unit (after a full tile), adds the parked values to its own and
+  // does the epilogue proper.  By then the parked half has long landed, and the slower epilogue of
+  // that one unit hides behind the MMAs of the next.  Integer addition keeps the result
+  // bit-identical.  INT8 only.  The first-half unit never waits for anybody and has the lower CTA
+  // numbers, which are dispatched first: the second-half unit's (bounded) wait cannot deadlock.
+  //
+  // Unit `it` of this pair: false when the pair has run out of work.  Full tiles fill every
+  // position that is not a half unit, in order of (it, pair).
+  auto decode_unit = [&](int it, int& tmi, int& tni, int& k_half, int& slot) -> bool {
+    const int S = split_tiles, P = num_pairs, p = pair;
+    const bool cut = p < 2 * S;
+    k_half = -1;
+    slot = 0;
+    int f;  // index among the full tiles
+    if (it == 0) {
+      if (cut && (p & 1) == 0) {
+        k_half = 0;
+        slot = p >> 1;
+      }
+      f = cut ? (p >> 1) : p - S;
+    } else if (it == 1) {
+      if (cut && (p & 1) == 1) {
+        k_half = 1;
+        slot = p >> 1;
+      }
+      f = (P - S) + (cut ? (p >> 1) : p - S);
+    } else {
+      f = 2 * (P - S) + (it - 2) * P + p;
+    }
+    int tile = slot;
+    if (k_half < 0) {
+      if (f >= num_tiles - S) return false;
+      tile = S + f;
+    }
+    gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
+    return true;
+  };
+  auto k_range = [&](int k_half, int& kb_begin, int& kb_end) {
+    kb_begin = k_half == 1 ? num_kb / 2 : 0;
+    kb_end = k_half == 0 ? num_kb / 2 : num_kb;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -190,16 +280,20 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int tmi, tni;
-        gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
+      VTLB_TR(long long tr_w = 0; const long long tr_0 = clock64();)
+      for (int it = 0; ok; ++it) {
+        int tmi, tni, kh, slot, kb_begin, kb_end;
+        if (!decode_unit(it, tmi, tni, kh, slot)) break;
+        k_range(kh, kb_begin, kb_end);
         const int m0 = tmi * 2 * BM + (int)rank * BM;
         const int n0 = tni * BN2 + (int)rank * (BN2 / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          VTLB_TR(const long long tr_a = clock64();)
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
+          VTLB_TR(tr_w += clock64() - tr_a;)
           const uint32_t leader_full = mapa(full_bar(stage), 0);
           if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE);
           const uint32_t sa = base + stage * C::STAGE;
@@ -221,26 +315,35 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           }
         }
       }
+      VTLB_TR(g_pair_trace[blockIdx.x][0] = clock64() - tr_0; g_pair_trace[blockIdx.x][1] = tr_w;)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
-          const int kb1 = kb0 + chunk_kb < num_kb ? kb0 + chunk_kb : num_kb;
+      VTLB_TR(long long tr_f = 0, tr_e = 0; const long long tr_0 = clock64();)
+      for (int it = 0; ok; ++it) {
+        int tmi, tni, kh, slot, kb_begin, kb_end;
+        if (!decode_unit(it, tmi, tni, kh, slot)) break;
+        k_range(kh, kb_begin, kb_end);
+        for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += chunk_kb) {
+          const int kb1 = kb0 + chunk_kb < kb_end ? kb0 + chunk_kb : kb_end;
+          VTLB_TR(const long long tr_a = clock64();)
           if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
+          VTLB_TR(tr_e += clock64() - tr_a;)
           ptx::tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN2;
           for (int kb = kb0; kb < kb1; ++kb) {
+            VTLB_TR(const long long tr_b = clock64();)
             if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
               ok = false;
               break;
             }
+            VTLB_TR(tr_f += clock64() - tr_b;)
             ptx::tc_fence_after();
             const uint32_t sa = base + stage * C::STAGE;
             const uint32_t sb = sa + NOP * C::A_TILE;
@@ -272,7 +375,10 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           acc ^= 1u;
           if (acc == 0) acc_phase ^= 1u;
         }
+        VTLB_TR(if (it < 8) g_pair_trace[blockIdx.x][8 + it] = clock64() - tr_0;)
       }
+      VTLB_TR(g_pair_trace[blockIdx.x][2] = clock64() - tr_0; g_pair_trace[blockIdx.x][3] = tr_f;
+              g_pair_trace[blockIdx.x][4] = tr_e;)
     }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
@@ -282,27 +388,78 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      int tmi, tni;
-      gemm::decode_tile(tile, tiles_m, tiles_n, group_m, tmi, tni);
-      const int m0 = tmi * 2 * BM + (int)rank * BM, n0 = tni * BN2;
+    VTLB_TR(long long tr_w = 0; const long long tr_0 = clock64();)
+    for (int it = 0; ok; ++it) {
+      int tmi, tni, kh, slot;
+      if (!decode_unit(it, tmi, tni, kh, slot)) break;
+      const int m0 = tmi * 2 * BM + (int)rank * BM;
+      const int n0 = tni * BN2;
       const int row0 = m0 + q * 32;
       if constexpr (KIND == gemm::KIND_I8) {
+        // Per-row and per-column operands of the epilogue (scales, bias) are fetched before the
+        // wait for the accumulator, one column per lane, and handed round by shuffles later:
+        // their latency would otherwise sit in front of every 32-column chunk.
+        const bool fast = epi.tma != 0;
+        typename Epi::Pre pre;
+        if (fast) pre = epi.prefetch(row0 + lane, n0 + half * 32 + lane, M, N);
+        VTLB_TR(const long long tr_a = clock64();)
         ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        VTLB_TR(tr_w += clock64() - tr_a;)
         ptx::tc_fence_after();
-#pragma unroll 1
-        for (int c = half; c < BN2 / 32; c += 2) {
+        // K-split tile: the unit of the first K half parks its accumulators,
+        // [slot][rank][warp][chunk][value][lane], and the unit of the second half adds them to its own.
+        const int wslot = (slot * 2 + (int)rank) * gemm::EPI_WARPS + (warp - 2);
+        uint32_t* park = ksplit_buf + KSPLIT_FLAG_WORDS + (size_t)wslot * (BN2 / 64) * 1024;
+        if (kh == 1) {  // wait for the first K half of this tile
+          if (lane == 0) ok = flag_wait_bounded(ksplit_buf + wslot, ksplit_epoch, abort_flag, WAIT_LIMIT_NS);
+          ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, (int)ok, 0) != 0);
+          if (!ok) break;
+        }
+        auto do_chunk = [&](int cc, bool use_pre) {
+          const int c = 2 * cc + half;
           uint32_t v[32];
+          VTLB_TR(const long long tr_l = clock64();)
           ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
           ptx::tmem_wait_ld();
-          gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
+          VTLB_TR(if (threadIdx.x == 64) gemm::g_epi_trace[blockIdx.x][0] += clock64() - tr_l;)
+          uint32_t* pc = park + cc * 1024 + lane;
+          if (kh == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(pc + j * 32, v[j]);
+          } else {
+            if (kh == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __ldcg(pc + j * 32);
+            }
+            if (use_pre) {
+              VTLB_TR(const long long tr_t = clock64();)
+              epi.transform_pre(pre, cc, v);
+              VTLB_TR(if (threadIdx.x == 64) gemm::g_epi_trace[blockIdx.x][1] += clock64() - tr_t;)
+              gemm::stage_and_store(stg, &tm.out[0], lane, row0, n0 + c * 32, v, M, N);
+            } else {
+              gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
+            }
+          }
           __syncwarp();
+        };
+        if (fast) {
+#pragma unroll
+          for (int cc = 0; cc < BN2 / 64; ++cc) do_chunk(cc, true);
+        } else {
+#pragma unroll 1
+          for (int cc = 0; cc < BN2 / 64; ++cc) do_chunk(cc, false);
         }
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+        if (kh == 0) {  // publish: every lane's stores, then the flag
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) flag_release(ksplit_buf + wslot, ksplit_epoch);
+        }
+        VTLB_TR(if (warp == 2 && lane == 0 && it == 0) g_pair_trace[blockIdx.x][7] = clock64() - tr_0;)
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       } else {
@@ -339,6 +496,10 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         }
       }
     }
+    VTLB_TR(if (warp == 2 && lane == 0) {
+      g_pair_trace[blockIdx.x][5] = clock64() - tr_0;
+      g_pair_trace[blockIdx.x][6] = tr_w;
+    })
   }
 
   // ------------------------------------------------------------ teardown
@@ -365,7 +526,7 @@ inline bool pair_worthwhile(vtlb_ctx* ctx, int M, int N) {
 
 template <int KIND, class Epi>
 int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, int N, int K,
-                int a_chunk_k = 0) {
+                int a_chunk_k = 0, bool k_split = false) {
   using C = Cfg<KIND>;
   static_assert(C::SMEM_TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_pair_kernel<KIND, Epi>;
@@ -381,7 +542,21 @@ int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, i
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
   const int group_m = gemm::pick_group_m((M + 2 * BM - 1) / (2 * BM),
                                          (size_t)2 * BM * K * gemm::Traits<KIND>::ELEM * C::NOP);
-  kern<<<2 * pairs, NUM_THREADS, C::SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k,
+  // When the final wave would fill at most half of the pairs, cut that many tiles into two half-K
+  // units each (INT8 only: integer partial sums add up exactly); they all fit in the first wave.
+  int split_tiles = 0;
+  if (KIND == gemm::KIND_I8 && k_split) {
+    const int rem = tiles % pairs;
+    const int num_kb = (K + 127) / 128;
+    if (tiles > pairs && rem > 0 && 2 * rem <= pairs && rem <= KSPLIT_MAX_TILES && num_kb >= 8) split_tiles = rem;
+  }
+  if (split_tiles && !ctx->ksplit_buf) {
+    VTLB_CUDA(ctx, cudaMalloc(&ctx->ksplit_buf, KSPLIT_BYTES));
+    VTLB_CUDA(ctx, cudaMemsetAsync(ctx->ksplit_buf, 0, (size_t)KSPLIT_FLAG_WORDS * 4, ctx->stream));
+  }
+  if (split_tiles && ++ctx->ksplit_epoch == 0) ctx->ksplit_epoch = 1;  // flags hold the epoch of their launch
+  kern<<<2 * pairs, NUM_THREADS, C::SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k, split_tiles,
+                                                               (uint32_t*)ctx->ksplit_buf, ctx->ksplit_epoch,
                                                                ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);

@@ -163,6 +163,9 @@ struct EpiStoreI32 {
   int tma;  // store through the output tensor map (tm.out[0]) instead of per-thread stores
   __device__ __forceinline__ bool transform(int, int, uint32_t (&)[32], int, int) const { return false; }
   __device__ __forceinline__ void activate(uint32_t (&)[32]) const {}
+  struct Pre {};  // nothing to fetch ahead of the accumulator
+  __device__ __forceinline__ Pre prefetch(int, int, int, int) const { return Pre{}; }
+  __device__ __forceinline__ void transform_pre(const Pre&, int, uint32_t (&)[32]) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
@@ -220,6 +223,33 @@ struct EpiDequant {
     return false;
   }
   __device__ __forceinline__ void activate(uint32_t (&)[32]) const {}
+  // The same dequantisation with its operands fetched ahead (CTA-pair kernel): this lane's row
+  // scale, and for each of the warp's four 32-column chunks (64 columns apart) the weight scale
+  // and bias of ONE column, `col` being this lane's column in the first chunk.
+  struct Pre {
+    float s;
+    float w[4], b[4];
+  };
+  __device__ __forceinline__ Pre prefetch(int row, int col, int M, int N) const {
+    Pre p;
+    p.s = row < M ? __ldg(sa + row) : 0.0f;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c = col + cc * 64;
+      p.w[cc] = c < N ? __ldg(sw + c) : 0.0f;
+      p.b[cc] = (bias != nullptr && c < N) ? __ldg(bias + c) : 0.0f;
+    }
+    return p;
+  }
+  __device__ __forceinline__ void transform_pre(const Pre& p, int cc, uint32_t (&v)[32]) const {
+    const bool hb = bias != nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float w = __shfl_sync(0xffffffffu, p.w[cc], j);
+      const float b = __shfl_sync(0xffffffffu, p.b[cc], j);
+      v[j] = __float_as_uint(dequant1(v[j], p.s, w, b, hb, relu));
+    }
+  }
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
@@ -421,7 +451,14 @@ int run_i8(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, E
       return rc;
     tm.a[1] = tm.a[0];
   }
-  if (pair) return gemm2::launch_pair<gemm::KIND_I8, Epi>(ctx, tm, epi, M, N, K, chunk_k);
+  if (pair) {
+    static int k_split = -1;
+    if (k_split < 0) {
+      const char* e = getenv("VTLB_I8_K_SPLIT");
+      k_split = e ? atoi(e) : 1;
+    }
+    return gemm2::launch_pair<gemm::KIND_I8, Epi>(ctx, tm, epi, M, N, K, chunk_k, k_split != 0);
+  }
   if (bn == 256) return gemm::launch<gemm::KIND_I8, 256, 4, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
   if (bn == 128) return gemm::launch<gemm::KIND_I8, 128, 6, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
   return gemm::launch<gemm::KIND_I8, 64, 8, Epi>(ctx, tm, epi, M, N, K, 1, chunk_k);
@@ -541,3 +578,16 @@ VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards
   EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, N, relu};
   return run_i8(ctx, d_Aq_shards, d_Wq, M, N, K, epi, d_Y, shards);
 }
+
+#ifdef VTLB_PAIR_TRACE
+// Tuning aid (not part of the C ABI): copies the wait-cycle counters of the last INT8 pair-kernel launch.
+VTLB_API int vtlb_debug_pair_trace(vtlb_ctx* ctx, long long* out) {
+  VTLB_ENTER(ctx);
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  VTLB_CUDA(ctx, cudaMemcpyFromSymbol(out, gemm2::g_pair_trace, sizeof(gemm2::g_pair_trace)));
+  VTLB_CUDA(ctx, cudaMemcpyFromSymbol(out + 160 * 16, gemm::g_epi_trace, sizeof(gemm::g_epi_trace)));
+  static long long zeros[160 * 8];
+  VTLB_CUDA(ctx, cudaMemcpyToSymbol(gemm::g_epi_trace, zeros, sizeof(zeros)));
+  return VTLB_OK;
+}
+#endif
