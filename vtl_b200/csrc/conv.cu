@@ -9,7 +9,7 @@
 // weight tensor's own (ic, kh, kw) order so the weights need no re-layout:
 //   forward : y[(b,oh,ow), oc] = col[(b,oh,ow), k] . W[oc, k]^T + bias[oc]
 //   d_weight: dW[oc, k]        = gT[oc, m] . colT[k, m]^T      (split-K over m = (b,oh,ow))
-//   d_input : dcol[m, k]       = gM[m, oc] . Wt[k, oc]^T, then a col2im gather
+//   d_input : dcolT[k, m]      = Wt[k, oc] . gM[m, oc]^T, then a col2im gather
 //   d_bias  : per-channel sums of g (f64 partials)
 #include "f32_common.cuh"
 
@@ -24,85 +24,140 @@ struct ConvDims {
   __host__ __device__ long long M() const { return (long long)B * OH * OW; }
 };
 
-// value of the im2col matrix at (m, k); zero in the padding
-__device__ __forceinline__ float im2col_at(const float* __restrict__ x, const ConvDims& d, long long m, int k) {
-  const int P = d.OH * d.OW;
-  const int b = (int)(m / P), p = (int)(m - (long long)b * P);
-  const int oh = p / d.OW, ow = p - oh * d.OW;
-  const int ic = k / (d.kh * d.kw), r = k - ic * d.kh * d.kw;
-  const int kh = r / d.kw, kw = r - kh * d.kw;
-  const int ih = oh * d.sh - d.ph + kh, iw = ow * d.sw - d.pw + kw;
-  if (ih < 0 || ih >= d.H || iw < 0 || iw >= d.W) return 0.0f;
-  return x[(((size_t)b * d.C + ic) * d.H + ih) * d.W + iw];
-}
-
-// colT planes [K, ld >= M]: consecutive threads take consecutive m, so the reads of x and the
-// writes are both (nearly) contiguous.
+// colT planes [K, ld >= M]: one row k = (ic, kh, kw) per blockIdx.y, so the decomposition of k
+// costs nothing per element; a thread produces four consecutive m (one 16-byte store per plane)
+// and walks (b, oh, ow) incrementally.  All index arithmetic is 32-bit (M < 2^31 is checked).
 __global__ void __launch_bounds__(256) im2colT_split_kernel(const float* __restrict__ x, ConvDims d, int ld,
                                                             float* __restrict__ hi, float* __restrict__ lo) {
-  const long long M = d.M();
-  const long long n = M * d.K();
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int k = (int)(i / M);
-    const long long m = i - (long long)k * M;
-    float h, l;
-    split1(im2col_at(x, d, m, k), h, l);
-    hi[(size_t)k * ld + m] = h;
-    lo[(size_t)k * ld + m] = l;
+  const int M = (int)d.M(), K = d.K(), P = d.OH * d.OW, khw = d.kh * d.kw;
+  const bool vec = (ld & 3) == 0;
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const int ic = k / khw, r = k - ic * khw;
+    const int kh = r / d.kw, kw = r - kh * d.kw;
+    float* hrow = hi + (size_t)k * ld;
+    float* lrow = lo + (size_t)k * ld;
+    for (int m4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4; m4 < M; m4 += gridDim.x * blockDim.x * 4) {
+      int b = m4 / P;
+      const int p = m4 - b * P;
+      int oh = p / d.OW, ow = p - oh * d.OW;
+      float h[4], l[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = 0.0f;
+        const int ih = oh * d.sh - d.ph + kh, iw = ow * d.sw - d.pw + kw;
+        if (m4 + j < M && ih >= 0 && ih < d.H && iw >= 0 && iw < d.W)
+          v = __ldg(x + (((size_t)b * d.C + ic) * d.H + ih) * d.W + iw);
+        split1(v, h[j], l[j]);
+        if (++ow == d.OW) {
+          ow = 0;
+          if (++oh == d.OH) {
+            oh = 0;
+            ++b;
+          }
+        }
+      }
+      if (vec && m4 + 3 < M) {
+        *reinterpret_cast<float4*>(hrow + m4) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lrow + m4) = make_float4(l[0], l[1], l[2], l[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (m4 + j < M) {
+            hrow[m4 + j] = h[j];
+            lrow[m4 + j] = l[j];
+          }
+      }
+    }
   }
 }
 
-// col planes [M, ld >= K]: 32x32 tiles through shared memory (read along m, write along k).
+// col planes [M, ld >= K]: 32 x 32 tiles through shared memory (read along m, write along k).
+// blockIdx.y picks the 32 columns k, whose (ic, kh, kw) are worked out once per block.
 __global__ void __launch_bounds__(256) im2col_split_kernel(const float* __restrict__ x, ConvDims d, int ld,
                                                            float* __restrict__ hi, float* __restrict__ lo) {
   __shared__ float tile[32][33];
-  const long long M = d.M();
-  const int K = d.K();
-  const long long tiles_m = (M + 31) / 32;
-  const int tiles_k = (K + 31) / 32;
-  const long long ntiles = tiles_m * tiles_k;
+  __shared__ int k_off[32], k_h[32], k_w[32];  // offset of (ic, kh, kw) inside an image; -1: k >= K
+  const int M = (int)d.M(), K = d.K(), P = d.OH * d.OW, khw = d.kh * d.kw;
+  const int tiles_m = (M + 31) / 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const long long m0 = (t / tiles_k) * 32;
-    const int k0 = (int)(t % tiles_k) * 32;
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const int k = k0 + ty + j;
-      const long long m = m0 + tx;
-      tile[ty + j][tx] = (k < K && m < M) ? im2col_at(x, d, m, k) : 0.0f;
-    }
+  for (int k0 = blockIdx.y * 32; k0 < K; k0 += gridDim.y * 32) {
     __syncthreads();
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      const long long m = m0 + ty + j;
-      const int k = k0 + tx;
-      if (m < M && k < K) {
-        float h, l;
-        split1(tile[tx][ty + j], h, l);
-        hi[(size_t)m * ld + k] = h;
-        lo[(size_t)m * ld + k] = l;
+    if (threadIdx.x < 32) {
+      const int k = k0 + threadIdx.x;
+      if (k < K) {
+        const int ic = k / khw, r = k - ic * khw;
+        const int kh = r / d.kw, kw = r - kh * d.kw;
+        k_off[threadIdx.x] = (ic * d.H + kh) * d.W + kw;
+        k_h[threadIdx.x] = kh;
+        k_w[threadIdx.x] = kw;
+      } else {
+        k_off[threadIdx.x] = -1;
+        k_h[threadIdx.x] = 0;
+        k_w[threadIdx.x] = 0;
       }
     }
     __syncthreads();
+    for (int t = blockIdx.x; t < tiles_m; t += gridDim.x) {
+      const int m0 = t * 32;
+      const int m = m0 + tx;
+      const int b = m / P, p = m - b * P;
+      const int oh = p / d.OW, ow = p - oh * d.OW;
+      const int ih0 = oh * d.sh - d.ph, iw0 = ow * d.sw - d.pw;
+      const long long xb = ((long long)b * d.C * d.H + ih0) * d.W + iw0;  // + k_off: inside x whenever in bounds
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        const int kk = ty + j;
+        const int ih = ih0 + k_h[kk], iw = iw0 + k_w[kk];
+        float v = 0.0f;
+        if (m < M && k_off[kk] >= 0 && ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) v = __ldg(x + (xb + k_off[kk]));
+        tile[kk][tx] = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        const int mo = m0 + ty + j;
+        const int k = k0 + tx;
+        if (mo < M && k < K) {
+          float h, l;
+          split1(tile[tx][ty + j], h, l);
+          hi[(size_t)mo * ld + k] = h;
+          lo[(size_t)mo * ld + k] = l;
+        }
+      }
+      __syncthreads();
+    }
   }
 }
 
 // g is NCHW [B, O, P].  gT planes [O, ld >= M]: gT[oc][b*P + p] = g[b][oc][p] (rows of P copied).
+// blockIdx.y walks the (b, oc) rows; four values per thread where the rows allow 16-byte accesses.
 __global__ void __launch_bounds__(256) grad_to_OM_split_kernel(const float* __restrict__ g, int B, int O, int P,
                                                                int ld, float* __restrict__ hi,
                                                                float* __restrict__ lo) {
-  const long long n = (long long)B * O * P;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int p = (int)(i % P);
-    const long long bo = i / P;
-    const int oc = (int)(bo % O), b = (int)(bo / O);
-    float h, l;
-    split1(g[i], h, l);
-    const size_t o = (size_t)oc * ld + (size_t)b * P + p;
-    hi[o] = h;
-    lo[o] = l;
+  const bool vec = (P & 3) == 0 && (ld & 3) == 0;
+  for (int row = blockIdx.y; row < B * O; row += gridDim.y) {
+    const int b = row / O, oc = row - b * O;
+    const float* src = g + (size_t)row * P;
+    const size_t o = (size_t)oc * ld + (size_t)b * P;
+    for (int p4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4; p4 < P; p4 += gridDim.x * blockDim.x * 4) {
+      if (vec) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src + p4));
+        float4 h, l;
+        split1(v.x, h.x, l.x);
+        split1(v.y, h.y, l.y);
+        split1(v.z, h.z, l.z);
+        split1(v.w, h.w, l.w);
+        *reinterpret_cast<float4*>(hi + o + p4) = h;
+        *reinterpret_cast<float4*>(lo + o + p4) = l;
+      } else {
+        for (int j = 0; j < 4 && p4 + j < P; ++j) {
+          float h, l;
+          split1(src[p4 + j], h, l);
+          hi[o + p4 + j] = h;
+          lo[o + p4 + j] = l;
+        }
+      }
+    }
   }
 }
 
@@ -139,34 +194,44 @@ __global__ void __launch_bounds__(256) grad_to_MO_split_kernel(const float* __re
   }
 }
 
-// dx[b, ic, ih, iw] = sum over (kh, kw) of dcol[(b, oh, ow), (ic, kh, kw)] where the window
-// position maps back onto (ih, iw); a gather, so no atomics and a fixed summation order.
-__global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restrict__ dcol, ConvDims d, int ldc,
+// dx[b, ic, ih, iw] = sum over (kh, kw) of dcolT[(ic, kh, kw), (b, oh, ow)] where the window
+// position maps back onto (ih, iw); a gather, so no atomics and a fixed summation order.  dcolT is
+// stored [K, ldm >= M]: consecutive threads (iw) read consecutive m.
+__global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restrict__ dcolT, ConvDims d, int ldm,
                                                             float* __restrict__ dx) {
-  const long long n = (long long)d.B * d.C * d.H * d.W;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int iw = (int)(i % d.W);
-    long long r = i / d.W;
-    const int ih = (int)(r % d.H);
-    r /= d.H;
-    const int ic = (int)(r % d.C), b = (int)(r / d.C);
-    float s = 0.0f;
-    for (int kh = 0; kh < d.kh; ++kh) {
-      const int th = ih + d.ph - kh;
-      if (th < 0 || th % d.sh) continue;
-      const int oh = th / d.sh;
-      if (oh >= d.OH) continue;
-      for (int kw = 0; kw < d.kw; ++kw) {
-        const int tw = iw + d.pw - kw;
-        if (tw < 0 || tw % d.sw) continue;
-        const int ow = tw / d.sw;
-        if (ow >= d.OW) continue;
-        const size_t m = ((size_t)b * d.OH + oh) * d.OW + ow;
-        s = __fadd_rn(s, dcol[m * ldc + (ic * d.kh + kh) * d.kw + kw]);
+  // blockIdx.y walks the (b, ic) planes, threads the H*W positions of a plane; 32-bit arithmetic
+  const int HW = d.H * d.W, khw = d.kh * d.kw;
+  const bool unit_stride = d.sh == 1 && d.sw == 1;
+  for (int plane = blockIdx.y; plane < d.B * d.C; plane += gridDim.y) {
+    const int b = plane / d.C, ic = plane - b * d.C;
+    const float* src = dcolT + (size_t)ic * khw * ldm + (size_t)b * d.OH * d.OW;
+    float* dst = dx + (size_t)plane * HW;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < HW; i += gridDim.x * blockDim.x) {
+      const int ih = i / d.W, iw = i - ih * d.W;
+      float s = 0.0f;
+      for (int kh = 0; kh < d.kh; ++kh) {
+        const int th = ih + d.ph - kh;
+        if (th < 0) continue;
+        int oh = th;
+        if (!unit_stride) {
+          if (th % d.sh) continue;
+          oh = th / d.sh;
+        }
+        if (oh >= d.OH) continue;
+        for (int kw = 0; kw < d.kw; ++kw) {
+          const int tw = iw + d.pw - kw;
+          if (tw < 0) continue;
+          int ow = tw;
+          if (!unit_stride) {
+            if (tw % d.sw) continue;
+            ow = tw / d.sw;
+          }
+          if (ow >= d.OW) continue;
+          s = __fadd_rn(s, __ldg(src + (size_t)(kh * d.kw + kw) * ldm + oh * d.OW + ow));
+        }
       }
+      dst[i] = s;
     }
-    dx[i] = s;
   }
 }
 
@@ -178,7 +243,19 @@ __global__ void __launch_bounds__(256) chan_sum_partial_kernel(const float* __re
   double acc = 0.0;
   for (int b = s; b < B; b += S) {
     const float* row = g + ((size_t)b * O + oc) * P;
-    for (int p = threadIdx.x; p < P; p += blockDim.x) acc += (double)row[p];
+    if ((P & 3) == 0) {  // rows start 16-byte aligned
+      double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+      for (int p = threadIdx.x * 4; p < P; p += blockDim.x * 4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(row + p));
+        a0 += (double)v.x;
+        a1 += (double)v.y;
+        a2 += (double)v.z;
+        a3 += (double)v.w;
+      }
+      acc += (a0 + a1) + (a2 + a3);
+    } else {
+      for (int p = threadIdx.x; p < P; p += blockDim.x) acc += (double)row[p];
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -231,13 +308,13 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
                                                           int32_t* __restrict__ idx, int B, int C, int H, int W,
                                                           int kh, int kw, int ph, int pw, int sh, int sw,
                                                           int OH, int OW) {
-  const long long n = (long long)B * C * OH * OW;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int w = (int)(i % OW);
-    long long r = i / OW;
-    const int h = (int)(r % OH);
-    const long long nc = r / OH;
+  // 32-bit arithmetic: the host checks B*C*H*W < 2^31
+  const int n = B * C * OH * OW;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int w = i % OW;
+    const int r = i / OW;
+    const int h = r % OH;
+    const int nc = r / OH;
     int hs = h * sh - ph, ws = w * sw - pw;
     int he = hs + kh, we = ws + kw;
     hs = max(hs, 0);
@@ -245,10 +322,10 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
     he = min(he, H);
     we = min(we, W);
     float best = -INFINITY;
-    long long bi = -1;
+    int bi = -1;
     for (int a = hs; a < he; ++a)
       for (int c = ws; c < we; ++c) {
-        const long long fi = (nc * H + a) * W + c;
+        const int fi = (nc * H + a) * W + c;
         const float val = x[fi];
         if (bi < 0 || val > best) {
           best = val;
@@ -256,7 +333,7 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
         }
       }
     y[i] = best;
-    idx[i] = (int32_t)bi;
+    idx[i] = bi;
   }
 }
 __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx,
@@ -274,7 +351,8 @@ int check_conv(vtlb_ctx* ctx, const char* fn, ConvDims& d) {
   d.OH = (d.H + 2 * d.ph - (d.kh - 1) - 1) / d.sh + 1;
   d.OW = (d.W + 2 * d.pw - (d.kw - 1) - 1) / d.sw + 1;
   if (d.OH <= 0 || d.OW <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "%s: empty output", fn);
-  if (d.M() > 0x7fffffffLL || d.M() * d.K() > (1LL << 40))
+  if (d.M() > 0x7fffffffLL || d.M() * d.K() > (1LL << 40) || (long long)d.B * d.O > 0x7fffffffLL ||
+      (long long)d.B * d.C * d.H * d.W > 0x7fffffffLL)
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: problem too large for the lowered GEMM", fn);
   return VTLB_OK;
 }
@@ -292,9 +370,12 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
   const int M = (int)d.M(), K = d.K();
   f32::Planes p;
   if ((rc = f32::alloc_planes(ctx, M, O, K, 0, &p))) return rc;
-  const long long tiles = ((long long)(M + 31) / 32) * ((K + 31) / 32);
-  im2col_split_kernel<<<f32::grid_for(ctx, (size_t)tiles, 1), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld,
-                                                                                    p.a_hi, p.a_lo);
+  {
+    const int ky = (K + 31) / 32 < 64 ? (K + 31) / 32 : 64;
+    int gx = (ctx->sm_count * 16 + ky - 1) / ky;
+    if (gx > (M + 31) / 32) gx = (M + 31) / 32;
+    im2col_split_kernel<<<dim3(gx, ky), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld, p.a_hi, p.a_lo);
+  }
   VTLB_LAUNCHED(ctx);
   if ((rc = f32::split_operand(ctx, (const float*)d_w, O, K, false, p.ld, p.b_hi, p.b_lo))) return rc;
   EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
@@ -320,11 +401,19 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     const int S = f32::effective_splits(M, want);
     f32::Planes p;
     if ((rc = f32::alloc_planes(ctx, O, K, M, (size_t)S * O * K * sizeof(float), &p))) return rc;
-    grad_to_OM_split_kernel<<<f32::grid_for(ctx, (size_t)B * O * P, 1024), 256, 0, ctx->stream>>>(g, B, O, P, p.ld,
-                                                                                                 p.a_hi, p.a_lo);
+    {
+      const long long rows = (long long)B * O;
+      grad_to_OM_split_kernel<<<dim3((P + 1023) / 1024, (unsigned)(rows < 32768 ? rows : 32768)), 256, 0,
+                                ctx->stream>>>(g, B, O, P, p.ld, p.a_hi, p.a_lo);
+    }
     VTLB_LAUNCHED(ctx);
-    im2colT_split_kernel<<<f32::grid_for(ctx, (size_t)M * K, 1024), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld,
-                                                                                          p.b_hi, p.b_lo);
+    {
+      const int ky = K < 4096 ? K : 4096;
+      int gx = (ctx->sm_count * 16 + ky - 1) / ky;
+      if (gx > (M + 1023) / 1024) gx = (M + 1023) / 1024;
+      if (gx < 1) gx = 1;
+      im2colT_split_kernel<<<dim3(gx, ky), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld, p.b_hi, p.b_lo);
+    }
     VTLB_LAUNCHED(ctx);
     if (S == 1) {
       f32::EpiBiasRelu epi{(float*)d_dw_or_null, nullptr, nullptr, K, 0};
@@ -336,20 +425,24 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
       if ((rc = f32::reduce_splits(ctx, (const float*)p.extra, S, (size_t)O * K, (float*)d_dw_or_null))) return rc;
     }
   }
-  if (d_dx_or_null) {  // dcol[m, k] = sum_oc g[m, oc] * W[oc, k]; dx = col2im(dcol)
+  if (d_dx_or_null) {  // dcolT[k, m] = sum_oc W[oc, k] * g[m, oc]; dx = col2im(dcolT)
     if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
-    const int ldc = (int)vtlb_round_up((size_t)K, 4);
+    const int ldm = (int)vtlb_round_up((size_t)M, 4);
     f32::Planes p;
-    if ((rc = f32::alloc_planes(ctx, M, K, O, (size_t)M * ldc * sizeof(float), &p))) return rc;
+    if ((rc = f32::alloc_planes(ctx, K, M, O, (size_t)K * ldm * sizeof(float), &p))) return rc;
+    if ((rc = f32::split_operand(ctx, (const float*)d_w, K, O, true, p.ld, p.a_hi, p.a_lo))) return rc;
     const long long tiles = (long long)B * ((O + 31) / 32) * ((P + 31) / 32);
-    grad_to_MO_split_kernel<<<f32::grid_for(ctx, (size_t)tiles, 1), 256, 0, ctx->stream>>>(g, B, O, P, p.ld, p.a_hi,
-                                                                                          p.a_lo);
+    grad_to_MO_split_kernel<<<f32::grid_for(ctx, (size_t)tiles, 1), 256, 0, ctx->stream>>>(g, B, O, P, p.ld, p.b_hi,
+                                                                                          p.b_lo);
     VTLB_LAUNCHED(ctx);
-    if ((rc = f32::split_operand(ctx, (const float*)d_w, K, O, true, p.ld, p.b_hi, p.b_lo))) return rc;
-    f32::EpiBiasRelu epi{(float*)p.extra, nullptr, nullptr, ldc, 0};
-    if ((rc = f32::launch_tf32x3(ctx, p, M, K, O, epi))) return rc;
-    col2im_gather_kernel<<<f32::grid_for(ctx, (size_t)B * C * H * W, 1024), 256, 0, ctx->stream>>>(
-        (const float*)p.extra, d, ldc, (float*)d_dx_or_null);
+    f32::EpiBiasRelu epi{(float*)p.extra, nullptr, nullptr, ldm, 0};
+    if ((rc = f32::launch_tf32x3(ctx, p, K, M, O, epi))) return rc;
+    {
+      const long long planes = (long long)B * C;
+      col2im_gather_kernel<<<dim3((H * W + 255) / 256 < 64 ? (H * W + 255) / 256 : 64,
+                                  (unsigned)(planes < 32768 ? planes : 32768)),
+                             256, 0, ctx->stream>>>((const float*)p.extra, d, ldm, (float*)d_dx_or_null);
+    }
     VTLB_LAUNCHED(ctx);
   }
   if (d_db_or_null) {

@@ -116,14 +116,29 @@ __global__ void __launch_bounds__(256) colsum_short_kernel(const float* __restri
   }
 }
 
+// out[i] = sum over splits of partial[k][i].  One element per thread; eight running sums per
+// element keep eight loads in flight (the order of the additions is fixed: split k goes to sum
+// k mod 8, the eight sums are combined pairwise at the end).
 __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial,
                                                             int splits, size_t n,
                                                             float* __restrict__ out) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x) {
-    float s = partial[i];
-    for (int k = 1; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * n + i]);
-    out[i] = s;
+    float s[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] = 0.0f;
+    int k = 0;
+    for (; k + 8 <= splits; k += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = partial[(size_t)(k + j) * n + i];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] = __fadd_rn(s[j], v[j]);
+    }
+    for (int j = 0; k < splits; ++k, ++j) s[j] = __fadd_rn(s[j], partial[(size_t)k * n + i]);
+    const float a = __fadd_rn(__fadd_rn(s[0], s[1]), __fadd_rn(s[2], s[3]));
+    const float b = __fadd_rn(__fadd_rn(s[4], s[5]), __fadd_rn(s[6], s[7]));
+    out[i] = __fadd_rn(a, b);
   }
 }
 
@@ -201,7 +216,7 @@ int check_f32(vtlb_ctx* ctx, const char* fn, int M, int N, int K) {
 }  // namespace
 
 int f32::reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out) {
-  reduce_splits_kernel<<<f32::grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(partial, splits, n, out);
+  reduce_splits_kernel<<<f32::grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(partial, splits, n, out);
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
