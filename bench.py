@@ -314,14 +314,14 @@ def run_int8(args, ranks):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor",
-                         "kernel": "gemm2::gemm_i8_pair_kernel<EpiDequant> (tcgen05 kind::i8, cta_group::2, "
-                                   "fused dequant+bias+ReLU, TMA-store epilogue)",
+                         "kernel": "gemm2::gemm_pair_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, cta_group::2, "
+                                   "fused dequant+bias+ReLU, TMA-store epilogue, K-split of surplus tiles)",
                          "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
                          "frac": gemm_tops / int8_peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on
                          # this workload, from the ncu capture summarised in
                          # profiles/gemm_i8_pair_fused_4096.md (algorithmic operand bytes: 33.6 MB read)
-                         "traffic": 54.2e6, "traffic_unit": "bytes per launch (ncu, 34.0 MB read + 20.2 MB written)",
+                         "traffic": 59.9e6, "traffic_unit": "bytes per launch (ncu, 34.55 MB read + 25.38 MB written)",
                          "algorithmic_ops_per_launch": 2.0 * M * N * K,
                          "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
                                         "dense INT8 issues at twice the bf16 rate)",
