@@ -378,7 +378,7 @@ def main():
                     help="training workloads only: global batch override, for small profiling captures")
     args = ap.parse_args()
     defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5),
-                "int8_mlp_c5": (20, 3)}
+                "int8_mlp_c5": (20, 3), "ckpt_c4": (20, 3)}
     if args.workload not in defaults:
         raise SystemExit(f"unknown workload {args.workload}; choose from {sorted(defaults)}")
     if args.steps is None:
@@ -396,6 +396,12 @@ def main():
             out = bench_infer.run_reference(args, ranks)
         else:
             out = bench_infer.run(args, ranks, ClockSampler, peaks, cuda_sync)
+    elif args.workload == "ckpt_c4":
+        import bench_ckpt
+        if args.impl == "reference":
+            out = bench_ckpt.run_reference(args, ranks)
+        else:
+            out = bench_ckpt.run(args, ranks, ClockSampler, peaks, cuda_sync)
     else:
         import bench_train
         if args.impl == "reference":

@@ -244,6 +244,19 @@ int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int sha
                                  const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
                                  void* d_Y, int M, int N, int K, int relu);
 
+/* ---- checkpoint tensor payloads --------------------------------------------
+ * The reference writes every tensor of a checkpoint as text: each element widened to f64, its
+ * 8 bytes most significant first, the bytes in standard base64 with '=' padding
+ * (encode_tensor / decode_tensor, nn/models/serialization.v:421-473; callers save_checkpoint
+ * :109-262 and load_weights :279-373).  These two run that byte work on the device, so that only
+ * the text crosses to the host: vtlb_ckpt_text_len(n) = 4*ceil(8n/3) characters for n elements.
+ * d_text must be 16-byte aligned.  decode converts f64 -> f32 by plain rounding (vtl.cast),
+ * refuses a length that does not match n, characters outside the alphabet and malformed
+ * padding (VTLB_EINVAL), and blocks until the result is known; encode returns at once. */
+size_t vtlb_ckpt_text_len(size_t n);
+int vtlb_ckpt_encode_f32(vtlb_ctx* ctx, const void* d_src, size_t n, void* d_text);
+int vtlb_ckpt_decode_f32(vtlb_ctx* ctx, const void* d_text, size_t text_len, void* d_dst, size_t n);
+
 /* ---- collectives (NCCL over NVLink) ---------------------------------------
  * No counterpart in the reference (single device).  One ctx per rank/process.
  * vtlb_comm_unique_id fills a 128-byte id on one rank; the caller ships it to

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_python_binding_covers_every_declared_symbol():
     from vtl_b200 import capi
-    bound = set(capi._PROTOS) | {"vtlb_last_error", "vtlb_launch_count", "vtlb_stream"}
+    bound = set(capi._PROTOS) | {"vtlb_last_error", "vtlb_launch_count", "vtlb_stream", "vtlb_ckpt_text_len"}
     assert set(declared_functions()) <= bound, set(declared_functions()) - bound
 
 

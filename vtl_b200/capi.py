@@ -60,6 +60,8 @@ _PROTOS = {
     "vtlb_relu_bwd_f32": [_vp, _vp, _vp, _vp, _sz],
     "vtlb_add_inplace_f32": [_vp, _vp, _vp, _sz],
     "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
+    "vtlb_ckpt_encode_f32": [_vp, _vp, _sz, _vp],
+    "vtlb_ckpt_decode_f32": [_vp, _vp, _sz, _vp, _sz],
     "vtlb_conv2d_fwd_f32": [_vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_vp],
     "vtlb_conv2d_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 11,
     "vtlb_maxpool2d_fwd_f32": [_vp, _vp, _vp, _vp] + [_i] * 10,
@@ -104,6 +106,8 @@ def load() -> C.CDLL:
         lib.vtlb_launch_count.restype = C.c_uint64
         lib.vtlb_stream.argtypes = [_vp]
         lib.vtlb_stream.restype = _vp
+        lib.vtlb_ckpt_text_len.argtypes = [_sz]
+        lib.vtlb_ckpt_text_len.restype = _sz
         _lib = lib
     return _lib
 
@@ -285,6 +289,16 @@ class Device:
 
     def fill_f32(self, dst, value, n):
         self._ck(self.lib.vtlb_fill_f32(self.h, _ptr(dst), value, n))
+
+    # -- checkpoint payloads (text of nn/models/serialization.v:421-473)
+    def ckpt_text_len(self, n: int) -> int:
+        return int(self.lib.vtlb_ckpt_text_len(n))
+
+    def ckpt_encode_f32(self, src, n, text):
+        self._ck(self.lib.vtlb_ckpt_encode_f32(self.h, _ptr(src), n, _ptr(text)))
+
+    def ckpt_decode_f32(self, text, text_len, dst, n):
+        self._ck(self.lib.vtlb_ckpt_decode_f32(self.h, _ptr(text), text_len, _ptr(dst), n))
 
     def conv2d_fwd_f32(self, x, w, bias, y, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, relu=False, pre=None):
         self._ck(self.lib.vtlb_conv2d_fwd_f32(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), B, Cc, H, W, O,

@@ -15,6 +15,7 @@
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../../include/vtlb.h"
@@ -123,6 +124,10 @@ struct Layer {
   virtual std::vector<VarPtr> variables() { return {}; }
   virtual std::vector<int> output_shape() const = 0;  // without the batch dimension
   virtual const char* kind() const = 0;
+  // what a checkpoint records about the layer: the reference's type name and the configuration
+  // map its builder registers (nn/models/sequential_info.v:40-215), in insertion order
+  virtual const char* type_name() const = 0;
+  virtual std::vector<std::pair<std::string, int>> config() const { return {}; }
 };
 
 // nn/layers/input.v
@@ -132,6 +137,12 @@ struct InputLayer : Layer {
   VarPtr forward(const VarPtr& input) override { return input; }
   std::vector<int> output_shape() const override { return shape; }
   const char* kind() const override { return "input"; }
+  const char* type_name() const override { return "InputLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override {
+    std::vector<std::pair<std::string, int>> c;
+    for (size_t i = 0; i < shape.size(); ++i) c.emplace_back("shape_" + std::to_string(i), shape[i]);
+    return c;
+  }
 };
 
 // nn/layers/linear.v:17-74 -- weights [out,in], bias [1,out]
@@ -146,6 +157,10 @@ struct LinearLayer : Layer {
   std::vector<VarPtr> variables() override { return {weights, bias}; }
   std::vector<int> output_shape() const override { return {out_features}; }
   const char* kind() const override { return "linear"; }
+  const char* type_name() const override { return "LinearLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override {
+    return {{"in_features", in_features}, {"out_features", out_features}};
+  }
 };
 
 // nn/layers/relu.v
@@ -155,6 +170,7 @@ struct ReLULayer : Layer {
   VarPtr forward(const VarPtr& input) override;
   std::vector<int> output_shape() const override { return shape; }
   const char* kind() const override { return "relu"; }
+  const char* type_name() const override { return "ReLULayer"; }
 };
 
 // nn/layers/flatten.v:38-48
@@ -164,6 +180,7 @@ struct FlattenLayer : Layer {
   VarPtr forward(const VarPtr& input) override;
   std::vector<int> output_shape() const override;
   const char* kind() const override { return "flatten"; }
+  const char* type_name() const override { return "FlattenLayer"; }
 };
 
 // nn/layers/conv2d.v:15-105 -- weight [oc, ic, kh, kw], bias [1, oc]; groups = 1, dilation = 1
@@ -181,6 +198,13 @@ struct Conv2DLayer : Layer {
   std::vector<VarPtr> variables() override { return {weight, bias}; }
   std::vector<int> output_shape() const override;
   const char* kind() const override { return "conv2d"; }
+  const char* type_name() const override { return "Conv2DLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override {
+    return {{"in_channels", in_ch},        {"out_channels", out_ch},      {"kernel_h", kh},
+            {"kernel_w", kw},              {"padding_h", cfg.pad_h},      {"padding_w", cfg.pad_w},
+            {"stride_h", cfg.stride_h},    {"stride_w", cfg.stride_w},    {"dilation_h", 1},
+            {"dilation_w", 1},             {"groups", 1}};
+  }
 
  private:
   VarPtr run(const VarPtr& input, bool relu);
@@ -194,6 +218,10 @@ struct MaxPool2DLayer : Layer {
   VarPtr forward(const VarPtr& input) override;
   std::vector<int> output_shape() const override;
   const char* kind() const override { return "maxpool2d"; }
+  const char* type_name() const override { return "MaxPool2DLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override {
+    return {{"kernel_h", kh}, {"kernel_w", kw}, {"padding_h", ph}, {"padding_w", pw}, {"stride_h", sh}, {"stride_w", sw}};
+  }
 };
 
 // nn/types/loss.v:7-27, nn/loss/mse.v:30-41, nn/loss/softmax_cross_entropy.v
@@ -209,7 +237,9 @@ struct SoftmaxCrossEntropyLoss : Loss {
   VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows) override;
 };
 
-// nn/models/sequential.v:11-220 + sequential_info.v
+class AdamOptimizer;
+
+// nn/models/sequential.v:11-220 + sequential_info.v; checkpoints: nn/models/serialization.v
 class Sequential {
  public:
   explicit Sequential(Session* s);
@@ -224,6 +254,13 @@ class Sequential {
   void softmax_cross_entropy_loss();
   VarPtr forward(const VarPtr& train);                                  // sequential.v:204-215
   VarPtr loss(const VarPtr& output, const Tensor& target, int global_rows = -1);  // :218-220
+  // serialization.v:102-262: weights (and, beyond the reference, the optimizer's moments when
+  // `opt` is given) as JSON with base64 payloads; :266-276: (epoch, loss) of a file; :279-373:
+  // weights into this already-constructed model, with the reference's checks and error texts.
+  void save(const std::string& path);
+  void save_checkpoint(const std::string& path, int epoch, double loss, const AdamOptimizer* opt = nullptr);
+  static std::pair<int, double> load_checkpoint(const std::string& path);
+  void load_weights(const std::string& path, AdamOptimizer* opt = nullptr);
   std::vector<std::unique_ptr<Layer>> layers;
   std::unique_ptr<Loss> loss_fn;
   bool fuse_relu = true;  // run Linear/Conv + ReLU pairs as one launch

@@ -55,6 +55,13 @@ int vtlh_model_get_input_grad(vtlh_model* m, float* host);
  * C and the gradients of A and B to the host (any of the outputs may be null) */
 int vtlh_matmul_mse_backprop(vtlh_session* s, const void* d_A, int M, int K, const void* d_B, int N,
                              const void* d_T, float* h_loss, float* h_C, float* h_dA, float* h_dB);
+/* Checkpoints in the reference's file format (nn/models/serialization.v): save_checkpoint writes
+ * the weights and, with_optimizer != 0, the optimizer's moments; load_weights restores them into a
+ * model of the same architecture (with_optimizer != 0: the moments too); load_checkpoint reads
+ * (epoch, loss) of a file. */
+int vtlh_model_save_checkpoint(vtlh_model* m, const char* path, int epoch, double loss, int with_optimizer);
+int vtlh_model_load_weights(vtlh_model* m, const char* path, int with_optimizer);
+int vtlh_load_checkpoint(const char* path, int* epoch, double* loss);
 #ifdef __cplusplus
 }
 #endif

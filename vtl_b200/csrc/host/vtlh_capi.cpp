@@ -229,3 +229,23 @@ int vtlh_model_get_input_grad(vtlh_model* m, float* host) {
     m->last_input->grad.to_array(host);
   });
 }
+
+int vtlh_model_save_checkpoint(vtlh_model* m, const char* path, int epoch, double loss, int with_optimizer) {
+  return guard([&] {
+    if (with_optimizer && !m->opt) throw Error(VTLB_ESTATE, "save_checkpoint: the model has no optimizer");
+    m->seq->save_checkpoint(path, epoch, loss, with_optimizer ? m->opt.get() : nullptr);
+  });
+}
+int vtlh_model_load_weights(vtlh_model* m, const char* path, int with_optimizer) {
+  return guard([&] {
+    if (with_optimizer && !m->opt) throw Error(VTLB_ESTATE, "load_weights: the model has no optimizer");
+    m->seq->load_weights(path, with_optimizer ? m->opt.get() : nullptr);
+  });
+}
+int vtlh_load_checkpoint(const char* path, int* epoch, double* loss) {
+  return guard([&] {
+    const auto meta = Sequential::load_checkpoint(path);
+    if (epoch) *epoch = meta.first;
+    if (loss) *loss = meta.second;
+  });
+}

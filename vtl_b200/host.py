@@ -50,6 +50,9 @@ def load() -> C.CDLL:
             "vtlh_model_train_step": [vp, vp, i, ip, vp, i, ip, i, i, C.POINTER(C.c_float)],
             "vtlh_model_get_input_grad": [vp, vp], "vtlh_model_zero_grad": [vp],
             "vtlh_matmul_mse_backprop": [vp, vp, i, i, vp, i, vp, vp, vp, vp, vp],
+            "vtlh_model_save_checkpoint": [vp, C.c_char_p, i, d, i],
+            "vtlh_model_load_weights": [vp, C.c_char_p, i],
+            "vtlh_load_checkpoint": [C.c_char_p, ip, C.POINTER(d)],
         }
         for name, args in protos.items():
             fn = getattr(lib, name)
@@ -198,3 +201,22 @@ class Model:
         out = np.empty(shape, np.float32)
         _ck(self.lib.vtlh_model_get_input_grad(self.h, out.ctypes.data))
         return out
+
+    # -- checkpoints in the reference's format (nn/models/serialization.v)
+    def save(self, path):
+        """Sequential.save: weights only, epoch 0, loss 0 (serialization.v:102-104)."""
+        self.save_checkpoint(path, 0, 0.0)
+
+    def save_checkpoint(self, path, epoch=0, loss=0.0, with_optimizer=False):
+        _ck(self.lib.vtlh_model_save_checkpoint(self.h, os.fsencode(path), int(epoch), float(loss),
+                                                int(with_optimizer)))
+
+    def load_weights(self, path, with_optimizer=False):
+        _ck(self.lib.vtlh_model_load_weights(self.h, os.fsencode(path), int(with_optimizer)))
+
+
+def load_checkpoint(path):
+    """Sequential.load_checkpoint: (epoch, loss) stored in a checkpoint (serialization.v:266-276)."""
+    epoch, loss = C.c_int(0), C.c_double(0.0)
+    _ck(load().vtlh_load_checkpoint(os.fsencode(path), C.byref(epoch), C.byref(loss)))
+    return epoch.value, loss.value
