@@ -261,33 +261,41 @@ def run_int8(args, ranks):
     gemm_ms = statistics.mean(dev.elapsed_ms(a, c) for a, c in evs)
     assert dev.check_status() == 0
 
-    # end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    # end to end through the C ABI with host buffers (pinned), copies inside the timed region: every
+    # step's A comes from the host and every step's Y goes back; the copy of the next A and of the
+    # last Y run on the library's copy streams while the current step computes (double buffering)
     import ctypes as C
-    hA, hY = C.c_void_p(), C.c_void_p()
-    assert dev.lib.vtlb_host_alloc(A.nbytes, C.byref(hA)) == 0
-    assert dev.lib.vtlb_host_alloc(M * N * 4, C.byref(hY)) == 0
-    C.memmove(hA.value, A.ctypes.data, A.nbytes)
+    hA, hY = [C.c_void_p(), C.c_void_p()], [C.c_void_p(), C.c_void_p()]
+    for h in hA:
+        assert dev.lib.vtlb_host_alloc(A.nbytes, C.byref(h)) == 0
+        C.memmove(h.value, A.ctypes.data, A.nbytes)
+    for h in hY:
+        assert dev.lib.vtlb_host_alloc(M * N * 4, C.byref(h)) == 0
 
-    def e2e_step(i):
-        s = i % NSETS
-        dev.h2d_raw(dA[s], hA.value, A.nbytes)
-        dev.quant_rows_i8(dA[s], M, K, dQa[s], dSa[s])
-        dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
-        dev.d2h_raw(hY.value, dY[s], M * N * 4)  # blocks until the result is on the host
+    def e2e_run(steps):
+        dev.copy_h2d_async(dA[0], hA[0].value, A.nbytes)
+        for i in range(steps):
+            s = i % NSETS
+            dev.copy_wait(dev.COPY_IN_BEFORE_COMPUTE)          # A of this step has landed
+            if i + 1 < steps:                                  # next A into a buffer no step is using
+                dev.copy_h2d_async(dA[(i + 1) % NSETS], hA[(i + 1) % 2].value, A.nbytes)
+            dev.quant_rows_i8(dA[s], M, K, dQa[s], dSa[s])
+            dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
+            dev.copy_wait(dev.COPY_OUT_BEFORE_COMPUTE)         # later steps wait for the earlier copies out
+            dev.copy_d2h_async(hY[i % 2].value, dY[s], M * N * 4)
+        dev.copy_wait(dev.COPY_OUT_DONE)                       # the last result is on the host
 
-    for i in range(2):
-        e2e_step(i)
+    e2e_run(3)
     cuda_sync(dev)
     ranks.barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
+    e2e_run(args.steps)
     cuda_sync(dev)
     e2e_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = ranks.max_f32(e2e_ms)
     clocks = sampler.stop() if ranks.rank == 0 else None
-    dev.lib.vtlb_host_free(hA)
-    dev.lib.vtlb_host_free(hY)
+    for h in hA + hY:
+        dev.lib.vtlb_host_free(h)
 
     ops_step = 2.0 * M * N * K * ranks.world
     ms_step = ms_total / args.steps

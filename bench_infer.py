@@ -58,7 +58,8 @@ class ShardedInt8MLP:
                                     q_all=dev.zeros((self.C, world, self.Mc, n), np.int8), sa=dev.zeros(tokens)))
         self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
 
-    def forward(self, dX):
+    def forward(self, dX, y_out=None):
+        """`y_out`: an alternative buffer for the last layer's output (for double buffering)."""
         dev, M, R, C, Mc = self.dev, self.M, self.R, self.C, self.Mc
         dev.quant_rows_i8(dX, M, self.dims[0], self.q_in, self.sa_in)  # replicated input
         # per row block: where its quantised activations live and in how many column shards
@@ -74,7 +75,7 @@ class ShardedInt8MLP:
                 if gathered_at[c] > waited:  # the block's codes must have arrived
                     dev.comm_wait()
                     waited = issued
-                y = L["Y"].ptr + 4 * c * Mc * n
+                y = (y_out.ptr if (last and y_out is not None) else L["Y"].ptr) + 4 * c * Mc * n
                 dev.linear_i8_fwd_sharded_a(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K,
                                             relu=not last)
                 if last:
@@ -99,7 +100,7 @@ class ShardedInt8MLP:
             shards = R
         if issued > waited:
             dev.comm_wait()
-        return self.layers[-1]["Y"]
+        return y_out if y_out is not None else self.layers[-1]["Y"]
 
 
 def cpu_sample(tokens=64, budget_s=15.0):
@@ -189,18 +190,29 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
     assert dev.lib.vtlb_host_alloc(out_bytes, C.byref(hY)) == 0
     C.memmove(hX.value, X.ctypes.data, X.nbytes)
 
-    def e2e_step():
-        dev.h2d_raw(dX, hX.value, X.nbytes)
-        y = model.forward(dX)
-        dev.d2h_raw(hY.value, y, out_bytes)
+    # tokens in from pinned host memory and the output slab back to it every step; the next input
+    # and the last output are copied on the library's copy streams while the current pass computes
+    dXs = [dX, dev.empty(X.shape, X.dtype)]
+    last = model.layers[-1]
+    dYs = [last["Y"], dev.empty(last["Y"].shape, np.float32)]
 
-    e2e_step()
+    def e2e_run(steps):
+        dev.copy_h2d_async(dXs[0], hX.value, X.nbytes)
+        for i in range(steps):
+            dev.copy_wait(dev.COPY_IN_BEFORE_COMPUTE)
+            if i + 1 < steps:
+                dev.copy_h2d_async(dXs[(i + 1) % 2], hX.value, X.nbytes)
+            y = model.forward(dXs[i % 2], y_out=dYs[i % 2])
+            dev.copy_wait(dev.COPY_OUT_BEFORE_COMPUTE)
+            dev.copy_d2h_async(hY.value, y, out_bytes)
+        dev.copy_wait(dev.COPY_OUT_DONE)
+
+    e2e_run(2)
     cuda_sync(dev)
     ranks.barrier()
     esteps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
-    for _ in range(esteps):
-        e2e_step()
+    e2e_run(esteps)
     cuda_sync(dev)
     e2e_ms = ranks.max_f32((time.perf_counter() - t0) * 1e3)
     clocks = sampler.stop() if ranks.rank == 0 else None

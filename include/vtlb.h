@@ -244,6 +244,40 @@ int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int sha
                                  const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
                                  void* d_Y, int M, int N, int K, int relu);
 
+/* ---- input pipeline: copies that overlap the compute stream -------------------
+ * The reference stages every batch through the host synchronously (cuda_memcpy_host_to_device
+ * in storage/cuda_d_cuda.v:32-60 and GpuBufF64.upload, then a blocking download); its loader
+ * (datasets/dataloader.v:87-143) builds one batch at a time.  Here the next batch comes in and
+ * the last result goes out on copy streams of their own while the current step computes.
+ *   vtlb_copy_h2d_async  starts after the compute work enqueued so far (the last reader of
+ *                        d_dst) and returns at once; h_src should come from vtlb_host_alloc.
+ *   vtlb_copy_d2h_async  starts after the compute work enqueued so far (the producer of d_src).
+ *   vtlb_copy_wait       VTLB_COPY_IN_BEFORE_COMPUTE: compute enqueued from now on waits for the
+ *                        host->device copies enqueued so far; VTLB_COPY_OUT_BEFORE_COMPUTE: ...
+ *                        for the device->host copies (before their source is overwritten);
+ *                        VTLB_COPY_OUT_DONE: the host blocks until the device->host copies have
+ *                        landed.  Bits may be combined.
+ * A double-buffered loop: copy batch 0 in; for each step i: wait(IN_BEFORE_COMPUTE); start the
+ * copy of batch i+1 into the other buffer; run step i; copy its result out.  vtlb_sync also waits
+ * for both copy streams. */
+#define VTLB_COPY_IN_BEFORE_COMPUTE 1
+#define VTLB_COPY_OUT_BEFORE_COMPUTE 2
+#define VTLB_COPY_OUT_DONE 4
+int vtlb_copy_h2d_async(vtlb_ctx* ctx, void* d_dst, const void* h_src, size_t bytes);
+int vtlb_copy_d2h_async(vtlb_ctx* ctx, void* h_dst, const void* d_src, size_t bytes);
+int vtlb_copy_wait(vtlb_ctx* ctx, int what);
+
+/* ---- batch assembly for a device-resident dataset ---------------------------
+ * vtlb_gather_rows_f32: dst[j, :] = src[indices[j], :] for j < n_rows, rows of row_elems values:
+ * what DataLoader.batch / batch_with_labels do element by element on the host
+ * (datasets/dataloader.v:41-143).  vtlb_one_hot_f32: out[i, c] = (labels[i] == c), the
+ * [N, classes] label tensor the reference's examples build on the host.  An index or label out
+ * of range is never dereferenced / leaves a zero row; with check != 0 the call blocks and
+ * reports it as VTLB_EINVAL. */
+int vtlb_gather_rows_f32(vtlb_ctx* ctx, const void* d_src, int src_rows, size_t row_elems,
+                         const void* d_indices_i32, int n_rows, void* d_dst, int check);
+int vtlb_one_hot_f32(vtlb_ctx* ctx, const void* d_labels_i32, size_t n, int classes, void* d_out, int check);
+
 /* ---- checkpoint tensor payloads --------------------------------------------
  * The reference writes every tensor of a checkpoint as text: each element widened to f64, its
  * 8 bytes most significant first, the bytes in standard base64 with '=' padding

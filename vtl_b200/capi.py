@@ -61,6 +61,11 @@ _PROTOS = {
     "vtlb_add_inplace_f32": [_vp, _vp, _vp, _sz],
     "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
     "vtlb_ckpt_encode_f32": [_vp, _vp, _sz, _vp],
+    "vtlb_copy_h2d_async": [_vp, _vp, _vp, _sz],
+    "vtlb_copy_d2h_async": [_vp, _vp, _vp, _sz],
+    "vtlb_copy_wait": [_vp, _i],
+    "vtlb_gather_rows_f32": [_vp, _vp, _i, _sz, _vp, _i, _vp, _i],
+    "vtlb_one_hot_f32": [_vp, _vp, _sz, _i, _vp, _i],
     "vtlb_ckpt_decode_f32": [_vp, _vp, _sz, _vp, _sz],
     "vtlb_conv2d_fwd_f32": [_vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_vp],
     "vtlb_conv2d_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 11,
@@ -289,6 +294,26 @@ class Device:
 
     def fill_f32(self, dst, value, n):
         self._ck(self.lib.vtlb_fill_f32(self.h, _ptr(dst), value, n))
+
+    # -- input pipeline: copies on their own streams (host pointers as integers, pinned memory)
+    COPY_IN_BEFORE_COMPUTE, COPY_OUT_BEFORE_COMPUTE, COPY_OUT_DONE = 1, 2, 4
+
+    def copy_h2d_async(self, dst, hptr: int, nbytes: int):
+        self._ck(self.lib.vtlb_copy_h2d_async(self.h, _ptr(dst), hptr, nbytes))
+
+    def copy_d2h_async(self, hptr: int, src, nbytes: int):
+        self._ck(self.lib.vtlb_copy_d2h_async(self.h, hptr, _ptr(src), nbytes))
+
+    def copy_wait(self, what: int):
+        self._ck(self.lib.vtlb_copy_wait(self.h, what))
+
+    # -- batch assembly on the device (datasets/dataloader.v:41-143)
+    def gather_rows_f32(self, src, src_rows, row_elems, indices, n_rows, dst, check=True):
+        self._ck(self.lib.vtlb_gather_rows_f32(self.h, _ptr(src), src_rows, row_elems, _ptr(indices), n_rows,
+                                               _ptr(dst), int(check)))
+
+    def one_hot_f32(self, labels, n, classes, out, check=True):
+        self._ck(self.lib.vtlb_one_hot_f32(self.h, _ptr(labels), n, classes, _ptr(out), int(check)))
 
     # -- checkpoint payloads (text of nn/models/serialization.v:421-473)
     def ckpt_text_len(self, n: int) -> int:

@@ -21,6 +21,10 @@ struct vtlb_ctx {
   cudaStream_t comm_stream = nullptr;  // collectives
   cudaEvent_t ev_compute = nullptr;    // compute -> comm ordering
   cudaEvent_t ev_comm = nullptr;       // comm -> compute ordering
+  // input pipeline: host -> device and device -> host copies on streams of their own, so that the
+  // next batch comes in and the last result goes out while the current step computes
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_copy = nullptr;       // ordering between the copy streams and compute
   uint32_t* d_status = nullptr;        // device status word
   void* scratch = nullptr;             // operand-split buffers, partial sums
   size_t scratch_bytes = 0;

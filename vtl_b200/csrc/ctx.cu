@@ -65,6 +65,9 @@ VTLB_API int vtlb_ctx_create(int device, vtlb_ctx** out) {
   }
   if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (e = cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaEventCreateWithFlags(&ctx->ev_copy, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess ||
@@ -83,6 +86,8 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
   if (ctx->comm) vtlb_comm_destroy(ctx);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
+  if (ctx->copy_in) cudaStreamSynchronize(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamSynchronize(ctx->copy_out);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->ksplit_buf) cudaFree(ctx->ksplit_buf);
   if (ctx->d_status) cudaFree(ctx->d_status);
@@ -90,14 +95,58 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
   if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
   if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
+  if (ctx->ev_copy) cudaEventDestroy(ctx->ev_copy);
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
   delete ctx;
   return VTLB_OK;
 }
 
 VTLB_API int vtlb_sync(vtlb_ctx* ctx) {
   VTLB_ENTER(ctx);
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_in));
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->comm_stream));
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_out));
+  return VTLB_OK;
+}
+
+// ---------------------------------------------------------------- input pipeline copies
+VTLB_API int vtlb_copy_h2d_async(vtlb_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!d_dst || !h_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_copy_h2d_async: null pointer");
+  // the destination may still be read by compute work enqueued so far (the step that used this
+  // buffer last): the copy starts after it
+  VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_copy, ctx->stream));
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_copy, 0));
+  VTLB_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_copy_d2h_async(vtlb_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+  VTLB_ENTER(ctx);
+  if (bytes == 0) return VTLB_OK;
+  if (!h_dst || !d_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_copy_d2h_async: null pointer");
+  VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_copy, ctx->stream));  // after the work that produces d_src
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_copy, 0));
+  VTLB_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->copy_out));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_copy_wait(vtlb_ctx* ctx, int what) {
+  VTLB_ENTER(ctx);
+  if (what & ~(VTLB_COPY_IN_BEFORE_COMPUTE | VTLB_COPY_OUT_BEFORE_COMPUTE | VTLB_COPY_OUT_DONE))
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_copy_wait: unknown bits 0x%x", what);
+  if (what & VTLB_COPY_IN_BEFORE_COMPUTE) {
+    VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_copy, ctx->copy_in));
+    VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
+  }
+  if (what & VTLB_COPY_OUT_BEFORE_COMPUTE) {
+    VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_copy, ctx->copy_out));
+    VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_copy, 0));
+  }
+  if (what & VTLB_COPY_OUT_DONE) VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_out));
   return VTLB_OK;
 }
 

@@ -286,4 +286,38 @@ class AdamOptimizer {
   std::vector<Tensor> first_moments, second_moments;
 };
 
+// datasets.DataLoader (datasets/dataloader.v:19-331) over device-resident dataset and label
+// tensors: same configuration, index order (LCG Fisher-Yates, seed + epoch), drop_last rules, len,
+// reset and split; batch(i) gathers the rows of batch i on the device.
+struct DataLoaderConfig {
+  int batch_size = 32;
+  bool shuffle = true, drop_last = true;
+  uint64_t seed = 0;
+};
+class DataLoader {
+ public:
+  DataLoader(const Tensor& dataset, const Tensor& labels /* may be undefined */, DataLoaderConfig c);
+  bool batch(int i, Tensor* features);                                   // false = none (:41-84)
+  bool batch_with_labels(int i, Tensor* features, Tensor* labels_out);   // (:87-143)
+  int len() const;                                                       // (:146-154)
+  int total_samples() const { return (int)indices.size(); }
+  int mini_batch_count() const { return len(); }
+  void reset();                                                          // (:160-165)
+  std::pair<std::unique_ptr<DataLoader>, std::unique_ptr<DataLoader>> split(double val_fraction) const;
+  Tensor dataset, labels;
+  int batch_size;
+  bool shuffle, drop_last;
+  uint64_t seed;
+  std::vector<int> indices;
+  int epoch = 0;
+
+ private:
+  void shuffle_indices();
+  bool range(int i, int& start, int& end) const;
+  void sync_indices();
+  Tensor gather(const Tensor& src, int start, int end);
+  std::shared_ptr<DeviceBuf> d_indices_;
+  bool indices_dirty_ = true;
+};
+
 }  // namespace vtl

@@ -62,6 +62,20 @@ int vtlh_matmul_mse_backprop(vtlh_session* s, const void* d_A, int M, int K, con
 int vtlh_model_save_checkpoint(vtlh_model* m, const char* path, int epoch, double loss, int with_optimizer);
 int vtlh_model_load_weights(vtlh_model* m, const char* path, int with_optimizer);
 int vtlh_load_checkpoint(const char* path, int* epoch, double* loss);
+/* datasets.DataLoader over device-resident tensors the caller owns (d_dataset [n, ...] f32;
+ * d_labels [n, ...] f32 or null).  batch copies batch i into d_features (and d_labels_out when the
+ * loader has labels and it is non-null) and returns its row count in *rows, 0 meaning "none". */
+typedef struct vtlh_loader vtlh_loader;
+int vtlh_loader_create(vtlh_session* s, const void* d_dataset, int ndim, const int* shape, const void* d_labels,
+                       int lndim, const int* lshape, int batch_size, int shuffle, int drop_last,
+                       unsigned long long seed, vtlh_loader** out);
+int vtlh_loader_destroy(vtlh_loader* l);
+int vtlh_loader_len(vtlh_loader* l);
+int vtlh_loader_total_samples(vtlh_loader* l);
+int vtlh_loader_reset(vtlh_loader* l);
+int vtlh_loader_indices(vtlh_loader* l, int* out); /* total_samples() entries */
+int vtlh_loader_batch(vtlh_loader* l, int i, void* d_features, void* d_labels_out, int* rows);
+int vtlh_loader_split(vtlh_loader* l, double val_fraction, vtlh_loader** train, vtlh_loader** val);
 #ifdef __cplusplus
 }
 #endif

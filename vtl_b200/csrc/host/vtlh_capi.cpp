@@ -249,3 +249,63 @@ int vtlh_load_checkpoint(const char* path, int* epoch, double* loss) {
     if (loss) *loss = meta.second;
   });
 }
+
+struct vtlh_loader {
+  Session* s;
+  std::unique_ptr<DataLoader> dl;
+};
+
+int vtlh_loader_create(vtlh_session* s, const void* d_dataset, int ndim, const int* shape, const void* d_labels,
+                       int lndim, const int* lshape, int batch_size, int shuffle, int drop_last,
+                       unsigned long long seed, vtlh_loader** out) {
+  return guard([&] {
+    Session* ss = s->s.get();
+    Tensor data = borrow(ss, d_dataset, ndim, shape);
+    Tensor lab = d_labels ? borrow(ss, d_labels, lndim, lshape) : Tensor();
+    DataLoaderConfig c;
+    c.batch_size = batch_size;
+    c.shuffle = shuffle != 0;
+    c.drop_last = drop_last != 0;
+    c.seed = seed;
+    auto p = new vtlh_loader{ss, nullptr};
+    try {
+      p->dl = std::make_unique<DataLoader>(data, lab, c);
+    } catch (...) {
+      delete p;
+      throw;
+    }
+    *out = p;
+  });
+}
+int vtlh_loader_destroy(vtlh_loader* l) {
+  delete l;
+  return VTLB_OK;
+}
+int vtlh_loader_len(vtlh_loader* l) { return l->dl->len(); }
+int vtlh_loader_total_samples(vtlh_loader* l) { return l->dl->total_samples(); }
+int vtlh_loader_reset(vtlh_loader* l) {
+  return guard([&] { l->dl->reset(); });
+}
+int vtlh_loader_indices(vtlh_loader* l, int* out) {
+  std::memcpy(out, l->dl->indices.data(), l->dl->indices.size() * sizeof(int));
+  return VTLB_OK;
+}
+int vtlh_loader_batch(vtlh_loader* l, int i, void* d_features, void* d_labels_out, int* rows) {
+  return guard([&] {
+    Tensor f, lab;
+    *rows = 0;
+    const bool with_labels = l->dl->labels.defined() && d_labels_out;
+    const bool ok = with_labels ? l->dl->batch_with_labels(i, &f, &lab) : l->dl->batch(i, &f);
+    if (!ok) return;
+    l->s->check(vtlb_d2d(l->s->ctx, d_features, f.data(), f.size() * sizeof(float)));
+    if (with_labels) l->s->check(vtlb_d2d(l->s->ctx, d_labels_out, lab.data(), lab.size() * sizeof(float)));
+    *rows = f.shape()[0];
+  });
+}
+int vtlh_loader_split(vtlh_loader* l, double val_fraction, vtlh_loader** train, vtlh_loader** val) {
+  return guard([&] {
+    auto parts = l->dl->split(val_fraction);
+    *train = new vtlh_loader{l->s, std::move(parts.first)};
+    *val = new vtlh_loader{l->s, std::move(parts.second)};
+  });
+}

@@ -53,6 +53,11 @@ def load() -> C.CDLL:
             "vtlh_model_save_checkpoint": [vp, C.c_char_p, i, d, i],
             "vtlh_model_load_weights": [vp, C.c_char_p, i],
             "vtlh_load_checkpoint": [C.c_char_p, ip, C.POINTER(d)],
+            "vtlh_loader_create": [vp, vp, i, ip, vp, i, ip, i, i, i, C.c_ulonglong, C.POINTER(vp)],
+            "vtlh_loader_destroy": [vp], "vtlh_loader_len": [vp], "vtlh_loader_total_samples": [vp],
+            "vtlh_loader_reset": [vp], "vtlh_loader_indices": [vp, ip],
+            "vtlh_loader_batch": [vp, i, vp, vp, ip],
+            "vtlh_loader_split": [vp, d, C.POINTER(vp), C.POINTER(vp)],
         }
         for name, args in protos.items():
             fn = getattr(lib, name)
@@ -220,3 +225,72 @@ def load_checkpoint(path):
     epoch, loss = C.c_int(0), C.c_double(0.0)
     _ck(load().vtlh_load_checkpoint(os.fsencode(path), C.byref(epoch), C.byref(loss)))
     return epoch.value, loss.value
+
+
+class DataLoader:
+    """datasets.DataLoader (datasets/dataloader.v) over device-resident dataset / label buffers
+    (capi.DBuf, f32, first dimension = samples).  batch(i) returns device buffers."""
+
+    def __init__(self, session: Session, dataset, labels=None, batch_size=32, shuffle=True, drop_last=True,
+                 seed=0, _handle=None):
+        self.lib, self.session, self.dataset, self.labels = load(), session, dataset, labels
+        self.batch_size = batch_size
+        if _handle is not None:
+            self.h = _handle
+            return
+        h = C.c_void_p()
+        ln, ls = _shape(labels.shape) if labels is not None else (0, None)
+        _ck(self.lib.vtlh_loader_create(session.h, capi._ptr(dataset), *_shape(dataset.shape),
+                                        capi._ptr(labels), ln, ls, int(batch_size), int(shuffle),
+                                        int(drop_last), int(seed), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.vtlh_loader_destroy(self.h)
+            self.h = None
+
+    def __len__(self):
+        return int(self.lib.vtlh_loader_len(self.h))
+
+    def total_samples(self) -> int:
+        return int(self.lib.vtlh_loader_total_samples(self.h))
+
+    def reset(self):
+        _ck(self.lib.vtlh_loader_reset(self.h))
+
+    @property
+    def indices(self):
+        out = (C.c_int * max(self.total_samples(), 1))()
+        _ck(self.lib.vtlh_loader_indices(self.h, out))
+        return list(out[: self.total_samples()])
+
+    def _batch(self, i, with_labels):
+        dev = self.session.dev
+        feat = dev.empty((self.batch_size,) + tuple(self.dataset.shape[1:]), np.float32)
+        lab = dev.empty((self.batch_size,) + tuple(self.labels.shape[1:]), np.float32) if with_labels else None
+        rows = C.c_int(0)
+        _ck(self.lib.vtlh_loader_batch(self.h, int(i), feat.ptr, lab.ptr if lab else None, C.byref(rows)))
+        if rows.value == 0:
+            feat.free()
+            if lab:
+                lab.free()
+            return None
+        feat.shape = (rows.value,) + tuple(self.dataset.shape[1:])
+        if lab:
+            lab.shape = (rows.value,) + tuple(self.labels.shape[1:])
+        return (feat, lab) if with_labels else feat
+
+    def batch(self, i):
+        return self._batch(i, False)
+
+    def batch_with_labels(self, i):
+        if self.labels is None:
+            return None
+        return self._batch(i, True)
+
+    def split(self, val_fraction):
+        t, v = C.c_void_p(), C.c_void_p()
+        _ck(self.lib.vtlh_loader_split(self.h, float(val_fraction), C.byref(t), C.byref(v)))
+        mk = lambda h: DataLoader(self.session, self.dataset, self.labels, self.batch_size, _handle=h)
+        return mk(t), mk(v)
