@@ -212,6 +212,15 @@ int vtlb_adam_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* ten
 int vtlb_adamw_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors,
                         double beta1, double beta2, double lr_t, double epsilon,
                         double weight_decay, int zero_grad);
+/* SGD  : theta -= (f32)lr * g in f32 (internal.sgd_optimize, nn/internal/optimizers.v:6-13, called
+ *        by SgdOptimizer.update, nn/optimizers/sgd.v:45-52); d_m and d_v of the tensors are unused.
+ * RMSProp: sq = alpha*sq + (1-alpha)*g*g; theta -= lr*(g/(sqrt(sq)+eps) + wd*theta), each element in
+ *        f64 and rounded to f32, the update reading the stored sq (RMSPropOptimizer.update,
+ *        nn/optimizers/rmsprop.v:70-91); d_v holds sq_avg, d_m is unused. */
+int vtlb_sgd_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors, double learning_rate,
+                      int zero_grad);
+int vtlb_rmsprop_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors, double learning_rate,
+                          double alpha, double epsilon, double weight_decay, int zero_grad);
 
 /* ---- INT8 quantised linear ------------------------------------------------
  * No counterpart in the reference (it has no quantisation code); defined here:
@@ -243,6 +252,38 @@ int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa, const 
 int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards, const void* d_sa,
                                  const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
                                  void* d_Y, int M, int N, int K, int relu);
+
+/* ---- layers next to the GEMMs -------------------------------------------------
+ * Softmax over the last dimension of x[rows, n]: forward in f64 (max, exp(x - max), sum in
+ * order, divide; internal.softmax_forward, nn/internal/activation.v:423-457); backward
+ * dx_k = s_k (g_k - sum_i g_i s_i) with the softmax recomputed from the cached INPUT in f32
+ * (deriv_softmax, :285-332).
+ * Average pooling (NCHW): window sum of the in-bounds taps / (kh*kw) in f64
+ * (internal.avgpool2d_forward, nn/internal/pool.v:6-45); the backward hands g/(kh*kw) to every
+ * tap (the reference's :48-59 returns zeros of the wrong shape; standard rule instead); global
+ * average pooling as :62-101.
+ * BatchNorm1D on x[B, F]: train = batch mean and biased variance per feature in f64,
+ * y = gamma*(x-mean)/sqrt(var+eps)+beta, the f32-rounded statistics returned and blended into
+ * the running ones with `momentum` (internal.batchnorm1d_training, nn/internal/batchnorm.v:27-70;
+ * nn/layers/batchnorm.v:84-97; running pointers may both be null); infer = the f32 path on the
+ * running statistics (:7-24); bwd = the reference's formulas as written (:73-140):
+ * dx = gamma*(g - mean_B(g))/std, dgamma = sum g*(x-mean)/std, dbeta = sum g. */
+int vtlb_softmax_fwd_f32(vtlb_ctx* ctx, const void* d_x, size_t rows, size_t n, void* d_y);
+int vtlb_softmax_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, size_t rows, size_t n, void* d_dx);
+int vtlb_avgpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, int B, int C, int H, int W, int kh, int kw,
+                           int ph, int pw, int sh, int sw);
+int vtlb_avgpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, void* d_dx, int B, int C, int H, int W, int kh, int kw,
+                           int ph, int pw, int sh, int sw);
+int vtlb_global_avgpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, int B, int C, int H, int W);
+int vtlb_global_avgpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, void* d_dx, int B, int C, int H, int W);
+int vtlb_batchnorm1d_train_f32(vtlb_ctx* ctx, const void* d_x, int B, int F, const void* d_gamma, const void* d_beta,
+                               double eps, void* d_y, void* d_batch_mean, void* d_batch_var,
+                               void* d_running_mean_or_null, void* d_running_var_or_null, double momentum);
+int vtlb_batchnorm1d_infer_f32(vtlb_ctx* ctx, const void* d_x, int B, int F, const void* d_gamma, const void* d_beta,
+                               const void* d_running_mean, const void* d_running_var, double eps, void* d_y);
+int vtlb_batchnorm1d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, int B, int F, const void* d_gamma,
+                             const void* d_batch_mean, const void* d_batch_var, double eps, void* d_dx_or_null,
+                             void* d_dgamma_or_null, void* d_dbeta_or_null);
 
 /* ---- input pipeline: copies that overlap the compute stream -------------------
  * The reference stages every batch through the host synchronously (cuda_memcpy_host_to_device

@@ -497,3 +497,205 @@ ORC_API int orc_max_threads(void) {
   return 1;
 #endif
 }
+
+/* ------------------------------------------------- layers and optimizers next to the GEMMs */
+
+/* internal.softmax_forward over the last dimension (nn/internal/activation.v:423-457): per row,
+ * in f64: max, e_c = exp(x_c - max), sum in order, e_c / sum; cast to f32. */
+ORC_API void orc_softmax_fwd_f32(const float *x, size_t rows, size_t n, float *y) {
+  for (size_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * n;
+    double mx = (double)xr[0];
+    for (size_t c = 1; c < n; ++c)
+      if ((double)xr[c] > mx) mx = (double)xr[c];
+    double sum = 0.0;
+    double *e = (double *)malloc(n * sizeof(double));
+    for (size_t c = 0; c < n; ++c) {
+      e[c] = exp((double)xr[c] - mx);
+      sum += e[c];
+    }
+    for (size_t c = 0; c < n; ++c) y[r * n + c] = (float)(e[c] / sum);
+    free(e);
+  }
+}
+
+/* internal.deriv_softmax (nn/internal/activation.v:285-332) for T = f32: the softmax is
+ * recomputed from the INPUT in f32 (exp evaluated in f64 on the f32 difference, cast back),
+ * sums are sequential f32; dx_k = s_k * (g_k - sum_i g_i s_i). */
+ORC_API void orc_softmax_bwd_f32(const float *g, const float *x, size_t rows, size_t n, float *dx) {
+  float *s = (float *)malloc(n * sizeof(float));
+  for (size_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * n, *gr = g + r * n;
+    float mx = xr[0];
+    for (size_t c = 1; c < n; ++c)
+      if (xr[c] > mx) mx = xr[c];
+    float sum = 0.0f;
+    for (size_t c = 0; c < n; ++c) {
+      float d = xr[c] - mx;
+      s[c] = (float)exp((double)d);
+      sum += s[c];
+    }
+    for (size_t c = 0; c < n; ++c) s[c] = s[c] / sum;
+    float ws = 0.0f;
+    for (size_t c = 0; c < n; ++c) {
+      float p = gr[c] * s[c];
+      ws += p;
+    }
+    for (size_t c = 0; c < n; ++c) {
+      float d = gr[c] - ws;
+      dx[r * n + c] = s[c] * d;
+    }
+  }
+  free(s);
+}
+
+/* internal.avgpool2d_forward (nn/internal/pool.v:6-45): f64 window sum over the in-bounds taps,
+ * divided by kh*kw (padding counts in the divisor), cast to f32. */
+ORC_API void orc_avgpool2d_fwd_f32(const float *x, float *y, int B, int C, int H, int W, int kh, int kw,
+                                   int ph, int pw, int sh, int sw) {
+  const int OH = (H + 2 * ph - kh) / sh + 1, OW = (W + 2 * pw - kw) / sw + 1;
+  for (int n = 0; n < B * C; ++n)
+    for (int oh = 0; oh < OH; ++oh)
+      for (int ow = 0; ow < OW; ++ow) {
+        double sum = 0.0;
+        for (int a = 0; a < kh; ++a) {
+          const int ih = oh * sh - ph + a;
+          if (ih < 0 || ih >= H) continue;
+          for (int b = 0; b < kw; ++b) {
+            const int iw = ow * sw - pw + b;
+            if (iw < 0 || iw >= W) continue;
+            sum += (double)x[((size_t)n * H + ih) * W + iw];
+          }
+        }
+        y[((size_t)n * OH + oh) * OW + ow] = (float)(sum / (double)(kh * kw));
+      }
+}
+
+/* The reference's avgpool2d_backward (nn/internal/pool.v:48-59) returns zeros of the WRONG shape;
+ * as for max-pool the standard rule is restated instead: every tap of a window receives
+ * g / (kh*kw); contributions to one input element are added in (oh, ow) order in f64. */
+ORC_API void orc_avgpool2d_bwd_f32(const float *g, float *dx, int B, int C, int H, int W, int kh, int kw,
+                                   int ph, int pw, int sh, int sw) {
+  const int OH = (H + 2 * ph - kh) / sh + 1, OW = (W + 2 * pw - kw) / sw + 1;
+  for (int n = 0; n < B * C; ++n)
+    for (int ih = 0; ih < H; ++ih)
+      for (int iw = 0; iw < W; ++iw) {
+        double sum = 0.0;
+        for (int oh = 0; oh < OH; ++oh) {
+          const int a = ih - (oh * sh - ph);
+          if (a < 0 || a >= kh) continue;
+          for (int ow = 0; ow < OW; ++ow) {
+            const int b = iw - (ow * sw - pw);
+            if (b < 0 || b >= kw) continue;
+            sum += (double)g[((size_t)n * OH + oh) * OW + ow];
+          }
+        }
+        dx[((size_t)n * H + ih) * W + iw] = (float)(sum / (double)(kh * kw));
+      }
+}
+
+/* internal.global_avgpool2d_forward / _backward (nn/internal/pool.v:62-101) */
+ORC_API void orc_global_avgpool2d_fwd_f32(const float *x, float *y, int BC, int HW) {
+  for (int n = 0; n < BC; ++n) {
+    double sum = 0.0;
+    for (int i = 0; i < HW; ++i) sum += (double)x[(size_t)n * HW + i];
+    y[n] = (float)(sum / (double)HW);
+  }
+}
+ORC_API void orc_global_avgpool2d_bwd_f32(const float *g, float *dx, int BC, int HW) {
+  for (int n = 0; n < BC; ++n)
+    for (int i = 0; i < HW; ++i) dx[(size_t)n * HW + i] = (float)((double)g[n] / (double)HW);
+}
+
+/* internal.batchnorm1d_training (nn/internal/batchnorm.v:27-70) and the running-statistics update
+ * of BatchNorm1DLayer.forward (nn/layers/batchnorm.v:84-97): f64 throughout, batch mean and
+ * (biased) variance per feature, both also returned rounded to f32; the running statistics blend
+ * the ROUNDED batch statistics with momentum. */
+ORC_API void orc_batchnorm1d_train_f32(const float *x, int B, int F, const float *gamma, const float *beta,
+                                       double eps, float *y, float *mean_out, float *var_out,
+                                       float *running_mean, float *running_var, double momentum) {
+  for (int c = 0; c < F; ++c) {
+    double sum = 0.0;
+    for (int n = 0; n < B; ++n) sum += (double)x[(size_t)n * F + c];
+    const double mean = sum / (double)B;
+    double sq = 0.0;
+    for (int n = 0; n < B; ++n) {
+      const double d = (double)x[(size_t)n * F + c] - mean;
+      sq += d * d;
+    }
+    const double var = sq / (double)B;
+    mean_out[c] = (float)mean;
+    var_out[c] = (float)var;
+    for (int n = 0; n < B; ++n) {
+      const double normalized = ((double)x[(size_t)n * F + c] - mean) / sqrt(var + eps);
+      y[(size_t)n * F + c] = (float)((double)gamma[c] * normalized + (double)beta[c]);
+    }
+    if (running_mean) {
+      running_mean[c] = (float)(momentum * (double)mean_out[c] + (1.0 - momentum) * (double)running_mean[c]);
+      running_var[c] = (float)(momentum * (double)var_out[c] + (1.0 - momentum) * (double)running_var[c]);
+    }
+  }
+}
+
+/* internal.batchnorm1d_forward, the inference path (nn/internal/batchnorm.v:7-24), all in f32
+ * except the reciprocal standard deviation: std = (f32)(1 / sqrt((f64)var + eps));
+ * y = ((x - mean) * std) * gamma + beta with separate f32 roundings. */
+ORC_API void orc_batchnorm1d_infer_f32(const float *x, int B, int F, const float *gamma, const float *beta,
+                                       const float *running_mean, const float *running_var, double eps,
+                                       float *y) {
+  for (int n = 0; n < B; ++n)
+    for (int c = 0; c < F; ++c) {
+      const float std = (float)(1.0 / sqrt((double)running_var[c] + eps));
+      const float centered = x[(size_t)n * F + c] - running_mean[c];
+      const float normalized = centered * std;
+      const float scaled = normalized * gamma[c];
+      y[(size_t)n * F + c] = scaled + beta[c];
+    }
+}
+
+/* internal.batchnorm1d_backward (nn/internal/batchnorm.v:73-140), as written: dx = gamma *
+ * (g - mean_batch(g)) / sqrt(var + eps); dgamma = sum g * (x - mean)/std; dbeta = sum g; f64
+ * sums in batch order; `mean` and `var` are the f32-rounded batch statistics. */
+ORC_API void orc_batchnorm1d_bwd_f32(const float *g, const float *x, int B, int F, const float *gamma,
+                                     const float *mean, const float *var, double eps, float *dx,
+                                     float *dgamma, float *dbeta) {
+  for (int c = 0; c < F; ++c) {
+    double gsum = 0.0;
+    for (int n = 0; n < B; ++n) gsum += (double)g[(size_t)n * F + c];
+    const double gmean = gsum / (double)B;
+    const double std = sqrt((double)var[c] + eps);
+    for (int n = 0; n < B; ++n)
+      dx[(size_t)n * F + c] = (float)((double)gamma[c] * ((double)g[(size_t)n * F + c] - gmean) / std);
+    double dg = 0.0;
+    for (int n = 0; n < B; ++n) {
+      const double normalized = ((double)x[(size_t)n * F + c] - (double)mean[c]) / std;
+      dg += (double)g[(size_t)n * F + c] * normalized;
+    }
+    dgamma[c] = (float)dg;
+    dbeta[c] = (float)gsum;
+  }
+}
+
+/* internal.sgd_optimize (nn/internal/optimizers.v:6-13) for T = f32:
+ * theta = theta - (f32)lr * g, one f32 multiply and one f32 subtract. */
+ORC_API void orc_sgd_step_f32(const float *grad, float *theta, size_t n, double lr) {
+  const float lrf = (float)lr;
+  for (size_t i = 0; i < n; ++i) {
+    const float step = lrf * grad[i];
+    theta[i] = theta[i] - step;
+  }
+}
+
+/* RMSPropOptimizer.update (nn/optimizers/rmsprop.v:70-91) for T = f32: two passes, each element in
+ * f64 and cast to f32; the second pass reads the freshly stored (f32) squared-gradient average. */
+ORC_API void orc_rmsprop_step_f32(const float *grad, float *theta, float *sq_avg, size_t n, double lr,
+                                  double alpha, double epsilon, double wd) {
+  for (size_t i = 0; i < n; ++i) {
+    const double g = (double)grad[i];
+    sq_avg[i] = (float)(alpha * (double)sq_avg[i] + (1.0 - alpha) * g * g);
+  }
+  for (size_t i = 0; i < n; ++i) {
+    const double th = (double)theta[i], gr = (double)grad[i], vv = (double)sq_avg[i];
+    theta[i] = (float)(th - lr * (gr / (sqrt(vv) + epsilon) + wd * th));
+  }
+}

@@ -290,6 +290,108 @@ def adamw_step_f32(grad, theta, m, v, beta1, beta2, lr_t, eps, wd):
     return theta, m, v
 
 
+# ---------------------------------------------------------------- layers and optimizers next to the GEMMs
+def softmax_fwd_f32(x):
+    """internal.softmax_forward over the last dimension (nn/internal/activation.v:423-457)."""
+    x = _f32(x)
+    n = x.shape[-1]
+    y = np.empty_like(x)
+    lib().orc_softmax_fwd_f32(_p(x), C.c_size_t(x.size // n), C.c_size_t(n), _p(y))
+    return y
+
+
+def softmax_bwd_f32(g, x):
+    """internal.deriv_softmax (nn/internal/activation.v:285-332)."""
+    g, x = _f32(g), _f32(x)
+    n = x.shape[-1]
+    dx = np.empty_like(x)
+    lib().orc_softmax_bwd_f32(_p(g), _p(x), C.c_size_t(x.size // n), C.c_size_t(n), _p(dx))
+    return dx
+
+
+def avgpool2d_fwd_f32(x, kernel=(2, 2), pad=(0, 0), stride=(2, 2)):
+    """internal.avgpool2d_forward (nn/internal/pool.v:6-45)."""
+    x = _f32(x)
+    B, Cc, H, W = x.shape
+    OH = (H + 2 * pad[0] - kernel[0]) // stride[0] + 1
+    OW = (W + 2 * pad[1] - kernel[1]) // stride[1] + 1
+    y = np.empty((B, Cc, OH, OW), np.float32)
+    lib().orc_avgpool2d_fwd_f32(_p(x), _p(y), B, Cc, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1])
+    return y
+
+
+def avgpool2d_bwd_f32(g, in_shape, kernel=(2, 2), pad=(0, 0), stride=(2, 2)):
+    """Standard average-pool backward (the reference's returns zeros of the wrong shape)."""
+    g = _f32(g)
+    B, Cc, H, W = in_shape
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_avgpool2d_bwd_f32(_p(g), _p(dx), B, Cc, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1])
+    return dx
+
+
+def global_avgpool2d_fwd_f32(x):
+    x = _f32(x)
+    B, Cc, H, W = x.shape
+    y = np.empty((B, Cc, 1, 1), np.float32)
+    lib().orc_global_avgpool2d_fwd_f32(_p(x), _p(y), B * Cc, H * W)
+    return y
+
+
+def global_avgpool2d_bwd_f32(g, in_shape):
+    g = _f32(g)
+    B, Cc, H, W = in_shape
+    dx = np.empty(in_shape, np.float32)
+    lib().orc_global_avgpool2d_bwd_f32(_p(g), _p(dx), B * Cc, H * W)
+    return dx
+
+
+def batchnorm1d_train_f32(x, gamma, beta, eps=1e-5, running_mean=None, running_var=None, momentum=0.1):
+    """batchnorm1d_training + the layer's running-statistics update; returns
+    (y, batch_mean, batch_var, running_mean, running_var)."""
+    x, gamma, beta = _f32(x), _f32(gamma).reshape(-1), _f32(beta).reshape(-1)
+    B, F = x.shape
+    y, mean, var = np.empty_like(x), np.empty(F, np.float32), np.empty(F, np.float32)
+    rm = _f32(running_mean).reshape(-1).copy() if running_mean is not None else None
+    rv = _f32(running_var).reshape(-1).copy() if running_var is not None else None
+    lib().orc_batchnorm1d_train_f32(_p(x), B, F, _p(gamma), _p(beta), C.c_double(eps), _p(y), _p(mean), _p(var),
+                                    _p(rm), _p(rv), C.c_double(momentum))
+    return y, mean, var, rm, rv
+
+
+def batchnorm1d_infer_f32(x, gamma, beta, running_mean, running_var, eps=1e-5):
+    x = _f32(x)
+    B, F = x.shape
+    y = np.empty_like(x)
+    lib().orc_batchnorm1d_infer_f32(_p(x), B, F, _p(_f32(gamma).reshape(-1)), _p(_f32(beta).reshape(-1)),
+                                    _p(_f32(running_mean).reshape(-1)), _p(_f32(running_var).reshape(-1)),
+                                    C.c_double(eps), _p(y))
+    return y
+
+
+def batchnorm1d_bwd_f32(g, x, gamma, mean, var, eps=1e-5):
+    g, x = _f32(g), _f32(x)
+    B, F = x.shape
+    dx, dgamma, dbeta = np.empty_like(x), np.empty(F, np.float32), np.empty(F, np.float32)
+    lib().orc_batchnorm1d_bwd_f32(_p(g), _p(x), B, F, _p(_f32(gamma).reshape(-1)), _p(_f32(mean).reshape(-1)),
+                                  _p(_f32(var).reshape(-1)), C.c_double(eps), _p(dx), _p(dgamma), _p(dbeta))
+    return dx, dgamma, dbeta
+
+
+def sgd_step_f32(grad, theta, lr):
+    """internal.sgd_optimize (nn/internal/optimizers.v:6-13)."""
+    grad, theta = _f32(grad), _f32(theta).copy()
+    lib().orc_sgd_step_f32(_p(grad), _p(theta), C.c_size_t(grad.size), C.c_double(lr))
+    return theta
+
+
+def rmsprop_step_f32(grad, theta, sq_avg, lr, alpha=0.99, eps=1e-8, wd=0.0):
+    """RMSPropOptimizer.update (nn/optimizers/rmsprop.v:70-91)."""
+    grad, theta, sq = _f32(grad), _f32(theta).copy(), _f32(sq_avg).copy()
+    lib().orc_rmsprop_step_f32(_p(grad), _p(theta), _p(sq), C.c_size_t(grad.size), C.c_double(lr),
+                               C.c_double(alpha), C.c_double(eps), C.c_double(wd))
+    return theta, sq
+
+
 # ---------------------------------------------------------------- int8
 def quant_rows_i8(A):
     """Symmetric per-row int8 quantisation -> (codes int8 [M,K], scale f32 [M])."""

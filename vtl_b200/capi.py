@@ -62,6 +62,17 @@ _PROTOS = {
     "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
     "vtlb_ckpt_encode_f32": [_vp, _vp, _sz, _vp],
     "vtlb_copy_h2d_async": [_vp, _vp, _vp, _sz],
+    "vtlb_sgd_step_f32": [_vp, _i, _vp, _d, _i],
+    "vtlb_rmsprop_step_f32": [_vp, _i, _vp, _d, _d, _d, _d, _i],
+    "vtlb_softmax_fwd_f32": [_vp, _vp, _sz, _sz, _vp],
+    "vtlb_softmax_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp],
+    "vtlb_avgpool2d_fwd_f32": [_vp, _vp, _vp] + [_i] * 10,
+    "vtlb_avgpool2d_bwd_f32": [_vp, _vp, _vp] + [_i] * 10,
+    "vtlb_global_avgpool2d_fwd_f32": [_vp, _vp, _vp] + [_i] * 4,
+    "vtlb_global_avgpool2d_bwd_f32": [_vp, _vp, _vp] + [_i] * 4,
+    "vtlb_batchnorm1d_train_f32": [_vp, _vp, _i, _i, _vp, _vp, _d, _vp, _vp, _vp, _vp, _vp, _d],
+    "vtlb_batchnorm1d_infer_f32": [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _d, _vp],
+    "vtlb_batchnorm1d_bwd_f32": [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _d, _vp, _vp, _vp],
     "vtlb_copy_d2h_async": [_vp, _vp, _vp, _sz],
     "vtlb_copy_wait": [_vp, _i],
     "vtlb_gather_rows_f32": [_vp, _vp, _i, _sz, _vp, _i, _vp, _i],
@@ -363,6 +374,43 @@ class Device:
     def adamw_step_f32(self, table, beta1, beta2, lr_t, eps, wd, zero_grad=True):
         self._ck(self.lib.vtlb_adamw_step_f32(self.h, len(table), table, beta1, beta2, lr_t, eps,
                                               wd, int(zero_grad)))
+
+    def sgd_step_f32(self, table, lr, zero_grad=True):
+        self._ck(self.lib.vtlb_sgd_step_f32(self.h, len(table), table, lr, int(zero_grad)))
+
+    def rmsprop_step_f32(self, table, lr, alpha, eps, wd, zero_grad=True):
+        self._ck(self.lib.vtlb_rmsprop_step_f32(self.h, len(table), table, lr, alpha, eps, wd, int(zero_grad)))
+
+    # -- layers next to the GEMMs
+    def softmax_fwd_f32(self, x, rows, n, y):
+        self._ck(self.lib.vtlb_softmax_fwd_f32(self.h, _ptr(x), rows, n, _ptr(y)))
+
+    def softmax_bwd_f32(self, g, x, rows, n, dx):
+        self._ck(self.lib.vtlb_softmax_bwd_f32(self.h, _ptr(g), _ptr(x), rows, n, _ptr(dx)))
+
+    def avgpool2d_fwd_f32(self, x, y, B, Cc, H, W, kh, kw, ph, pw, sh, sw):
+        self._ck(self.lib.vtlb_avgpool2d_fwd_f32(self.h, _ptr(x), _ptr(y), B, Cc, H, W, kh, kw, ph, pw, sh, sw))
+
+    def avgpool2d_bwd_f32(self, g, dx, B, Cc, H, W, kh, kw, ph, pw, sh, sw):
+        self._ck(self.lib.vtlb_avgpool2d_bwd_f32(self.h, _ptr(g), _ptr(dx), B, Cc, H, W, kh, kw, ph, pw, sh, sw))
+
+    def global_avgpool2d_fwd_f32(self, x, y, B, Cc, H, W):
+        self._ck(self.lib.vtlb_global_avgpool2d_fwd_f32(self.h, _ptr(x), _ptr(y), B, Cc, H, W))
+
+    def global_avgpool2d_bwd_f32(self, g, dx, B, Cc, H, W):
+        self._ck(self.lib.vtlb_global_avgpool2d_bwd_f32(self.h, _ptr(g), _ptr(dx), B, Cc, H, W))
+
+    def batchnorm1d_train_f32(self, x, B, F, gamma, beta, eps, y, mean, var, rmean=None, rvar=None, momentum=0.1):
+        self._ck(self.lib.vtlb_batchnorm1d_train_f32(self.h, _ptr(x), B, F, _ptr(gamma), _ptr(beta), eps, _ptr(y),
+                                                     _ptr(mean), _ptr(var), _ptr(rmean), _ptr(rvar), momentum))
+
+    def batchnorm1d_infer_f32(self, x, B, F, gamma, beta, rmean, rvar, eps, y):
+        self._ck(self.lib.vtlb_batchnorm1d_infer_f32(self.h, _ptr(x), B, F, _ptr(gamma), _ptr(beta), _ptr(rmean),
+                                                     _ptr(rvar), eps, _ptr(y)))
+
+    def batchnorm1d_bwd_f32(self, g, x, B, F, gamma, mean, var, eps, dx=None, dgamma=None, dbeta=None):
+        self._ck(self.lib.vtlb_batchnorm1d_bwd_f32(self.h, _ptr(g), _ptr(x), B, F, _ptr(gamma), _ptr(mean), _ptr(var),
+                                                   eps, _ptr(dx), _ptr(dgamma), _ptr(dbeta)))
 
     # -- int8
     def i8_ld(self, K: int) -> int:

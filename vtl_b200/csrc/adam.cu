@@ -1,11 +1,13 @@
-// Fused multi-tensor Adam / AdamW.  One launch updates every parameter tensor
+// Fused multi-tensor optimizer steps: Adam, AdamW, SGD, RMSProp.  One launch updates every parameter tensor
 // of the model: 28 bytes of HBM traffic per parameter (read g, theta, m, v;
 // write theta, m, v), 32 with the fused gradient clear.
 //
 // Adam follows adam_step_f32_cpu (nn/optimizers/adam_step_f32.v:6-21) in f32
 // with each operation rounded on its own; AdamW follows AdamWOptimizer.update
 // (nn/optimizers/adamw.v:84-104): f64 arithmetic on f32 state, m and v rounded
-// to f32 before the parameter update reads them.
+// to f32 before the parameter update reads them.  SGD follows internal.sgd_optimize
+// (nn/internal/optimizers.v:6-13: theta - (f32)lr * g in f32, 12 bytes per parameter) and RMSProp
+// RMSPropOptimizer.update (nn/optimizers/rmsprop.v:70-91: f64 arithmetic on f32 state, 20 bytes).
 #include "common.cuh"
 
 namespace {
@@ -23,6 +25,7 @@ struct Table {
 };
 
 struct AdamF32 {
+  static constexpr bool kUseM = true, kUseV = true;
   float b1, b2, omb1, omb2, lr, eps;
   __device__ __forceinline__ void operator()(float g, float& th, float& m, float& v) const {
     m = __fadd_rn(__fmul_rn(b1, m), __fmul_rn(omb1, g));
@@ -33,6 +36,7 @@ struct AdamF32 {
 };
 
 struct AdamWF64 {
+  static constexpr bool kUseM = true, kUseV = true;
   double b1, b2, omb1, omb2, lr_t, eps, wd;
   __device__ __forceinline__ void operator()(float g, float& th, float& m, float& v) const {
     const double gd = (double)g;
@@ -41,6 +45,26 @@ struct AdamWF64 {
     const double t = (double)th, mm = (double)m, vv = (double)v;
     const double upd = __dadd_rn(__ddiv_rn(mm, __dadd_rn(__dsqrt_rn(vv), eps)), __dmul_rn(wd, t));
     th = (float)__dsub_rn(t, __dmul_rn(lr_t, upd));
+  }
+};
+
+struct SgdF32 {  // no state
+  static constexpr bool kUseM = false, kUseV = false;
+  float lr;
+  __device__ __forceinline__ void operator()(float g, float& th, float&, float&) const {
+    th = __fsub_rn(th, __fmul_rn(lr, g));
+  }
+};
+
+struct RmsPropF64 {  // v = running average of the squared gradient
+  static constexpr bool kUseM = false, kUseV = true;
+  double lr, alpha, oma, eps, wd;
+  __device__ __forceinline__ void operator()(float g, float& th, float&, float& v) const {
+    const double gd = (double)g;
+    v = (float)__dadd_rn(__dmul_rn(alpha, (double)v), __dmul_rn(__dmul_rn(oma, gd), gd));
+    const double t = (double)th, vv = (double)v;
+    const double upd = __dadd_rn(__ddiv_rn(gd, __dadd_rn(__dsqrt_rn(vv), eps)), __dmul_rn(wd, t));
+    th = (float)__dsub_rn(t, __dmul_rn(lr, upd));
   }
 };
 
@@ -56,32 +80,36 @@ __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ Table
   float* __restrict__ th = tb.th[ti];
   float* __restrict__ m = tb.m[ti];
   float* __restrict__ v = tb.v[ti];
-  const bool vec = ((((uintptr_t)g) | ((uintptr_t)th) | ((uintptr_t)m) | ((uintptr_t)v)) & 15u) == 0;
+  const bool vec = ((((uintptr_t)g) | ((uintptr_t)th) | (Op::kUseM ? (uintptr_t)m : 0) |
+                     (Op::kUseV ? (uintptr_t)v : 0)) & 15u) == 0;
   size_t i = start;
   if (vec) {
     const size_t vend = start + ((end - start) & ~(size_t)3);
     for (size_t j = start + threadIdx.x * 4; j < vend; j += 256 * 4) {
       float4 g4 = *reinterpret_cast<const float4*>(g + j);
       float4 t4 = *reinterpret_cast<float4*>(th + j);
-      float4 m4 = *reinterpret_cast<float4*>(m + j);
-      float4 v4 = *reinterpret_cast<float4*>(v + j);
+      float4 m4 = make_float4(0.f, 0.f, 0.f, 0.f), v4 = m4;
+      if constexpr (Op::kUseM) m4 = *reinterpret_cast<float4*>(m + j);
+      if constexpr (Op::kUseV) v4 = *reinterpret_cast<float4*>(v + j);
       op(g4.x, t4.x, m4.x, v4.x);
       op(g4.y, t4.y, m4.y, v4.y);
       op(g4.z, t4.z, m4.z, v4.z);
       op(g4.w, t4.w, m4.w, v4.w);
       *reinterpret_cast<float4*>(th + j) = t4;
-      *reinterpret_cast<float4*>(m + j) = m4;
-      *reinterpret_cast<float4*>(v + j) = v4;
+      if constexpr (Op::kUseM) *reinterpret_cast<float4*>(m + j) = m4;
+      if constexpr (Op::kUseV) *reinterpret_cast<float4*>(v + j) = v4;
       if (zero_grad) *reinterpret_cast<float4*>(g + j) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     i = vend;
   }
   for (size_t j = i + threadIdx.x; j < end; j += 256) {
-    float tt = th[j], mm = m[j], vv = v[j];
+    float tt = th[j], mm = 0.0f, vv = 0.0f;
+    if constexpr (Op::kUseM) mm = m[j];
+    if constexpr (Op::kUseV) vv = v[j];
     op(g[j], tt, mm, vv);
     th[j] = tt;
-    m[j] = mm;
-    v[j] = vv;
+    if constexpr (Op::kUseM) m[j] = mm;
+    if constexpr (Op::kUseV) v[j] = vv;
     if (zero_grad) g[j] = 0.0f;
   }
 }
@@ -99,7 +127,7 @@ int run(vtlb_ctx* ctx, const char* fn, int n_tensors, const vtlb_adam_tensor* te
     while (i < n_tensors && tb.nt < MAXT) {
       const vtlb_adam_tensor& t = tensors[i++];
       if (t.n == 0) continue;
-      if (!t.d_grad || !t.d_theta || !t.d_m || !t.d_v)
+      if (!t.d_grad || !t.d_theta || (Op::kUseM && !t.d_m) || (Op::kUseV && !t.d_v))
         return vtlb_fail(ctx, VTLB_EINVAL, "%s: tensor %d has a null pointer", fn, i - 1);
       const int k = tb.nt++;
       tb.g[k] = (float*)t.d_grad;
@@ -135,4 +163,19 @@ VTLB_API int vtlb_adamw_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_t
   VTLB_ENTER(ctx);
   AdamWF64 op{beta1, beta2, 1.0 - beta1, 1.0 - beta2, lr_t, epsilon, weight_decay};
   return run(ctx, "vtlb_adamw_step_f32", n_tensors, tensors, op, zero_grad);
+}
+
+VTLB_API int vtlb_sgd_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors, double learning_rate,
+                               int zero_grad) {
+  VTLB_ENTER(ctx);
+  SgdF32 op{(float)learning_rate};
+  return run(ctx, "vtlb_sgd_step_f32", n_tensors, tensors, op, zero_grad);
+}
+
+VTLB_API int vtlb_rmsprop_step_f32(vtlb_ctx* ctx, int n_tensors, const vtlb_adam_tensor* tensors,
+                                   double learning_rate, double alpha, double epsilon, double weight_decay,
+                                   int zero_grad) {
+  VTLB_ENTER(ctx);
+  RmsPropF64 op{learning_rate, alpha, 1.0 - alpha, epsilon, weight_decay};
+  return run(ctx, "vtlb_rmsprop_step_f32", n_tensors, tensors, op, zero_grad);
 }
