@@ -59,13 +59,15 @@ def decode_tensor(encoded: str, shape, dtype=np.float32) -> np.ndarray:
 
 
 # ---------------------------------------------------------------- whole files
-_WEIGHT_KEYS = {"LinearLayer": ("weight", "bias"), "Conv2DLayer": ("weight", "bias")}
+_WEIGHT_KEYS = {"LinearLayer": ("weight", "bias"), "Conv2DLayer": ("weight", "bias"),
+                "BatchNorm1DLayer": ("gamma", "beta")}
 
 
 def layer_defs(spec):
     """spec: the layer list of tests' SequentialOracle / the host mirror's builder calls:
     ("input", shape) | ("linear", out) | ("relu",) | ("flatten",) |
-    ("conv2d", in_ch, out_ch, kh, kw, ph, pw, sh, sw) | ("maxpool2d", kh, kw, ph, pw, sh, sw).
+    ("conv2d", in_ch, out_ch, kh, kw, ph, pw, sh, sw) | ("maxpool2d", kh, kw, ph, pw, sh, sw) |
+    ("avgpool2d", kh, kw, ph, pw, sh, sw) | ("global_avgpool2d",) | ("softmax",) | ("batchnorm1d", F).
     Returns [(layer_type, in_shape, config, [param shapes])] as save_checkpoint would see them."""
     out = []
     cur = []
@@ -103,6 +105,22 @@ def layer_defs(spec):
                    "stride_w": sw}
             out.append(("MaxPool2DLayer", in_shape, cfg, []))
             cur = [cur[0], (cur[1] + 2 * ph - kh) // sh + 1, (cur[2] + 2 * pw - kw) // sw + 1]
+        elif kind == "avgpool2d":
+            _, kh, kw, ph, pw, sh, sw = item
+            cfg = {"kernel_h": kh, "kernel_w": kw, "padding_h": ph, "padding_w": pw, "stride_h": sh,
+                   "stride_w": sw}
+            out.append(("AvgPool2DLayer", in_shape, cfg, []))
+            cur = [cur[0], (cur[1] + 2 * ph - kh) // sh + 1, (cur[2] + 2 * pw - kw) // sw + 1]
+        elif kind == "global_avgpool2d":
+            out.append(("GlobalAvgPool2DLayer", in_shape, {}, []))
+            cur = [cur[0], 1, 1]
+        elif kind == "softmax":
+            out.append(("SoftmaxLayer", in_shape, {}, []))
+            cur = []  # SoftmaxLayer.output_shape() is empty in the reference (nn/layers/softmax.v:36-38)
+        elif kind == "batchnorm1d":
+            f = int(item[1])
+            out.append(("BatchNorm1DLayer", in_shape, {"num_features": f}, [[1, f], [1, f]]))
+            cur = [f]
         else:
             raise ValueError(f"unknown layer {kind}")
     return out

@@ -92,6 +92,8 @@ def sess():
 CNN = [("input", [3, 8, 8]), ("conv2d", 3, 4, 3, 3, 1, 1, 1, 1), ("relu",), ("maxpool2d", 2, 2, 0, 0, 2, 2),
        ("flatten",), ("linear", 5)]
 MLP = [("input", [6]), ("linear", 7), ("relu",), ("linear", 3)]
+BNM = [("input", [2, 4, 4]), ("avgpool2d", 2, 2, 0, 0, 2, 2), ("flatten",), ("linear", 5), ("batchnorm1d", 5),
+       ("relu",), ("linear", 3), ("softmax",)]
 
 
 def build(sess, spec, loss="mse", opt="adam"):
@@ -111,6 +113,14 @@ def build(sess, spec, loss="mse", opt="adam"):
             m.conv2d(item[1], item[2], (item[3], item[4]), padding=(item[5], item[6]), stride=(item[7], item[8]))
         elif kind == "maxpool2d":
             m.maxpool2d((item[1], item[2]), (item[3], item[4]), (item[5], item[6]))
+        elif kind == "avgpool2d":
+            m.avgpool2d((item[1], item[2]), (item[3], item[4]), (item[5], item[6]))
+        elif kind == "global_avgpool2d":
+            m.global_avgpool2d()
+        elif kind == "softmax":
+            m.softmax()
+        elif kind == "batchnorm1d":
+            m.batchnorm1d(item[1])
     m.mse_loss() if loss == "mse" else m.softmax_cross_entropy_loss()
     m.adam(lr=1e-2) if opt == "adam" else m.adamw(lr=1e-2)
     return m
@@ -123,7 +133,7 @@ def random_params(m, rng):
     return ps
 
 
-@pytest.mark.parametrize("spec", [MLP, CNN], ids=["mlp", "cnn"])
+@pytest.mark.parametrize("spec", [MLP, CNN, BNM], ids=["mlp", "cnn", "batchnorm"])
 def test_saved_file_is_what_the_oracle_writes(sess, tmp_path, spec):
     rng = np.random.default_rng(11)
     m = build(sess, spec)
@@ -139,7 +149,7 @@ def test_saved_file_is_what_the_oracle_writes(sess, tmp_path, spec):
     m.close()
 
 
-@pytest.mark.parametrize("spec", [MLP, CNN], ids=["mlp", "cnn"])
+@pytest.mark.parametrize("spec", [MLP, CNN, BNM], ids=["mlp", "cnn", "batchnorm"])
 def test_load_weights_from_an_oracle_file(sess, tmp_path, spec):
     from vtl_b200 import host
     rng = np.random.default_rng(12)

@@ -243,6 +243,7 @@ void decode_tensor_into(const std::string& encoded, const Tensor& dst) {
 
 const char* weight_key(const std::string& layer_type, size_t j, std::string& scratch) {
   if (layer_type == "LinearLayer" || layer_type == "Conv2DLayer") return j == 0 ? "weight" : "bias";
+  if (layer_type == "BatchNorm1DLayer" && j < 2) return j == 0 ? "gamma" : "beta";
   scratch = "var_" + std::to_string(j);
   return scratch.c_str();
 }

@@ -224,6 +224,54 @@ struct MaxPool2DLayer : Layer {
   }
 };
 
+// nn/layers/softmax.v: softmax over the last dimension; output_shape() is empty as in the reference
+struct SoftmaxLayer : Layer {
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override { return {}; }
+  const char* kind() const override { return "softmax"; }
+  const char* type_name() const override { return "SoftmaxLayer"; }
+};
+
+// nn/layers/pool.v: average pooling (backward: the standard rule, see include/vtlb.h)
+struct AvgPool2DLayer : Layer {
+  std::vector<int> in_shape;  // [C, H, W]
+  int kh, kw, ph, pw, sh, sw;
+  AvgPool2DLayer(std::vector<int> in_shape, int kh, int kw, int ph, int pw, int sh, int sw);
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override;
+  const char* kind() const override { return "avgpool2d"; }
+  const char* type_name() const override { return "AvgPool2DLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override {
+    return {{"kernel_h", kh}, {"kernel_w", kw}, {"padding_h", ph}, {"padding_w", pw}, {"stride_h", sh}, {"stride_w", sw}};
+  }
+};
+struct GlobalAvgPool2DLayer : Layer {
+  std::vector<int> in_shape;  // [C, H, W]
+  explicit GlobalAvgPool2DLayer(std::vector<int> s) : in_shape(std::move(s)) {}
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<int> output_shape() const override { return {in_shape[0], 1, 1}; }
+  const char* kind() const override { return "global_avgpool2d"; }
+  const char* type_name() const override { return "GlobalAvgPool2DLayer"; }
+};
+
+// nn/layers/batchnorm.v:16-108 -- gamma, beta [1, F]; running statistics are plain tensors
+struct BatchNorm1DConfig {
+  double eps = 1e-5, momentum = 0.1;
+};
+struct BatchNorm1DLayer : Layer {
+  VarPtr gamma, beta;
+  Tensor running_mean, running_var;
+  int num_features, num_batches_tracked = 0;
+  double eps, momentum;
+  BatchNorm1DLayer(Context* ctx, int num_features, BatchNorm1DConfig c);
+  VarPtr forward(const VarPtr& input) override;
+  std::vector<VarPtr> variables() override { return {gamma, beta}; }
+  std::vector<int> output_shape() const override { return {num_features}; }
+  const char* kind() const override { return "batchnorm1d"; }
+  const char* type_name() const override { return "BatchNorm1DLayer"; }
+  std::vector<std::pair<std::string, int>> config() const override { return {{"num_features", num_features}}; }
+};
+
 // nn/types/loss.v:7-27, nn/loss/mse.v:30-41, nn/loss/softmax_cross_entropy.v
 struct Loss {
   virtual ~Loss() = default;
@@ -250,6 +298,10 @@ class Sequential {
   void flatten();
   void conv2d(int in_channels, int out_channels, int kh, int kw, Conv2DConfig cfg);
   void maxpool2d(int kh, int kw, int ph, int pw, int sh, int sw);
+  void softmax();
+  void avgpool2d(int kh, int kw, int ph, int pw, int sh, int sw);
+  void global_avgpool2d();
+  void batchnorm1d(int num_features, BatchNorm1DConfig c = {});
   void mse_loss();
   void softmax_cross_entropy_loss();
   VarPtr forward(const VarPtr& train);                                  // sequential.v:204-215
@@ -284,6 +336,29 @@ class AdamOptimizer {
   bool adamw;
   std::vector<VarPtr> params;
   std::vector<Tensor> first_moments, second_moments;
+};
+
+// nn/optimizers/sgd.v:9-52 and rmsprop.v:19-91
+class SgdOptimizer {
+ public:
+  explicit SgdOptimizer(double lr) : learning_rate(lr) {}
+  void build_params(const std::vector<std::unique_ptr<Layer>>& layers);
+  void update();
+  double learning_rate;
+  std::vector<VarPtr> params;
+};
+struct RMSPropConfig {
+  double learning_rate = 0.001, alpha = 0.99, epsilon = 1e-8, weight_decay = 0.0;
+};
+class RMSPropOptimizer {
+ public:
+  explicit RMSPropOptimizer(RMSPropConfig c)
+      : learning_rate(c.learning_rate), epsilon(c.epsilon), alpha(c.alpha), weight_decay(c.weight_decay) {}
+  void build_params(const std::vector<std::unique_ptr<Layer>>& layers);
+  void update();
+  double learning_rate, epsilon, alpha, weight_decay;
+  std::vector<VarPtr> params;
+  std::vector<Tensor> sq_avg;
 };
 
 // datasets.DataLoader (datasets/dataloader.v:19-331) over device-resident dataset and label

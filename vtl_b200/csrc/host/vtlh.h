@@ -33,6 +33,15 @@ int vtlh_model_set_fuse_relu(vtlh_model* m, int on);
 int vtlh_model_adam(vtlh_model* m, double lr, double beta1, double beta2, double eps);
 int vtlh_model_adamw(vtlh_model* m, double lr, double beta1, double beta2, double eps, double wd);
 
+int vtlh_model_sgd(vtlh_model* m, double lr);
+int vtlh_model_rmsprop(vtlh_model* m, double lr, double alpha, double eps, double wd);
+int vtlh_model_softmax(vtlh_model* m);
+int vtlh_model_avgpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw);
+int vtlh_model_global_avgpool2d(vtlh_model* m);
+int vtlh_model_batchnorm1d(vtlh_model* m, int num_features, double eps, double momentum);
+int vtlh_model_get_running_stat(vtlh_model* m, int bn_index, int which, float* host); /* 0 mean, 1 variance */
+int vtlh_model_get_sq_avg(vtlh_model* m, int i, float* host);
+
 int vtlh_model_num_params(vtlh_model* m);
 int vtlh_model_param_size(vtlh_model* m, int i, size_t* n);
 int vtlh_model_set_param(vtlh_model* m, int i, const float* host);

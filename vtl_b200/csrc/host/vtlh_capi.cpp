@@ -16,6 +16,8 @@ struct vtlh_model {
   Session* s;
   std::unique_ptr<Sequential> seq;
   std::unique_ptr<AdamOptimizer> opt;
+  std::unique_ptr<SgdOptimizer> sgd;
+  std::unique_ptr<RMSPropOptimizer> rms;
   std::vector<VarPtr> params;
   VarPtr last_input;
 };
@@ -102,6 +104,8 @@ static void collect_params(vtlh_model* m) {
 }
 int vtlh_model_adam(vtlh_model* m, double lr, double b1, double b2, double eps) {
   return guard([&] {
+    m->sgd.reset();
+    m->rms.reset();
     m->opt = std::make_unique<AdamOptimizer>(AdamConfig{lr, b1, b2, eps, 0.0}, false);
     m->opt->build_params(m->seq->layers);
     collect_params(m);
@@ -109,9 +113,61 @@ int vtlh_model_adam(vtlh_model* m, double lr, double b1, double b2, double eps) 
 }
 int vtlh_model_adamw(vtlh_model* m, double lr, double b1, double b2, double eps, double wd) {
   return guard([&] {
+    m->sgd.reset();
+    m->rms.reset();
     m->opt = std::make_unique<AdamOptimizer>(AdamConfig{lr, b1, b2, eps, wd}, true);
     m->opt->build_params(m->seq->layers);
     collect_params(m);
+  });
+}
+
+int vtlh_model_sgd(vtlh_model* m, double lr) {
+  return guard([&] {
+    m->opt.reset();
+    m->rms.reset();
+    m->sgd = std::make_unique<SgdOptimizer>(lr);
+    m->sgd->build_params(m->seq->layers);
+    collect_params(m);
+  });
+}
+int vtlh_model_rmsprop(vtlh_model* m, double lr, double alpha, double eps, double wd) {
+  return guard([&] {
+    m->opt.reset();
+    m->sgd.reset();
+    m->rms = std::make_unique<RMSPropOptimizer>(RMSPropConfig{lr, alpha, eps, wd});
+    m->rms->build_params(m->seq->layers);
+    collect_params(m);
+  });
+}
+int vtlh_model_softmax(vtlh_model* m) {
+  return guard([&] { m->seq->softmax(); });
+}
+int vtlh_model_avgpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw) {
+  return guard([&] { m->seq->avgpool2d(kh, kw, ph, pw, sh, sw); });
+}
+int vtlh_model_global_avgpool2d(vtlh_model* m) {
+  return guard([&] { m->seq->global_avgpool2d(); });
+}
+int vtlh_model_batchnorm1d(vtlh_model* m, int num_features, double eps, double momentum) {
+  return guard([&] { m->seq->batchnorm1d(num_features, BatchNorm1DConfig{eps, momentum}); });
+}
+// running statistics of the i-th BatchNorm1D layer of the model (which = 0: mean, 1: variance)
+int vtlh_model_get_running_stat(vtlh_model* m, int bn_index, int which, float* host) {
+  return guard([&] {
+    int k = 0;
+    for (auto& l : m->seq->layers)
+      if (!std::strcmp(l->kind(), "batchnorm1d") && k++ == bn_index) {
+        auto* bn = static_cast<BatchNorm1DLayer*>(l.get());
+        (which ? bn->running_var : bn->running_mean).to_array(host);
+        return;
+      }
+    throw Error(VTLB_EINVAL, "no such BatchNorm1D layer");
+  });
+}
+int vtlh_model_get_sq_avg(vtlh_model* m, int i, float* host) {
+  return guard([&] {
+    if (!m->rms || i < 0 || i >= (int)m->rms->sq_avg.size()) throw Error(VTLB_EINVAL, "no RMSProp optimizer or bad index");
+    m->rms->sq_avg[i].to_array(host);
   });
 }
 
@@ -186,8 +242,14 @@ int vtlh_model_train_step(vtlh_model* m, const void* d_x, int ndim, const int* x
     VarPtr l = m->seq->loss(y, t, global_rows > 0 ? global_rows : -1);
     l->backprop();
     if (do_update) {
-      if (!m->opt) throw Error(VTLB_ESTATE, "train_step: no optimizer configured");
-      m->opt->update();
+      if (m->opt)
+        m->opt->update();
+      else if (m->sgd)
+        m->sgd->update();
+      else if (m->rms)
+        m->rms->update();
+      else
+        throw Error(VTLB_ESTATE, "train_step: no optimizer configured");
     } else if (m->s->nranks > 1) {
       m->s->check(vtlb_comm_wait(m->s->ctx));
     }

@@ -50,6 +50,10 @@ def load() -> C.CDLL:
             "vtlh_model_train_step": [vp, vp, i, ip, vp, i, ip, i, i, C.POINTER(C.c_float)],
             "vtlh_model_get_input_grad": [vp, vp], "vtlh_model_zero_grad": [vp],
             "vtlh_matmul_mse_backprop": [vp, vp, i, i, vp, i, vp, vp, vp, vp, vp],
+            "vtlh_model_sgd": [vp, d], "vtlh_model_rmsprop": [vp, d, d, d, d],
+            "vtlh_model_softmax": [vp], "vtlh_model_avgpool2d": [vp] + [i] * 6,
+            "vtlh_model_global_avgpool2d": [vp], "vtlh_model_batchnorm1d": [vp, i, d, d],
+            "vtlh_model_get_running_stat": [vp, i, i, vp], "vtlh_model_get_sq_avg": [vp, i, vp],
             "vtlh_model_save_checkpoint": [vp, C.c_char_p, i, d, i],
             "vtlh_model_load_weights": [vp, C.c_char_p, i],
             "vtlh_load_checkpoint": [C.c_char_p, ip, C.POINTER(d)],
@@ -144,6 +148,33 @@ class Model:
     def maxpool2d(self, kernel, padding, stride):
         _ck(self.lib.vtlh_model_maxpool2d(self.h, kernel[0], kernel[1], padding[0], padding[1], stride[0],
                                           stride[1]))
+
+    def softmax(self):
+        _ck(self.lib.vtlh_model_softmax(self.h))
+
+    def avgpool2d(self, kernel, padding, stride):
+        _ck(self.lib.vtlh_model_avgpool2d(self.h, kernel[0], kernel[1], padding[0], padding[1], stride[0],
+                                          stride[1]))
+
+    def global_avgpool2d(self):
+        _ck(self.lib.vtlh_model_global_avgpool2d(self.h))
+
+    def batchnorm1d(self, num_features, eps=1e-5, momentum=0.1):
+        _ck(self.lib.vtlh_model_batchnorm1d(self.h, int(num_features), float(eps), float(momentum)))
+
+    def running_stat(self, bn_index, num_features, variance=False):
+        out = np.empty(num_features, np.float32)
+        _ck(self.lib.vtlh_model_get_running_stat(self.h, bn_index, int(variance), out.ctypes.data))
+        return out
+
+    def sgd(self, lr=1e-3):
+        _ck(self.lib.vtlh_model_sgd(self.h, lr))
+
+    def rmsprop(self, lr=1e-3, alpha=0.99, eps=1e-8, weight_decay=0.0):
+        _ck(self.lib.vtlh_model_rmsprop(self.h, lr, alpha, eps, weight_decay))
+
+    def get_sq_avg(self, i):
+        return self._get(self.lib.vtlh_model_get_sq_avg, i)
 
     def mse_loss(self):
         _ck(self.lib.vtlh_model_mse_loss(self.h))
