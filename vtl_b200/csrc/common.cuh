@@ -28,8 +28,12 @@ struct vtlb_ctx {
   uint32_t* d_status = nullptr;        // device status word
   void* scratch = nullptr;             // operand-split buffers, partial sums
   size_t scratch_bytes = 0;
-  // INT8 pair GEMM, K-split final wave: flags + parked accumulators (allocated on first use);
-  // every launch that splits stamps its flags with a fresh epoch, so nothing is ever reset.
+  // INT8 pair GEMM, K-split tiles: flags + parked accumulators (kKsplitBytes, allocated with the
+  // context so that no launch ever allocates); every launch that splits stamps its flags with a
+  // fresh epoch, so nothing is ever reset.
+  static constexpr size_t kKsplitTiles = 64;  // cut tiles per launch at most (half of the CTA pairs)
+  static constexpr size_t kKsplitFlagBytes = kKsplitTiles * 2 * 8 * 4;       // [tile][rank][epilogue warp]
+  static constexpr size_t kKsplitBytes = kKsplitFlagBytes + kKsplitTiles * 256 * 256 * 4;
   void* ksplit_buf = nullptr;
   uint32_t ksplit_epoch = 0;
   void* comm = nullptr;  // ncclComm_t

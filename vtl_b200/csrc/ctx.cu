@@ -71,7 +71,9 @@ VTLB_API int vtlb_ctx_create(int device, vtlb_ctx** out) {
       (e = cudaEventCreateWithFlags(&ctx->ev_compute, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming)) != cudaSuccess ||
       (e = cudaMalloc(&ctx->d_status, 256)) != cudaSuccess ||
-      (e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess) {
+      (e = cudaMemset(ctx->d_status, 0, 256)) != cudaSuccess ||
+      (e = cudaMalloc(&ctx->ksplit_buf, vtlb_ctx::kKsplitBytes)) != cudaSuccess ||
+      (e = cudaMemset(ctx->ksplit_buf, 0, vtlb_ctx::kKsplitFlagBytes)) != cudaSuccess) {
     int rc = vtlb_fail(nullptr, VTLB_ECUDA, "vtlb_ctx_create: %s", cudaGetErrorString(e));
     vtlb_ctx_destroy(ctx);
     return rc;

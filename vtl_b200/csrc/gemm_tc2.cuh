@@ -132,6 +132,9 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
 constexpr int KSPLIT_MAX_TILES = 64;  // at most half of the CTA pairs of a device
 constexpr int KSPLIT_FLAG_WORDS = KSPLIT_MAX_TILES * 2 * gemm::EPI_WARPS;  // [tile][rank][warp]
 constexpr size_t KSPLIT_BYTES = (size_t)KSPLIT_FLAG_WORDS * 4 + (size_t)KSPLIT_MAX_TILES * 2 * BM * BN2 * 4;
+static_assert(KSPLIT_MAX_TILES == vtlb_ctx::kKsplitTiles && KSPLIT_FLAG_WORDS * 4 == vtlb_ctx::kKsplitFlagBytes &&
+                  KSPLIT_BYTES == vtlb_ctx::kKsplitBytes,
+              "the context allocates the K-split buffer with these sizes");
 
 __device__ __forceinline__ void flag_release(uint32_t* flag, uint32_t value) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
@@ -549,10 +552,6 @@ int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, i
     const int rem = tiles % pairs;
     const int num_kb = (K + 127) / 128;
     if (tiles > pairs && rem > 0 && 2 * rem <= pairs && rem <= KSPLIT_MAX_TILES && num_kb >= 8) split_tiles = rem;
-  }
-  if (split_tiles && !ctx->ksplit_buf) {
-    VTLB_CUDA(ctx, cudaMalloc(&ctx->ksplit_buf, KSPLIT_BYTES));
-    VTLB_CUDA(ctx, cudaMemsetAsync(ctx->ksplit_buf, 0, (size_t)KSPLIT_FLAG_WORDS * 4, ctx->stream));
   }
   if (split_tiles && ++ctx->ksplit_epoch == 0) ctx->ksplit_epoch = 1;  // flags hold the epoch of their launch
   kern<<<2 * pairs, NUM_THREADS, C::SMEM_TOTAL, ctx->stream>>>(tm, epi, M, N, K, group_m, a_chunk_k, split_tiles,
