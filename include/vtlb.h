@@ -76,7 +76,12 @@ int vtlb_profile_gemm_read(vtlb_ctx* ctx, double* total_ms, uint64_t* launches, 
  * (storage/cuda_d_cuda.v:32-107), the raw C.cudaMalloc/cudaMemcpy/cudaFree of
  * autograd_cuda/device_session_gpu_d_cuda.v:24-45,118-152 and
  * compute.GpuBufF64{ensure,upload,download,release}
- * (autograd_cuda/device_session_optimizer_d_cuda.v:7-59). */
+ * (autograd_cuda/device_session_optimizer_d_cuda.v:7-59).
+ * vtlb_alloc / vtlb_free are ordered on the context's compute stream (a freed block may be handed
+ * to the next vtlb_alloc at once: whatever is enqueued for the new owner runs after everything that
+ * was enqueued for the old one).  Blocks come from the device's stream-ordered pool; blocks of up to
+ * 1 MiB are additionally recycled by the context itself (up to 256 MiB of them), because a pool call
+ * per small tensor costs more host time than a small kernel takes to run. */
 int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out);
 int vtlb_free(vtlb_ctx* ctx, void* d_ptr);
 int vtlb_h2d(vtlb_ctx* ctx, void* d_dst, const void* h_src, size_t bytes);

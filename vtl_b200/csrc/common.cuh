@@ -7,6 +7,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <unordered_map>
+#include <vector>
+
 #include "../../include/vtlb.h"
 
 #define VTLB_API extern "C" __attribute__((visibility("default")))
@@ -36,6 +39,13 @@ struct vtlb_ctx {
   static constexpr size_t kKsplitBytes = kKsplitFlagBytes + kKsplitTiles * 256 * 256 * 4;
   void* ksplit_buf = nullptr;
   uint32_t ksplit_epoch = 0;
+  // Small blocks (<= kCacheBlockMax) are recycled by the context itself: a training step of a small
+  // model makes dozens of sub-megabyte allocations, and a pool call per tensor costs more host time
+  // than the kernels that use it take to run.  Blocks are reused in stream order, like the pool's.
+  static constexpr size_t kCacheBlockMax = 1u << 20, kCacheTotalMax = 256u << 20;
+  std::unordered_map<void*, size_t> small_live;                 // block -> rounded size
+  std::unordered_map<size_t, std::vector<void*>> small_free;    // rounded size -> free blocks
+  size_t small_cached_bytes = 0;
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
   uint64_t launches = 0;

@@ -90,6 +90,9 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
   if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
   if (ctx->copy_in) cudaStreamSynchronize(ctx->copy_in);
   if (ctx->copy_out) cudaStreamSynchronize(ctx->copy_out);
+  for (auto& kv : ctx->small_free)
+    for (void* p : kv.second) cudaFreeAsync(p, ctx->stream);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->ksplit_buf) cudaFree(ctx->ksplit_buf);
   if (ctx->d_status) cudaFree(ctx->d_status);
@@ -237,6 +240,18 @@ VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
   if (!d_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_alloc: null out");
   *d_out = nullptr;
   if (bytes == 0) return VTLB_OK;
+  const bool small = bytes <= vtlb_ctx::kCacheBlockMax;
+  if (small) {
+    bytes = vtlb_round_up(bytes, 256);
+    auto it = ctx->small_free.find(bytes);
+    if (it != ctx->small_free.end() && !it->second.empty()) {
+      *d_out = it->second.back();
+      it->second.pop_back();
+      ctx->small_cached_bytes -= bytes;
+      ctx->small_live.emplace(*d_out, bytes);
+      return VTLB_OK;
+    }
+  }
   // Stream-ordered allocation from the device's pool: no device-wide synchronisation,
   // and freed blocks are reused by later allocations on the same stream.
   cudaError_t e = cudaMallocAsync(d_out, bytes, ctx->stream);
@@ -244,6 +259,7 @@ VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
     cudaGetLastError();
     return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
   }
+  if (small) ctx->small_live.emplace(*d_out, bytes);
   return VTLB_OK;
 }
 
@@ -255,6 +271,17 @@ VTLB_API int vtlb_free(vtlb_ctx* ctx, void* d_ptr) {
   if (ctx->comm) {
     VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
     VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  }
+  auto it = ctx->small_live.find(d_ptr);
+  if (it != ctx->small_live.end()) {
+    const size_t bytes = it->second;
+    ctx->small_live.erase(it);
+    if (ctx->small_cached_bytes + bytes <= vtlb_ctx::kCacheTotalMax) {
+      // the next owner's work is enqueued on the same stream, after everything that used the block
+      ctx->small_free[bytes].push_back(d_ptr);
+      ctx->small_cached_bytes += bytes;
+      return VTLB_OK;
+    }
   }
   VTLB_CUDA(ctx, cudaFreeAsync(d_ptr, ctx->stream));
   return VTLB_OK;
