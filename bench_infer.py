@@ -76,14 +76,15 @@ class ShardedInt8MLP:
                     dev.comm_wait()
                     waited = issued
                 y = (y_out.ptr if (last and y_out is not None) else L["Y"].ptr) + 4 * c * Mc * n
-                dev.linear_i8_fwd_sharded_a(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K,
-                                            relu=not last)
                 if last:
+                    dev.linear_i8_fwd_sharded_a(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K,
+                                                relu=False)
                     continue
                 amax = L["amax"].ptr + 4 * c * Mc
                 sa_out = L["sa"].ptr + 4 * c * Mc
                 q_all = L["q_all"].ptr + c * R * Mc * n
-                dev.row_absmax_f32(y, Mc, n, amax)
+                # the GEMM's epilogue also leaves the row maxima of its output slab (no second pass over Y)
+                dev.linear_i8_fwd_amax(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K, True, amax)
                 if R > 1:
                     q_loc = L["q_local"].ptr + c * Mc * n
                     dev.allreduce_max_f32_async(amax, Mc)

@@ -257,6 +257,13 @@ int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa, const 
 int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards, const void* d_sa,
                                  const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
                                  void* d_Y, int M, int N, int K, int relu);
+/* The same (shards >= 1) with the row maxima of |Y| written to d_row_amax[M] by the GEMM's epilogue:
+ * what vtlb_row_absmax_f32 would compute from Y, without reading Y again - the next layer's dynamic
+ * quantisation (vtlb_quant_rows_i8 with d_amax_in) can start from it.  The maxima are exact (a
+ * maximum does not depend on the order it is taken in). */
+int vtlb_linear_i8_fwd_amax(vtlb_ctx* ctx, const void* d_Aq_shards, int shards, const void* d_sa,
+                            const void* d_Wq, const void* d_sw, const void* d_bias_or_null, void* d_Y,
+                            int M, int N, int K, int relu, void* d_row_amax);
 
 /* ---- layers next to the GEMMs -------------------------------------------------
  * Softmax over the last dimension of x[rows, n]: forward in f64 (max, exp(x - max), sum in

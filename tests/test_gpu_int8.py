@@ -150,3 +150,29 @@ def test_int8_argument_errors(dev):
         dev.gemm_i8_i32(d.ptr + 1, d, 64, 16, 16, c)  # misaligned operand
     dev.gemm_i8_i32(d, d, 0, 16, 16, c)  # empty M is a no-op
     d.free(); c.free()
+
+
+@pytest.mark.parametrize("M,N,K,relu", [
+    (2, 300, 256, False),            # dp4a path: the maxima come from a pass over Y
+    (200, 328, 400, True),           # single-CTA kernel, TMA-store epilogue
+    (129, 258, 144, False),          # N % 4 != 0: direct stores
+    (2304, 2300, 1024, False),       # CTA pairs with K-split tiles, negative outputs
+    (1024, 4096, 512, True),
+])
+def test_linear_i8_fwd_amax_returns_the_row_maxima_of_its_output(dev, orc, M, N, K, relu):
+    rng = np.random.default_rng(M * 3 + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.01).astype(np.float32)
+    dQw, dSw, wq, sw = _quant_gpu(dev, W)
+    dQa, dSa, _, _ = _quant_gpu(dev, A)
+    db, dY = dev.to_device(b), dev.zeros((M, N), np.float32)
+    dmax = dev.to_device(np.full(M, 7.0, np.float32))  # stale contents must not survive
+    dev.linear_i8_fwd_amax(dQa, 1, dSa, dQw, dSw, db, dY, M, N, K, relu, dmax)
+    assert dev.check_status() == 0
+    ref = orc.linear_i8_fwd(A, wq, sw, b, relu)
+    got = dY.numpy()
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    assert np.array_equal(dmax.numpy().view(np.uint32), np.abs(ref).max(axis=1).view(np.uint32))
+    for buf in (dQw, dSw, dQa, dSa, db, dY, dmax):
+        buf.free()

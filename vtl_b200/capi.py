@@ -61,6 +61,7 @@ _PROTOS = {
     "vtlb_add_inplace_f32": [_vp, _vp, _vp, _sz],
     "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
     "vtlb_ckpt_encode_f32": [_vp, _vp, _sz, _vp],
+    "vtlb_linear_i8_fwd_amax": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "vtlb_copy_h2d_async": [_vp, _vp, _vp, _sz],
     "vtlb_sgd_step_f32": [_vp, _i, _vp, _d, _i],
     "vtlb_rmsprop_step_f32": [_vp, _i, _vp, _d, _d, _d, _d, _i],
@@ -433,6 +434,10 @@ class Device:
     def linear_i8_fwd_sharded_a(self, Aq_shards, shards, sa, Wq, sw, bias, Y, M, N, K, relu=False):
         self._ck(self.lib.vtlb_linear_i8_fwd_sharded_a(self.h, _ptr(Aq_shards), shards, _ptr(sa), _ptr(Wq),
                                                        _ptr(sw), _ptr(bias), _ptr(Y), M, N, K, int(relu)))
+
+    def linear_i8_fwd_amax(self, Aq_shards, shards, sa, Wq, sw, bias, Y, M, N, K, relu, row_amax):
+        self._ck(self.lib.vtlb_linear_i8_fwd_amax(self.h, _ptr(Aq_shards), shards, _ptr(sa), _ptr(Wq), _ptr(sw),
+                                                  _ptr(bias), _ptr(Y), M, N, K, int(relu), _ptr(row_amax)))
 
     # -- collectives
     def comm_unique_id(self) -> bytes:

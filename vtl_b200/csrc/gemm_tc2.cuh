@@ -420,6 +420,7 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           ok = __all_sync(0xffffffffu, __shfl_sync(0xffffffffu, (int)ok, 0) != 0);
           if (!ok) break;
         }
+        float row_amax = 0.0f;
         auto do_chunk = [&](int cc, bool use_pre) {
           const int c = 2 * cc + half;
           uint32_t v[32];
@@ -439,6 +440,7 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
             if (use_pre) {
               VTLB_TR(const long long tr_t = clock64();)
               epi.transform_pre(pre, cc, v);
+              row_amax = fmaxf(row_amax, epi.chunk_amax(n0 + c * 32, v, N));  // one atomic per warp and tile
               VTLB_TR(if (threadIdx.x == 64) gemm::g_epi_trace[blockIdx.x][1] += clock64() - tr_t;)
               gemm::stage_and_store(stg, &tm.out[0], lane, row0, n0 + c * 32, v, M, N);
             } else {
@@ -454,6 +456,7 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
 #pragma unroll 1
           for (int cc = 0; cc < BN2 / 64; ++cc) do_chunk(cc, false);
         }
+        if (fast && kh != 0) epi.commit_amax(row0 + lane, M, row_amax);
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));

@@ -166,6 +166,8 @@ struct EpiStoreI32 {
   struct Pre {};  // nothing to fetch ahead of the accumulator
   __device__ __forceinline__ Pre prefetch(int, int, int, int) const { return Pre{}; }
   __device__ __forceinline__ void transform_pre(const Pre&, int, uint32_t (&)[32]) const {}
+  __device__ __forceinline__ float chunk_amax(int, const uint32_t (&)[32], int) const { return 0.0f; }
+  __device__ __forceinline__ void commit_amax(int, int, float) const {}
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
@@ -203,6 +205,25 @@ struct EpiDequant {
   int ldy;
   int relu;
   int tma;  // store through the output tensor map (needs N % 4 == 0)
+  // when set: amax[row] = max(amax[row], max_col |y[row, col]|), the row maxima the next layer's
+  // dynamic quantisation needs, so that nobody has to read Y again for them.  Non-negative floats
+  // order like their bit patterns, hence an integer atomicMax; the caller zeroes the array.
+  float* amax = nullptr;
+  // largest |v| of a chunk (columns at or past N do not count); commit_amax folds it into amax[row]
+  __device__ __forceinline__ float chunk_amax(int col0, const uint32_t (&v)[32], int N) const {
+    float m = 0.0f;
+    if (amax == nullptr) return m;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < N) m = fmaxf(m, fabsf(__uint_as_float(v[j])));
+    return m;
+  }
+  __device__ __forceinline__ void commit_amax(int row, int M, float m) const {
+    if (amax != nullptr && row < M) atomicMax(reinterpret_cast<int*>(amax + row), __float_as_int(m));
+  }
+  __device__ __forceinline__ void note_amax(int row, int col0, const uint32_t (&v)[32], int M, int N) const {
+    commit_amax(row, M, chunk_amax(col0, v, N));
+  }
   // dequantises the chunk in registers; rows and columns past the edge yield values the
   // clipped TMA store never writes
   __device__ __forceinline__ bool transform(int row, int col0, uint32_t (&v)[32], int M, int N) const {
@@ -220,6 +241,7 @@ struct EpiDequant {
       v[j + 2] = __float_as_uint(dequant1(v[j + 2], s, w4.z, b4.z, hb, relu));
       v[j + 3] = __float_as_uint(dequant1(v[j + 3], s, w4.w, b4.w, hb, relu));
     }
+    note_amax(row, col0, v, M, N);
     return false;
   }
   __device__ __forceinline__ void activate(uint32_t (&)[32]) const {}
@@ -256,24 +278,22 @@ struct EpiDequant {
     const float s = sa[row];
     float* y = Y + (size_t)row * ldy + col0;
     const bool hb = bias != nullptr;
+    uint32_t o[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      o[j] = col0 + j < N ? __float_as_uint(dequant1(v[j], s, __ldg(sw + col0 + j), hb ? __ldg(bias + col0 + j) : 0.0f,
+                                                      hb, relu))
+                          : 0u;
+    note_amax(row, col0, o, M, N);
     if (col0 + 32 <= N && (ldy & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 w4 = __ldg(reinterpret_cast<const float4*>(sw + col0 + j));
-        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (hb) b4 = __ldg(reinterpret_cast<const float4*>(bias + col0 + j));
-        float4 o;
-        o.x = dequant1(v[j], s, w4.x, b4.x, hb, relu);
-        o.y = dequant1(v[j + 1], s, w4.y, b4.y, hb, relu);
-        o.z = dequant1(v[j + 2], s, w4.z, b4.z, hb, relu);
-        o.w = dequant1(v[j + 3], s, w4.w, b4.w, hb, relu);
-        *reinterpret_cast<float4*>(y + j) = o;
-      }
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(y + j) = make_float4(__uint_as_float(o[j]), __uint_as_float(o[j + 1]),
+                                                        __uint_as_float(o[j + 2]), __uint_as_float(o[j + 3]));
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < N)
-          y[j] = dequant1(v[j], s, sw[col0 + j], hb ? bias[col0 + j] : 0.0f, hb, relu);
+        if (col0 + j < N) y[j] = __uint_as_float(o[j]);
     }
   }
 };
@@ -537,25 +557,41 @@ VTLB_API int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq,
   return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_acc);
 }
 
+// The general form behind the three entry points below.
+static int linear_i8_fwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_Aq, int shards, const void* d_sa,
+                              const void* d_Wq, const void* d_sw, const void* d_bias_or_null, void* d_Y, int M, int N,
+                              int K, int relu, void* d_row_amax_or_null) {
+  int rc = check_i8_args(ctx, fn, M, N, K);
+  if (rc) return rc;
+  if (shards < 1 || K % shards || (shards > 1 && (K / shards) % 128))
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: K=%d must split into %d shards of a multiple of 128 columns", fn, K, shards);
+  if (M == 0 || N == 0) return VTLB_OK;
+  if (!d_Aq || !d_Wq || !d_sa || !d_sw || !d_Y) return vtlb_fail(ctx, VTLB_EINVAL, "%s: null pointer", fn);
+  if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) || !vtlb_aligned16(d_sw) ||
+      (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: pointers must be 16-byte aligned", fn);
+  if (shards == 1 && M <= kGemvMaxM) {
+    rc = launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr, (float*)d_Y,
+                           (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, relu);
+    if (rc || !d_row_amax_or_null) return rc;
+    row_absmax_kernel<<<M, 256, 0, ctx->stream>>>((const float*)d_Y, M, N, (float*)d_row_amax_or_null);
+    VTLB_LAUNCHED(ctx);
+    return VTLB_OK;
+  }
+  EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, N, relu};
+  if (d_row_amax_or_null) {
+    VTLB_CUDA(ctx, cudaMemsetAsync(d_row_amax_or_null, 0, (size_t)M * sizeof(float), ctx->stream));
+    epi.amax = (float*)d_row_amax_or_null;
+  }
+  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_Y, shards);
+}
+
 VTLB_API int vtlb_linear_i8_fwd(vtlb_ctx* ctx, const void* d_Aq, const void* d_sa,
                                 const void* d_Wq, const void* d_sw, const void* d_bias_or_null,
                                 void* d_Y, int M, int N, int K, int relu) {
   VTLB_ENTER(ctx);
-  int rc = check_i8_args(ctx, "vtlb_linear_i8_fwd", M, N, K);
-  if (rc) return rc;
-  if (M == 0 || N == 0) return VTLB_OK;
-  if (!d_Aq || !d_Wq || !d_sa || !d_sw || !d_Y)
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd: null pointer");
-  if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) ||
-      !vtlb_aligned16(d_sw) || (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd: pointers must be 16-byte aligned");
-  if (M <= kGemvMaxM)
-    return launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr,
-                             (float*)d_Y, (const float*)d_sa, (const float*)d_sw,
-                             (const float*)d_bias_or_null, relu);
-  EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null,
-                 N, relu};
-  return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_Y);
+  return linear_i8_fwd_impl(ctx, "vtlb_linear_i8_fwd", d_Aq, 1, d_sa, d_Wq, d_sw, d_bias_or_null, d_Y, M, N, K, relu,
+                            nullptr);
 }
 
 VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards, int shards,
@@ -563,20 +599,17 @@ VTLB_API int vtlb_linear_i8_fwd_sharded_a(vtlb_ctx* ctx, const void* d_Aq_shards
                                           const void* d_bias_or_null, void* d_Y, int M, int N, int K,
                                           int relu) {
   VTLB_ENTER(ctx);
-  int rc = check_i8_args(ctx, "vtlb_linear_i8_fwd_sharded_a", M, N, K);
-  if (rc) return rc;
-  if (shards < 1 || K % shards || (K / shards) % 128)
-    return vtlb_fail(ctx, VTLB_EINVAL,
-                     "vtlb_linear_i8_fwd_sharded_a: K=%d must split into %d shards of a multiple of 128 columns",
-                     K, shards);
-  if (M == 0 || N == 0) return VTLB_OK;
-  if (!d_Aq_shards || !d_Wq || !d_sa || !d_sw || !d_Y)
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_sharded_a: null pointer");
-  if (!vtlb_aligned16(d_Aq_shards) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) || !vtlb_aligned16(d_sw) ||
-      (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_sharded_a: pointers must be 16-byte aligned");
-  EpiDequant epi{(float*)d_Y, (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, N, relu};
-  return run_i8(ctx, d_Aq_shards, d_Wq, M, N, K, epi, d_Y, shards);
+  return linear_i8_fwd_impl(ctx, "vtlb_linear_i8_fwd_sharded_a", d_Aq_shards, shards, d_sa, d_Wq, d_sw, d_bias_or_null,
+                            d_Y, M, N, K, relu, nullptr);
+}
+
+VTLB_API int vtlb_linear_i8_fwd_amax(vtlb_ctx* ctx, const void* d_Aq_shards, int shards, const void* d_sa,
+                                     const void* d_Wq, const void* d_sw, const void* d_bias_or_null, void* d_Y,
+                                     int M, int N, int K, int relu, void* d_row_amax) {
+  VTLB_ENTER(ctx);
+  if (!d_row_amax) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_i8_fwd_amax: null row-maximum output");
+  return linear_i8_fwd_impl(ctx, "vtlb_linear_i8_fwd_amax", d_Aq_shards, shards, d_sa, d_Wq, d_sw, d_bias_or_null, d_Y,
+                            M, N, K, relu, d_row_amax);
 }
 
 #ifdef VTLB_PAIR_TRACE
