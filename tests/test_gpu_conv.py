@@ -60,6 +60,10 @@ def test_conv2d_reference_kat(dev):
     (3, 5, 9, 11, 7, 3, 0, 1),        # ragged everything, no padding
     (2, 4, 12, 10, 6, 2, 1, 2),       # even kernel, stride 2
     (1, 1, 4, 4, 1, 2, 0, 1),         # conv2d_cuda_test.v:7-19 shape case -> [1,1,3,3]
+    (2, 6, 13, 13, 70, 5, 2, 1),      # 25 taps, more output channels than one 64-wide tile
+    (1, 3, 7, 9, 4, 7, 3, 1),         # 49 taps: beyond the implicit GEMM's tap mask, lowered path
+    (3, 2, 10, 8, 5, 3, 2, 3),        # stride 3: implicit forward, lowered input gradient
+    (5, 16, 11, 6, 8, 1, 0, 1),       # 1x1 kernel
 ])
 def test_conv2d_fwd_bwd_vs_oracle(dev, orc, B, C, H, W, O, k, pad, stride):
     rng = np.random.default_rng(B * 100 + C * 10 + O)

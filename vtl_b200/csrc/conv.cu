@@ -11,6 +11,7 @@
 //   d_weight: dW[oc, k]        = gT[oc, m] . colT[k, m]^T      (split-K over m = (b,oh,ow))
 //   d_input : dcolT[k, m]      = Wt[k, oc] . gM[m, oc]^T, then a col2im gather
 //   d_bias  : per-channel sums of g (f64 partials)
+#include "conv_igemm.cuh"
 #include "f32_common.cuh"
 
 namespace {
@@ -344,6 +345,34 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
   }
 }
 
+// Wt planes [C, ld >= O*kh*kw]: Wt[ic][(oc, a, b)] = W[oc][ic][a][b], the B operand of the
+// input-gradient product of the implicit GEMM.
+__global__ void __launch_bounds__(256) regroup_weights_split_kernel(const float* __restrict__ w, int O, int C, int taps,
+                                                                    int ld, float* __restrict__ hi,
+                                                                    float* __restrict__ lo) {
+  const int n = O * C * taps;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int t = i % taps, r = i / taps, ic = r % C, oc = r / C;
+    float h, l;
+    split1(w[i], h, l);
+    const size_t o = (size_t)ic * ld + (size_t)oc * taps + t;
+    hi[o] = h;
+    lo[o] = l;
+  }
+}
+
+// The implicit GEMM serves the forward product and (for unit stride) the input gradient as long
+// as the (channel, tap) table fits in shared memory; VTLB_CONV_IGEMM=0 keeps the lowered path.
+bool use_igemm(int K) {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("VTLB_CONV_IGEMM");
+    env = e ? atoi(e) : 1;
+  }
+  return env != 0 && K <= igemm::MAX_K;
+}
+bool igemm_taps_ok(int kh, int kw) { return kh * kw <= 32; }  // one validity bit per tap in a 32-bit word
+
 int check_conv(vtlb_ctx* ctx, const char* fn, ConvDims& d) {
   if (d.B <= 0 || d.C <= 0 || d.H <= 0 || d.W <= 0 || d.O <= 0 || d.kh <= 0 || d.kw <= 0 || d.ph < 0 ||
       d.pw < 0 || d.sh <= 0 || d.sw <= 0)
@@ -369,6 +398,13 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
   if (!d_x || !d_w || !d_y) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_fwd_f32: null pointer");
   const int M = (int)d.M(), K = d.K();
   f32::Planes p;
+  if (use_igemm(K) && igemm_taps_ok(kh, kw)) {
+    if ((rc = f32::alloc_planes(ctx, 0, O, K, 0, &p))) return rc;
+    if ((rc = f32::split_operand(ctx, (const float*)d_w, O, K, false, p.ld, p.b_hi, p.b_lo))) return rc;
+    const igemm::Geometry g{B, C, H, W, d.OH, d.OW, sh, sw, kh, kw, -ph, -pw, 1, K};
+    EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
+    return igemm::launch(ctx, (const float*)d_x, g, p.b_hi, p.b_lo, p.ld, epi, M, O);
+  }
   if ((rc = f32::alloc_planes(ctx, M, O, K, 0, &p))) return rc;
   {
     const int ky = (K + 31) / 32 < 64 ? (K + 31) / 32 : 64;
@@ -425,7 +461,20 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
       if ((rc = f32::reduce_splits(ctx, (const float*)p.extra, S, (size_t)O * K, (float*)d_dw_or_null))) return rc;
     }
   }
-  if (d_dx_or_null) {  // dcolT[k, m] = sum_oc W[oc, k] * g[m, oc]; dx = col2im(dcolT)
+  if (d_dx_or_null && sh == 1 && sw == 1 && use_igemm(O * kh * kw) && igemm_taps_ok(kh, kw) &&
+      (long long)B * O * d.OH * d.OW <= 0x7fffffffLL) {
+    // dx[(b, ih, iw), ic] = sum over (oc, a, b) of g[b][oc][ih + ph - a][iw + pw - b] * W[oc][ic][a][b]
+    if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
+    const int Kd = O * kh * kw;
+    f32::Planes p;
+    if ((rc = f32::alloc_planes(ctx, 0, C, Kd, 0, &p))) return rc;
+    regroup_weights_split_kernel<<<f32::grid_for(ctx, (size_t)O * C * kh * kw, 256), 256, 0, ctx->stream>>>(
+        (const float*)d_w, O, C, kh * kw, p.ld, p.b_hi, p.b_lo);
+    VTLB_LAUNCHED(ctx);
+    const igemm::Geometry gg{B, O, d.OH, d.OW, H, W, 1, 1, kh, kw, ph, pw, -1, Kd};
+    EpiConvOut epi{(float*)d_dx_or_null, nullptr, nullptr, C, H * W, 0};
+    if ((rc = igemm::launch(ctx, g, gg, p.b_hi, p.b_lo, p.ld, epi, B * H * W, C))) return rc;
+  } else if (d_dx_or_null) {  // dcolT[k, m] = sum_oc W[oc, k] * g[m, oc]; dx = col2im(dcolT)
     if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
     const int ldm = (int)vtlb_round_up((size_t)M, 4);
     f32::Planes p;

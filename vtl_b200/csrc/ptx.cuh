@@ -52,13 +52,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // `limit_ns`.  Gives up early when *abort_flag (shared memory, set by whichever
 // thread of the CTA timed out first) is non-zero.  Returns false when it gave
 // up; the caller then leaves its loop and the kernel tears down normally.
+// `sleep_ns` > 0 puts the thread to sleep between polls: for roles that wait long while other warps
+// of the CTA do the work (a polling warp otherwise takes issue slots from them).
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag,
-                                                  uint64_t limit_ns) {
+                                                  uint64_t limit_ns, uint32_t sleep_ns = 0) {
   uint64_t t0 = 0;
 #pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
