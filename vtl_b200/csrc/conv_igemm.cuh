@@ -27,7 +27,7 @@ using gemm::WAIT_LIMIT_NS;
 
 constexpr int BN = 64;
 constexpr int STAGES = 3;
-constexpr int EPI_WARPS = 4, GATHER_WARPS = 4;
+constexpr int EPI_WARPS = 4, GATHER_WARPS = 8;  // two gather threads per tile row: half a K block each
 constexpr int NUM_THREADS = 64 + 32 * (EPI_WARPS + GATHER_WARPS);
 // The gather warps are the ones with work to do; everybody else sleeps between polls of a barrier
 // (measured: polling warps executed two thirds of the kernel's instructions).
@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_constant__ gemm::TmapSet tm,
                   const Epi epi, int M, int N, uint32_t* status) {
   constexpr int BK = 32, KSTEPS = 4, CHUNK_KB = 4;
+  constexpr int HB = BK * BM / (32 * GATHER_WARPS);  // elements of a row's K block per gather thread
   constexpr uint32_t TMEM_COLS = 4 * BN;  // two buffers x (main + small cross-term accumulator)
   constexpr uint32_t IDESC = ptx::umma_idesc(ptx::kCfmtF32, ptx::kFmtTF32, BM, BN);
 
@@ -225,7 +226,9 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
     }
   } else {
     // ------------------------------------------------------------ gather (A planes)
-    const int r = threadIdx.x - 32 * (2 + EPI_WARPS);  // tile row of this thread, 0..127
+    const int gt = threadIdx.x - 32 * (2 + EPI_WARPS);
+    const int r = gt & (BM - 1);   // tile row of this thread, 0..127
+    const int kh0 = (gt / BM) * HB;  // its half of the K block: elements kh0 .. kh0 + HB - 1
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -247,27 +250,28 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       }
       // the 32 values of this row for K block kb: all loads are issued before anything waits on
       // them, and the next block's loads are in flight while this one is split and stored
-      auto load_kb = [&](int kb, float (&v)[BK]) {
+      auto load_kb = [&](int kb, float (&v)[HB]) {
 #pragma unroll
-        for (int j = 0; j < BK; ++j) {
-          const int2 e = ktab[kb * BK + j];
+        for (int j = 0; j < HB; ++j) {
+          const int2 e = ktab[kb * BK + kh0 + j];
           v[j] = 0.0f;
           if (valid & (uint32_t)e.y) v[j] = __ldg(src + (img + e.x));  // skipping the load beat loading a dummy
         }
       };
       // splits one K block held in v and stores it into the current stage
-      auto store_kb = [&](const float (&v)[BK]) -> bool {
+      auto store_kb = [&](const float (&v)[HB]) -> bool {
         bool good = ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS);
         good = __all_sync(0xffffffffu, good);
         if (!good) return false;
         const uint32_t row_hi = base + stage * STAGE + (uint32_t)r * ROW_BYTES;
         const uint32_t row_lo = row_hi + A_TILE;
 #pragma unroll
-        for (int c4 = 0; c4 < BK / 4; ++c4) {
+        for (int q4 = 0; q4 < HB / 4; ++q4) {
           float hi[4], lo[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) f32::split1(v[c4 * 4 + j], hi[j], lo[j]);
-          const uint32_t off = ((uint32_t)c4 ^ ((uint32_t)r & 7u)) << 4;  // 128-byte swizzle of the 16-byte piece
+          for (int j = 0; j < 4; ++j) f32::split1(v[q4 * 4 + j], hi[j], lo[j]);
+          const uint32_t c4 = (uint32_t)(kh0 / 4 + q4);
+          const uint32_t off = (c4 ^ ((uint32_t)r & 7u)) << 4;  // 128-byte swizzle of the 16-byte piece
           ptx::st_shared_v4(row_hi + off, __float_as_uint(hi[0]), __float_as_uint(hi[1]), __float_as_uint(hi[2]),
                             __float_as_uint(hi[3]));
           ptx::st_shared_v4(row_lo + off, __float_as_uint(lo[0]), __float_as_uint(lo[1]), __float_as_uint(lo[2]),
@@ -282,15 +286,19 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
         }
         return true;
       };
-      // the next K block's loads are in flight while this one is split and stored (copying the
-      // registers over measured faster than unrolling the loop twice)
-      float cur[BK], nxt[BK];
+      // the loads of the next two K blocks are in flight while this one is split and stored (copying
+      // the registers over measured faster than unrolling the loop)
+      float cur[HB], nxt[HB], nn[HB];
       load_kb(0, cur);
+      if (num_kb > 1) load_kb(1, nxt);
       for (int kb = 0; kb < num_kb && ok; ++kb) {
-        if (kb + 1 < num_kb) load_kb(kb + 1, nxt);
+        if (kb + 2 < num_kb) load_kb(kb + 2, nn);
         ok = store_kb(cur);
 #pragma unroll
-        for (int j = 0; j < BK; ++j) cur[j] = nxt[j];
+        for (int j = 0; j < HB; ++j) {
+          cur[j] = nxt[j];
+          nxt[j] = nn[j];
+        }
       }
     }
   }
