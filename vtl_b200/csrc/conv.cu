@@ -345,17 +345,18 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
   }
 }
 
-// Wt planes [C, ld >= O*kh*kw]: Wt[ic][(oc, a, b)] = W[oc][ic][a][b], the B operand of the
-// input-gradient product of the implicit GEMM.
+// B operand of the implicit GEMM with the channel running fastest in k (t = tap index):
+//   forward        planes [O, ld >= taps*C]: out[oc][t*C + ic] = W[oc][ic][t]
+//   input gradient planes [C, ld >= taps*O]: out[ic][t*O + oc] = W[oc][ic][t]
 __global__ void __launch_bounds__(256) regroup_weights_split_kernel(const float* __restrict__ w, int O, int C, int taps,
-                                                                    int ld, float* __restrict__ hi,
+                                                                    int for_input_grad, int ld, float* __restrict__ hi,
                                                                     float* __restrict__ lo) {
   const int n = O * C * taps;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int t = i % taps, r = i / taps, ic = r % C, oc = r / C;
     float h, l;
     split1(w[i], h, l);
-    const size_t o = (size_t)ic * ld + (size_t)oc * taps + t;
+    const size_t o = for_input_grad ? (size_t)ic * ld + (size_t)t * O + oc : (size_t)oc * ld + (size_t)t * C + ic;
     hi[o] = h;
     lo[o] = l;
   }
@@ -400,7 +401,9 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
   f32::Planes p;
   if (use_igemm(K) && igemm_taps_ok(kh, kw)) {
     if ((rc = f32::alloc_planes(ctx, 0, O, K, 0, &p))) return rc;
-    if ((rc = f32::split_operand(ctx, (const float*)d_w, O, K, false, p.ld, p.b_hi, p.b_lo))) return rc;
+    regroup_weights_split_kernel<<<f32::grid_for(ctx, (size_t)O * K, 256), 256, 0, ctx->stream>>>(
+        (const float*)d_w, O, C, kh * kw, 0, p.ld, p.b_hi, p.b_lo);
+    VTLB_LAUNCHED(ctx);
     const igemm::Geometry g{B, C, H, W, d.OH, d.OW, sh, sw, kh, kw, -ph, -pw, 1, K};
     EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
     return igemm::launch(ctx, (const float*)d_x, g, p.b_hi, p.b_lo, p.ld, epi, M, O);
@@ -469,7 +472,7 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     f32::Planes p;
     if ((rc = f32::alloc_planes(ctx, 0, C, Kd, 0, &p))) return rc;
     regroup_weights_split_kernel<<<f32::grid_for(ctx, (size_t)O * C * kh * kw, 256), 256, 0, ctx->stream>>>(
-        (const float*)d_w, O, C, kh * kw, p.ld, p.b_hi, p.b_lo);
+        (const float*)d_w, O, C, kh * kw, 1, p.ld, p.b_hi, p.b_lo);
     VTLB_LAUNCHED(ctx);
     const igemm::Geometry gg{B, O, d.OH, d.OW, H, W, 1, 1, kh, kw, ph, pw, -1, Kd};
     EpiConvOut epi{(float*)d_dx_or_null, nullptr, nullptr, C, H * W, 0};
@@ -534,3 +537,4 @@ VTLB_API int vtlb_maxpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* 
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
+

@@ -4,9 +4,14 @@
 // stored: four warps of the CTA gather it straight from the NCHW tensor, split every value into
 // its TF32 hi/lo parts and write both into the 128-byte-swizzled shared-memory tiles the MMAs
 // read.  B (the weights, a few KB) comes in by TMA from pre-split planes as in gemm_tc.cuh.
-//   forward        src = x, rows = output pixels, k = (ic, kh, kw), dy = kh - ph, dx = kw - pw
-//   input gradient src = g, rows = input pixels,  k = (oc, kh, kw), dy = ph - kh, dx = pw - kw
-//                  (unit stride), B = the weights regrouped as [ic][(oc, kh, kw)]
+//   forward        src = x, rows = output pixels, k = (kh, kw, ic), dy = kh - ph, dx = kw - pw,
+//                  B = the weights regrouped as [oc][(kh, kw, ic)]
+//   input gradient src = g, rows = input pixels,  k = (kh, kw, oc), dy = ph - kh, dx = pw - kw
+//                  (unit stride), B = the weights regrouped as [ic][(kh, kw, oc)]
+// The channel runs fastest in k: when the channel count is a multiple of 32, a K block of 32
+// columns is one tap of 32 consecutive channels, so a gather thread tests its pixel's tap once and
+// then loads at a fixed stride (one plane apart) - about five times fewer instructions per element
+// than looking every column up in the table, which remains the general path.
 // Replaces the im2col / col2im passes of the lowered path for these two products.
 //
 // One persistent CTA per SM, 320 threads: warp 0 = TMA producer for B (one lane), warp 1 = MMA
@@ -44,10 +49,11 @@ struct Geometry {
   int B, Cs, Hs, Ws;   // source tensor [B, Cs, Hs, Ws]
   int Ho, Wo;          // grid of the GEMM rows: m = (b, y, x), y < Ho, x < Wo
   int sy, sx;          // source row/column of a grid point = y*sy + dy, x*sx + dx
-  int kh, kw;          // taps per channel; k = (ch * kh + a) * kw + b
+  int kh, kw;          // taps; k = (a * kw + b) * Cs + ch
   int dy0, dx0, dsign; // dy = dy0 + dsign * a, dx = dx0 + dsign * b
   int K;               // Cs * kh * kw
 };
+
 
 template <class Epi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -81,7 +87,7 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
   for (int k = threadIdx.x; k < num_kb * BK; k += NUM_THREADS) {
     int2 e = make_int2(0, 0);  // k >= K: no tap
     if (k < g.K) {
-      const int ch = k / taps, r = k - ch * taps;
+      const int r = k / g.Cs, ch = k - r * g.Cs;
       const int a = r / g.kw, b = r - a * g.kw;
       const int dy = g.dy0 + g.dsign * a, dx = g.dx0 + g.dsign * b;
       e.x = (ch * g.Hs + dy) * g.Ws + dx;
@@ -250,7 +256,21 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       }
       // the 32 values of this row for K block kb: all loads are issued before anything waits on
       // them, and the next block's loads are in flight while this one is split and stored
+      const bool one_tap = (g.Cs % BK) == 0;  // every K block lies inside one tap
+      const int plane = g.Hs * g.Ws;
       auto load_kb = [&](int kb, float (&v)[HB]) {
+        if (one_tap) {
+          const int2 e = ktab[kb * BK + kh0];  // this thread's first column: its channel's offset, the tap's bit
+          if (valid & (uint32_t)e.y) {
+            const float* p = src + (img + e.x);
+#pragma unroll
+            for (int j = 0; j < HB; ++j) v[j] = __ldg(p + (size_t)j * plane);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HB; ++j) v[j] = 0.0f;
+          }
+          return;
+        }
 #pragma unroll
         for (int j = 0; j < HB; ++j) {
           const int2 e = ktab[kb * BK + kh0 + j];
@@ -286,19 +306,21 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
         }
         return true;
       };
-      // the loads of the next two K blocks are in flight while this one is split and stored (copying
-      // the registers over measured faster than unrolling the loop)
-      float cur[HB], nxt[HB], nn[HB];
-      load_kb(0, cur);
-      if (num_kb > 1) load_kb(1, nxt);
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        if (kb + 2 < num_kb) load_kb(kb + 2, nn);
-        ok = store_kb(cur);
-#pragma unroll
-        for (int j = 0; j < HB; ++j) {
-          cur[j] = nxt[j];
-          nxt[j] = nn[j];
-        }
+      // Three register buffers rotate: the loads of the next two K blocks are in flight while one is
+      // split and stored.  (Copying buffers over instead of rotating them made every iteration wait
+      // for the loads it had just issued.)
+      float va[HB], vb[HB], vc[HB];
+      load_kb(0, va);
+      if (num_kb > 1) load_kb(1, vb);
+      for (int kb = 0; kb < num_kb && ok; kb += 3) {
+        if (kb + 2 < num_kb) load_kb(kb + 2, vc);
+        ok = store_kb(va);
+        if (!ok || kb + 1 >= num_kb) break;
+        if (kb + 3 < num_kb) load_kb(kb + 3, va);
+        ok = store_kb(vb);
+        if (!ok || kb + 2 >= num_kb) break;
+        if (kb + 4 < num_kb) load_kb(kb + 4, vb);
+        ok = store_kb(vc);
       }
     }
   }
