@@ -285,6 +285,10 @@ struct EpiConvOut {
   const float* bias;
   float* pre;
   int O, P, relu;
+  // accumulator of output channel oc -> pre-activation value (the implicit GEMM's staged epilogue)
+  __device__ __forceinline__ float preact(int oc, float acc, int N) const {
+    return (bias && oc < N) ? __fadd_rn(acc, __ldg(bias + oc)) : acc;
+  }
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
                                              int /*split*/) const {
     if (row >= M) return;

@@ -42,8 +42,12 @@ constexpr uint32_t A_TILE = BM * ROW_BYTES, B_TILE = BN * ROW_BYTES;
 constexpr uint32_t STAGE = 2 * (A_TILE + B_TILE);
 constexpr uint32_t TILES = STAGES * STAGE;
 constexpr uint32_t TABLE_OFF = TILES;                 // int2 per k: {offset, bit of its tap (0 for k >= K)}
-constexpr uint32_t BARS_OFF = TABLE_OFF + MAX_K * 8;
-constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES + 4) + 16 + 1024;
+// Output staging: two plain [BN channels][BM pixels] f32 tiles (pre-activation and output), from which
+// one TMA store each writes the tile as BN runs of 512 bytes into the NCHW tensor.
+constexpr uint32_t OUT_TILE = BN * BM * 4;
+constexpr uint32_t OUT_OFF = TABLE_OFF + MAX_K * 8;
+constexpr uint32_t BARS_OFF = OUT_OFF + 2 * OUT_TILE;
+constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES + 5) + 16 + 1024;
 
 struct Geometry {
   int B, Cs, Hs, Ws;   // source tensor [B, Cs, Hs, Ws]
@@ -58,7 +62,7 @@ struct Geometry {
 template <class Epi>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_constant__ gemm::TmapSet tm,
-                  const Epi epi, int M, int N, uint32_t* status) {
+                  const Epi epi, int M, int N, int staged_out, uint32_t* status) {
   constexpr int BK = 32, KSTEPS = 4, CHUNK_KB = 4;
   constexpr int HB = BK * BM / (32 * GATHER_WARPS);  // elements of a row's K block per gather thread
   constexpr uint32_t TMEM_COLS = 4 * BN;  // two buffers x (main + small cross-term accumulator)
@@ -72,7 +76,8 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 4));
+  const uint32_t epi_bar = bars + 8u * (2 * STAGES + 4);  // the four epilogue warps meet here
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 5));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int2* ktab = reinterpret_cast<int2*>(smem_raw + (base - raw) + TABLE_OFF);
 
@@ -104,6 +109,7 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 32 * EPI_WARPS);
     }
+    ptx::mbar_init(epi_bar, 32 * EPI_WARPS);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -193,7 +199,7 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0, epi_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -222,12 +228,45 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
         if (acc == 0) acc_phase ^= 1u;
       }
       if (!ok) break;
+      if (staged_out) {
+        // The tile lies inside one image (the host checked that the pixels of an image are a multiple
+        // of BM): write it channel-major into shared memory, pixels contiguous, and let one TMA
+        // store per tensor put it into the NCHW output as BN runs of 512 bytes.  (Storing from
+        // registers, one 128-byte piece per instruction 4 KB apart, took 14 k cycles per tile and
+        // made the epilogue the bound of the whole kernel.)
+        const uint32_t stg_y = base + OUT_OFF, stg_pre = stg_y + OUT_TILE;
+        auto meet = [&]() -> bool {  // bounded rendezvous of the 128 epilogue threads
+          ptx::mbar_arrive(epi_bar);
+          const bool good = ptx::mbar_wait_bounded(epi_bar, epi_phase, abort_flag, WAIT_LIMIT_NS);
+          epi_phase ^= 1u;
+          return __all_sync(0xffffffffu, good);
+        };
+        if (warp == 2 && lane == 0) ptx::bulk_wait_read_all();  // the previous tile's stores have read the staging tiles
+        if (!(ok = meet())) break;
+        const uint32_t rr = (uint32_t)(q * 32 + lane) * 4u;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
+        for (int j = 0; j < BN; ++j) {
+          float o = sum[j];
+          o = epi.preact(n0 + j, o, N);
+          if (epi.pre) ptx::st_shared_f32(stg_pre + (uint32_t)j * (BM * 4) + rr, o);
+          ptx::st_shared_f32(stg_y + (uint32_t)j * (BM * 4) + rr, epi.relu && o < 0.f ? 0.f : o);
+        }
+        ptx::fence_proxy_async();
+        if (!(ok = meet())) break;
+        if (warp == 2 && lane == 0) {
+          const int img = m0 / epi.P, p0 = m0 - img * epi.P;
+          if (epi.pre) ptx::tma_store_3d(&tm.out[1], p0, n0, img, stg_pre);
+          ptx::tma_store_3d(&tm.out[0], p0, n0, img, stg_y);
+          ptx::bulk_commit_group();
+        }
+      } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
-        epi(row0 + lane, n0 + c * 32, v, M, N, 0);
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[c * 32 + j]);
+          epi(row0 + lane, n0 + c * 32, v, M, N, 0);
+        }
       }
     }
   } else {
@@ -326,6 +365,7 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
   }
 
   // ------------------------------------------------------------ teardown
+  if (warp == 2 && lane == 0) ptx::bulk_wait_read_all();  // staged stores have left shared memory
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -347,6 +387,15 @@ int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, const float* b_hi
   static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
   gemm::TmapSet tm;
   int rc;
+  // outputs go through staged TMA stores when every tile lies inside one image
+  const int staged = (epi.P % BM == 0) && vtlb_aligned16(epi.Y) && (!epi.pre || vtlb_aligned16(epi.pre));
+  if (staged) {
+    const uint64_t images = (uint64_t)M / epi.P;
+    if ((rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[0], epi.Y, epi.P, epi.O, images, BM, BN))) return rc;
+    tm.out[1] = tm.out[0];
+    if (epi.pre && (rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[1], epi.pre, epi.P, epi.O, images, BM, BN)))
+      return rc;
+  }
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, b_hi, g.K, N, (uint64_t)ldb * 4, 32, BN))) return rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, b_lo, g.K, N, (uint64_t)ldb * 4, 32, BN))) return rc;
   auto kern = conv_igemm_kernel<Epi>;
@@ -359,7 +408,7 @@ int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, const float* b_hi
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  kern<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(src, g, tm, epi, M, N, ctx->d_status);
+  kern<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(src, g, tm, epi, M, N, staged, ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;

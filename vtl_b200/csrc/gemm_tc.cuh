@@ -413,6 +413,8 @@ int encode_tmap_3d_u8(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_
 int encode_tmap_2d(vtlb_ctx* ctx, CUtensorMap* out, bool f32, const void* base, uint64_t inner,
                    uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
                    uint32_t box_outer);
+int encode_tmap_3d_f32_plain(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows,
+                             uint64_t planes, uint32_t box_inner, uint32_t box_rows);
 
 template <int KIND, int BN, int STAGES, class Epi>
 int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K, int splits = 1,

@@ -70,4 +70,22 @@ int encode_tmap_3d_u8(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_
   return VTLB_OK;
 }
 
+// 3-D f32 tensor [planes][rows][inner] without swizzle, for tiled stores of box_inner x box_rows x 1
+// boxes out of a plain row-major shared-memory tile.
+int encode_tmap_3d_f32_plain(vtlb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows,
+                             uint64_t planes, uint32_t box_inner, uint32_t box_rows) {
+  CUtensorMap probe;
+  int rc = encode_tmap_2d(ctx, &probe, true, base, inner, rows, inner * 4, 32, 1);
+  if (rc) return rc;  // resolves the driver entry point and checks alignment
+  cuuint64_t dims[3] = {inner, rows, planes};
+  cuuint64_t strides[2] = {inner * 4, inner * rows * 4};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return vtlb_fail(ctx, VTLB_ECUDA, "cuTensorMapEncodeTiled (3-D f32) failed (%d)", (int)r);
+  return VTLB_OK;
+}
+
 }  // namespace gemm
