@@ -285,10 +285,11 @@ struct EpiConvOut {
   const float* bias;
   float* pre;
   int O, P, relu;
-  // accumulator of output channel oc -> pre-activation value (the implicit GEMM's staged epilogue)
-  __device__ __forceinline__ float preact(int oc, float acc, int N) const {
-    return (bias && oc < N) ? __fadd_rn(acc, __ldg(bias + oc)) : acc;
+  // the implicit GEMM's staged epilogue: the bias of channel oc, and accumulator -> pre-activation value
+  __device__ __forceinline__ float bias_at(int oc, int N) const {
+    return (bias && oc < N) ? __ldg(bias + oc) : 0.0f;
   }
+  __device__ __forceinline__ float add_bias(float acc, float b) const { return bias ? __fadd_rn(acc, b) : acc; }
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
                                              int /*split*/) const {
     if (row >= M) return;

@@ -1,7 +1,7 @@
 // Convolution as an implicit GEMM on tcgen05 (f32 as 3xTF32): D[m, n] = sum_k A[m, k] . B[n, k]
 // where the rows m are pixels (b, y, x) of an output grid, the columns k are (channel, tap) pairs
 // and A[m, k] = src[b][ch(k)][y*sy + dy(k)][x*sx + dx(k)] (zero outside the image) is never
-// stored: four warps of the CTA gather it straight from the NCHW tensor, split every value into
+// stored: eight warps of the CTA gather it straight from the NCHW tensor, split every value into
 // its TF32 hi/lo parts and write both into the 128-byte-swizzled shared-memory tiles the MMAs
 // read.  B (the weights, a few KB) comes in by TMA from pre-split planes as in gemm_tc.cuh.
 //   forward        src = x, rows = output pixels, k = (kh, kw, ic), dy = kh - ph, dx = kw - pw,
@@ -14,12 +14,12 @@
 // than looking every column up in the table, which remains the general path.
 // Replaces the im2col / col2im passes of the lowered path for these two products.
 //
-// One persistent CTA per SM, 320 threads: warp 0 = TMA producer for B (one lane), warp 1 = MMA
+// One persistent CTA per SM, 448 threads: warp 0 = TMA producer for B (one lane), warp 1 = MMA
 // issuer and tensor-memory owner, warps 2..5 = epilogue (one per tensor-memory lane quarter),
-// warps 6..9 = gather (one thread per tile row).  full[s] collects the producer's expect_tx
-// arrive, the TMA bytes and one arrive per gather warp (after fence.proxy.async: the tensor core
-// reads shared memory through the async proxy); empty[s] is the MMA commit.  All waits are
-// bounded as in gemm_tc.cuh.
+// warps 6..13 = gather (two threads per tile row, half a K block each).  full[s] collects the
+// producer's expect_tx arrive, the TMA bytes and one arrive per gather warp (after
+// fence.proxy.async: the tensor core reads shared memory through the async proxy); empty[s] is the
+// MMA commit.  All waits are bounded as in gemm_tc.cuh.
 #pragma once
 #include "f32_common.cuh"
 #include "gemm_tc.cuh"
@@ -42,12 +42,14 @@ constexpr uint32_t A_TILE = BM * ROW_BYTES, B_TILE = BN * ROW_BYTES;
 constexpr uint32_t STAGE = 2 * (A_TILE + B_TILE);
 constexpr uint32_t TILES = STAGES * STAGE;
 constexpr uint32_t TABLE_OFF = TILES;                 // int2 per k: {offset, bit of its tap (0 for k >= K)}
-// Output staging: two plain [BN channels][BM pixels] f32 tiles (pre-activation and output), from which
-// one TMA store each writes the tile as BN runs of 512 bytes into the NCHW tensor.
-constexpr uint32_t OUT_TILE = BN * BM * 4;
+// Output staging, per epilogue warp: [half of the channels][output, pre-activation][32 channels][32
+// pixels] f32, 4 KB each.  One TMA store per piece writes it as 32 runs of 128 bytes into the NCHW
+// tensor; the two halves alternate, so a warp fills one while the other drains.
+constexpr uint32_t OUT_PIECE = 32 * 32 * 4;
+constexpr uint32_t OUT_WARP = 4 * OUT_PIECE;
 constexpr uint32_t OUT_OFF = TABLE_OFF + MAX_K * 8;
-constexpr uint32_t BARS_OFF = OUT_OFF + 2 * OUT_TILE;
-constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES + 5) + 16 + 1024;
+constexpr uint32_t BARS_OFF = OUT_OFF + 4 * OUT_WARP;
+constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * STAGES + 4) + 16 + 1024;
 
 struct Geometry {
   int B, Cs, Hs, Ws;   // source tensor [B, Cs, Hs, Ws]
@@ -76,8 +78,7 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t epi_bar = bars + 8u * (2 * STAGES + 4);  // the four epilogue warps meet here
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 5));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * (2 * STAGES + 4));
   volatile uint32_t* abort_flag = tmem_slot + 1;
   int2* ktab = reinterpret_cast<int2*>(smem_raw + (base - raw) + TABLE_OFF);
 
@@ -109,7 +110,6 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 32 * EPI_WARPS);
     }
-    ptx::mbar_init(epi_bar, 32 * EPI_WARPS);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -199,11 +199,19 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint32_t acc = 0, acc_phase = 0, epi_phase = 0;
+    uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
+    const uint32_t stg = base + OUT_OFF + (uint32_t)q * OUT_WARP;
+    const bool even_n = (N % BN) == 0;  // every tile stores two halves: one may drain while the other fills
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const int row0 = m0 + q * 32;
+      // lane j holds the bias of channels n0 + j and n0 + 32 + j (handed round by shuffles below)
+      float bias0 = 0.0f, bias1 = 0.0f;
+      if (staged_out) {
+        bias0 = epi.bias_at(n0 + lane, N);
+        bias1 = epi.bias_at(n0 + 32 + lane, N);
+      }
       float sum[BN];
 #pragma unroll
       for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
@@ -229,35 +237,40 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       }
       if (!ok) break;
       if (staged_out) {
-        // The tile lies inside one image (the host checked that the pixels of an image are a multiple
-        // of BM): write it channel-major into shared memory, pixels contiguous, and let one TMA
-        // store per tensor put it into the NCHW output as BN runs of 512 bytes.  (Storing from
-        // registers, one 128-byte piece per instruction 4 KB apart, took 14 k cycles per tile and
-        // made the epilogue the bound of the whole kernel.)
-        const uint32_t stg_y = base + OUT_OFF, stg_pre = stg_y + OUT_TILE;
-        auto meet = [&]() -> bool {  // bounded rendezvous of the 128 epilogue threads
-          ptx::mbar_arrive(epi_bar);
-          const bool good = ptx::mbar_wait_bounded(epi_bar, epi_phase, abort_flag, WAIT_LIMIT_NS);
-          epi_phase ^= 1u;
-          return __all_sync(0xffffffffu, good);
-        };
-        if (warp == 2 && lane == 0) ptx::bulk_wait_read_all();  // the previous tile's stores have read the staging tiles
-        if (!(ok = meet())) break;
-        const uint32_t rr = (uint32_t)(q * 32 + lane) * 4u;
+        // The 32 rows of this warp are one run of pixels of one image (the host checked that the
+        // pixels of an image are a multiple of 32): write them channel-major into this warp's
+        // staging pieces and let TMA stores put them into the NCHW output as runs of 128 bytes.
+        // (Storing from registers, one 128-byte piece per instruction 4 KB apart, took 14 k cycles
+        // per tile and made the epilogue the bound of the whole kernel.)  No warp waits for another.
+        if (row0 < M) {
+          const int img = row0 / epi.P, p0 = row0 - img * epi.P;
 #pragma unroll
-        for (int j = 0; j < BN; ++j) {
-          float o = sum[j];
-          o = epi.preact(n0 + j, o, N);
-          if (epi.pre) ptx::st_shared_f32(stg_pre + (uint32_t)j * (BM * 4) + rr, o);
-          ptx::st_shared_f32(stg_y + (uint32_t)j * (BM * 4) + rr, epi.relu && o < 0.f ? 0.f : o);
-        }
-        ptx::fence_proxy_async();
-        if (!(ok = meet())) break;
-        if (warp == 2 && lane == 0) {
-          const int img = m0 / epi.P, p0 = m0 - img * epi.P;
-          if (epi.pre) ptx::tma_store_3d(&tm.out[1], p0, n0, img, stg_pre);
-          ptx::tma_store_3d(&tm.out[0], p0, n0, img, stg_y);
-          ptx::bulk_commit_group();
+          for (int h = 0; h < BN / 32; ++h) {
+            if (n0 + 32 * h >= N) break;
+            const uint32_t s_y = stg + (uint32_t)h * (2 * OUT_PIECE) + (uint32_t)lane * 4u, s_pre = s_y + OUT_PIECE;
+            if (lane == 0) {  // the stores that last read this half have finished reading
+              if (even_n)
+                ptx::bulk_wait_read<1>();
+              else
+                ptx::bulk_wait_read<0>();
+            }
+            __syncwarp();
+            const float bh = h ? bias1 : bias0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float o = epi.add_bias(sum[h * 32 + j], __shfl_sync(0xffffffffu, bh, j));
+              if (epi.pre) ptx::st_shared_f32(s_pre + (uint32_t)j * 128u, o);
+              ptx::st_shared_f32(s_y + (uint32_t)j * 128u, epi.relu && o < 0.f ? 0.f : o);
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t piece = stg + (uint32_t)h * (2 * OUT_PIECE);
+              if (epi.pre) ptx::tma_store_3d(&tm.out[1], p0, n0 + 32 * h, img, piece + OUT_PIECE);
+              ptx::tma_store_3d(&tm.out[0], p0, n0 + 32 * h, img, piece);
+              ptx::bulk_commit_group();
+            }
+          }
         }
       } else {
 #pragma unroll
@@ -276,11 +289,18 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
     const int kh0 = (gt / BM) * HB;  // its half of the K block: elements kh0 .. kh0 + HB - 1
     uint32_t stage = 0, phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    // The (tile, K block) pairs of this CTA form one sequence, and the loads run two items ahead of
+    // the stores across tile boundaries as well (restarting the pipeline at every tile left two
+    // load latencies exposed per tile: most of the time of a layer with one K block per tile).
+    const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total = my_tiles * num_kb;
+    int l_tile = blockIdx.x, l_kb = 0;  // the item the next load belongs to
+    uint32_t valid = 0u;                // bit t: tap t of this row's pixel lies inside the image (at most 32 taps)
+    int img = 0;                        // element index of (b, channel 0, y0, x0); the tensor has < 2^31 elements
+    auto locate = [&](int tile) {       // position of this thread's row in `tile`; rows past M produce zeros
       const int m = (tile % tiles_m) * BM + r;
-      // position of this row's pixel; rows past M produce zeros (y far outside)
-      uint32_t valid = 0u;              // bit t: tap t of this pixel lies inside the image (at most 32 taps)
-      int img = 0;                      // element index of (b, channel 0, y0, x0); the tensor has < 2^31 elements
+      valid = 0u;
+      img = 0;
       if (m < M) {
         const int per = g.Ho * g.Wo;
         const int b = m / per, p = m - b * per;
@@ -293,6 +313,9 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
           if ((unsigned)yy < (unsigned)g.Hs && (unsigned)xx < (unsigned)g.Ws) valid |= 1u << t;
         }
       }
+    };
+    if (total > 0) locate(l_tile);
+    {
       // the 32 values of this row for K block kb: all loads are issued before anything waits on
       // them, and the next block's loads are in flight while this one is split and stored
       const bool one_tap = (g.Cs % BK) == 0;  // every K block lies inside one tap
@@ -348,24 +371,32 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
       // Three register buffers rotate: the loads of the next two K blocks are in flight while one is
       // split and stored.  (Copying buffers over instead of rotating them made every iteration wait
       // for the loads it had just issued.)
+      auto load_next = [&](float (&v)[HB]) {
+        load_kb(l_kb, v);
+        if (++l_kb == num_kb) {
+          l_kb = 0;
+          l_tile += gridDim.x;
+          if (l_tile < num_tiles) locate(l_tile);
+        }
+      };
       float va[HB], vb[HB], vc[HB];
-      load_kb(0, va);
-      if (num_kb > 1) load_kb(1, vb);
-      for (int kb = 0; kb < num_kb && ok; kb += 3) {
-        if (kb + 2 < num_kb) load_kb(kb + 2, vc);
+      if (total > 0) load_next(va);
+      if (total > 1) load_next(vb);
+      for (int i = 0; i < total && ok; i += 3) {
+        if (i + 2 < total) load_next(vc);
         ok = store_kb(va);
-        if (!ok || kb + 1 >= num_kb) break;
-        if (kb + 3 < num_kb) load_kb(kb + 3, va);
+        if (!ok || i + 1 >= total) break;
+        if (i + 3 < total) load_next(va);
         ok = store_kb(vb);
-        if (!ok || kb + 2 >= num_kb) break;
-        if (kb + 4 < num_kb) load_kb(kb + 4, vb);
+        if (!ok || i + 2 >= total) break;
+        if (i + 4 < total) load_next(vb);
         ok = store_kb(vc);
       }
     }
   }
 
   // ------------------------------------------------------------ teardown
-  if (warp == 2 && lane == 0) ptx::bulk_wait_read_all();  // staged stores have left shared memory
+  if (warp >= 2 && warp < 2 + EPI_WARPS && lane == 0) ptx::bulk_wait_read_all();  // staged stores have left shared memory
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -388,12 +419,12 @@ int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, const float* b_hi
   gemm::TmapSet tm;
   int rc;
   // outputs go through staged TMA stores when every tile lies inside one image
-  const int staged = (epi.P % BM == 0) && vtlb_aligned16(epi.Y) && (!epi.pre || vtlb_aligned16(epi.pre));
+  const int staged = (epi.P % 32 == 0) && vtlb_aligned16(epi.Y) && (!epi.pre || vtlb_aligned16(epi.pre));
   if (staged) {
     const uint64_t images = (uint64_t)M / epi.P;
-    if ((rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[0], epi.Y, epi.P, epi.O, images, BM, BN))) return rc;
+    if ((rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[0], epi.Y, epi.P, epi.O, images, 32, 32))) return rc;
     tm.out[1] = tm.out[0];
-    if (epi.pre && (rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[1], epi.pre, epi.P, epi.O, images, BM, BN)))
+    if (epi.pre && (rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[1], epi.pre, epi.P, epi.O, images, 32, 32)))
       return rc;
   }
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, b_hi, g.K, N, (uint64_t)ldb * 4, 32, BN))) return rc;
