@@ -312,7 +312,9 @@ int vtlb_batchnorm1d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, in
  *                        landed.  Bits may be combined.
  * A double-buffered loop: copy batch 0 in; for each step i: wait(IN_BEFORE_COMPUTE); start the
  * copy of batch i+1 into the other buffer; run step i; copy its result out.  vtlb_sync also waits
- * for both copy streams. */
+ * for both copy streams.  vtlb_free orders a block after the compute (and collective) work
+ * enqueued so far, not after copies still running on the copy streams: call vtlb_copy_wait with
+ * the matching BEFORE_COMPUTE bit before freeing a buffer such a copy reads or writes. */
 #define VTLB_COPY_IN_BEFORE_COMPUTE 1
 #define VTLB_COPY_OUT_BEFORE_COMPUTE 2
 #define VTLB_COPY_OUT_DONE 4

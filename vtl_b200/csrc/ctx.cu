@@ -93,6 +93,11 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
   for (auto& kv : ctx->small_free)
     for (void* p : kv.second) cudaFreeAsync(p, ctx->stream);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->prof_ev) {
+    for (int i = 0; i < 2 * vtlb_ctx::kProfSlots; ++i)
+      if (ctx->prof_ev[i]) cudaEventDestroy(ctx->prof_ev[i]);
+    delete[] ctx->prof_ev;
+  }
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->ksplit_buf) cudaFree(ctx->ksplit_buf);
   if (ctx->d_status) cudaFree(ctx->d_status);
@@ -176,7 +181,7 @@ VTLB_API void* vtlb_stream(vtlb_ctx* ctx) { return ctx ? (void*)ctx->stream : nu
 VTLB_API int vtlb_profile_gemm(vtlb_ctx* ctx, int enable) {
   VTLB_ENTER(ctx);
   if (enable && !ctx->prof_ev) {
-    ctx->prof_ev = new (std::nothrow) cudaEvent_t[2 * vtlb_ctx::kProfSlots];
+    ctx->prof_ev = new (std::nothrow) cudaEvent_t[2 * vtlb_ctx::kProfSlots]();
     if (!ctx->prof_ev) return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_profile_gemm: host allocation failed");
     for (int i = 0; i < 2 * vtlb_ctx::kProfSlots; ++i) VTLB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[i]));
   }

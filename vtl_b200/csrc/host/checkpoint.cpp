@@ -49,6 +49,14 @@ class JParser {
  private:
   const std::string& s_;
   size_t p_ = 0;
+  int depth_ = 0;  // nesting of the value being read; a checkpoint has five levels
+  struct Nest {
+    JParser& p;
+    explicit Nest(JParser& parser) : p(parser) {
+      if (++p.depth_ > 64) p.fail("nested too deeply");
+    }
+    ~Nest() { --p.depth_; }
+  };
   [[noreturn]] void fail(const char* what) const {
     throw Error(VTLB_EINVAL, std::string("checkpoint: malformed JSON (") + what + " at byte " + std::to_string(p_) + ")");
   }
@@ -110,6 +118,7 @@ class JParser {
   JValue value() {
     ws();
     if (p_ >= s_.size()) fail("unexpected end");
+    const Nest nest(*this);
     JValue v;
     const char c = s_[p_];
     if (c == '{') {
@@ -181,6 +190,7 @@ void json_string(std::string& out, const std::string& s) {
   out += '"';
 }
 std::string json_number(double v) {
+  if (!(v - v == 0.0)) return "null";  // JSON has no NaN or infinity
   char buf[40];
   std::snprintf(buf, sizeof buf, "%.17g", v);
   return buf;
