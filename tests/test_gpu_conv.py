@@ -64,6 +64,10 @@ def test_conv2d_reference_kat(dev):
     (1, 3, 7, 9, 4, 7, 3, 1),         # 49 taps: beyond the implicit GEMM's tap mask, lowered path
     (3, 2, 10, 8, 5, 3, 2, 3),        # stride 3: implicit forward, lowered input gradient
     (5, 16, 11, 6, 8, 1, 0, 1),       # 1x1 kernel
+    (3, 64, 12, 8, 96, 3, 1, 1),      # slab kernel: two / three channel groups, two 64-wide output tiles
+    (2, 32, 9, 8, 40, 5, 2, 1),       # slab kernel: 25 taps, one partly filled tile per image
+    (2, 32, 10, 14, 32, 3, 0, 1),     # slab kernel forward without padding (input gradient: gathered)
+    (5, 32, 33, 32, 64, 3, 1, 1),     # slab kernel: 11 tiles of 3 rows per image, the last one clipped
 ])
 def test_conv2d_fwd_bwd_vs_oracle(dev, orc, B, C, H, W, O, k, pad, stride):
     rng = np.random.default_rng(B * 100 + C * 10 + O)

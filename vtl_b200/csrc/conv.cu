@@ -12,6 +12,7 @@
 //   d_input : dcolT[k, m]      = Wt[k, oc] . gM[m, oc]^T, then a col2im gather
 //   d_bias  : per-channel sums of g (f64 partials)
 #include "conv_igemm.cuh"
+#include "conv_slab.cuh"
 #include "f32_common.cuh"
 
 namespace {
@@ -285,11 +286,10 @@ struct EpiConvOut {
   const float* bias;
   float* pre;
   int O, P, relu;
-  // the implicit GEMM's staged epilogue: the bias of channel oc, and accumulator -> pre-activation value
+  // the staged epilogues of the implicit-GEMM kernels: the bias of channel oc (0 without a bias)
   __device__ __forceinline__ float bias_at(int oc, int N) const {
     return (bias && oc < N) ? __ldg(bias + oc) : 0.0f;
   }
-  __device__ __forceinline__ float add_bias(float acc, float b) const { return bias ? __fadd_rn(acc, b) : acc; }
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M, int N,
                                              int /*split*/) const {
     if (row >= M) return;
@@ -411,6 +411,9 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
     VTLB_LAUNCHED(ctx);
     const igemm::Geometry g{B, C, H, W, d.OH, d.OW, sh, sw, kh, kw, -ph, -pw, 1, K};
     EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
+    cslab::Tiling tl;
+    if (cslab::usable(g, &tl) && vtlb_aligned16(d_y) && (!d_pre_or_null || vtlb_aligned16(d_pre_or_null)))
+      return cslab::launch(ctx, (const float*)d_x, g, tl, p.b_hi, p.b_lo, p.ld, epi, O);
     return igemm::launch(ctx, (const float*)d_x, g, p.b_hi, p.b_lo, p.ld, epi, M, O);
   }
   if ((rc = f32::alloc_planes(ctx, M, O, K, 0, &p))) return rc;
@@ -481,7 +484,12 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     VTLB_LAUNCHED(ctx);
     const igemm::Geometry gg{B, O, d.OH, d.OW, H, W, 1, 1, kh, kw, ph, pw, -1, Kd};
     EpiConvOut epi{(float*)d_dx_or_null, nullptr, nullptr, C, H * W, 0};
-    if ((rc = igemm::launch(ctx, g, gg, p.b_hi, p.b_lo, p.ld, epi, B * H * W, C))) return rc;
+    cslab::Tiling tl;
+    if (cslab::usable(gg, &tl) && vtlb_aligned16(d_dx_or_null))
+      rc = cslab::launch(ctx, g, gg, tl, p.b_hi, p.b_lo, p.ld, epi, C);
+    else
+      rc = igemm::launch(ctx, g, gg, p.b_hi, p.b_lo, p.ld, epi, B * H * W, C);
+    if (rc) return rc;
   } else if (d_dx_or_null) {  // dcolT[k, m] = sum_oc W[oc, k] * g[m, oc]; dx = col2im(dcolT)
     if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
     const int ldm = (int)vtlb_round_up((size_t)M, 4);

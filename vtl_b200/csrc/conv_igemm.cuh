@@ -256,11 +256,15 @@ conv_igemm_kernel(const float* __restrict__ src, const Geometry g, const __grid_
             }
             __syncwarp();
             const float bh = h ? bias1 : bias0;
+            // (flags copied out of the parameter struct: each store below is an asm statement that
+            // clobbers memory, after which the compiler reloads whatever it reads from epi)
+            const bool has_pre = epi.pre != nullptr, relu = epi.relu != 0, has_bias = epi.bias != nullptr;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float o = epi.add_bias(sum[h * 32 + j], __shfl_sync(0xffffffffu, bh, j));
-              if (epi.pre) ptx::st_shared_f32(s_pre + (uint32_t)j * 128u, o);
-              ptx::st_shared_f32(s_y + (uint32_t)j * 128u, epi.relu && o < 0.f ? 0.f : o);
+              const float bj = __shfl_sync(0xffffffffu, bh, j);
+              const float o = has_bias ? __fadd_rn(sum[h * 32 + j], bj) : sum[h * 32 + j];
+              if (has_pre) ptx::st_shared_f32(s_pre + (uint32_t)j * 128u, o);
+              ptx::st_shared_f32(s_y + (uint32_t)j * 128u, relu && o < 0.f ? 0.f : o);
             }
             ptx::fence_proxy_async();
             __syncwarp();
