@@ -32,7 +32,7 @@ using gemm::WAIT_LIMIT_NS;
 using igemm::Geometry;
 
 constexpr int BN = 64;
-constexpr int B_STAGES = 3;
+constexpr int MAX_B_STAGES = 6;  // as many weight stages as the shared memory left by the staging tiles holds
 constexpr int EPI_WARPS = 4, FILL_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * (EPI_WARPS + FILL_WARPS);
 constexpr uint32_t POLL_SLEEP_NS = 40;
@@ -40,15 +40,14 @@ constexpr int SLAB_ROWS = 200;  // 128 positions + the largest tap shift: (kh - 
 constexpr uint32_t SLAB_PLANE = SLAB_ROWS * ROW_BYTES;  // hi or lo part: 25 x 1024 bytes
 constexpr uint32_t SLAB = 2 * SLAB_PLANE;
 constexpr uint32_t B_TILE = BN * ROW_BYTES, B_STAGE = 2 * B_TILE;
-constexpr uint32_t B_OFF = 2 * SLAB;
-constexpr uint32_t OUT_TILE = BN * BM * 4;  // [BN channels][R * Wo <= 128 pixels] f32
-constexpr uint32_t OUT_OFF = B_OFF + B_STAGES * B_STAGE;
-constexpr uint32_t BARS_OFF = OUT_OFF + 2 * OUT_TILE;
-constexpr int NUM_BARS = 2 * B_STAGES + 4 + 4 + 1;  // weights full/empty, slab full/empty, tfull/tempty, epilogue
+// Layout: two slabs | one or two staging tiles [BN channels][R * Wo pixels] f32 (output, pre-activation)
+// | weight stages | barriers, tensor-memory slot, tap table.
+constexpr uint32_t OUT_OFF = 2 * SLAB;
+constexpr int NUM_BARS = 2 * MAX_B_STAGES + 4 + 4 + 1;  // weights full/empty, slab full/empty, tfull/tempty, epilogue
 constexpr int MAX_TAPS = 32;
-constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * NUM_BARS + 16 + 4 * MAX_TAPS + 1024;
+constexpr uint32_t TAIL_BYTES = 8 * NUM_BARS + 16 + 4 * MAX_TAPS;
+constexpr uint32_t SMEM_MAX = 232448;
 static_assert(SLAB_PLANE % 1024 == 0, "slab planes must keep the swizzle phase");
-static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
 
 struct Tiling {
   int Wp;             // pitch of the padded grid
@@ -56,6 +55,9 @@ struct Tiling {
   int tiles_per_img;  // ceil(Ho / R)
   int dy_min, dx_min;
   int G;              // channel groups of 32
+  int b_stages;       // weight stages (launch() fills these three in)
+  uint32_t out_tile;  // bytes of one staging tile, a multiple of 1024
+  uint32_t b_off;     // offset of the weight stages
 };
 
 inline bool usable(const Geometry& g, Tiling* t) {
@@ -91,14 +93,15 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t bars = base + BARS_OFF;
+  const uint32_t B_STAGES = (uint32_t)tl.b_stages, B_OFF = tl.b_off;
+  const uint32_t bars = base + B_OFF + B_STAGES * B_STAGE;
   auto bfull_bar = [&](int s) { return bars + 8u * s; };
-  auto bempty_bar = [&](int s) { return bars + 8u * (B_STAGES + s); };
-  auto sfull_bar = [&](int s) { return bars + 8u * (2 * B_STAGES + s); };
-  auto sempty_bar = [&](int s) { return bars + 8u * (2 * B_STAGES + 2 + s); };
-  auto tfull_bar = [&](int a) { return bars + 8u * (2 * B_STAGES + 4 + a); };
-  auto tempty_bar = [&](int a) { return bars + 8u * (2 * B_STAGES + 6 + a); };
-  const uint32_t epi_bar = bars + 8u * (2 * B_STAGES + 8);
+  auto bempty_bar = [&](int s) { return bars + 8u * (MAX_B_STAGES + s); };
+  auto sfull_bar = [&](int s) { return bars + 8u * (2 * MAX_B_STAGES + s); };
+  auto sempty_bar = [&](int s) { return bars + 8u * (2 * MAX_B_STAGES + 2 + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * MAX_B_STAGES + 4 + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * MAX_B_STAGES + 6 + a); };
+  const uint32_t epi_bar = bars + 8u * (2 * MAX_B_STAGES + 8);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars - raw) + 8u * NUM_BARS);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint32_t* shift_tab = tmem_slot + 4;  // per tap: its row shift in the slab, in descriptor units (16 bytes)
@@ -115,7 +118,7 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
     shift_tab[threadIdx.x] = (uint32_t)shift * (ROW_BYTES >> 4);
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < B_STAGES; ++s) {
+    for (int s = 0; s < (int)B_STAGES; ++s) {
       ptx::mbar_init(bfull_bar(s), 1);
       ptx::mbar_init(bempty_bar(s), 1);
     }
@@ -131,6 +134,8 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
     ptx::fence_proxy_async();
     ptx::prefetch_tmap(&tm.b[0]);
     ptx::prefetch_tmap(&tm.b[1]);
+    ptx::prefetch_tmap(&tm.out[0]);
+    ptx::prefetch_tmap(&tm.out[1]);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), TMEM_COLS);
@@ -236,7 +241,7 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
     const int m = q * 32 + lane;                 // this thread's position inside a tile
     const int pr = m / tl.Wp, pc = m - pr * tl.Wp;  // row of the tile, column of the padded grid
     const int rw = tl.R * g.Wo;                  // pixels of a full tile = pitch of the staging tile
-    const uint32_t stg_y = base + OUT_OFF, stg_pre = stg_y + OUT_TILE;  // stg_pre = stg_y + OUT_TILE
+    const uint32_t stg_y = base + OUT_OFF, stg_pre = stg_y + tl.out_tile;
     auto meet = [&]() -> bool {  // bounded rendezvous of the 128 epilogue threads
       ptx::mbar_arrive(epi_bar);
       const bool good = ptx::mbar_wait_bounded(epi_bar, epi_phase, abort_flag, WAIT_LIMIT_NS);
@@ -283,13 +288,14 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
       // asm statement that clobbers memory, after which the compiler reloads whatever it reads from epi)
       const bool keep = pc < g.Wo && pr < tl.R;
       const bool keep_pre = keep && epi.pre != nullptr, relu = epi.relu != 0, has_bias = epi.bias != nullptr;
+      const uint32_t to_pre = tl.out_tile;
       const uint32_t pitch = (uint32_t)rw * 4u;
       uint32_t at = stg_y + (uint32_t)(pr * g.Wo + pc) * 4u;  // a running address: one add per channel
 #pragma unroll
       for (int j = 0; j < BN; ++j) {
         const float bj = __shfl_sync(0xffffffffu, j < 32 ? bias0 : bias1, j & 31);
         const float o = has_bias ? __fadd_rn(sum[j], bj) : sum[j];
-        if (keep_pre) ptx::st_shared_f32(at + OUT_TILE, o);
+        if (keep_pre) ptx::st_shared_f32(at + to_pre, o);
         if (keep) ptx::st_shared_f32(at, relu && o < 0.f ? 0.f : o);
         at += pitch;
       }
@@ -400,11 +406,16 @@ conv_slab_kernel(const float* __restrict__ src, const Geometry g, const Tiling t
 
 // B planes: [N rows, ld >= K] hi and lo, k = tap * Cs + channel (regroup_weights_split_kernel)
 template <class Epi>
-int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, const Tiling& tl, const float* b_hi, const float* b_lo,
+int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, Tiling tl, const float* b_hi, const float* b_lo,
            int ldb, const Epi& epi, int N) {
   gemm::TmapSet tm;
   int rc;
   const int box_px = tl.R * g.Wo;  // a multiple of 4 pixels (16 bytes), at most 128
+  tl.out_tile = (uint32_t)vtlb_round_up((size_t)BN * box_px * 4, 1024);
+  tl.b_off = OUT_OFF + (epi.pre ? 2u : 1u) * tl.out_tile;
+  tl.b_stages = (int)((SMEM_MAX - 1024 - TAIL_BYTES - tl.b_off) / B_STAGE);
+  if (tl.b_stages > MAX_B_STAGES) tl.b_stages = MAX_B_STAGES;
+  const uint32_t smem_total = tl.b_off + tl.b_stages * B_STAGE + TAIL_BYTES + 1024;
   if ((rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[0], epi.Y, epi.P, epi.O, g.B, box_px, BN))) return rc;
   tm.out[1] = tm.out[0];
   if (epi.pre && (rc = gemm::encode_tmap_3d_f32_plain(ctx, &tm.out[1], epi.pre, epi.P, epi.O, g.B, box_px, BN)))
@@ -414,14 +425,14 @@ int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, const Tiling& tl,
   auto kern = conv_slab_kernel<Epi>;
   static uint64_t configured = 0;
   if (!(configured >> (ctx->device & 63) & 1)) {
-    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_TOTAL));
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
     configured |= 1ull << (ctx->device & 63);
   }
   const int tiles = g.B * tl.tiles_per_img * ((N + BN - 1) / BN);
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  kern<<<grid, NUM_THREADS, SMEM_TOTAL, ctx->stream>>>(src, g, tl, tm, epi, N, ctx->d_status);
+  kern<<<grid, NUM_THREADS, smem_total, ctx->stream>>>(src, g, tl, tm, epi, N, ctx->d_status);
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;
