@@ -172,10 +172,11 @@ def cuda_sync(dev):
 
 
 # ------------------------------------------------------------------ INT8 workload
-def make_int8_inputs(seed: int, rank: int):
-    """Config 2 of the baseline: A ~ N(0,1) [4096,4096] (same on every rank), this rank's
-    W shard ~ N(0,0.02) [4096,4096], bias ~ N(0,0.01) [4096]."""
-    A = np.random.default_rng(seed).standard_normal((I8_M, I8_K), dtype=np.float32)
+def make_int8_inputs(seed: int, rank: int, M: int = I8_M):
+    """Config 2 of the baseline: A ~ N(0,1) [M,4096] (same on every rank; M = 4096 unless the
+    run is one point of the config's M sweep), this rank's W shard ~ N(0,0.02) [4096,4096],
+    bias ~ N(0,0.01) [4096]."""
+    A = np.random.default_rng(seed).standard_normal((M, I8_K), dtype=np.float32)
     r = np.random.default_rng(seed + 1000 + rank)
     W = (r.standard_normal((I8_N, I8_K), dtype=np.float32) * np.float32(0.02))
     b = (r.standard_normal(I8_N, dtype=np.float32) * np.float32(0.01))
@@ -188,19 +189,21 @@ def cpu_int8_sample(A, W, b, budget_s=12.0):
     from oracle import oracle
     oracle.build()
     wq, sw = oracle.quant_rows_i8(W)
-    rows = 32
+    M = A.shape[0]
+    rows = min(32, M)
     t0 = time.perf_counter()
     oracle.linear_i8_fwd(A[:rows], wq, sw, b, True)
     dt = time.perf_counter() - t0
-    rows = int(max(32, min(I8_M, rows * budget_s / max(dt, 1e-3))))
+    rows = int(max(32, min(M, rows * budget_s / max(dt, 1e-3))))
     rows -= rows % 32
+    rows = max(1, min(rows, M))
     reps, t0 = 0, time.perf_counter()
     while reps == 0 or time.perf_counter() - t0 < 0.8 * budget_s:
         oracle.linear_i8_fwd(A[:rows], wq, sw, b, True)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     tops = 2.0 * rows * I8_N * I8_K / dt / 1e12
-    return (tops, oracle.max_threads(), f"first {rows} of {I8_M} rows of A against all {I8_N} "
+    return (tops, oracle.max_threads(), f"first {rows} of {M} rows of A against all {I8_N} "
             f"channels, {reps} repeats, {dt * reps:.1f} s in total", rows, dt)
 
 
@@ -208,9 +211,12 @@ def run_int8(args, ranks):
     from vtl_b200 import capi
     dev = capi.Device(ranks.local_rank)
     ranks.attach(dev)
-    M, N, K = I8_M, I8_N, I8_K
-    A, W, b = make_int8_inputs(2, ranks.rank)
-    NSETS = 4  # operand copies rotated between steps: 4 x 160 MiB >> 126 MB of L2
+    M, N, K = (args.rows or I8_M), I8_N, I8_K
+    A, W, b = make_int8_inputs(2, ranks.rank, M)
+    # operand copies rotated between steps so that no step finds its operands in the 126 MB L2:
+    # 4 x 160 MiB at M = 4096; with few rows a set is little more than the 16 MiB of weight codes
+    set_bytes = M * K * 5 + M * N * 4 + N * K
+    NSETS = max(4, -(-170_000_000 // set_bytes))
     dA = [dev.to_device(A) for _ in range(NSETS)]
     dQa = [dev.zeros((M, K), np.int8) for _ in range(NSETS)]
     dSa = [dev.zeros(M) for _ in range(NSETS)]
@@ -302,6 +308,39 @@ def run_int8(args, ranks):
     pk = peaks()
     int8_peak = 2.0 * pk["bf16_tflops"]  # INT8 issues at twice the bf16 rate on B200
     gemm_tops = 2.0 * M * N * K / (gemm_ms * 1e-3) / 1e12
+    # roofline of the dominant kernel (the GEMM with its fused epilogue).  It is bound by the tensor
+    # cores once 2*M*N*K / peak exceeds the time HBM needs for the operands (M >= 256 at N = K = 4096);
+    # with fewer rows it is bound by streaming the weight codes once.
+    op_bytes = float(N * K + M * K + 4 * M * N + 4 * (M + 2 * N))
+    tensor_bound = 2.0 * M * N * K / (int8_peak * 1e12) >= op_bytes / (pk["hbm_gbs"] * 1e9)
+    if M <= 2:
+        kname = "gemv_i8_kernel (dp4a, one output channel per warp, a whole weight row in flight)"
+    elif M <= 128:
+        kname = ("skinny::gemm_i8_skinny_kernel (tcgen05 kind::i8 with the weights on the M side, K cut "
+                 "across a cluster of 4 CTAs, partial sums added through distributed shared memory)")
+    elif M < 1024:
+        kname = "gemm::gemm_tc_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, one CTA per tile, TMA-store epilogue)"
+    else:
+        kname = ("gemm2::gemm_pair_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, cta_group::2, "
+                 "fused dequant+bias+ReLU, TMA-store epilogue, K-split of surplus tiles)")
+    if tensor_bound:
+        roof = {"bound": "tensor", "kernel": kname, "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
+                "frac": gemm_tops / int8_peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on the
+                # M = 4096 workload, from the ncu capture summarised in
+                # profiles/gemm_i8_pair_fused_4096.md (algorithmic operand bytes: 33.6 MB read)
+                "traffic": 59.9e6 if M == I8_M else None,
+                "traffic_unit": "bytes per launch (ncu, 34.55 MB read + 25.38 MB written)" if M == I8_M else None,
+                "algorithmic_ops_per_launch": 2.0 * M * N * K,
+                "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
+                               "dense INT8 issues at twice the bf16 rate)",
+                "kernel_ms": gemm_ms}
+    else:
+        gbs = op_bytes / (gemm_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": kname, "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                "algorithmic_bytes_per_launch": op_bytes,
+                "peak_source": f"hbm_gbs of {pk['_source']}", "kernel_ms": gemm_ms}
     out = None
     if ranks.rank == 0:
         cpu_tops, cores, sample, _, _ = cpu_int8_sample(A, W, b) if ranks.world == 1 else (None, None, None, None, None)
@@ -310,30 +349,20 @@ def run_int8(args, ranks):
             "unit": "TOPS", "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
-            "config": {"workload": "INT8 quantised Linear forward (baseline config 2): per-row "
-                       "dynamic quantisation of A f32 [4096,4096] ~N(0,1) + int8 GEMM against "
+            "config": {"workload": "INT8 quantised Linear forward (baseline config 2"
+                       + ("" if M == I8_M else f", M = {M} of its M sweep") + "): per-row "
+                       f"dynamic quantisation of A f32 [{M},4096] ~N(0,1) + int8 GEMM against "
                        "pre-quantised W [4096,4096] ~N(0,0.02) + fused dequant+bias+ReLU",
                        "M": M, "N_per_gpu": N, "K": K, "parallelism":
                        f"output-column sharded x{ranks.world}, activations replicated, no collective",
-                       "l2": "every operand rotates over 4 copies (640 MiB) between steps, larger than the 126 MB L2"},
+                       "l2": f"every operand rotates over {NSETS} copies ({NSETS * set_bytes / 2**20:.0f} MiB) "
+                             "between steps, larger than the 126 MB L2"},
             "e2e": {"value": ops_step / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TOPS",
                     "h2d_bytes_per_step": int(A.nbytes), "d2h_bytes_per_step": int(M * N * 4),
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor",
-                         "kernel": "gemm2::gemm_pair_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, cta_group::2, "
-                                   "fused dequant+bias+ReLU, TMA-store epilogue, K-split of surplus tiles)",
-                         "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
-                         "frac": gemm_tops / int8_peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on
-                         # this workload, from the ncu capture summarised in
-                         # profiles/gemm_i8_pair_fused_4096.md (algorithmic operand bytes: 33.6 MB read)
-                         "traffic": 59.9e6, "traffic_unit": "bytes per launch (ncu, 34.55 MB read + 25.38 MB written)",
-                         "algorithmic_ops_per_launch": 2.0 * M * N * K,
-                         "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
-                                        "dense INT8 issues at twice the bf16 rate)",
-                         "kernel_ms": gemm_ms},
+            "roofline": roof,
         }
         if cpu_tops is not None:
             out["cpu_baseline"] = {"value": cpu_tops, "unit": "TOPS", "cores": cores, "kind": "port",
@@ -383,7 +412,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="int8_linear")
     ap.add_argument("--rows", type=int, default=None,
-                    help="training workloads only: global batch override, for small profiling captures")
+                    help="int8_linear: rows M of the activations (the M sweep of baseline config 2; "
+                         "default 4096); training workloads: global batch override, for small "
+                         "profiling captures")
     args = ap.parse_args()
     defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5),
                 "int8_mlp_c5": (20, 3), "ckpt_c4": (20, 3)}

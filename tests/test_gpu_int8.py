@@ -59,9 +59,13 @@ def _codes(rng, rows, K, ld):
 
 
 SHAPES = [
-    (1, 64, 128), (5, 100, 48), (16, 4096, 4096),          # small-M (dp4a) path
+    (1, 64, 128), (2, 1000, 4100), (5, 100, 48), (16, 4096, 4096),   # dp4a path (M <= 2), few-row kernel
     (17, 64, 32), (128, 256, 128), (128, 64, 4096),        # one tile, each tile width
     (200, 328, 400), (129, 257, 144),                      # ragged M, N, K
+    # few rows: swapped-operand kernel, every row-count class, K cut over clusters of 1, 2 and 4
+    (7, 512, 520), (20, 4100, 1024), (33, 1000, 8192), (64, 4096, 4096), (100, 130, 272),
+    (128, 18944, 256), (128, 4096, 4096),
+    (48, 640, 1152),                                       # 9 K blocks over 4 CTAs: the last range is empty
     (512, 1024, 512), (1024, 4096, 1024),
     # more 256 x 256 tiles than CTA pairs with a short final wave: its tiles are cut along K
     # between two pairs (90 tiles and 256 tiles on 74 pairs)
@@ -88,6 +92,7 @@ def test_gemm_i8_i32_bit_exact(dev, orc, M, N, K):
 
 @pytest.mark.parametrize("M,N,K,relu,bias", [
     (1, 256, 512, True, True), (16, 300, 128, False, True),
+    (9, 4096, 4096, True, True), (40, 1002, 1152, False, True), (128, 4096, 2048, True, False),  # few-row kernel
     (128, 256, 256, True, True), (300, 500, 272, True, False), (512, 512, 1024, False, True),
     (2304, 2300, 1024, True, True),  # K-split final wave through the fused epilogue
 ])
@@ -154,6 +159,7 @@ def test_int8_argument_errors(dev):
 
 @pytest.mark.parametrize("M,N,K,relu", [
     (2, 300, 256, False),            # dp4a path: the maxima come from a pass over Y
+    (24, 1024, 1024, False),         # few-row kernel: likewise
     (200, 328, 400, True),           # single-CTA kernel, TMA-store epilogue
     (129, 258, 144, False),          # N % 4 != 0: direct stores
     (2304, 2300, 1024, False),       # CTA pairs with K-split tiles, negative outputs

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 #include "gemm_tc2.cuh"
+#include "gemm_i8_skinny.cuh"
 
 namespace {
 
@@ -298,13 +299,14 @@ struct EpiDequant {
   }
 };
 
-// ---------------------------------------------------------------- small M (GEMV-like)
-// For M <= 16 the 128-row tensor-core tile would be mostly padding and the
-// problem is bound by streaming W once from HBM (N*K bytes).  Each warp owns
-// NPW output channels at a time and walks K in 512-byte steps (16 bytes per
-// lane), accumulating with dp4a against up to MT rows of A (exact int32).
-template <int MT, int NPW, bool FUSED>
-__global__ void __launch_bounds__(256) gemv_i8_kernel(const int8_t* __restrict__ Aq,
+// ---------------------------------------------------------------- very small M (GEMV-like)
+// With one or two rows of activations the problem is streaming W once from HBM (N*K
+// bytes).  Each warp owns one output channel at a time and walks its row of W in pieces of
+// U * 512 bytes, all U 16-byte loads of a lane issued before the first is used (a whole
+// 4096-byte row in flight per warp at U = 8), accumulating with dp4a against up to MT
+// rows of A (exact int32).
+template <int MT, int U, bool FUSED>
+__global__ void __launch_bounds__(128) gemv_i8_kernel(const int8_t* __restrict__ Aq,
                                                       const int8_t* __restrict__ Wq, int M, int N,
                                                       int K, int ldk, int32_t* __restrict__ acc_out,
                                                       float* __restrict__ Y,
@@ -314,92 +316,103 @@ __global__ void __launch_bounds__(256) gemv_i8_kernel(const int8_t* __restrict__
   const int lane = threadIdx.x & 31;
   const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int n0 = gwarp * NPW; n0 < N; n0 += nwarps * NPW) {
-    int acc[NPW][MT];
+  for (int n = gwarp; n < N; n += nwarps) {
+    int acc[MT];
 #pragma unroll
-    for (int p = 0; p < NPW; ++p)
+    for (int m = 0; m < MT; ++m) acc[m] = 0;
+    const int8_t* wrow = Wq + (size_t)n * ldk;
+    for (int k0 = lane * 16; k0 < ldk; k0 += 512 * U) {
+      int4 w[U];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) acc[p][m] = 0;
-    for (int k = lane * 16; k < ldk; k += 32 * 16) {
-      int4 w[NPW];
-#pragma unroll
-      for (int p = 0; p < NPW; ++p) {
-        w[p] = make_int4(0, 0, 0, 0);
-        if (n0 + p < N) w[p] = *reinterpret_cast<const int4*>(Wq + (size_t)(n0 + p) * ldk + k);
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + 512 * u;
+        w[u] = make_int4(0, 0, 0, 0);
+        if (k < ldk) w[u] = __ldcs(reinterpret_cast<const int4*>(wrow + k));  // read once: streaming
       }
-      // bytes at k >= K inside the padded leading dimension are never used: mask them
-      int4 mask = make_int4(-1, -1, -1, -1);
-      if (k + 16 > K) {
-        int valid = K - k;  // 1..15 valid bytes (ldk is K rounded up to 16)
-        int mm[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int vb = valid - 4 * j;
-          mm[j] = vb >= 4 ? -1 : (vb <= 0 ? 0 : (int)((1u << (8 * vb)) - 1u));
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + 512 * u;
+        if (k >= ldk) break;
+        // bytes at k >= K inside the padded leading dimension are never used: mask them
+        if (k + 16 > K) {
+          const int valid = K - k;  // 1..15 valid bytes (ldk is K rounded up to 16)
+          int* wp = reinterpret_cast<int*>(&w[u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int vb = valid - 4 * j;
+            wp[j] &= vb >= 4 ? -1 : (vb <= 0 ? 0 : (int)((1u << (8 * vb)) - 1u));
+          }
         }
-        mask = make_int4(mm[0], mm[1], mm[2], mm[3]);
-      }
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        if (m < M) {
-          int4 a = __ldg(reinterpret_cast<const int4*>(Aq + (size_t)m * ldk + k));
-          a.x &= mask.x; a.y &= mask.y; a.z &= mask.z; a.w &= mask.w;
-#pragma unroll
-          for (int p = 0; p < NPW; ++p) {
-            int s = acc[p][m];
-            s = __dp4a(a.x, w[p].x, s);
-            s = __dp4a(a.y, w[p].y, s);
-            s = __dp4a(a.z, w[p].z, s);
-            s = __dp4a(a.w, w[p].w, s);
-            acc[p][m] = s;
+        for (int m = 0; m < MT; ++m) {
+          if (m < M) {
+            const int4 a = __ldg(reinterpret_cast<const int4*>(Aq + (size_t)m * ldk + k));
+            int t = acc[m];
+            t = __dp4a(a.x, w[u].x, t);
+            t = __dp4a(a.y, w[u].y, t);
+            t = __dp4a(a.z, w[u].z, t);
+            t = __dp4a(a.w, w[u].w, t);
+            acc[m] = t;
           }
         }
       }
     }
 #pragma unroll
-    for (int p = 0; p < NPW; ++p)
+    for (int m = 0; m < MT; ++m) {
+      int t = acc[m];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        int s = acc[p][m];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        acc[p][m] = s;
-      }
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      acc[m] = t;
+    }
     if (lane == 0) {
 #pragma unroll
-      for (int p = 0; p < NPW; ++p) {
-        const int n = n0 + p;
-        if (n >= N) continue;
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-          if (m >= M) continue;
-          if (FUSED)
-            Y[(size_t)m * N + n] = dequant1((uint32_t)acc[p][m], sa[m], sw[n],
-                                            bias ? bias[n] : 0.0f, bias != nullptr, relu);
-          else
-            acc_out[(size_t)m * N + n] = acc[p][m];
-        }
+      for (int m = 0; m < MT; ++m) {
+        if (m >= M) continue;
+        if (FUSED)
+          Y[(size_t)m * N + n] = dequant1((uint32_t)acc[m], sa[m], sw[n], bias ? bias[n] : 0.0f,
+                                          bias != nullptr, relu);
+        else
+          acc_out[(size_t)m * N + n] = acc[m];
       }
     }
   }
 }
 
-// Above this many rows the tensor-core kernel (narrow tiles) is faster than dp4a.
-constexpr int kGemvMaxM = 4;
+// Above this many rows the tensor-core kernels are faster than dp4a
+// (VTLB_I8_GEMV_MAX_M overrides, 0..16, for measurements).
+int gemv_max_m() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("VTLB_I8_GEMV_MAX_M");
+    v = e ? atoi(e) : 2;
+    if (v < 0) v = 0;
+    if (v > 16) v = 16;
+  }
+  return v;
+}
+
+// Few rows (up to 128) on one wave of 128-channel tiles: the swapped-operand kernel with K
+// cut across a cluster (gemm_i8_skinny.cuh).  VTLB_I8_SKINNY=0 switches it off.
+bool use_skinny(vtlb_ctx* ctx, int M, int N) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("VTLB_I8_SKINNY");
+    on = e ? atoi(e) != 0 : 1;
+  }
+  return on && skinny::usable(ctx, M, N);
+}
 
 template <bool FUSED>
 int launch_gemv(vtlb_ctx* ctx, const int8_t* Aq, const int8_t* Wq, int M, int N, int K,
                 int32_t* acc, float* Y, const float* sa, const float* sw, const float* bias,
                 int relu) {
   const int ldk = vtlb_i8_ld(K);
-  constexpr int NPW = 4;
-  const int warps_needed = (N + NPW - 1) / NPW;
-  int blocks = (warps_needed + 7) / 8;
-  if (blocks > ctx->sm_count * 4) blocks = ctx->sm_count * 4;
+  int blocks = (N + 3) / 4;  // four warps per block, one channel per warp at a time
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
   if (blocks < 1) blocks = 1;
-#define VTLB_GEMV(MT)                                                                          \
-  gemv_i8_kernel<MT, NPW, FUSED><<<blocks, 256, 0, ctx->stream>>>(Aq, Wq, M, N, K, ldk, acc, Y, \
-                                                                  sa, sw, bias, relu)
+#define VTLB_GEMV(MT)                                                                        \
+  gemv_i8_kernel<MT, 8, FUSED><<<blocks, 128, 0, ctx->stream>>>(Aq, Wq, M, N, K, ldk, acc, Y, \
+                                                                sa, sw, bias, relu)
   if (M <= 1) VTLB_GEMV(1);
   else if (M <= 2) VTLB_GEMV(2);
   else if (M <= 4) VTLB_GEMV(4);
@@ -550,9 +563,14 @@ VTLB_API int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq,
   if (!d_Aq || !d_Wq || !d_acc) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: null pointer");
   if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_acc))
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_gemm_i8_i32: pointers must be 16-byte aligned");
-  if (M <= kGemvMaxM)
+  if (M <= gemv_max_m())
     return launch_gemv<false>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K,
                               (int32_t*)d_acc, nullptr, nullptr, nullptr, nullptr, 0);
+  if (use_skinny(ctx, M, N)) {
+    skinny::Params p = {};
+    p.acc = (int32_t*)d_acc;
+    return skinny::launch<false>(ctx, d_Aq, d_Wq, M, N, K, p);
+  }
   EpiStoreI32 epi{(int32_t*)d_acc, N};
   return run_i8(ctx, d_Aq, d_Wq, M, N, K, epi, d_acc);
 }
@@ -570,9 +588,19 @@ static int linear_i8_fwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_Aq, i
   if (!vtlb_aligned16(d_Aq) || !vtlb_aligned16(d_Wq) || !vtlb_aligned16(d_Y) || !vtlb_aligned16(d_sw) ||
       (d_bias_or_null && !vtlb_aligned16(d_bias_or_null)))
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: pointers must be 16-byte aligned", fn);
-  if (shards == 1 && M <= kGemvMaxM) {
-    rc = launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr, (float*)d_Y,
-                           (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, relu);
+  if (shards == 1 && (M <= gemv_max_m() || use_skinny(ctx, M, N))) {
+    if (M <= gemv_max_m()) {
+      rc = launch_gemv<true>(ctx, (const int8_t*)d_Aq, (const int8_t*)d_Wq, M, N, K, nullptr, (float*)d_Y,
+                             (const float*)d_sa, (const float*)d_sw, (const float*)d_bias_or_null, relu);
+    } else {
+      skinny::Params p = {};
+      p.Y = (float*)d_Y;
+      p.sa = (const float*)d_sa;
+      p.sw = (const float*)d_sw;
+      p.bias = (const float*)d_bias_or_null;
+      p.relu = relu;
+      rc = skinny::launch<true>(ctx, d_Aq, d_Wq, M, N, K, p);
+    }
     if (rc || !d_row_amax_or_null) return rc;
     row_absmax_kernel<<<M, 256, 0, ctx->stream>>>((const float*)d_Y, M, N, (float*)d_row_amax_or_null);
     VTLB_LAUNCHED(ctx);
