@@ -59,7 +59,7 @@ def _codes(rng, rows, K, ld):
 
 
 SHAPES = [
-    (1, 64, 128), (2, 1000, 4100), (5, 100, 48), (16, 4096, 4096),   # dp4a path (M <= 2), few-row kernel
+    (1, 64, 128), (2, 1000, 4100), (5, 100, 48), (16, 4096, 4096),   # dp4a path (M = 1), few-row kernel
     (17, 64, 32), (128, 256, 128), (128, 64, 4096),        # one tile, each tile width
     (200, 328, 400), (129, 257, 144),                      # ragged M, N, K
     # few rows: swapped-operand kernel, every row-count class, K cut over clusters of 1, 2 and 4

@@ -8,11 +8,14 @@
 //     by MN = 16/32/64/128 activation rows (the N side), so the bytes a CTA pulls are almost
 //     all weights, each read once;
 //   * the S CTAs of a cluster (1, 2 or 4) take K ranges of the same tile, so S times as many
-//     SMs stream the weights; each leaves its int32 partial sums in its own shared memory
-//     ([m][128 channels], over the operand ring, which is idle by then), the cluster meets at
-//     a barrier, and every CTA finishes the rows m = rank (mod S): it adds the S partials
-//     through distributed shared memory (integer sums: exact in any order) and applies the
-//     epilogue, a warp writing 512 contiguous bytes of a row of Y.
+//     SMs stream the weights; CTA r finishes the rows m = r (mod S), so every CTA sends each
+//     row of its int32 partial sums to the landing zone of the row's owner (st.shared::cluster,
+//     a warp writing 128 contiguous bytes), the cluster meets at a barrier, and the owner
+//     adds the S partials from its own shared memory (integer sums: exact in any order) and
+//     applies the epilogue, a warp writing 512 contiguous bytes of a row of Y.  Nobody reads a
+//     peer's memory after the barrier, so a CTA may leave as soon as it is done; the barrier
+//     that guarantees every peer has started before it is written to is entered at the top
+//     and only waited for after the K loop.
 // One tile per CTA (grid = tiles * S); warp 0 = TMA producer, warp 1 = MMA issuer and owner
 // of the tensor memory, warps 2..5 = epilogue.  Waits are bounded as in gemm_tc.cuh and both
 // cluster barriers are reached on every path.
@@ -28,11 +31,12 @@ namespace skinny {
 
 constexpr int BNCH = 128;                      // output channels per tile = TMEM lanes
 constexpr uint32_t W_TILE = BNCH * 128;        // 16 KB of weights per stage
-constexpr uint32_t RING_BYTES = 192 * 1024;    // operand ring, later the partial sums
+constexpr uint32_t RING_BYTES = 128 * 1024;    // operand ring
+constexpr uint32_t LZ_BYTES = 64 * 1024;       // landing zone: [source CTA][owned row][128 channels] int32
 constexpr int MAX_STAGES = 8;
 constexpr int NUM_THREADS = 192;
-constexpr uint32_t BARS_OFF = RING_BYTES;
-constexpr uint32_t SMEM_TOTAL = RING_BYTES + 8 * (2 * MAX_STAGES + 1) + 16 + 1024;
+constexpr uint32_t BARS_OFF = RING_BYTES + LZ_BYTES;
+constexpr uint32_t SMEM_TOTAL = BARS_OFF + 8 * (2 * MAX_STAGES + 1) + 16 + 1024;
 
 struct Params {
   CUtensorMap w;     // W codes [N, K], box 128 rows x 128 bytes
@@ -58,6 +62,12 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -66,16 +76,16 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ int4 ld_cluster_v4(uint32_t cluster_addr) {
+__device__ __forceinline__ int4 ld_shared_v4(uint32_t addr) {
   int4 v;
-  asm volatile("ld.shared::cluster.v4.s32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(cluster_addr)
+               : "r"(addr)
                : "memory");
   return v;
 }
-__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
-  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float dequant(int acc, float sa, float sw, float bias, bool has_bias, int relu) {
@@ -86,7 +96,7 @@ __device__ __forceinline__ float dequant(int acc, float sa, float sw, float bias
   return y;
 }
 
-template <bool FUSED>
+template <bool FUSED, int S>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -99,7 +109,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t S = cluster_nctarank(), rank = cluster_ctarank();
+  const uint32_t rank = S > 1 ? cluster_ctarank() : 0u;
+  const uint32_t lz = base + RING_BYTES;
   const int tile = blockIdx.x / S;
   const int n0 = tile * BNCH;
   const int MN = p.MN;
@@ -107,7 +118,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
   const uint32_t stride = W_TILE + a_bytes;
   const int stages = (int)(RING_BYTES / stride) < MAX_STAGES ? (int)(RING_BYTES / stride) : MAX_STAGES;
   const int total_kb = (p.K + 127) / 128;
-  const int per = (total_kb + (int)S - 1) / (int)S;
+  const int per = (total_kb + S - 1) / S;
   const int kb_begin = (int)rank * per;
   const int kb_end = kb_begin + per < total_kb ? kb_begin + per : total_kb;
   const bool has_work = kb_begin < kb_end;
@@ -133,6 +144,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // "this CTA runs": waited for (by then for nothing) before the first store into a peer's memory
+  if (S > 1) cluster_arrive_relaxed();
 
   float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = w4;  // epilogue warps: weight scales and bias of 4 channels
   float sa_mine = 0.0f;                                   // and the scale of the lane-th row this warp finishes
@@ -200,8 +213,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
         if (n + 2 < p.N) { w4.z = __ldg(p.sw + n + 2); if (hb) b4.z = __ldg(p.bias + n + 2); }
         if (n + 3 < p.N) { w4.w = __ldg(p.sw + n + 3); if (hb) b4.w = __ldg(p.bias + n + 3); }
       }
-      // row scales of the rows this warp finishes, one per lane: row (rank + S*(warp-2)) + 4*S*lane
-      const int mrow = (int)rank + (int)S * (warp - 2) + 4 * (int)S * lane;
+      // row scales of the rows this warp finishes, one per lane: row rank + S*(warp-2) + 4*S*lane
+      const int mrow = (int)rank + S * (warp - 2) + 4 * S * lane;
       sa_mine = mrow < p.M ? __ldg(p.sa + mrow) : 0.0f;
     }
     bool ok = true;
@@ -210,8 +223,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
       ok = __all_sync(0xffffffffu, ok);
       ptx::tc_fence_after();
     }
-    // the operand ring is free now: every load has landed and every MMA has read it
-    const uint32_t col_addr = base + (uint32_t)(q * 32 + lane) * 4u;
+    // Row m belongs to CTA m % S, which keeps it as its row m / S; this CTA's copy goes to slot
+    // [rank][m / S] of the owner's landing zone.  Lane = channel, so a warp's store is 128
+    // contiguous bytes.  32 % S == 0: the owner of accumulator column j of a chunk is j % S.
+    if (S > 1) cluster_wait();  // every peer has started (entered at the top of the kernel)
+    const int rows_per = MN / S;  // slots per source CTA
+    uint32_t dst[S];
+#pragma unroll
+    for (int o = 0; o < S; ++o)
+      dst[o] = mapa(lz + (uint32_t)((int)rank * rows_per) * 512u + (uint32_t)(q * 32 + lane) * 4u, (uint32_t)o);
 #pragma unroll 1
     for (int c = 0; c * 32 < p.M; ++c) {
       uint32_t v[32];
@@ -224,18 +244,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
       }
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (c * 32 + j < p.M) st_shared_u32(col_addr + (uint32_t)(c * 32 + j) * 512u, v[j]);
+        if (c * 32 + j < p.M) st_cluster_u32(dst[j % S] + (uint32_t)((c * 32 + j) / S) * 512u, v[j]);
     }
     ptx::tc_fence_before();
   }
+  if (S > 1 && warp < 2) cluster_wait();  // the producer's and the MMA warp's half of the first barrier
 
-  cluster_sync_all();  // every CTA's partial sums are in its shared memory
+  // every CTA's partial sums have reached their owners
+  if (S > 1) cluster_sync_all();
+  else __syncthreads();
 
   if (warp >= 2) {
     // ------------------------------------------------------------ epilogue, part 2: rows m = rank (mod S)
     const int n = n0 + lane * 4;
     const bool hb = p.bias != nullptr;
-    const int step = 4 * (int)S;
     auto finish = [&](int m, int4 s, float a) {
       const size_t off = (size_t)m * p.N + n;
       if (FUSED) {
@@ -263,38 +285,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
         }
       }
     };
-    // two rows at a time, all their partials requested before the first is used
+    const int rows_per = MN / S;
     int i = 0;
-    for (int m = (int)rank + (int)S * (warp - 2); m < p.M; m += 2 * step, i += 2) {
-      const int m2 = m + step;
-      const bool two = m2 < p.M;
-      const uint32_t mine = base + (uint32_t)m * 512u + (uint32_t)lane * 16u;
-      int4 t[2][4];
+    for (int l = warp - 2; l * S + (int)rank < p.M; l += 4, ++i) {  // l = owned row index
+      const int m = l * S + (int)rank;
+      const uint32_t mine = lz + (uint32_t)l * 512u + (uint32_t)lane * 16u;
+      int4 t[S];
 #pragma unroll
-      for (uint32_t r = 0; r < 4; ++r) {
-        t[0][r] = make_int4(0, 0, 0, 0);
-        t[1][r] = make_int4(0, 0, 0, 0);
-        if (r < S) {
-          t[0][r] = ld_cluster_v4(mapa(mine, r));
-          if (two) t[1][r] = ld_cluster_v4(mapa(mine + (uint32_t)step * 512u, r));
-        }
-      }
-      const float a0 = __shfl_sync(0xffffffffu, sa_mine, i & 31);
-      const float a1 = __shfl_sync(0xffffffffu, sa_mine, (i + 1) & 31);
+      for (int r = 0; r < S; ++r) t[r] = ld_shared_v4(mine + (uint32_t)(r * rows_per) * 512u);
+      int4 s = t[0];
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        int4 s;
-        s.x = t[k][0].x + t[k][1].x + t[k][2].x + t[k][3].x;
-        s.y = t[k][0].y + t[k][1].y + t[k][2].y + t[k][3].y;
-        s.z = t[k][0].z + t[k][1].z + t[k][2].z + t[k][3].z;
-        s.w = t[k][0].w + t[k][1].w + t[k][2].w + t[k][3].w;
-        if (k == 0) finish(m, s, a0);
-        else if (two) finish(m2, s, a1);
+      for (int r = 1; r < S; ++r) {
+        s.x += t[r].x; s.y += t[r].y; s.z += t[r].z; s.w += t[r].w;
       }
+      finish(m, s, __shfl_sync(0xffffffffu, sa_mine, i & 31));
     }
   }
-
-  cluster_sync_all();  // nobody leaves (or frees anything) while a peer may still read its partial sums
 
   // ------------------------------------------------------------ teardown
   if (*abort_flag) {
@@ -318,38 +324,53 @@ inline bool usable(vtlb_ctx* ctx, int M, int N) {
   return M >= 1 && M <= kMaxM && N >= 1 && (N + BNCH - 1) / BNCH <= ctx->sm_count;
 }
 
-template <bool FUSED>
-int configure(vtlb_ctx* ctx, int* max_clusters /* [3]: S = 1, 2, 4 */) {
-  auto kern = gemm_i8_skinny_kernel<FUSED>;
+template <bool FUSED, int S>
+int configure(vtlb_ctx* ctx, int* max_clusters) {
+  auto kern = gemm_i8_skinny_kernel<FUSED, S>;
   VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_TOTAL));
-  for (int i = 0; i < 3; ++i) {
-    const int S = 1 << i;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(ctx->sm_count / S * S));
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = SMEM_TOTAL;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = (unsigned)S;
-    at[0].val.clusterDim.y = 1;
-    at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    int n = 0;
-    VTLB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
-    max_clusters[i] = n;
-  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(ctx->sm_count / S * S));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_TOTAL;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)S;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  VTLB_CUDA(ctx, cudaOccupancyMaxActiveClusters(max_clusters, kern, &cfg));
+  return VTLB_OK;
+}
+
+template <bool FUSED, int S>
+int launch_s(vtlb_ctx* ctx, int tiles, const Params& p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * S));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = SMEM_TOTAL;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)S;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_i8_skinny_kernel<FUSED, S>, p));
   return VTLB_OK;
 }
 
 // `p` arrives with the output pointers, scales, bias and relu filled in.
 template <bool FUSED>
 int launch(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, Params p) {
-  static int max_clusters[64][3];
+  static int max_clusters[64][3];  // per device: clusters of 1, 2, 4 CTAs resident at a time
   static uint64_t configured = 0;
   const int d = ctx->device & 63;
   if (!(configured >> d & 1)) {
-    int rc = configure<FUSED>(ctx, max_clusters[d]);
+    int rc = configure<FUSED, 1>(ctx, &max_clusters[d][0]);
+    if (!rc) rc = configure<FUSED, 2>(ctx, &max_clusters[d][1]);
+    if (!rc) rc = configure<FUSED, 4>(ctx, &max_clusters[d][2]);
     if (rc) return rc;
     configured |= 1ull << d;
   }
@@ -373,21 +394,11 @@ int launch(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, P
   const void* out = FUSED ? (const void*)p.Y : (const void*)p.acc;
   p.vec = (N % 4 == 0) && vtlb_aligned16(out) &&
           (!FUSED || (vtlb_aligned16(p.sw) && (p.bias == nullptr || vtlb_aligned16(p.bias))));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(tiles * S));
-  cfg.blockDim = dim3(NUM_THREADS);
-  cfg.dynamicSmemBytes = SMEM_TOTAL;
-  cfg.stream = ctx->stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = (unsigned)S;
-  at[0].val.clusterDim.y = 1;
-  at[0].val.clusterDim.z = 1;
-  cfg.attrs = at;
-  cfg.numAttrs = 1;
   const bool timed = ctx->prof_on && ctx->prof_ev && ctx->prof_n < vtlb_ctx::kProfSlots;
   if (timed) cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream);
-  VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_i8_skinny_kernel<FUSED>, p));
+  rc = S == 4 ? launch_s<FUSED, 4>(ctx, tiles, p) : S == 2 ? launch_s<FUSED, 2>(ctx, tiles, p)
+                                                          : launch_s<FUSED, 1>(ctx, tiles, p);
+  if (rc) return rc;
   if (timed) {
     cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream);
     ctx->prof_n++;

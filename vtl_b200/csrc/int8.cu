@@ -384,7 +384,7 @@ int gemv_max_m() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("VTLB_I8_GEMV_MAX_M");
-    v = e ? atoi(e) : 2;
+    v = e ? atoi(e) : 1;
     if (v < 0) v = 0;
     if (v > 16) v = 16;
   }
