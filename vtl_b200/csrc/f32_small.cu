@@ -5,8 +5,12 @@
 // straight from the caller's row-major operands (either may be transposed), with the same
 // fused epilogue (bias, pre-activation copy, ReLU).  Because a CTA that walks a long K loop
 // pays one global-memory latency per step, K is cut into ranges that run as separate CTAs
-// (grid.z) and a second tiny kernel adds the partial sums in a fixed order and applies the
-// epilogue.  f32 FMA accumulation differs from the reference's f64 accumulation by
+// (grid.z).  With up to 8 ranges the CTAs of a tile form a thread-block cluster: row m of the
+// tile belongs to CTA m % S, every CTA sends its partial rows to their owners' shared memory
+// (st.shared::cluster), the cluster meets at a barrier and the owners add the partial sums in
+// range order and apply the epilogue -- one launch.  With more ranges the partial sums go
+// through global memory and a second tiny kernel adds them, in the same order.
+// f32 FMA accumulation differs from the reference's f64 accumulation by
 // ~sqrt(K) * 2^-24 relative, two orders inside the 1e-5 * sqrt(K) * max|A| * max|B| bound.
 #include "f32_common.cuh"
 
@@ -22,8 +26,35 @@ __device__ __forceinline__ void small_epilogue(float o, int m, int n, int N, con
   C[(size_t)m * N + n] = o;
 }
 
+constexpr int NST = 4;                                           // stages of the operand ring
+constexpr int kStageFloats = TK * (TM + 1) + TK * (TN + 4);      // 3232 floats: the B tile starts 16-byte aligned
+constexpr int kStageBytes = NST * kStageFloats * (int)sizeof(float);
+constexpr int kMaxClusterSplits = 8;
+constexpr int kLandRows = 36;  // max over S = 2..8 of S * ceil(TM / S)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 4-byte asynchronous copy global -> shared; with ok == false nothing is read and zero is written
+__device__ __forceinline__ void cp_async_f32(uint32_t dst, const float* src, bool ok) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(ok ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
 // grid = (tiles_n, tiles_m, splits).  With splits == 1 the epilogue is applied here and C is
-// written; otherwise the raw partial sums go to partial[z][M][N].
+// written.  With `cluster` set the launch has cluster dimensions (1, 1, splits) and the partial
+// sums are exchanged through shared memory; otherwise they go to partial[z][M][N].
 template <bool TA, bool TB>
 __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restrict__ A,
                                                           const float* __restrict__ B,
@@ -31,39 +62,61 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
                                                           const float* __restrict__ bias,
                                                           float* __restrict__ pre, int M, int N, int K,
                                                           int k_per_split, int relu,
-                                                          float* __restrict__ partial) {
-  __shared__ float As[TK][TM + 1];
-  __shared__ float Bs[TK][TN + 4];
+                                                          float* __restrict__ partial, int cluster) {
+  // NST stages of (A tile [TK][TM+1], B tile [TK][TN+4]) in dynamic shared memory, filled by
+  // cp.async: the loads of up to NST K steps (a whole K range of 128) are in flight at once, so
+  // a CTA pays one global-memory latency, not one per step
+  extern __shared__ __align__(16) float stage_mem[];
+  // landing zone of the cluster exchange: [source CTA][owned row][TN]; written by the peers
+  // while this CTA may still be in its K loop, so it shares nothing with the stages
+  __shared__ __align__(16) float Land[kLandRows][TN];
+  // "this CTA runs": entered here, waited for before the first store into a peer's memory
+  if (cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   const int tid = threadIdx.x;
   const int ty = tid >> 4, tx = tid & 15;  // 16 x 16 threads, 2 x 4 outputs each
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
   const int kbeg = blockIdx.z * k_per_split;
   const int kend = kbeg + k_per_split < K ? kbeg + k_per_split : K;
-  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  for (int k0 = kbeg; k0 < kend; k0 += TK) {
+  const int nsteps = kend > kbeg ? (kend - kbeg + TK - 1) / TK : 0;
+  auto load_stage = [&](int st, int k0) {
+    float* as = stage_mem + st * kStageFloats;
+    float* bs = as + TK * (TM + 1);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {  // A tile 32 x 32; index order follows the contiguous dimension
       const int e = tid + i * 256;
       const int m = TA ? (e & 31) : (e >> 5), k = TA ? (e >> 5) : (e & 31);
       const int gm = m0 + m, gk = k0 + k;
-      float v = 0.f;
-      if (gm < M && gk < kend) v = TA ? A[(size_t)gk * M + gm] : A[(size_t)gm * K + gk];
-      As[k][m] = v;
+      const bool ok = gm < M && gk < kend;
+      const float* src = ok ? (TA ? A + (size_t)gk * M + gm : A + (size_t)gm * K + gk) : A;
+      cp_async_f32(smem_addr(as + k * (TM + 1) + m), src, ok);  // zero-filled outside the operand
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {  // B tile 32 x 64
       const int e = tid + i * 256;
       const int n = TB ? (e >> 5) : (e & 63), k = TB ? (e & 31) : (e >> 6);
       const int gn = n0 + n, gk = k0 + k;
-      float v = 0.f;
-      if (gn < N && gk < kend) v = TB ? B[(size_t)gn * K + gk] : B[(size_t)gk * N + gn];
-      Bs[k][n] = v;
+      const bool ok = gn < N && gk < kend;
+      const float* src = ok ? (TB ? B + (size_t)gn * K + gk : B + (size_t)gk * N + gn) : B;
+      cp_async_f32(smem_addr(bs + k * (TN + 4) + n), src, ok);
     }
+  };
+  // one commit group per K step, empty ones included, so that "all but the newest NST-1 groups
+  // are complete" always means "step s has landed"
+#pragma unroll
+  for (int st = 0; st < NST; ++st) {
+    if (st < nsteps) load_stage(st, kbeg + st * TK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  for (int s = 0; s < nsteps; ++s) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
     __syncthreads();
+    const float* as = stage_mem + (s % NST) * kStageFloats;
+    const float* bs = as + TK * (TM + 1);
 #pragma unroll
     for (int kk = 0; kk < TK; ++kk) {
-      const float a0 = As[kk][ty * 2], a1 = As[kk][ty * 2 + 1];
-      const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float a0 = as[kk * (TM + 1) + ty * 2], a1 = as[kk * (TM + 1) + ty * 2 + 1];
+      const float4 b = *reinterpret_cast<const float4*>(bs + kk * (TN + 4) + tx * 4);
       acc[0][0] = fmaf(a0, b.x, acc[0][0]);
       acc[0][1] = fmaf(a0, b.y, acc[0][1]);
       acc[0][2] = fmaf(a0, b.z, acc[0][2]);
@@ -74,6 +127,32 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
       acc[1][3] = fmaf(a1, b.w, acc[1][3]);
     }
     __syncthreads();
+    if (s + NST < nsteps) load_stage(s % NST, kbeg + (s + NST) * TK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (cluster) {
+    const int S = gridDim.z;
+    const int z = (int)cluster_rank();  // = blockIdx.z: the cluster spans the whole z extent of the grid
+    const int rows_per = (TM + S - 1) / S;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every peer has started
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int m = ty * 2 + r;  // row of the tile: owner m % S keeps it as its row m / S
+      const uint32_t dst = map_to_rank(smem_addr(&Land[(int)blockIdx.z * rows_per + m / S][tx * 4]), (uint32_t)(m % S));
+      st_cluster_v4(dst, acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // this CTA's rows: partial sums added in range order, like small_reduce_kernel
+    for (int e = tid; e < rows_per * TN; e += 256) {
+      const int slot = e / TN, nl = e % TN;
+      const int ml = slot * S + z;
+      const int m = m0 + ml, n = n0 + nl;
+      if (ml >= TM || m >= M || n >= N) continue;
+      float s0 = Land[slot][nl];
+      for (int r = 1; r < S; ++r) s0 = __fadd_rn(s0, Land[r * rows_per + slot][nl]);
+      small_epilogue(s0, m, n, N, bias, pre, relu, C);
+    }
+    return;
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -112,23 +191,45 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   int kps = (K + splits - 1) / splits;
   kps = (kps + TK - 1) / TK * TK;
   splits = (K + kps - 1) / kps;
+  const bool cluster = splits > 1 && splits <= kMaxClusterSplits;
   float* partial = nullptr;
-  if (splits > 1) {
+  if (splits > 1 && !cluster) {
     void* scr = nullptr;
     int rc = vtlb_scratch(ctx, (size_t)splits * M * N * sizeof(float), &scr);
     if (rc) return rc;
     partial = (float*)scr;
   }
   dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, splits);
-#define VTLB_SMALL(TA, TB)                                                                              \
-  sgemm_small_kernel<TA, TB><<<grid, 256, 0, ctx->stream>>>(A, B, C, bias, pre, M, N, K, kps, relu, partial)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = kStageBytes;
+  cfg.stream = ctx->stream;
+  static uint64_t configured = 0;  // one bit per device
+  if (!(configured >> (ctx->device & 63) & 1)) {
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+    VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
+    configured |= 1ull << (ctx->device & 63);
+  }
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = (unsigned)(cluster ? splits : 1);
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+#define VTLB_SMALL(TA, TB)                                                                               \
+  VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, sgemm_small_kernel<TA, TB>, A, B, C, bias, pre, M, N, K, kps, relu, \
+                                    partial, (int)cluster))
   if (transA && transB) VTLB_SMALL(true, true);
   else if (transA) VTLB_SMALL(true, false);
   else if (transB) VTLB_SMALL(false, true);
   else VTLB_SMALL(false, false);
 #undef VTLB_SMALL
   VTLB_LAUNCHED(ctx);
-  if (splits > 1) {
+  if (splits > 1 && !cluster) {
     small_reduce_kernel<<<(M * N + 255) / 256, 256, 0, ctx->stream>>>(partial, splits, M, N, bias, pre, relu, C);
     VTLB_LAUNCHED(ctx);
   }
