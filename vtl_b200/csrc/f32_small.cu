@@ -12,6 +12,8 @@
 // through global memory and a second tiny kernel adds them, in the same order.
 // f32 FMA accumulation differs from the reference's f64 accumulation by
 // ~sqrt(K) * 2^-24 relative, two orders inside the 1e-5 * sqrt(K) * max|A| * max|B| bound.
+#include <stdlib.h>
+
 #include "f32_common.cuh"
 
 namespace {
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
                                                           int k_per_split, int relu,
                                                           float* __restrict__ partial, int cluster) {
   // NST stages of (A tile [TK][TM+1], B tile [TK][TN+4]) in dynamic shared memory, filled by
-  // cp.async: the loads of up to NST K steps (a whole K range of 128) are in flight at once, so
+  // cp.async: the loads of up to NST K steps (a whole K range) are in flight at once, so
   // a CTA pays one global-memory latency, not one per step
   extern __shared__ __align__(16) float stage_mem[];
   // landing zone of the cluster exchange: [source CTA][owned row][TN]; written by the peers
@@ -186,7 +188,16 @@ __global__ void __launch_bounds__(256) small_reduce_kernel(const float* __restri
 int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
                      const float* B, float* C, const float* bias, int relu, float* pre) {
   const int tiles = ((N + TN - 1) / TN) * ((M + TM - 1) / TM);
-  int splits = (K + 127) / 128;  // at most four 32-wide steps per CTA
+  // K ranges of `kps_want` (VTLB_SMALL_KPS overrides): the product is spread over as many SMs as
+  // the cluster limit of 8 ranges allows, since a CTA that walks a long K alone is bound by its own
+  // shared-memory reads (measured on config 1: no split 100 us per step, ranges of 256 80 us, of 128 74 us, of 64 67.5 us)
+  static int kps_want = -1;
+  if (kps_want < 0) {
+    const char* e = getenv("VTLB_SMALL_KPS");
+    kps_want = e ? atoi(e) : 64;
+    if (kps_want < 32) kps_want = 32;
+  }
+  int splits = (K + kps_want - 1) / kps_want;
   while (splits > 1 && tiles * splits > 4 * ctx->sm_count) --splits;
   int kps = (K + splits - 1) / splits;
   kps = (kps + TK - 1) / TK * TK;
