@@ -259,13 +259,20 @@ VTLB_API int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X
                             (float*)d_dX_or_null, nullptr, 0, nullptr)))
       return rc;
   }
+  bool db_done = false;
   if (d_dW_or_null) {  // dW[N,K] = G^T[N,M] . X[M,K]
     if (!d_X) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_bwd_f32: dW needs X");
-    if ((rc = gemm_f32_impl(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X,
-                            (float*)d_dW_or_null, nullptr, 0, nullptr)))
+    if (d_db_or_null && 2.0 * M * N * K <= ctx->small_gemm_flops && vtlb_aligned16(d_dW_or_null)) {
+      // small product: the CUDA-core kernel sums the rows of G^T (= the bias gradient) on the way
+      if ((rc = f32::sgemm_small(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X, (float*)d_dW_or_null,
+                                 nullptr, 0, nullptr, (float*)d_db_or_null, &db_done)))
+        return rc;
+    } else if ((rc = gemm_f32_impl(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X,
+                                   (float*)d_dW_or_null, nullptr, 0, nullptr))) {
       return rc;
+    }
   }
-  if (d_db_or_null) {
+  if (d_db_or_null && !db_done) {
     if ((rc = colsum(ctx, (const float*)d_G, M, N, (float*)d_db_or_null))) return rc;
   }
   return VTLB_OK;

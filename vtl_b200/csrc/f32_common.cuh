@@ -208,8 +208,11 @@ int split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool tran
                   float* hi, float* lo);
 
 // C[M,N] = op(A).op(B) (+bias, pre-activation copy, ReLU) on CUDA cores, for small products.
+// With `a_rowsum` the launch also writes a_rowsum[m] = sum over k of op(A)(m, k) (f64 sums, rounded
+// once) when it can (K not cut into ranges); *rowsum_done says whether it did.
 int sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
-                const float* B, float* C, const float* bias, int relu, float* pre);
+                const float* B, float* C, const float* bias, int relu, float* pre,
+                float* a_rowsum = nullptr, bool* rowsum_done = nullptr);
 
 // out[i] = sum_s partial[s][i] (fixed order, f32 round-to-nearest), n elements.
 int reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out);

@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
                                                           const float* __restrict__ bias,
                                                           float* __restrict__ pre, int M, int N, int K,
                                                           int k_per_split, int relu,
-                                                          float* __restrict__ partial, int cluster) {
+                                                          float* __restrict__ partial, int cluster,
+                                                          float* __restrict__ a_rowsum) {
   // NST stages of (A tile [TK][TM+1], B tile [TK][TN+4]) in dynamic shared memory, filled by
   // cp.async: the loads of up to NST K steps (a whole K range) are in flight at once, so
   // a CTA pays one global-memory latency, not one per step
@@ -110,6 +111,12 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  // Optional by-product (unsplit launches only): a_rowsum[m] = sum over k of A(m, k), summed in
+  // f64 and rounded once.  For dW = G^T . X these are the column sums of G, the bias gradient,
+  // which would otherwise cost a launch of its own; the first column of tiles computes them from
+  // the A tiles it loads anyway.
+  const bool want_sum = a_rowsum != nullptr && blockIdx.x == 0;
+  double rsum0 = 0.0, rsum1 = 0.0;
   for (int s = 0; s < nsteps; ++s) {
     asm volatile("cp.async.wait_group %0;" ::"n"(NST - 1) : "memory");
     __syncthreads();
@@ -127,10 +134,18 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
       acc[1][1] = fmaf(a1, b.y, acc[1][1]);
       acc[1][2] = fmaf(a1, b.z, acc[1][2]);
       acc[1][3] = fmaf(a1, b.w, acc[1][3]);
+      if (want_sum) {
+        rsum0 += (double)a0;
+        rsum1 += (double)a1;
+      }
     }
     __syncthreads();
     if (s + NST < nsteps) load_stage(s % NST, kbeg + (s + NST) * TK);
     asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (want_sum && tx == 0) {
+    if (m0 + ty * 2 < M) a_rowsum[m0 + ty * 2] = (float)rsum0;
+    if (m0 + ty * 2 + 1 < M) a_rowsum[m0 + ty * 2 + 1] = (float)rsum1;
   }
   if (cluster) {
     const int S = gridDim.z;
@@ -186,7 +201,8 @@ __global__ void __launch_bounds__(256) small_reduce_kernel(const float* __restri
 }  // namespace
 
 int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
-                     const float* B, float* C, const float* bias, int relu, float* pre) {
+                     const float* B, float* C, const float* bias, int relu, float* pre, float* a_rowsum,
+                     bool* rowsum_done) {
   const int tiles = ((N + TN - 1) / TN) * ((M + TM - 1) / TM);
   // K ranges of `kps_want` (VTLB_SMALL_KPS overrides): the product is spread over as many SMs as
   // the cluster limit of 8 ranges allows, since a CTA that walks a long K alone is bound by its own
@@ -203,6 +219,8 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   kps = (kps + TK - 1) / TK * TK;
   splits = (K + kps - 1) / kps;
   const bool cluster = splits > 1 && splits <= kMaxClusterSplits;
+  if (splits > 1) a_rowsum = nullptr;  // the by-product needs the whole K in one CTA
+  if (rowsum_done) *rowsum_done = a_rowsum != nullptr;
   float* partial = nullptr;
   if (splits > 1 && !cluster) {
     void* scr = nullptr;
@@ -233,7 +251,7 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   cfg.numAttrs = 1;
 #define VTLB_SMALL(TA, TB)                                                                               \
   VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, sgemm_small_kernel<TA, TB>, A, B, C, bias, pre, M, N, K, kps, relu, \
-                                    partial, (int)cluster))
+                                    partial, (int)cluster, a_rowsum))
   if (transA && transB) VTLB_SMALL(true, true);
   else if (transA) VTLB_SMALL(true, false);
   else if (transB) VTLB_SMALL(false, true);

@@ -13,6 +13,7 @@ Session::Session(int device) {
   if (rc != VTLB_OK) throw Error(rc, vtlb_last_error(nullptr));
 }
 Session::~Session() {
+  seed_one.reset();  // freed through the context: before the context goes
   if (ctx && owns_ctx) vtlb_ctx_destroy(ctx);
 }
 void Session::check(int rc) const {
@@ -106,10 +107,20 @@ void Context::register_node(std::string name, std::unique_ptr<Gate> gate, VarPtr
 // walk the tape backwards; parent.grad = parent.grad.add(diff).
 void Variable::backprop() {
   Session* s = context->device_session;
-  grad = Tensor::ones(s, value.shape());
-  grad_is_zero = false;
   auto& nodes = context->nodes;
   while (!nodes.empty() && nodes.back().result.get() != this) nodes.pop_back();
+  if (value.size() == 1 && !nodes.empty() && nodes.back().gate->ignores_upstream()) {
+    // a scalar loss: its gate never looks at the seed, so every step can share one tensor of ones
+    // (one launch less per training step; the loss variable's grad still reads 1.0 afterwards)
+    if (!s->seed_one) {
+      Tensor one = Tensor::ones(s, {1});
+      s->seed_one = one.buffer();
+    }
+    grad = Tensor::view(s->seed_one, 0, value.shape());
+  } else {
+    grad = Tensor::ones(s, value.shape());
+  }
+  grad_is_zero = false;
   while (!nodes.empty()) {
     Node node = std::move(nodes.back());
     nodes.pop_back();
@@ -227,6 +238,7 @@ struct MaxPool2DGate : Gate {
 struct LossGate : Gate {
   Tensor d_output;
   std::vector<Tensor> backward(const Tensor&) override { return {d_output}; }
+  bool ignores_upstream() const override { return true; }
 };
 
 }  // namespace

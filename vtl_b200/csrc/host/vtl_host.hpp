@@ -38,6 +38,7 @@ struct Session {
   void check(int rc) const;  // throws Error with vtlb_last_error on rc != 0
   void comm_init(int nranks_, int rank_, const void* id128);
   void sync() const { check(vtlb_sync(ctx)); }
+  std::shared_ptr<struct DeviceBuf> seed_one;  // a [1] tensor holding 1.0, filled once (Variable::backprop)
 };
 
 struct DeviceBuf {  // one vtlb_alloc; freed (stream-ordered) when the last Tensor view dies
@@ -95,6 +96,9 @@ using VarPtr = std::shared_ptr<Variable>;
 struct Gate {
   virtual ~Gate() = default;
   virtual std::vector<Tensor> backward(const Tensor& upstream) = 0;
+  // true for gates that never read their upstream gradient nor hand it on (the loss gates):
+  // backprop() may then seed them with a shared tensor of ones instead of filling a fresh one
+  virtual bool ignores_upstream() const { return false; }
 };
 struct Node {
   std::unique_ptr<Gate> gate;
