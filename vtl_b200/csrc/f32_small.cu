@@ -214,12 +214,6 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
     if (kps_want < 32) kps_want = 32;
   }
   int splits = (K + kps_want - 1) / kps_want;
-  static int cap8 = -1;
-  if (cap8 < 0) {
-    const char* e = getenv("VTLB_SMALL_CAP8");
-    cap8 = e ? atoi(e) : 0;
-  }
-  if (cap8 && splits > kMaxClusterSplits && K <= 32 * NST * kMaxClusterSplits) splits = kMaxClusterSplits;
   while (splits > 1 && tiles * splits > 4 * ctx->sm_count) --splits;
   int kps = (K + splits - 1) / splits;
   kps = (kps + TK - 1) / TK * TK;
