@@ -71,6 +71,7 @@ struct RmsPropF64 {  // v = running average of the squared gradient
 template <class Op>
 __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ Table tb, const Op op,
                                                    int zero_grad) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   int ti = 0;
   while (ti + 1 < tb.nt && (int)blockIdx.x >= tb.first_block[ti + 1]) ++ti;
   const size_t n = tb.n[ti];

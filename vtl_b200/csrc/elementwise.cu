@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(256) relu_fwd_kernel(const float* __restrict__
 __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__ g,
                                                        const float* __restrict__ c,
                                                        float* __restrict__ dx, size_t n, int vec) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t done = 0;
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(256) mse_short_kernel(const float* __restrict_
                                                         size_t n, double divisor, float* __restrict__ dp,
                                                         float* __restrict__ loss) {
   __shared__ double sm[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   double acc = 0.0;
   for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
     const float d = __fsub_rn(p[i], t[i]);

@@ -75,6 +75,12 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
   __shared__ __align__(16) float Land[kLandRows][TN];
   // "this CTA runs": entered here, waited for before the first store into a peer's memory
   if (cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  // Launched with programmatic stream serialisation: the CTAs may be resident before the kernel
+  // in front of this one in the stream has finished (its launch latency hidden behind that
+  // kernel's tail); nothing of that kernel's output is touched before this wait, which returns
+  // once it has completed and its writes are visible.  Then let the next kernel do the same.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x;
   const int ty = tid >> 4, tx = tid & 15;  // 16 x 16 threads, 2 x 4 outputs each
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -191,6 +197,7 @@ __global__ void __launch_bounds__(256) small_reduce_kernel(const float* __restri
                                                            int M, int N, const float* __restrict__ bias,
                                                            float* __restrict__ pre, int relu,
                                                            float* __restrict__ C) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this one may start early
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * N) return;
   float s = partial[i];
@@ -242,13 +249,20 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
     VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
     configured |= 1ull << (ctx->device & 63);
   }
-  cudaLaunchAttribute at[1];
+  static int pdl = -1;  // VTLB_SMALL_PDL=0 switches the early launch off (measurements)
+  if (pdl < 0) {
+    const char* e = getenv("VTLB_SMALL_PDL");
+    pdl = e ? atoi(e) != 0 : 1;
+  }
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 1;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = (unsigned)(cluster ? splits : 1);
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
 #define VTLB_SMALL(TA, TB)                                                                               \
   VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, sgemm_small_kernel<TA, TB>, A, B, C, bias, pre, M, N, K, kps, relu, \
                                     partial, (int)cluster, a_rowsum))
