@@ -71,6 +71,7 @@ struct RmsPropF64 {  // v = running average of the squared gradient
 template <class Op>
 __global__ void __launch_bounds__(256) adam_kernel(const __grid_constant__ Table tb, const Op op,
                                                    int zero_grad) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   int ti = 0;
   while (ti + 1 < tb.nt && (int)blockIdx.x >= tb.first_block[ti + 1]) ++ti;
@@ -141,7 +142,7 @@ int run(vtlb_ctx* ctx, const char* fn, int n_tensors, const vtlb_adam_tensor* te
     }
     if (tb.nt == 0) break;
     tb.first_block[tb.nt] = blocks;
-    adam_kernel<Op><<<blocks, 256, 0, ctx->stream>>>(tb, op, zero_grad);
+    VTLB_CUDA(ctx, vtlb_launch_early(adam_kernel<Op>, dim3(blocks), dim3(256), 0, ctx->stream, tb, op, zero_grad));
     VTLB_LAUNCHED(ctx);
   }
   return VTLB_OK;

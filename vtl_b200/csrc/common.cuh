@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <unordered_map>
@@ -97,6 +98,32 @@ int vtlb_fail(vtlb_ctx* ctx, int code, const char* fmt, ...);
 // Returns a scratch region of at least `bytes` (grown on demand; growth
 // synchronises the stream first because earlier kernels may still use the old one).
 int vtlb_scratch(vtlb_ctx* ctx, size_t bytes, void** out);
+
+// Launch with programmatic stream serialisation: the kernel's CTAs may become resident while
+// the kernel in front of it in the stream is still finishing, which hides the launch latency
+// of short dependent kernels.  Only for kernels that execute griddepcontrol.wait before their
+// first access to memory (the wait returns once the kernel in front has completed and its
+// writes are visible).  VTLB_EARLY_LAUNCH=0 turns the attribute off (measurements).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vtlb_launch_early(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, Args&&... args) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("VTLB_EARLY_LAUNCH");
+    on = e ? atoi(e) != 0 : 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = on ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<Args&&>(args)...);
+}
 
 static inline bool vtlb_aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0; }
 static inline size_t vtlb_round_up(size_t x, size_t m) { return (x + m - 1) / m * m; }

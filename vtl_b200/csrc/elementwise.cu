@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(256) relu_fwd_kernel(const float* __restrict__
 __global__ void __launch_bounds__(256) relu_bwd_kernel(const float* __restrict__ g,
                                                        const float* __restrict__ c,
                                                        float* __restrict__ dx, size_t n, int vec) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(256) mse_short_kernel(const float* __restrict_
                                                         size_t n, double divisor, float* __restrict__ dp,
                                                         float* __restrict__ loss) {
   __shared__ double sm[8];
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this kernel may start early
   double acc = 0.0;
   for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -193,8 +195,8 @@ VTLB_API int vtlb_relu_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_cac
   if (n == 0) return VTLB_OK;
   if (!d_g || !d_cached_x || !d_dx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_relu_bwd_f32: null pointer");
   const int vec = vtlb_aligned16(d_g) && vtlb_aligned16(d_cached_x) && vtlb_aligned16(d_dx);
-  relu_bwd_kernel<<<ew_grid(ctx, n, 1024), 256, 0, ctx->stream>>>(
-      (const float*)d_g, (const float*)d_cached_x, (float*)d_dx, n, vec);
+  VTLB_CUDA(ctx, vtlb_launch_early(relu_bwd_kernel, dim3(ew_grid(ctx, n, 1024)), dim3(256), 0, ctx->stream,
+                                   (const float*)d_g, (const float*)d_cached_x, (float*)d_dx, n, vec));
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
@@ -205,8 +207,8 @@ VTLB_API int vtlb_mse_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_P, const void* d_
   if (n == 0 || n_div == 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: empty input");
   if (!d_P || !d_T || !d_loss) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: null pointer");
   if (n <= 8192) {
-    mse_short_kernel<<<1, 256, 0, ctx->stream>>>((const float*)d_P, (const float*)d_T, n, (double)n_div,
-                                                 (float*)d_dP_or_null, (float*)d_loss);
+    VTLB_CUDA(ctx, vtlb_launch_early(mse_short_kernel, dim3(1), dim3(256), 0, ctx->stream, (const float*)d_P,
+                                     (const float*)d_T, n, (double)n_div, (float*)d_dP_or_null, (float*)d_loss));
     VTLB_LAUNCHED(ctx);
     return VTLB_OK;
   }

@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(256) small_reduce_kernel(const float* __restri
                                                            int M, int N, const float* __restrict__ bias,
                                                            float* __restrict__ pre, int relu,
                                                            float* __restrict__ C) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this one may start early
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * N) return;
@@ -273,7 +274,8 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
 #undef VTLB_SMALL
   VTLB_LAUNCHED(ctx);
   if (splits > 1 && !cluster) {
-    small_reduce_kernel<<<(M * N + 255) / 256, 256, 0, ctx->stream>>>(partial, splits, M, N, bias, pre, relu, C);
+    VTLB_CUDA(ctx, vtlb_launch_early(small_reduce_kernel, dim3((M * N + 255) / 256), dim3(256), 0, ctx->stream,
+                                     (const float*)partial, splits, M, N, bias, pre, relu, C));
     VTLB_LAUNCHED(ctx);
   }
   return VTLB_OK;
