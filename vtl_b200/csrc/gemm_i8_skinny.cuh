@@ -144,6 +144,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_i8_skinny_kernel(const __
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // launched early (programmatic stream serialisation): the set-up above overlapped the tail of the
+  // kernel in front; global memory is first touched after this wait
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // "this CTA runs": waited for (by then for nothing) before the first store into a peer's memory
   if (S > 1) cluster_arrive_relaxed();
 
@@ -350,13 +354,15 @@ int launch_s(vtlb_ctx* ctx, int tiles, const Params& p) {
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = SMEM_TOTAL;
   cfg.stream = ctx->stream;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = (unsigned)S;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_i8_skinny_kernel<FUSED, S>, p));
   return VTLB_OK;
 }

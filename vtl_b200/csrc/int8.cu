@@ -11,6 +11,10 @@
 
 namespace {
 
+// Row counts up to which the register-resident quantise kernel is launched early
+// (programmatic stream serialisation, common.cuh).
+constexpr int kEarlyQuantRows = 512;
+
 // ---------------------------------------------------------------- quantise rows
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -35,6 +39,8 @@ __global__ void __launch_bounds__(256) quant_rows_i8_kernel(const float* __restr
                                                             const float* __restrict__ amax_in) {
   __shared__ float s_part[8];
   __shared__ float s_amax;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early: the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int row = blockIdx.x;
   if (row >= M) return;
   const float* a = A + (size_t)row * K;
@@ -96,6 +102,8 @@ __global__ void __launch_bounds__(256) quant_rows_i8_reg_kernel(const float* __r
                                                                 const float* __restrict__ amax_in) {
   __shared__ float s_part[8];
   __shared__ float s_amax;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early: the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int row = blockIdx.x;
   const float4* a4 = reinterpret_cast<const float4*>(A + (size_t)row * K);
   const int n4 = K >> 2;
@@ -313,6 +321,8 @@ __global__ void __launch_bounds__(128) gemv_i8_kernel(const int8_t* __restrict__
                                                       const float* __restrict__ sa,
                                                       const float* __restrict__ sw,
                                                       const float* __restrict__ bias, int relu) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early: the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int gwarp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -411,8 +421,8 @@ int launch_gemv(vtlb_ctx* ctx, const int8_t* Aq, const int8_t* Wq, int M, int N,
   if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
   if (blocks < 1) blocks = 1;
 #define VTLB_GEMV(MT)                                                                        \
-  gemv_i8_kernel<MT, 8, FUSED><<<blocks, 128, 0, ctx->stream>>>(Aq, Wq, M, N, K, ldk, acc, Y, \
-                                                                sa, sw, bias, relu)
+  VTLB_CUDA(ctx, vtlb_launch_early(gemv_i8_kernel<MT, 8, FUSED>, dim3(blocks), dim3(128), 0, ctx->stream, \
+                                   Aq, Wq, M, N, K, ldk, acc, Y, sa, sw, bias, relu))
   if (M <= 1) VTLB_GEMV(1);
   else if (M <= 2) VTLB_GEMV(2);
   else if (M <= 4) VTLB_GEMV(4);
@@ -522,8 +532,15 @@ VTLB_API int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, vo
     const float* am = (const float*)d_amax_in_or_null;
 #define VTLB_QREG(VPT)                                                                            \
   do {                                                                                            \
-    if (am) quant_rows_i8_reg_kernel<VPT, true><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);  \
-    else quant_rows_i8_reg_kernel<VPT, false><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);    \
+    if (M > kEarlyQuantRows) { /* long launches gain nothing from an early start (measured) */   \
+      if (am) quant_rows_i8_reg_kernel<VPT, true><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);  \
+      else quant_rows_i8_reg_kernel<VPT, false><<<M, 256, 0, ctx->stream>>>(A, M, K, ldq, Q, sc, am);    \
+    } else if (am)                                                                                \
+      VTLB_CUDA(ctx, vtlb_launch_early(quant_rows_i8_reg_kernel<VPT, true>, dim3(M), dim3(256), 0,    \
+                                       ctx->stream, A, M, K, ldq, Q, sc, am));                      \
+    else                                                                                          \
+      VTLB_CUDA(ctx, vtlb_launch_early(quant_rows_i8_reg_kernel<VPT, false>, dim3(M), dim3(256), 0,   \
+                                       ctx->stream, A, M, K, ldq, Q, sc, am));                      \
   } while (0)
     if (K <= 1024) VTLB_QREG(1);
     else if (K <= 2048) VTLB_QREG(2);
