@@ -346,8 +346,11 @@ def run_int8(args, ranks):
                 "kernel_ms": gemm_ms}
     else:
         gbs = op_bytes / (gemm_ms * 1e-3) / 1e9
+        # ncu on the M = 16 launch (profiles/gemm_i8_skinny_m16.md): 16.9 MB of DRAM traffic against 17.1 MB
+        # of algorithmic bytes -- every weight code read once; other row counts scaled by their bytes
         roof = {"bound": "hbm", "kernel": kname, "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                "frac": gbs / pk["hbm_gbs"], "traffic": op_bytes * (16.9 / 17.14),
+                "traffic_unit": "bytes per launch (ncu capture at M = 16, scaled by the algorithmic bytes)",
                 "algorithmic_bytes_per_launch": op_bytes,
                 "peak_source": f"hbm_gbs of {pk['_source']}", "kernel_ms": gemm_ms}
     out = None
