@@ -105,11 +105,13 @@ def test_conv2d_split_k_path(dev, orc):
 
 @pytest.mark.parametrize("shape,kernel,pad,stride", [((2, 3, 6, 8), (2, 2), (0, 0), (2, 2)),
                                                       ((4, 64, 32, 32), (2, 2), (0, 0), (2, 2)),
+                                                      ((2, 3, 5, 6), (2, 2), (0, 0), (2, 2)),   # general kernel
                                                       ((1, 2, 7, 7), (3, 3), (1, 1), (2, 2))])
 def test_maxpool_bit_exact(dev, orc, shape, kernel, pad, stride):
     rng = np.random.default_rng(sum(shape))
     x = rng.standard_normal(shape).astype(np.float32)
     x[0, 0, 0, :2] = 5.0  # a tie inside the first window: the first maximum must win
+    x[0, 0, 0, 3] = x[0, 0, 1, 2] = 7.0  # and one across the two rows of the second window
     ry, ridx = orc.maxpool2d_fwd_f32(x, kernel, pad, stride)
     dx = dev.to_device(x)
     dy, didx = dev.zeros(ry.shape), dev.zeros(ry.shape, np.int32)

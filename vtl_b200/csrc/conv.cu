@@ -342,6 +342,36 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
     idx[i] = bi;
   }
 }
+// The common case, 2 x 2 windows at stride 2 without padding on rows of a multiple of 4 values:
+// a thread reads 16 bytes of two adjacent rows and writes two outputs.  Candidates are visited
+// in the same order, with the same comparison, as in the general kernel.
+__global__ void __launch_bounds__(256) maxpool2x2_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                             int32_t* __restrict__ idx, int planes, int H, int W) {
+  const int OH = H >> 1, OW = W >> 1, W4 = W >> 2;
+  const int n = planes * OH * W4;  // items: (plane, output row, group of 4 input columns)
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int j = i % W4;
+    const int r = i / W4;
+    const int h = r % OH;
+    const int nc = r / OH;
+    const int f0 = (nc * H + 2 * h) * W + 4 * j;  // flat index of the first value of the upper row
+    const float4 a = __ldg(reinterpret_cast<const float4*>(x + f0));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(x + f0 + W));
+    float best0 = a.x;
+    int bi0 = f0;
+    if (a.y > best0) { best0 = a.y; bi0 = f0 + 1; }
+    if (b.x > best0) { best0 = b.x; bi0 = f0 + W; }
+    if (b.y > best0) { best0 = b.y; bi0 = f0 + W + 1; }
+    float best1 = a.z;
+    int bi1 = f0 + 2;
+    if (a.w > best1) { best1 = a.w; bi1 = f0 + 3; }
+    if (b.z > best1) { best1 = b.z; bi1 = f0 + W + 2; }
+    if (b.w > best1) { best1 = b.w; bi1 = f0 + W + 3; }
+    const int o = (nc * OH + h) * OW + 2 * j;
+    *reinterpret_cast<float2*>(y + o) = make_float2(best0, best1);
+    *reinterpret_cast<int2*>(idx + o) = make_int2(bi0, bi1);
+  }
+}
 __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx,
                                                           float* __restrict__ dx, size_t n_out) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_out; i += (size_t)gridDim.x * blockDim.x) {
@@ -533,6 +563,13 @@ VTLB_API int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, v
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: input too large for 32-bit indices");
   if (!d_x || !d_y || !d_idx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2d_fwd_f32: null pointer");
   const size_t n = (size_t)B * C * OH * OW;
+  if (kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && (W & 3) == 0 && (H & 1) == 0 &&
+      vtlb_aligned16(d_x) && vtlb_aligned16(d_y) && vtlb_aligned16(d_idx)) {
+    maxpool2x2_fwd_kernel<<<f32::grid_for(ctx, n / 2, 1024), 256, 0, ctx->stream>>>(
+        (const float*)d_x, (float*)d_y, (int32_t*)d_idx, B * C, H, W);
+    VTLB_LAUNCHED(ctx);
+    return VTLB_OK;
+  }
   maxpool_fwd_kernel<<<f32::grid_for(ctx, n, 1024), 256, 0, ctx->stream>>>(
       (const float*)d_x, (float*)d_y, (int32_t*)d_idx, B, C, H, W, kh, kw, ph, pw, sh, sw, OH, OW);
   VTLB_LAUNCHED(ctx);
