@@ -31,6 +31,8 @@ struct ConvDims {
 // and walks (b, oh, ow) incrementally.  All index arithmetic is 32-bit (M < 2^31 is checked).
 __global__ void __launch_bounds__(256) im2colT_split_kernel(const float* __restrict__ x, ConvDims d, int ld,
                                                             float* __restrict__ hi, float* __restrict__ lo) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int M = (int)d.M(), K = d.K(), P = d.OH * d.OW, khw = d.kh * d.kw;
   const bool vec = (ld & 3) == 0;
   for (int k = blockIdx.y; k < K; k += gridDim.y) {
@@ -136,6 +138,8 @@ __global__ void __launch_bounds__(256) im2col_split_kernel(const float* __restri
 __global__ void __launch_bounds__(256) grad_to_OM_split_kernel(const float* __restrict__ g, int B, int O, int P,
                                                                int ld, float* __restrict__ hi,
                                                                float* __restrict__ lo) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const bool vec = (P & 3) == 0 && (ld & 3) == 0;
   for (int row = blockIdx.y; row < B * O; row += gridDim.y) {
     const int b = row / O, oc = row - b * O;
@@ -240,6 +244,8 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restr
 // per-channel sums of g [B, O, P] in f64: partial[s][oc] over images b == s (mod S)
 __global__ void __launch_bounds__(256) chan_sum_partial_kernel(const float* __restrict__ g, int B, int O, int P,
                                                                double* __restrict__ partial) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ double sm[8];
   const int oc = blockIdx.x, s = blockIdx.y, S = gridDim.y;
   double acc = 0.0;
@@ -270,6 +276,8 @@ __global__ void __launch_bounds__(256) chan_sum_partial_kernel(const float* __re
   }
 }
 __global__ void chan_sum_final_kernel(const double* __restrict__ partial, int S, int O, float* __restrict__ out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int oc = blockIdx.x * blockDim.x + threadIdx.x;
   if (oc >= O) return;
   double t = 0.0;
@@ -347,6 +355,8 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
 // in the same order, with the same comparison, as in the general kernel.
 __global__ void __launch_bounds__(256) maxpool2x2_fwd_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                              int32_t* __restrict__ idx, int planes, int H, int W) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int OH = H >> 1, OW = W >> 1, W4 = W >> 2;
   const int n = planes * OH * W4;  // items: (plane, output row, group of 4 input columns)
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -386,6 +396,8 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
 __global__ void __launch_bounds__(256) regroup_weights_split_kernel(const float* __restrict__ w, int O, int C, int taps,
                                                                     int for_input_grad, int ld, float* __restrict__ hi,
                                                                     float* __restrict__ lo) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int n = O * C * taps;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int t = i % taps, r = i / taps, ic = r % C, oc = r / C;
@@ -436,8 +448,8 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
   f32::Planes p;
   if (use_igemm(K) && igemm_taps_ok(kh, kw)) {
     if ((rc = f32::alloc_planes(ctx, 0, O, K, 0, &p))) return rc;
-    regroup_weights_split_kernel<<<f32::grid_for(ctx, (size_t)O * K, 256), 256, 0, ctx->stream>>>(
-        (const float*)d_w, O, C, kh * kw, 0, p.ld, p.b_hi, p.b_lo);
+    VTLB_CUDA(ctx, vtlb_launch_early(regroup_weights_split_kernel, dim3(f32::grid_for(ctx, (size_t)O * K, 256)), dim3(256),
+                                     0, ctx->stream, (const float*)d_w, O, C, kh * kw, 0, p.ld, p.b_hi, p.b_lo));
     VTLB_LAUNCHED(ctx);
     const igemm::Geometry g{B, C, H, W, d.OH, d.OW, sh, sw, kh, kw, -ph, -pw, 1, K};
     EpiConvOut epi{(float*)d_y, (const float*)d_bias_or_null, (float*)d_pre_or_null, O, d.P(), relu};
@@ -480,8 +492,9 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     if ((rc = f32::alloc_planes(ctx, O, K, M, (size_t)S * O * K * sizeof(float), &p))) return rc;
     {
       const long long rows = (long long)B * O;
-      grad_to_OM_split_kernel<<<dim3((P + 1023) / 1024, (unsigned)(rows < 32768 ? rows : 32768)), 256, 0,
-                                ctx->stream>>>(g, B, O, P, p.ld, p.a_hi, p.a_lo);
+      VTLB_CUDA(ctx, vtlb_launch_early(grad_to_OM_split_kernel,
+                                       dim3((P + 1023) / 1024, (unsigned)(rows < 32768 ? rows : 32768)), dim3(256), 0,
+                                       ctx->stream, g, B, O, P, p.ld, p.a_hi, p.a_lo));
     }
     VTLB_LAUNCHED(ctx);
     {
@@ -489,7 +502,8 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
       int gx = (ctx->sm_count * 16 + ky - 1) / ky;
       if (gx > (M + 1023) / 1024) gx = (M + 1023) / 1024;
       if (gx < 1) gx = 1;
-      im2colT_split_kernel<<<dim3(gx, ky), 256, 0, ctx->stream>>>((const float*)d_x, d, p.ld, p.b_hi, p.b_lo);
+      VTLB_CUDA(ctx, vtlb_launch_early(im2colT_split_kernel, dim3(gx, ky), dim3(256), 0, ctx->stream, (const float*)d_x,
+                                       d, p.ld, p.b_hi, p.b_lo));
     }
     VTLB_LAUNCHED(ctx);
     if (S == 1) {
@@ -509,8 +523,8 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     const int Kd = O * kh * kw;
     f32::Planes p;
     if ((rc = f32::alloc_planes(ctx, 0, C, Kd, 0, &p))) return rc;
-    regroup_weights_split_kernel<<<f32::grid_for(ctx, (size_t)O * C * kh * kw, 256), 256, 0, ctx->stream>>>(
-        (const float*)d_w, O, C, kh * kw, 1, p.ld, p.b_hi, p.b_lo);
+    VTLB_CUDA(ctx, vtlb_launch_early(regroup_weights_split_kernel, dim3(f32::grid_for(ctx, (size_t)O * C * kh * kw, 256)),
+                                     dim3(256), 0, ctx->stream, (const float*)d_w, O, C, kh * kw, 1, p.ld, p.b_hi, p.b_lo));
     VTLB_LAUNCHED(ctx);
     const igemm::Geometry gg{B, O, d.OH, d.OW, H, W, 1, 1, kh, kw, ph, pw, -1, Kd};
     EpiConvOut epi{(float*)d_dx_or_null, nullptr, nullptr, C, H * W, 0};
@@ -544,9 +558,11 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     int S = B < 32 ? B : 32;
     void* scr = nullptr;
     if ((rc = vtlb_scratch(ctx, (size_t)S * O * sizeof(double), &scr))) return rc;
-    chan_sum_partial_kernel<<<dim3(O, S), 256, 0, ctx->stream>>>(g, B, O, P, (double*)scr);
+    VTLB_CUDA(ctx, vtlb_launch_early(chan_sum_partial_kernel, dim3(O, S), dim3(256), 0, ctx->stream, g, B, O, P,
+                                     (double*)scr));
     VTLB_LAUNCHED(ctx);
-    chan_sum_final_kernel<<<(O + 127) / 128, 128, 0, ctx->stream>>>((const double*)scr, S, O, (float*)d_db_or_null);
+    VTLB_CUDA(ctx, vtlb_launch_early(chan_sum_final_kernel, dim3((O + 127) / 128), dim3(128), 0, ctx->stream,
+                                     (const double*)scr, S, O, (float*)d_db_or_null));
     VTLB_LAUNCHED(ctx);
   }
   return VTLB_OK;
@@ -565,8 +581,8 @@ VTLB_API int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, v
   const size_t n = (size_t)B * C * OH * OW;
   if (kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && (W & 3) == 0 && (H & 1) == 0 &&
       vtlb_aligned16(d_x) && vtlb_aligned16(d_y) && vtlb_aligned16(d_idx)) {
-    maxpool2x2_fwd_kernel<<<f32::grid_for(ctx, n / 2, 1024), 256, 0, ctx->stream>>>(
-        (const float*)d_x, (float*)d_y, (int32_t*)d_idx, B * C, H, W);
+    VTLB_CUDA(ctx, vtlb_launch_early(maxpool2x2_fwd_kernel, dim3(f32::grid_for(ctx, n / 2, 1024)), dim3(256), 0,
+                                     ctx->stream, (const float*)d_x, (float*)d_y, (int32_t*)d_idx, B * C, H, W));
     VTLB_LAUNCHED(ctx);
     return VTLB_OK;
   }

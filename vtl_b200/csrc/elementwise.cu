@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(256) loss_final_kernel(const double* __restric
                                                          int nparts, double divisor,
                                                          int divide_in_f32,
                                                          float* __restrict__ loss) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ double sm[8];
   double acc = 0.0;
   for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partial[i];
@@ -136,6 +138,8 @@ __global__ void __launch_bounds__(128) softmax_ce_kernel(const float* __restrict
                                                          const float* __restrict__ t, int B, int C,
                                                          double batch_div, float* __restrict__ dx,
                                                          double* __restrict__ partial) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ double sm[8];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   double li = 0.0;
@@ -219,8 +223,8 @@ VTLB_API int vtlb_mse_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_P, const void* d_
   mse_partial_kernel<<<blocks, 256, 0, ctx->stream>>>((const float*)d_P, (const float*)d_T, n,
                                                       (float*)d_dP_or_null, (double*)scr);
   VTLB_LAUNCHED(ctx);
-  loss_final_kernel<<<1, 256, 0, ctx->stream>>>((const double*)scr, blocks, (double)n_div, 1,
-                                                (float*)d_loss);
+  VTLB_CUDA(ctx, vtlb_launch_early(loss_final_kernel, dim3(1), dim3(256), 0, ctx->stream, (const double*)scr, blocks,
+                                   (double)n_div, 1, (float*)d_loss));
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
@@ -235,12 +239,11 @@ VTLB_API int vtlb_softmax_ce_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_X, const v
   void* scr = nullptr;
   int rc = vtlb_scratch(ctx, (size_t)blocks * sizeof(double), &scr);
   if (rc) return rc;
-  softmax_ce_kernel<<<blocks, 128, 0, ctx->stream>>>((const float*)d_X, (const float*)d_T, B, C,
-                                                     (double)batch_div, (float*)d_dX_or_null,
-                                                     (double*)scr);
+  VTLB_CUDA(ctx, vtlb_launch_early(softmax_ce_kernel, dim3(blocks), dim3(128), 0, ctx->stream, (const float*)d_X,
+                                   (const float*)d_T, B, C, (double)batch_div, (float*)d_dX_or_null, (double*)scr));
   VTLB_LAUNCHED(ctx);
-  loss_final_kernel<<<1, 256, 0, ctx->stream>>>((const double*)scr, blocks, (double)batch_div, 0,
-                                                (float*)d_loss);
+  VTLB_CUDA(ctx, vtlb_launch_early(loss_final_kernel, dim3(1), dim3(256), 0, ctx->stream, (const double*)scr, blocks,
+                                   (double)batch_div, 0, (float*)d_loss));
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }

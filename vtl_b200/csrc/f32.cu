@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(256) colsum_short_kernel(const float* __restri
 __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restrict__ partial,
                                                             int splits, size_t n,
                                                             float* __restrict__ out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x) {
     float s[8];
@@ -216,7 +218,8 @@ int check_f32(vtlb_ctx* ctx, const char* fn, int M, int N, int K) {
 }  // namespace
 
 int f32::reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out) {
-  reduce_splits_kernel<<<f32::grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(partial, splits, n, out);
+  VTLB_CUDA(ctx, vtlb_launch_early(reduce_splits_kernel, dim3(f32::grid_for(ctx, n, 256)), dim3(256), 0, ctx->stream, partial,
+                                   splits, n, out));
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;
 }
