@@ -394,7 +394,8 @@ def run_int8_reference(args, ranks):
     from oracle import oracle
     oracle.build()
     wq, sw = oracle.quant_rows_i8(W)
-    _, cores, _, rows, dt = cpu_int8_sample(A, W, b, budget_s=max(2.0, 60.0 / max(1, args.steps + args.warmup)))
+    # rows per step sized so that the whole --steps/--warmup run stays near a minute
+    _, cores, _, rows, dt = cpu_int8_sample(A, W, b, budget_s=min(20.0, max(0.02, 60.0 / max(1, args.steps + args.warmup))))
     for _ in range(args.warmup):
         oracle.linear_i8_fwd(A[:rows], wq, sw, b, True)
     t0 = time.perf_counter()
@@ -414,6 +415,23 @@ def run_int8_reference(args, ranks):
            "gpu_launches": 0}
     ranks.close()
     return out
+
+
+def use_all_host_threads():
+    """The CPU arm runs on every host core.  torch.distributed.run exports OMP_NUM_THREADS=1 to its
+    workers, which would leave the oracle's OpenMP loops and NumPy's BLAS on one thread at N > 1."""
+    n = os.cpu_count() or 1
+    try:
+        from oracle import oracle
+        oracle.build()
+        oracle.set_threads(n)
+    except Exception as e:  # an oracle built before the setter existed: report, keep going
+        print(f"bench: could not raise the oracle's thread count: {e}", file=sys.stderr)
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=n)
+    except Exception as e:
+        print(f"bench: could not raise the BLAS thread count: {e}", file=sys.stderr)
 
 
 def main():
@@ -439,6 +457,8 @@ def main():
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
     ranks = Ranks(args.gpus)
+    if args.impl == "reference" and ranks.rank == 0:
+        use_all_host_threads()
     if args.workload == "int8_linear":
         out = run_int8_reference(args, ranks) if args.impl == "reference" else run_int8(args, ranks)
     elif args.workload == "int8_mlp_c5":

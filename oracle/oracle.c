@@ -489,6 +489,17 @@ ORC_API void orc_linear_i8_fwd(const float *A, const int8_t *Wq, const float *sw
   free(acc);
 }
 
+/* Threads the OpenMP loops of this file may use from now on (a launcher may have set
+ * OMP_NUM_THREADS=1 in the environment; the CPU arm of the benchmark wants all host cores). */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+  extern void omp_set_num_threads(int);
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_max_threads(void) {
 #ifdef _OPENMP
   extern int omp_get_max_threads(void);

@@ -62,6 +62,11 @@ def max_threads() -> int:
     return int(lib().orc_max_threads())
 
 
+def set_threads(n: int) -> None:
+    """Lets the OpenMP loops of the C oracle use n threads from now on."""
+    lib().orc_set_threads(int(n))
+
+
 # ---------------------------------------------------------------- matmul
 def matmul_f32(A, B, ta=False, tb=False):
     """la.matmul[f32] (la/la.v:38-55): f64 multiply-accumulate, one final rounding."""
