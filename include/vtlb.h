@@ -240,7 +240,10 @@ int vtlb_i8_ld(int K);
 int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_Q, void* d_scale,
                        const void* d_amax_in_or_null);
 int vtlb_row_absmax_f32(vtlb_ctx* ctx, const void* d_A, int M, int K, void* d_amax);
-/* acc[M,N] (int32) = Aq[M,K].Wq[N,K]^T, exact (tcgen05 kind::i8). */
+/* acc[M,N] (int32) = Aq[M,K].Wq[N,K]^T, exact.  The kernel follows the shape, the result does
+ * not: one row of activations streams W through dp4a; up to 128 rows run on tcgen05 kind::i8
+ * with the output channels on the M side of the MMA and K cut across a thread-block cluster;
+ * larger products run as 128-row tiles, on CTA pairs (cta_group::2) when there are enough. */
 int vtlb_gemm_i8_i32(vtlb_ctx* ctx, const void* d_Aq, const void* d_Wq, int M, int N, int K,
                      void* d_acc);
 /* Y[M,N] = relu?( (float)acc * (sa[m]*sw[n]) + bias[n] ), the dequantisation
