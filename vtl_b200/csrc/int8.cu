@@ -308,8 +308,8 @@ struct EpiDequant {
 };
 
 // ---------------------------------------------------------------- very small M (GEMV-like)
-// With one or two rows of activations the problem is streaming W once from HBM (N*K
-// bytes).  Each warp owns one output channel at a time and walks its row of W in pieces of
+// With a single row of activations (up to VTLB_I8_GEMV_MAX_M rows) the problem is streaming W
+// once from HBM (N*K bytes).  Each warp owns one output channel at a time and walks its row of W in pieces of
 // U * 512 bytes, all U 16-byte loads of a lane issued before the first is used (a whole
 // 4096-byte row in flight per warp at U = 8), accumulating with dp4a against up to MT
 // rows of A (exact int32).
