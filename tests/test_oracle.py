@@ -170,3 +170,19 @@ def test_mlp_oracle_step_decreases_loss(orc):
     assert losses[-1] < losses[0]
     blas = orc.MLPOracle([W1, W2], [np.zeros(16), np.zeros(4)], [True, False], lr=1e-2, blas=True)
     assert abs(float(blas.step(X, T)) - losses[0]) < 1e-6
+
+
+def test_oracle_thread_count_can_be_raised_after_load():
+    """The benchmark's CPU arm sets the OpenMP thread count itself (a launcher may have exported
+    OMP_NUM_THREADS=1 before the library was loaded)."""
+    from oracle import oracle
+    oracle.build()
+    before = oracle.max_threads()
+    try:
+        oracle.set_threads(2)
+        assert oracle.max_threads() == 2
+        oracle.set_threads(1)
+        assert oracle.max_threads() == 1
+    finally:
+        oracle.set_threads(before)
+    assert oracle.max_threads() == before
