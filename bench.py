@@ -87,20 +87,30 @@ class ClockSampler:
                 return
             time.sleep(0.005)
 
+    def snapshot(self):
+        """Summary of the samples taken since the last snapshot (or since start)."""
+        mark = getattr(self, "_mark", 0)
+        part = self.samples[mark:]
+        self._mark = len(self.samples)
+        return self._summary(part)
+
     def stop(self):
         self.stop_flag = True
         if self.thread:
             self.thread.join(timeout=2)
-        if not self.samples:
+        return self._summary(self.samples)
+
+    def _summary(self, samples):
+        if not samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": [self.err or "no samples"]}
         nv = self.nv
         names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
                  "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
                  "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
                  "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
-        reasons = sorted(k for k, bit in names.items() if any(s[1] & bit for s in self.samples))
+        reasons = sorted(k for k, bit in names.items() if any(s[1] & bit for s in samples))
         # clocks idle low between kernels: the figure that matters is the clock under load
-        top = sorted(s[0] for s in self.samples)
+        top = sorted(s[0] for s in samples)
         return {"sm_mhz": statistics.median(top), "sm_mhz_p90": top[int(0.9 * (len(top) - 1))],
                 "sm_max_mhz": self.smax, "samples": len(top), "reasons": reasons}
 
@@ -139,26 +149,83 @@ class Ranks:
                 session.comm_init(self.world, self.rank, box[0])
             else:
                 dev.comm_init_rank(self.world, self.rank, box[0])
-            self._red = dev.zeros(4, np.float32)
+            self._red = dev.zeros(64, np.float32)
 
     def barrier(self):
         if self.dist:
             self.dist.barrier()
 
     def max_f32(self, x: float) -> float:
+        return self.max_many([x])[0]
+
+    def max_many(self, xs):
+        """Element-wise maximum over the ranks of up to 64 numbers (the library's own NCCL
+        communicator carries it)."""
+        xs = [float(x) for x in xs]
         if self.world == 1:
-            return x
+            return xs
+        assert len(xs) <= 64
         dev = self.dev
-        dev.h2d_raw(self._red, np.array([x, 0, 0, 0], np.float32).ctypes.data, 16)
+        h = np.zeros(64, np.float32)
+        h[:len(xs)] = xs
+        dev.h2d_raw(self._red, h.ctypes.data, 256)
         dev.sync()
-        dev.allreduce_max_f32_async(self._red, 4)
+        dev.allreduce_max_f32_async(self._red, 64)
         dev.comm_wait()
-        return float(self._red.numpy()[0])
+        return [float(v) for v in self._red.numpy()[:len(xs)]]
+
+    def gather_objects(self, obj):
+        """[obj of rank 0, ..., obj of rank N-1] on every rank (control plane, gloo)."""
+        if self.world == 1:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj)
+        return out
 
     def close(self):
         if self.dist:
             self.dist.barrier()
             self.dist.destroy_process_group()
+
+
+def timed_repeats(dev, ranks, run_steps, steps, min_repeat_s=0.25, min_repeats=5, max_total_s=8.0):
+    """Times `run_steps(n)` (n steps enqueued on the compute stream) as several repeats, each
+    bracketed by a rank barrier and a device synchronisation on both sides and by one CUDA event
+    pair on the launching stream.  A repeat runs a whole multiple of `steps` steps, as many as it
+    takes to keep the device busy for `min_repeat_s`; at least `min_repeats` repeats are taken
+    (fewer only if they would exceed `max_total_s`).  Returns (ms per step of every repeat, maximum
+    over the ranks; steps per repeat)."""
+    e0, e1 = dev.event(), dev.event()
+
+    def one(n):
+        dev.sync()
+        ranks.barrier()
+        dev.record(e0)
+        run_steps(n)
+        dev.record(e1)
+        ms = dev.elapsed_ms(e0, e1)
+        dev.sync()
+        ranks.barrier()
+        return ms
+
+    probe = ranks.max_f32(one(steps))  # also the last warm-up: clocks are up, caches in their steady state
+    mult = max(1, int(np.ceil(min_repeat_s * 1e3 / max(probe, 1e-3))))
+    per_repeat_s = probe * mult * 1e-3
+    reps = max(min_repeats, 1)
+    if reps * per_repeat_s > max_total_s:
+        reps = max(2, int(max_total_s / per_repeat_s))
+    n = steps * mult
+    local = [one(n) / n for _ in range(reps)]
+    out = []
+    for i in range(0, len(local), 64):
+        out += ranks.max_many(local[i:i + 64])
+    return out, n
+
+
+def spread(ms_list):
+    """median / min / max of the per-step times of the repeats."""
+    return {"repeats": len(ms_list), "median_ms_per_step": statistics.median(ms_list),
+            "min_ms_per_step": min(ms_list), "max_ms_per_step": max(ms_list)}
 
 
 def cuda_sync(dev):
@@ -207,73 +274,161 @@ def cpu_int8_sample(A, W, b, budget_s=12.0):
             f"channels, {reps} repeats, {dt * reps:.1f} s in total", rows, dt)
 
 
+class Int8Case:
+    """Operands of one point of config 2 (M rows of activations against this rank's 4096 x 4096
+    weight shard), every operand in as many rotating copies as it takes to exceed the 126 MB L2."""
+
+    def __init__(self, dev, M, rank, A=None, Wb=None):
+        self.dev, self.M, self.N, self.K = dev, M, I8_N, I8_K
+        M, N, K = self.M, self.N, self.K
+        if A is None:
+            A, W, b = make_int8_inputs(2, rank, M)
+        else:
+            W, b = Wb
+        self.A, self.W, self.b = A, W, b
+        self.set_bytes = M * K * 5 + M * N * 4 + N * K
+        self.nsets = n = max(4, -(-170_000_000 // self.set_bytes))
+        self.dA = [dev.to_device(A) for _ in range(n)]
+        self.dQa = [dev.zeros((M, K), np.int8) for _ in range(n)]
+        self.dSa = [dev.zeros(M) for _ in range(n)]
+        self.dY = [dev.zeros((M, N)) for _ in range(n)]
+        dW = dev.to_device(W)
+        self.dQw = [dev.zeros((N, K), np.int8) for _ in range(n)]
+        self.dSw = [dev.zeros(N) for _ in range(n)]
+        self.db = dev.to_device(b)
+        for i in range(n):  # weights are quantised once, ahead of time
+            dev.quant_rows_i8(dW, N, K, self.dQw[i], self.dSw[i])
+        dev.sync()
+        dW.free()
+
+    def quant(self, i):
+        s = i % self.nsets
+        self.dev.quant_rows_i8(self.dA[s], self.M, self.K, self.dQa[s], self.dSa[s])
+
+    def gemm(self, i):
+        s = i % self.nsets
+        self.dev.linear_i8_fwd(self.dQa[s], self.dSa[s], self.dQw[s], self.dSw[s], self.db, self.dY[s],
+                               self.M, self.N, self.K, True)
+
+    def step(self, i):
+        self.quant(i)
+        self.gemm(i)
+
+    def free(self):
+        for b in self.dA + self.dQa + self.dSa + self.dY + self.dQw + self.dSw + [self.db]:
+            b.free()
+
+    # ---- the dominant kernel alone
+    def gemm_kernel_ms(self, launches):
+        """Average duration of the GEMM launch (fused epilogue included), operands rotating.  From
+        M = 1024 on: one CUDA event pair around each launch.  Below, a launch of a few microseconds is
+        shorter than what an event pair around it adds, so the launches are timed back to back as
+        one batch behind their quantise passes."""
+        dev = self.dev
+        for i in range(self.nsets):
+            self.quant(i)
+        if self.M >= 1024:
+            evs = [(dev.event(), dev.event()) for _ in range(launches)]
+            for i in range(launches):
+                self.quant(i)
+                dev.record(evs[i][0])
+                self.gemm(i)
+                dev.record(evs[i][1])
+            dev.sync()
+            return statistics.mean(dev.elapsed_ms(a, c) for a, c in evs)
+        e0, e1 = dev.event(), dev.event()
+        for i in range(3):
+            self.gemm(i)
+        dev.record(e0)
+        for i in range(launches):
+            self.gemm(i)
+        dev.record(e1)
+        return dev.elapsed_ms(e0, e1) / launches
+
+    def kernel_name(self):
+        M = self.M
+        if M <= 2:
+            return "gemv_i8_kernel (dp4a, one output channel per warp, a whole weight row in flight)"
+        if M <= 128:
+            return ("skinny::gemm_i8_skinny_kernel (tcgen05 kind::i8 with the weights on the M side, K cut "
+                    "across a cluster of 4 CTAs, partial sums added through distributed shared memory)")
+        if M < 1024:
+            return "gemm::gemm_tc_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, one CTA per tile, TMA-store epilogue)"
+        return ("gemm2::gemm_pair_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, cta_group::2, "
+                "fused dequant+bias+ReLU, TMA-store epilogue, K-split of surplus tiles)")
+
+    def roofline(self, gemm_ms, pk):
+        """Roofline object of the GEMM launch.  Bound by the tensor cores once 2*M*N*K / peak exceeds
+        the time HBM needs for the operands (M >= 256 at N = K = 4096); with fewer rows by streaming
+        the weight codes once."""
+        M, N, K = self.M, self.N, self.K
+        int8_peak = 2.0 * pk["bf16_tflops"]  # INT8 issues at twice the bf16 rate on B200
+        op_bytes = float(N * K + M * K + 4 * M * N + 4 * (M + 2 * N))
+        ops = 2.0 * M * N * K
+        if ops / (int8_peak * 1e12) >= op_bytes / (pk["hbm_gbs"] * 1e9):
+            tops = ops / (gemm_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": self.kernel_name(), "achieved": tops, "peak": int8_peak,
+                    "unit": "TFLOP/s", "frac": tops / int8_peak, "traffic": None,
+                    "algorithmic_ops_per_launch": ops,
+                    "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
+                                   "dense INT8 issues at twice the bf16 rate)",
+                    "kernel_ms": gemm_ms}
+            if M == I8_M:
+                roof.update(NCU_TRAFFIC["pair_4096"])
+        else:
+            gbs = op_bytes / (gemm_ms * 1e-3) / 1e9
+            t = NCU_TRAFFIC["skinny_m16"]
+            roof = {"bound": "hbm", "kernel": self.kernel_name(), "achieved": gbs, "peak": pk["hbm_gbs"],
+                    "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                    "traffic": op_bytes * t["traffic_per_algorithmic_byte"], "traffic_source": t["traffic_source"],
+                    "algorithmic_bytes_per_launch": op_bytes,
+                    "peak_source": f"hbm_gbs of {pk['_source']}", "kernel_ms": gemm_ms}
+        return roof
+
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) is not measurable inside a
+# timed run; these are the figures of the ncu captures of the same launches, and say so.
+NCU_TRAFFIC = {
+    "pair_4096": {"traffic": 59.9e6,
+                  "traffic_source": "ncu capture of one launch at M = N = K = 4096 (34.55 MB read + 25.38 MB "
+                                    "written; most of the 67 MB output is still in L2 when the kernel ends), "
+                                    "not measured in this run"},
+    "skinny_m16": {"traffic_per_algorithmic_byte": 16.9 / 17.14,
+                   "traffic_source": "ncu capture of one launch at M = 16 (16.9 MB of DRAM traffic against "
+                                     "17.14 MB of algorithmic bytes), scaled by the algorithmic bytes; not "
+                                     "measured in this run"},
+}
+
+
 def run_int8(args, ranks):
     from vtl_b200 import capi
     dev = capi.Device(ranks.local_rank)
     ranks.attach(dev)
     M, N, K = (args.rows or I8_M), I8_N, I8_K
-    A, W, b = make_int8_inputs(2, ranks.rank, M)
-    # operand copies rotated between steps so that no step finds its operands in the 126 MB L2:
-    # 4 x 160 MiB at M = 4096; with few rows a set is little more than the 16 MiB of weight codes
-    set_bytes = M * K * 5 + M * N * 4 + N * K
-    NSETS = max(4, -(-170_000_000 // set_bytes))
-    dA = [dev.to_device(A) for _ in range(NSETS)]
-    dQa = [dev.zeros((M, K), np.int8) for _ in range(NSETS)]
-    dSa = [dev.zeros(M) for _ in range(NSETS)]
-    dY = [dev.zeros((M, N)) for _ in range(NSETS)]
-    dW = dev.to_device(W)
-    dQw = [dev.zeros((N, K), np.int8) for _ in range(NSETS)]
-    dSw = [dev.zeros(N) for _ in range(NSETS)]
-    db = dev.to_device(b)
-    for i in range(NSETS):  # weights are quantised once, ahead of time
-        dev.quant_rows_i8(dW, N, K, dQw[i], dSw[i])
-    dev.sync()
-
-    def step(i):
-        s = i % NSETS
-        dev.quant_rows_i8(dA[s], M, K, dQa[s], dSa[s])
-        dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
+    case = Int8Case(dev, M, ranks.rank)
+    A, W, b = case.A, case.W, case.b
+    NSETS, set_bytes = case.nsets, case.set_bytes
+    dA, dY = case.dA, case.dY
 
     cuda_sync(dev)  # also pays the one-off import costs now, not between warm-up and timing
     sampler = ClockSampler(ranks.local_rank)
     if ranks.rank == 0:
-        sampler.start()  # keeps sampling through all three timed passes below
+        sampler.start()  # keeps sampling through all timed passes below
     ranks.barrier()
     for i in range(args.warmup):  # directly before the timed region: the GPU must not idle
-        step(i)                   # (and drop its clocks) between warm-up and timing
+        case.step(i)              # (and drop its clocks) between warm-up and timing
     dev.sync()
-    ranks.barrier()
-    # pass 1: whole steps, one event pair around the timed region
+    # the dominant kernel alone (GEMM + fused epilogue), straight after the warm-up: a few
+    # milliseconds of launches, timed in isolation (the burst regime of the clocks)
+    gemm_ms = case.gemm_kernel_ms(min(max(args.steps, 20), 200))
+    kernel_clocks = sampler.snapshot() if ranks.rank == 0 else None
+    # whole steps: repeats of K-step regions, each behind a barrier + sync, one event pair per region;
+    # seconds of back-to-back steps, so these run under the power cap
     l0 = dev.launch_count()
-    e0, e1 = dev.event(), dev.event()
-    dev.record(e0)
-    for i in range(args.steps):
-        step(i)
-    dev.record(e1)
-    ms_total = dev.elapsed_ms(e0, e1)
+    per_step, steps_per_repeat = timed_repeats(dev, ranks, lambda n: [case.step(i) for i in range(n)], args.steps)
     launches = dev.launch_count() - l0
-    cuda_sync(dev)
-    ranks.barrier()
-    ms_total = ranks.max_f32(ms_total)
-    # the dominant kernel alone (GEMM + fused epilogue), events around each launch
-    evs = [(dev.event(), dev.event()) for _ in range(args.steps)]
-    for i in range(args.steps):
-        s = i % NSETS
-        dev.quant_rows_i8(dA[s], M, K, dQa[s], dSa[s])
-        dev.record(evs[i][0])
-        dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
-        dev.record(evs[i][1])
-    dev.sync()
-    gemm_ms = statistics.mean(dev.elapsed_ms(a, c) for a, c in evs)
-    if M < 1024:
-        # a launch of a few microseconds is shorter than what an event pair around it adds: time
-        # the GEMM launches as one batch instead (operands still rotating), one event pair around it
-        dev.record(e0)
-        for i in range(args.steps):
-            s = i % NSETS
-            dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
-        dev.record(e1)
-        gemm_ms = dev.elapsed_ms(e0, e1) / args.steps
+    ms_step = statistics.median(per_step)
+    step_clocks = sampler.snapshot() if ranks.rank == 0 else None
     assert dev.check_status() == 0
 
     # end to end through the C ABI with host buffers (pinned), copies inside the timed region: every
@@ -294,65 +449,51 @@ def run_int8(args, ranks):
             dev.copy_wait(dev.COPY_IN_BEFORE_COMPUTE)          # A of this step has landed
             if i + 1 < steps:                                  # next A into a buffer no step is using
                 dev.copy_h2d_async(dA[(i + 1) % NSETS], hA[(i + 1) % 2].value, A.nbytes)
-            dev.quant_rows_i8(dA[s], M, K, dQa[s], dSa[s])
-            dev.linear_i8_fwd(dQa[s], dSa[s], dQw[s], dSw[s], db, dY[s], M, N, K, True)
+            case.step(i)
             dev.copy_wait(dev.COPY_OUT_BEFORE_COMPUTE)         # later steps wait for the earlier copies out
             dev.copy_d2h_async(hY[i % 2].value, dY[s], M * N * 4)
         dev.copy_wait(dev.COPY_OUT_DONE)                       # the last result is on the host
 
+    def e2e_timed(steps):
+        cuda_sync(dev)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        e2e_run(steps)
+        cuda_sync(dev)
+        return (time.perf_counter() - t0) * 1e3
+
     e2e_run(3)
-    cuda_sync(dev)
-    ranks.barrier()
-    t0 = time.perf_counter()
-    e2e_run(args.steps)
-    cuda_sync(dev)
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = ranks.max_f32(e2e_ms)
-    clocks = sampler.stop() if ranks.rank == 0 else None
+    probe = ranks.max_f32(e2e_timed(args.steps))
+    mult = max(1, int(np.ceil(250.0 / max(probe, 1e-3))))
+    e2e_steps = args.steps * mult
+    e2e_per_step = ranks.max_many([e2e_timed(e2e_steps) / e2e_steps for _ in range(5)])
+    e2e_ms_step = statistics.median(e2e_per_step)
     for h in hA + hY:
         dev.lib.vtlb_host_free(h)
 
-    ops_step = 2.0 * M * N * K * ranks.world
-    ms_step = ms_total / args.steps
     pk = peaks()
-    int8_peak = 2.0 * pk["bf16_tflops"]  # INT8 issues at twice the bf16 rate on B200
-    gemm_tops = 2.0 * M * N * K / (gemm_ms * 1e-3) / 1e12
-    # roofline of the dominant kernel (the GEMM with its fused epilogue).  It is bound by the tensor
-    # cores once 2*M*N*K / peak exceeds the time HBM needs for the operands (M >= 256 at N = K = 4096);
-    # with fewer rows it is bound by streaming the weight codes once.
-    op_bytes = float(N * K + M * K + 4 * M * N + 4 * (M + 2 * N))
-    tensor_bound = 2.0 * M * N * K / (int8_peak * 1e12) >= op_bytes / (pk["hbm_gbs"] * 1e9)
-    if M <= 2:
-        kname = "gemv_i8_kernel (dp4a, one output channel per warp, a whole weight row in flight)"
-    elif M <= 128:
-        kname = ("skinny::gemm_i8_skinny_kernel (tcgen05 kind::i8 with the weights on the M side, K cut "
-                 "across a cluster of 4 CTAs, partial sums added through distributed shared memory)")
-    elif M < 1024:
-        kname = "gemm::gemm_tc_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, one CTA per tile, TMA-store epilogue)"
-    else:
-        kname = ("gemm2::gemm_pair_kernel<KIND_I8, EpiDequant> (tcgen05 kind::i8, cta_group::2, "
-                 "fused dequant+bias+ReLU, TMA-store epilogue, K-split of surplus tiles)")
-    if tensor_bound:
-        roof = {"bound": "tensor", "kernel": kname, "achieved": gemm_tops, "peak": int8_peak, "unit": "TFLOP/s",
-                "frac": gemm_tops / int8_peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on the
-                # M = 4096 workload, from the ncu capture summarised in
-                # profiles/gemm_i8_pair_fused_4096.md (algorithmic operand bytes: 33.6 MB read)
-                "traffic": 59.9e6 if M == I8_M else None,
-                "traffic_unit": "bytes per launch (ncu, 34.55 MB read + 25.38 MB written)" if M == I8_M else None,
-                "algorithmic_ops_per_launch": 2.0 * M * N * K,
-                "peak_source": f"2 x bf16_tflops of {pk['_source']} (cuBLAS bf16 burst rate; "
-                               "dense INT8 issues at twice the bf16 rate)",
-                "kernel_ms": gemm_ms}
-    else:
-        gbs = op_bytes / (gemm_ms * 1e-3) / 1e9
-        # ncu on the M = 16 launch (profiles/gemm_i8_skinny_m16.md): 16.9 MB of DRAM traffic against 17.1 MB
-        # of algorithmic bytes -- every weight code read once; other row counts scaled by their bytes
-        roof = {"bound": "hbm", "kernel": kname, "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": gbs / pk["hbm_gbs"], "traffic": op_bytes * (16.9 / 17.14),
-                "traffic_unit": "bytes per launch (ncu capture at M = 16, scaled by the algorithmic bytes)",
-                "algorithmic_bytes_per_launch": op_bytes,
-                "peak_source": f"hbm_gbs of {pk['_source']}", "kernel_ms": gemm_ms}
+    roof = case.roofline(gemm_ms, pk)
+    # the M sweep of config 2: the GEMM launch alone at every row count (single-GPU runs only)
+    sweep = None
+    if ranks.world == 1 and not args.rows:
+        sweep = []
+        case.free()
+        for m in (1, 16, 128, 1024, 8192):
+            c = Int8Case(dev, m, ranks.rank, A=A[:m] if m <= M else None, Wb=(W, b) if m <= M else None)
+            for i in range(5):
+                c.step(i)
+            k_ms = c.gemm_kernel_ms(200 if m < 1024 else 40)
+            st, _ = timed_repeats(dev, ranks, lambda n, c=c: [c.step(i) for i in range(n)], 50, min_repeat_s=0.05,
+                                  min_repeats=3, max_total_s=1.0)
+            r = c.roofline(k_ms, pk)
+            sweep.append({"M": m, "kernel_ms": k_ms, "bound": r["bound"], "achieved": r["achieved"],
+                          "unit": r["unit"], "frac": r["frac"], "step_ms": statistics.median(st),
+                          "kernel": r["kernel"].split(" (")[0]})
+            c.free()
+        assert dev.check_status() == 0
+    clocks = sampler.stop() if ranks.rank == 0 else None
+
+    ops_step = 2.0 * M * N * K * ranks.world
     out = None
     if ranks.rank == 0:
         cpu_tops, cores, sample, _, _ = cpu_int8_sample(A, W, b) if ranks.world == 1 else (None, None, None, None, None)
@@ -369,33 +510,50 @@ def run_int8(args, ranks):
                        f"output-column sharded x{ranks.world}, activations replicated, no collective",
                        "l2": f"every operand rotates over {NSETS} copies ({NSETS * set_bytes / 2**20:.0f} MiB) "
                              "between steps, larger than the 126 MB L2"},
-            "e2e": {"value": ops_step / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": "TOPS",
+            "timing": dict(spread(per_step), steps_per_repeat=steps_per_repeat,
+                           note="value and ms_per_step are the median repeat; every repeat is a whole multiple of "
+                                "--steps steps behind a barrier and a device synchronisation, timed by one CUDA "
+                                "event pair, maximum over the ranks"),
+            "e2e": {"value": ops_step / (e2e_ms_step * 1e-3) / 1e12, "unit": "TOPS",
                     "h2d_bytes_per_step": int(A.nbytes), "d2h_bytes_per_step": int(M * N * 4),
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms_step, "repeats": len(e2e_per_step),
+                    "min_ms_per_step": min(e2e_per_step), "max_ms_per_step": max(e2e_per_step),
+                    "steps_per_repeat": e2e_steps},
             "gpu_launches": int(launches),
-            "clocks": clocks,
-            "roofline": roof,
+            "clocks": dict(step_clocks, whole_run=clocks,
+                           note="sampled through NVML during the timed repeats of whole steps; whole_run covers "
+                                "every pass of this process (kernel-alone pass, repeats, end-to-end, sweep)"),
+            "roofline": dict(roof, clocks=kernel_clocks),
         }
+        if sweep is not None:
+            out["sweep"] = sweep
         if cpu_tops is not None:
             out["cpu_baseline"] = {"value": cpu_tops, "unit": "TOPS", "cores": cores, "kind": "port",
                                    "sample": sample}
-    ranks.close()
     dev.close()
     return out
 
 
 def run_int8_reference(args, ranks):
-    """The CPU arm: the oracle's quantised linear forward on all host threads, each step a
-    bounded sample (a block of rows of A against the full weight matrix)."""
+    """The CPU arm: the oracle's quantised linear forward on all host threads.  A step is the whole
+    configuration (all 4096 rows of A against the full weight matrix, about 1.7 s on 16 cores); only
+    if --steps + --warmup of those would run past four minutes is a step cut to the first rows of A,
+    and the line then says so in config.M."""
     if ranks.rank != 0:
-        ranks.close()
         return None
     A, W, b = make_int8_inputs(2, 0)
     from oracle import oracle
     oracle.build()
     wq, sw = oracle.quant_rows_i8(W)
-    # rows per step sized so that the whole --steps/--warmup run stays near a minute
-    _, cores, _, rows, dt = cpu_int8_sample(A, W, b, budget_s=min(20.0, max(0.02, 60.0 / max(1, args.steps + args.warmup))))
+    t0 = time.perf_counter()
+    oracle.linear_i8_fwd(A[:256], wq, sw, b, True)
+    oracle.linear_i8_fwd(A[:256], wq, sw, b, True)
+    t_full = (time.perf_counter() - t0) / 2 * (I8_M / 256)
+    rows = I8_M
+    total = (args.steps + args.warmup) * t_full
+    if total > 240.0:
+        rows = max(32, int(I8_M * 240.0 / total) // 32 * 32)
+    cores = oracle.max_threads()
     for _ in range(args.warmup):
         oracle.linear_i8_fwd(A[:rows], wq, sw, b, True)
     t0 = time.perf_counter()
@@ -403,7 +561,8 @@ def run_int8_reference(args, ranks):
         oracle.linear_i8_fwd(A[:rows], wq, sw, b, True)
     ms_step = (time.perf_counter() - t0) * 1e3 / args.steps
     tops = 2.0 * rows * I8_N * I8_K / (ms_step * 1e-3) / 1e12
-    sample = f"each step = first {rows} of {I8_M} rows of A against all {I8_N} channels"
+    sample = (f"each step = all {I8_M} rows of A against all {I8_N} channels (the whole configuration)" if rows == I8_M
+              else f"each step = first {rows} of {I8_M} rows of A against all {I8_N} channels")
     out = {"impl": "reference", "metric": "int8_quantized_linear_fwd_tops", "value": tops,
            "unit": "TOPS", "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -413,7 +572,6 @@ def run_int8_reference(args, ranks):
            "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port", "sample": sample},
            "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    ranks.close()
     return out
 
 
@@ -445,6 +603,9 @@ def main():
                     help="int8_linear: rows M of the activations (the M sweep of baseline config 2; "
                          "default 4096); training workloads: global batch override, for small "
                          "profiling captures")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="default workload: skip the dp_train / tp_infer objects (configs 4 and 5) and time "
+                         "config 2 alone, e.g. for profiler captures")
     args = ap.parse_args()
     defaults = {"int8_linear": (2000, 20), "mlp_c1": (1000, 20), "mlp_c4": (20, 3), "cnn_c3": (50, 5),
                 "int8_mlp_c5": (20, 3), "ckpt_c4": (20, 3)}
@@ -461,6 +622,17 @@ def main():
         use_all_host_threads()
     if args.workload == "int8_linear":
         out = run_int8_reference(args, ranks) if args.impl == "reference" else run_int8(args, ranks)
+        if args.impl == "ours" and not args.rows and not args.headline_only:
+            # the two workloads that carry collectives, in the same process and on the same ranks:
+            # config 4 (data-parallel f32 training, gradient all-reduce) and config 5 (column-sharded
+            # INT8 inference, all-gather of activations), each with its parity checks
+            import bench_infer
+            import bench_train
+            me = sys.modules[__name__]
+            dp = bench_train.run_dp(ranks, me)
+            tp = bench_infer.run_tp(ranks, me)
+            if out is not None:
+                out["dp_train"], out["tp_infer"] = dp, tp
     elif args.workload == "int8_mlp_c5":
         import bench_infer
         if args.impl == "reference":
@@ -479,6 +651,7 @@ def main():
             out = bench_train.run_reference(args, ranks)
         else:
             out = bench_train.run(args, ranks, ClockSampler, peaks, cuda_sync)
+    ranks.close()
     if out is not None:
         print(json.dumps(out), flush=True)
 

@@ -150,14 +150,12 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
             got = texts[0].numpy()[: lens[0]].tobytes().decode("ascii")
             assert got == text, "device text differs from the oracle's"
             out["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
-    ranks.close()
     return out
 
 
 def run_reference(args, ranks):
     """CPU arm: the oracle's encoder, each step one weight matrix."""
     if ranks.rank != 0:
-        ranks.close()
         return None
     from oracle import checkpoint as ock
     rng = np.random.default_rng(4)
@@ -179,5 +177,4 @@ def run_reference(args, ranks):
            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    ranks.close()
     return out

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
+import statistics
 import time
 
 import numpy as np
@@ -134,7 +135,6 @@ def cpu_sample(tokens=64, budget_s=15.0):
 
 def run_reference(args, ranks):
     if ranks.rank != 0:
-        ranks.close()
         return None
     cb, dt = cpu_sample(budget_s=max(5.0, 20.0 * max(1, args.steps)))
     out = {"impl": "reference", "metric": "int8_mlp_inference_tops", "value": cb["value"], "unit": "TOPS",
@@ -145,7 +145,6 @@ def run_reference(args, ranks):
            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
            "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    ranks.close()
     return out
 
 
@@ -248,6 +247,93 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
         if ranks.world == 1:
             cb, _ = cpu_sample()
             out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    ranks.close()
     dev.close()
     return out
+
+
+# ------------------------------------------------------------------ config 5 inside the default bench line
+def sharded_parity(ranks, dev, dims=(1024, 4096, 1024, 4096, 1024), tokens=512, chunks=2):
+    """The sharded forward on a reduced config 5 (same topology, widths / 8, 512 tokens), every
+    rank's output slab collected on rank 0 and compared with the UNSHARDED CPU oracle: the int32
+    GEMM is exact, max is associative and quantisation is element-wise, so the result must be the
+    same bit for bit however many ranks share the columns.  Rank 0 returns the report."""
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank, tokens=tokens, dims=list(dims), seed=55, chunks=chunks)
+    X = np.random.default_rng(56).standard_normal((tokens, dims[0]), dtype=np.float32)
+    dX = dev.to_device(X)
+    y = model.forward(dX)
+    dev.sync()
+    slabs = ranks.gather_objects(y.numpy())
+    if ranks.rank != 0:
+        return None
+    from oracle import oracle
+    oracle.build()
+    A = X
+    for li in range(len(dims) - 1):
+        Ws, bs = [], []
+        for r in range(ranks.world):  # the shards as the ranks generated them
+            rng = np.random.default_rng([55, li, r])
+            n = dims[li + 1] // ranks.world
+            Ws.append(rng.standard_normal((n, dims[li]), dtype=np.float32) * np.float32(0.02))
+            bs.append(rng.standard_normal(n, dtype=np.float32) * np.float32(0.01))
+        wq, sw = oracle.quant_rows_i8(np.concatenate(Ws))
+        A = oracle.linear_i8_fwd(A, wq, sw, np.concatenate(bs), relu=(li + 2 < len(dims)))
+    got = np.concatenate(slabs, axis=1)
+    return {"config": f"{'-'.join(map(str, dims))}, {tokens} tokens, {chunks} row blocks, sharded x{ranks.world}, "
+                      "against the unsharded CPU oracle",
+            "bit_exact": bool(np.array_equal(got.view(np.uint32), A.view(np.uint32))),
+            "max_abs_diff": float(np.abs(got - A).max())}
+
+
+def run_tp(ranks, tools, steps=10, warmup=3):
+    """Baseline config 5 on the ranks of this job (output columns sharded, strong scaling): TOPS, the
+    GEMM launches alone, the exposed part of the per-layer exchange, and the parity check of the
+    sharded pipeline.  Returns the object on rank 0."""
+    from vtl_b200 import capi
+    dev = capi.Device(ranks.local_rank)
+    ranks.attach(dev)
+    parity = sharded_parity(ranks, dev)
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank)
+    dX = dev.to_device(np.random.default_rng(5).standard_normal((TOKENS, DIMS[0]), dtype=np.float32))
+
+    def run_steps(n):
+        for _ in range(n):
+            model.forward(dX)
+
+    tools.cuda_sync(dev)
+    ranks.barrier()
+    run_steps(warmup)
+    l0 = dev.launch_count()
+    per_step, steps_per_repeat = tools.timed_repeats(dev, ranks, run_steps, steps, max_total_s=6.0)
+    launches = dev.launch_count() - l0
+    ms_step = statistics.median(per_step)
+    psteps = 4
+    dev.profile_gemm(True)
+    run_steps(psteps)
+    phases = dev.profile_read_phases()
+    gemm_ms, gemm_n, gemm_ops = dev.profile_gemm_read()
+    dev.profile_gemm(False)
+    assert dev.check_status() == 0
+    dev.close()
+    if ranks.rank != 0:
+        return None
+    pk = tools.peaks()
+    int8_peak = 2.0 * pk["bf16_tflops"]
+    gemm_tops = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    return {"workload": "INT8 weight-quantised MLP inference, 4 layers 8192->28672->8192->28672->8192, 16384 tokens "
+                        "~N(0,1), per-row dynamic activation quantisation, ReLU between layers (baseline config 5)",
+            "metric": "int8_mlp_inference_tops", "value": total_ops() / (ms_step * 1e-3) / 1e12, "unit": "TOPS",
+            "scaling": "strong", "tokens": TOKENS, "tokens_per_s": TOKENS / (ms_step * 1e-3), "ms_per_step": ms_step,
+            "timing": dict(tools.spread(per_step), steps_per_repeat=steps_per_repeat),
+            "gpu_launches": int(launches), "row_blocks": model.C,
+            "gemm_ms_per_step": gemm_ms / psteps, "gemm_launches_per_step": gemm_n / psteps,
+            "gemm_tops_per_gpu": gemm_tops, "gemm_frac_of_peak": gemm_tops / int8_peak if gemm_tops else None,
+            "gemm_peak": int8_peak, "gemm_peak_source": f"2 x bf16_tflops of {pk['_source']}",
+            "exchange_ms_per_step": {"quantise": phases["elementwise"][0] / psteps,
+                                     "exposed_collective_wait": phases["comm_wait"][0] / psteps,
+                                     "note": "quantise = the row-quantisation launches; exposed_collective_wait = "
+                                             "time the compute stream stood idle until an all-reduce(max) or "
+                                             "all-gather had finished (CUDA-event brackets, profiled passes)"},
+            "parallelism": (f"output columns sharded x{ranks.world}; per layer and row block: all-reduce(max) of row "
+                            "maxima, quantise, all-gather of int8 codes over NCCL; the next GEMM reads the gathered "
+                            "shards in place") if ranks.world > 1 else "single GPU",
+            "parity": parity}

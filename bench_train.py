@@ -170,7 +170,6 @@ def cpu_baseline(wl, steps=None, budget_s=15.0):
 
 def run_reference(args, ranks):
     if ranks.rank != 0:
-        ranks.close()
         return None
     wl = Workload(args.workload, 1, 0)
     cb, rows, dt = cpu_baseline(wl, steps=max(1, args.steps), budget_s=120.0)
@@ -181,7 +180,6 @@ def run_reference(args, ranks):
            "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
            "e2e": {"value": cb["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
            "gpu_launches": 0}
-    ranks.close()
     return out
 
 
@@ -302,6 +300,188 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
             cb, _, _ = cpu_baseline(wl)
             out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     model.close()
-    ranks.close()
     session.close()
     return out
+
+
+# ------------------------------------------------------------------ config 4 inside the default bench line
+def _bcast_params_from_last(ranks, params):
+    """Rank N-1's parameter arrays on rank 0 (control plane, gloo point to point); None elsewhere."""
+    import torch
+    dist, last = ranks.dist, ranks.world - 1
+    if ranks.rank == last:
+        for p in params:
+            dist.send(torch.from_numpy(np.ascontiguousarray(p)), dst=0)
+        return None
+    if ranks.rank == 0:
+        out = []
+        for p in params:
+            buf = torch.empty(p.shape, dtype=torch.float32)
+            dist.recv(buf, src=last)
+            out.append(buf.numpy())
+        return out
+    return None
+
+
+def replica_agreement(ranks, model):
+    """max |theta(rank 0) - theta(rank N-1)| over every parameter tensor.  The replicas start from
+    the same weights, add up the same all-reduced gradients and run the same optimizer kernel, so
+    anything but 0 is a bug.  Rank 0 returns the number, the others None."""
+    if ranks.world == 1:
+        return 0.0
+    mine = [model.get_param(i) for i in range(model.num_params())] if ranks.rank in (0, ranks.world - 1) else []
+    theirs = _bcast_params_from_last(ranks, mine)
+    ranks.barrier()
+    if ranks.rank != 0:
+        return None
+    return float(max(np.abs(a - b).max() for a, b in zip(mine, theirs)))
+
+
+def dp_matches_single_gpu(ranks, steps=3, width=512, layers=4, batch=4096):
+    """A reduced config 4 (4 Linear layers of width 512 with ReLU between, batch 4096, MSE, AdamW)
+    trained for `steps` steps (a) data-parallel over all ranks and (b) by rank 0 alone on the whole
+    batch, from the same weights.  The two runs differ only in the order in which the rows of the
+    batch are summed into dW and db, so the parameters must agree within the bound of the
+    weight-gradient product, 1e-5 * sqrt(K) * max|A| * max|B| with K = batch rows, A the loss
+    gradient P - T and B the layer inputs, taken at their largest over the layers.  Rank 0 returns
+    the report, the others None."""
+    from vtl_b200 import host
+    dims, relu = [width] * (layers + 1), [True] * (layers - 1) + [False]
+    rng = np.random.default_rng(44)
+    params = []
+    for i in range(layers):
+        params += [kaiming_uniform(rng, (dims[i + 1], dims[i]), dims[i]), np.zeros(dims[i + 1], np.float32)]
+    X = rng.standard_normal((batch, width), dtype=np.float32)
+    T = rng.standard_normal((batch, width), dtype=np.float32)
+
+    def build(session):
+        m = host.Model(session)
+        m.input([width])
+        for i in range(layers):
+            m.linear(width)
+            if relu[i]:
+                m.relu()
+        m.mse_loss()
+        m.adamw(lr=1e-4, weight_decay=0.01)
+        for i, p in enumerate(params):
+            m.set_param(i, p)
+        return m
+
+    def train(session, Xs, Ts):
+        m = build(session)
+        dX, dT = session.dev.to_device(Xs), session.dev.to_device(Ts)
+        losses = [m.train_step(dX, Xs.shape, dT, Ts.shape, global_rows=batch) for _ in range(steps)]
+        out = [m.get_param(i) for i in range(2 * layers)]
+        dX.free(); dT.free()
+        m.close()
+        return losses, out
+
+    # (a) all ranks, each on its rows
+    per = batch // ranks.world
+    sa = host.Session(ranks.local_rank)
+    if ranks.world > 1:
+        box = [sa.dev.comm_unique_id() if ranks.rank == 0 else None]
+        ranks.dist.broadcast_object_list(box, src=0)
+        sa.comm_init(ranks.world, ranks.rank, box[0])
+    lo = ranks.rank * per
+    dp_losses, dp_params = train(sa, X[lo:lo + per], T[lo:lo + per])
+    assert sa.dev.check_status() == 0
+    sa.close()
+    ranks.barrier()
+    if ranks.rank != 0:
+        return None
+    # (b) rank 0 alone on the whole batch (no communicator)
+    sb = host.Session(ranks.local_rank)
+    one_losses, one_params = train(sb, X, T)
+    sb.close()
+    # bound of the weight-gradient products: K = batch rows; |P - T| and the layer inputs at step 0
+    acts, amax_in, a = X, float(np.abs(X).max()), X
+    for i in range(layers):
+        a = a @ params[2 * i].T + params[2 * i + 1]
+        if relu[i]:
+            a = np.maximum(a, 0)
+            amax_in = max(amax_in, float(np.abs(a).max()))
+    gmax = float(np.abs(a - T).max())
+    bound = 1e-5 * np.sqrt(batch) * gmax * amax_in
+    diff = float(max(np.abs(p - q).max() for p, q in zip(dp_params, one_params)))
+    return {"config": f"{layers} x Linear({width}) + ReLU, batch {batch}, MSE, AdamW, {steps} steps",
+            "max_abs_param_diff_vs_one_gpu": diff, "bound": float(bound), "within_bound": bool(diff <= bound),
+            "loss_dp": dp_losses, "loss_one_gpu": one_losses,
+            "loss_rel_diff": float(max(abs(x - y) / abs(y) for x, y in zip(dp_losses, one_losses)))}
+
+
+def run_dp(ranks, tools, steps=8, warmup=3):
+    """Baseline config 4 on the ranks of this job (global batch 65536 split by rows, strong scaling):
+    samples/s, the time of the tensor-core GEMMs inside a step, a breakdown of the rest of the step
+    by phase, and the parity checks of the data-parallel path.  Returns the object on rank 0."""
+    from vtl_b200 import host
+    wl = Workload("mlp_c4", ranks.world, ranks.rank)
+    session = host.Session(ranks.local_rank)
+    dev = session.dev
+    ranks.attach(dev, session)
+    model = wl.build(session)
+    X, T = wl.batch()
+    dX, dT = dev.to_device(X), dev.to_device(T)
+    xs, ts, G = X.shape, T.shape, wl.global_rows
+    del X, T
+
+    def run_steps(n):
+        for _ in range(n):
+            model.train_step(dX, xs, dT, ts, global_rows=G, update=True, want_loss=False)
+
+    tools.cuda_sync(dev)
+    ranks.barrier()
+    run_steps(warmup)
+    l0 = dev.launch_count()
+    per_step, steps_per_repeat = tools.timed_repeats(dev, ranks, run_steps, steps, max_total_s=12.0)
+    launches = dev.launch_count() - l0
+    ms_step = statistics.median(per_step)
+    # one more step for the loss value: the sum over the ranks' rows (all-reduced), over the global divisor
+    loss = model.train_step(dX, xs, dT, ts, global_rows=G, update=True, want_loss=True)
+    losses = ranks.gather_objects(loss)
+    # phases of a step, each bracketed by CUDA events on the compute stream
+    prof_steps = 2
+    dev.profile_gemm(True)
+    run_steps(prof_steps)
+    phases = dev.profile_read_phases()
+    gemm_ms, gemm_n, gemm_ops = dev.profile_gemm_read()
+    dev.profile_gemm(False)
+    agree = replica_agreement(ranks, model)
+    assert dev.check_status() == 0
+    model.close()
+    dX.free(); dT.free()
+    session.close()
+    small = dp_matches_single_gpu(ranks)
+    if ranks.rank != 0:
+        return None
+    pk = tools.peaks()
+    long_step = ms_step > 50.0
+    bf16_peak = pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) if long_step else pk["bf16_tflops"]
+    tf32x3_peak = bf16_peak / 2.0 / 3.0
+    gemm_tflops = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    ph = {k: v[0] / prof_steps for k, v in phases.items()}
+    accounted = sum(ph.values())
+    return {
+        "workload": wl.describe(), "metric": "f32_train_samples_per_s", "value": G / (ms_step * 1e-3),
+        "unit": "samples/s", "scaling": "strong", "global_batch": G, "rows_per_gpu": wl.local_rows,
+        "ms_per_step": ms_step, "timing": dict(tools.spread(per_step), steps_per_repeat=steps_per_repeat),
+        "gpu_launches": int(launches),
+        "gemm_ms_per_step": gemm_ms / prof_steps, "gemm_launches_per_step": gemm_n / prof_steps,
+        "gemm_tflops": gemm_tflops, "gemm_frac_of_peak": gemm_tflops / tf32x3_peak if gemm_tflops else None,
+        "gemm_peak": tf32x3_peak,
+        "gemm_peak_source": f"{'bf16_tflops_sustained' if long_step else 'bf16_tflops'} of {pk['_source']} / 2 "
+                            "(TF32 rate) / 3 (three MMAs per algorithmic product)",
+        "phases_ms_per_step": {"gemm": ph["gemm"], "operand_split": ph["operand_split"], "optimizer": ph["optimizer"],
+                               "elementwise": ph["elementwise"], "exposed_allreduce_wait": ph["comm_wait"],
+                               "everything_else": max(0.0, ms_step - accounted),
+                               "note": "CUDA-event brackets on the compute stream over two profiled steps; "
+                                       "exposed_allreduce_wait is the time the compute stream stood idle before "
+                                       "the optimizer until the gradient all-reduces had finished"},
+        "parallelism": (f"dp{ranks.world}: batch rows sharded, one NCCL all-reduce(sum) per layer (dW and db in one "
+                        "bucket) on a communication stream, started as the layer's backward finishes; AdamW after the "
+                        "last one") if ranks.world > 1 else "single GPU",
+        "parity": {"loss": loss, "loss_is_global": "sum over the ranks' rows / global element count, all-reduced",
+                   "loss_equal_on_all_ranks": bool(all(x == losses[0] for x in losses)),
+                   "max_abs_param_diff_rank0_vs_last": agree,
+                   "dp_vs_one_gpu_reduced_config": small},
+    }

@@ -52,6 +52,13 @@ const char* vtlb_last_error(vtlb_ctx* ctx); /* ctx may be NULL: process-wide las
 /* Reads and clears the device status word written by kernels whose bounded
  * waits ran out (0 = none).  Blocks until the stream is idle. */
 int vtlb_check_status(vtlb_ctx* ctx, uint32_t* status);
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose GPU calls
+ * block on the default stream): launches a one-CTA kernel that waits on an mbarrier for at most
+ * limit_ns (1 ns .. 100 ms) with the same wait routine as the tcgen05 kernels.  arrive != 0: a
+ * second thread arrives and the wait is satisfied.  arrive == 0: nobody arrives, the wait gives
+ * up, the kernel returns normally and sets the status word, so the next vtlb_check_status
+ * returns VTLB_ETIMEOUT -- the failure path of a stuck pipeline, without anything being stuck. */
+int vtlb_wait_probe(vtlb_ctx* ctx, uint64_t limit_ns, int arrive);
 /* Number of kernels this library launched on ctx since creation. */
 uint64_t vtlb_launch_count(vtlb_ctx* ctx);
 /* cudaStream_t of the ctx (as void*), for callers that time with CUDA events. */
@@ -70,6 +77,20 @@ int vtlb_event_destroy(vtlb_ctx* ctx, void* ev);
  * algorithmic work (2*M*N*K each) and resets the counters. */
 int vtlb_profile_gemm(vtlb_ctx* ctx, int enable);
 int vtlb_profile_gemm_read(vtlb_ctx* ctx, double* total_ms, uint64_t* launches, double* total_ops);
+/* While vtlb_profile_gemm is enabled the same ring of event pairs also brackets the other phases
+ * of a training step, so that a step's time can be broken down: summed duration and number of
+ * spans of one phase since the last vtlb_profile_gemm_read (call this first; _gemm_read resets).
+ * VTLB_PHASE_COMM_WAIT is the time the compute stream stood idle in vtlb_comm_wait until the
+ * collectives on the communication stream had finished: the exposed, not-overlapped part. */
+enum {
+  VTLB_PHASE_GEMM = 0,       /* tensor-core GEMM / convolution launches */
+  VTLB_PHASE_SPLIT = 1,      /* f32 -> TF32 hi/lo operand planes */
+  VTLB_PHASE_OPTIMIZER = 2,  /* Adam / AdamW / SGD / RMSProp step */
+  VTLB_PHASE_COMM_WAIT = 3,  /* compute stream waiting for collectives */
+  VTLB_PHASE_ELEMENTWISE = 4,/* ReLU backward, bias-gradient column sums, loss kernels */
+  VTLB_PHASE_COUNT = 5
+};
+int vtlb_profile_read_phase(vtlb_ctx* ctx, int phase, double* total_ms, uint64_t* spans);
 
 /* ---- memory ---------------------------------------------------------------
  * Replaces: CpuStorage.cuda()/CudaStorage.cpu()/to_array()/release()
@@ -157,6 +178,19 @@ int vtlb_relu_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_cached_x, vo
  * dst[i] = value (ones_like for the backprop seed, autograd/variable.v:88). */
 int vtlb_add_inplace_f32(vtlb_ctx* ctx, void* d_dst, const void* d_src, size_t n);
 int vtlb_fill_f32(vtlb_ctx* ctx, void* d_dst, float value, size_t n);
+
+/* ---- parameter initialisers ---------------------------------------------------
+ * Random fills behind kaiming_uniform / kaiming_normal / variance_scaled
+ * (nn/internal/init.v:35-70), which call vtl.random(-limit, limit, shape) and
+ * vtl.normal(shape, mu, sigma) (rand.v:57-79).  The reference's generator is V's global
+ * one, seeded from the wall clock; here element i is a pure function of (seed, i):
+ *   z = splitmix64(seed + (i+1)*0x9E3779B97F4A7C15)
+ *   uniform: u = (z >> 40) * 2^-24;  x = lo + u*(hi - lo)      (f32, two roundings; x in [lo, hi))
+ *   normal : Box-Muller in f64 on u1 = ((z>>32)+1)*2^-32, u2 = (z & 0xffffffff)*2^-32,
+ *            x = (f32)(mu + sigma*sqrt(-2 ln u1)*cos(2 pi u2))
+ * so fills are reproducible and independent of the launch geometry. */
+int vtlb_init_uniform_f32(vtlb_ctx* ctx, void* d_out, size_t n, float lo, float hi, uint64_t seed);
+int vtlb_init_normal_f32(vtlb_ctx* ctx, void* d_out, size_t n, double mu, double sigma, uint64_t seed);
 
 /* ---- Conv2D / max pooling (NCHW, groups = 1, dilation = 1) ------------------
  * y[B,O,OH,OW] = conv(x[B,C,H,W], w[O,C,kh,kw]) + bias[O], OH = (H+2ph-kh)/sh+1; with

@@ -372,9 +372,22 @@ ORC_API void orc_adam_step_f64(const double *grad, double *theta, double *m, dou
   }
 }
 
-/* AdamWOptimizer.update for T = f32 (nn/optimizers/adamw.v:84-104): three
+/* AdamWOptimizer.update for T = f32 (nn/optimizers/adamw.v:78-106): three
  * passes, each element computed in f64 and cast to f32; the third pass reads
- * the freshly stored (f32) m and v. */
+ * the freshly stored (f32) m and v.
+ *
+ * DELIBERATE DEVIATION.  The moment updates here are the textbook ones,
+ *     m = beta1*m + (1-beta1)*g,   v = beta2*v + (1-beta2)*g*g,
+ * which is what the reference documents and what its Adam (adam_step_f32.v:6-21,
+ * "same math as napply path") computes.  As WRITTEN, adamw.v:86-93 gets the
+ * operands the other way round: Tensor.napply passes the receiver first
+ * (fun.v:37-44, iter.v: vals[0] = self, vals[1] = the tensor in the list), so
+ * with `first_moments[i].napply([v.grad], ...)` vals[0] is m and vals[1] is g,
+ * and the closures evaluate
+ *     m = beta1*g + (1-beta1)*m,   v = beta2*g + (1-beta2)*v_old*v_old.
+ * That variant is kept below as orc_adamw_step_f32_as_written for comparison
+ * only; the GPU kernel and every parity test follow the textbook form.  Both
+ * are pinned by hand-derived one-step vectors in tests/golden. */
 ORC_API void orc_adamw_step_f32(const float *grad, float *theta, float *m, float *v, size_t n,
                                 double beta1, double beta2, double lr_t, double epsilon,
                                 double wd) {
@@ -383,6 +396,23 @@ ORC_API void orc_adamw_step_f32(const float *grad, float *theta, float *m, float
   for (size_t i = 0; i < n; ++i) {
     double g = (double)grad[i];
     v[i] = (float)(beta2 * (double)v[i] + (1.0 - beta2) * g * g);
+  }
+  for (size_t i = 0; i < n; ++i) {
+    double th = (double)theta[i], mm = (double)m[i], vv = (double)v[i];
+    theta[i] = (float)(th - lr_t * (mm / (sqrt(vv) + epsilon) + wd * th));
+  }
+}
+
+/* The same update with the closures of adamw.v:86-93 taken literally (vals[0] = the moment
+ * tensor, vals[1] = the gradient).  Forensic only: nothing on the GPU side follows it. */
+ORC_API void orc_adamw_step_f32_as_written(const float *grad, float *theta, float *m, float *v,
+                                           size_t n, double beta1, double beta2, double lr_t,
+                                           double epsilon, double wd) {
+  for (size_t i = 0; i < n; ++i)
+    m[i] = (float)(beta1 * (double)grad[i] + (1.0 - beta1) * (double)m[i]);
+  for (size_t i = 0; i < n; ++i) {
+    double vo = (double)v[i];
+    v[i] = (float)(beta2 * (double)grad[i] + (1.0 - beta2) * vo * vo);
   }
   for (size_t i = 0; i < n; ++i) {
     double th = (double)theta[i], mm = (double)m[i], vv = (double)v[i];

@@ -286,13 +286,73 @@ def adam_step_f64(grad, theta, m, v, beta1, beta2, lr_t, eps):
 
 
 def adamw_step_f32(grad, theta, m, v, beta1, beta2, lr_t, eps, wd):
-    """AdamWOptimizer.update, T=f32 (nn/optimizers/adamw.v:84-104)."""
+    """AdamWOptimizer.update, T=f32 (nn/optimizers/adamw.v:78-106), moments in the textbook operand
+    order (see the note on orc_adamw_step_f32 in oracle.c for the as-written difference)."""
     grad = _f32(grad)
     theta, m, v = _f32(theta).copy(), _f32(m).copy(), _f32(v).copy()
     lib().orc_adamw_step_f32(_p(grad), _p(theta), _p(m), _p(v), C.c_size_t(grad.size),
                              C.c_double(beta1), C.c_double(beta2), C.c_double(lr_t),
                              C.c_double(eps), C.c_double(wd))
     return theta, m, v
+
+
+def adamw_step_f32_as_written(grad, theta, m, v, beta1, beta2, lr_t, eps, wd):
+    """adamw.v:86-93 with the closures' operands exactly as Tensor.napply hands them over
+    (m = b1*g + (1-b1)*m, v = b2*g + (1-b2)*v*v).  Forensic comparison only."""
+    grad = _f32(grad)
+    theta, m, v = _f32(theta).copy(), _f32(m).copy(), _f32(v).copy()
+    lib().orc_adamw_step_f32_as_written(_p(grad), _p(theta), _p(m), _p(v), C.c_size_t(grad.size),
+                                        C.c_double(beta1), C.c_double(beta2), C.c_double(lr_t),
+                                        C.c_double(eps), C.c_double(wd))
+    return theta, m, v
+
+
+# ---------------------------------------------------------------- initialisers (nn/internal/init.v)
+def compute_fans(shape):
+    """compute_fans as written (nn/internal/init.v:21-33): the product runs over shape[1..], so
+    shape[1] enters both fans: (shape[0]*prod(shape[1:]), shape[1]*prod(shape[1:]))."""
+    product = int(np.prod(shape[1:], dtype=np.int64))
+    return int(shape[0]) * product, int(shape[1]) * product
+
+
+def variance_scaled_std(shape, scale, fan_mode):
+    """std of variance_scaled (nn/internal/init.v:36-50); fan_mode in {"fan_in", "fan_out", "fan_avg"}."""
+    f0, f1 = compute_fans(shape)
+    if fan_mode == "fan_in":
+        return float(np.sqrt(scale / f0))
+    if fan_mode == "fan_out":
+        return float(np.sqrt(scale / f1))
+    return float(np.sqrt(scale * 2.0 / (f0 + f1)))
+
+
+def _splitmix64(seed, n):
+    """The counter-based generator of the device fills: z_i = mix(seed + (i+1)*golden)."""
+    with np.errstate(over="ignore"):
+        z = np.uint64(seed) + (np.arange(1, n + 1, dtype=np.uint64) * np.uint64(0x9E3779B97F4A7C15))
+        z ^= z >> np.uint64(30)
+        z *= np.uint64(0xBF58476D1CE4E5B9)
+        z ^= z >> np.uint64(27)
+        z *= np.uint64(0x94D049BB133111EB)
+        z ^= z >> np.uint64(31)
+    return z
+
+
+def init_uniform_f32(n, lo, hi, seed):
+    """vtl.random(lo, hi, shape) (rand.v:70-79) on the counter-based stream: u = (z >> 40) * 2^-24,
+    x = lo + u * (hi - lo) with each f32 operation rounded on its own."""
+    z = _splitmix64(seed, n)
+    u = (z >> np.uint64(40)).astype(np.float32) * np.float32(2.0 ** -24)
+    lo, hi = np.float32(lo), np.float32(hi)
+    return (lo + (u * np.float32(hi - lo)).astype(np.float32)).astype(np.float32)
+
+
+def init_normal_f32(n, mu, sigma, seed):
+    """vtl.normal(shape, mu, sigma) (rand.v:57-66) on the counter-based stream: Box-Muller in f64."""
+    z = _splitmix64(seed, n)
+    u1 = ((z >> np.uint64(32)).astype(np.float64) + 1.0) * 2.0 ** -32
+    u2 = (z & np.uint64(0xFFFFFFFF)).astype(np.float64) * 2.0 ** -32
+    r = np.sqrt(-2.0 * np.log(u1))
+    return (mu + sigma * (r * np.cos(6.283185307179586476925286766559 * u2))).astype(np.float32)
 
 
 # ---------------------------------------------------------------- layers and optimizers next to the GEMMs

@@ -119,6 +119,48 @@ kats["conv2d_4x4"] = {
 kats["conv2d_shape"] = {"source": "nn/internal/conv2d_cuda_test.v:7-19",
                         "in": [1, 1, 4, 4], "kernel": [2, 2], "pad": [0, 0], "out": [1, 1, 3, 3]}
 
+# nn/optimizers/adamw.v:78-106 -- no reference test holds an AdamW value; one step derived by hand
+# from the update's closures, (a) in the textbook operand order this build implements and (b) with
+# the operands as the closures receive them from Tensor.napply (fun.v:37-44: vals[0] is the receiver,
+# i.e. the moment tensor; vals[1] the gradient).  State is f32, each closure computes in f64 and
+# casts its result to f32 (vtl.cast[T]); f32() below rounds a Python float the same way.
+import struct
+
+
+def f32(x):
+    return struct.unpack("f", struct.pack("f", x))[0]
+
+
+aw = dict(b1=0.9, b2=0.999, lr_t=0.01, eps=1e-8, wd=0.01)
+aw_g, aw_th, aw_m, aw_v = [1.0, 2.0, 0.5, -0.25], [3.0, 4.0, 5.0, -1.5], [0.125, 0.25, 0.375, 0.0], [0.015625, 0.03125, 0.0625, 0.0]
+
+
+def adamw(order):
+    th, m, v = list(aw_th), list(aw_m), list(aw_v)
+    for i, g in enumerate(aw_g):
+        if order == "textbook":
+            m[i] = f32(aw["b1"] * m[i] + (1.0 - aw["b1"]) * g)
+            v[i] = f32(aw["b2"] * v[i] + (1.0 - aw["b2"]) * g * g)
+        else:  # adamw.v:86-93 literally: vals[0] = moment, vals[1] = gradient
+            m[i] = f32(aw["b1"] * g + (1.0 - aw["b1"]) * m[i])
+            v[i] = f32(aw["b2"] * g + (1.0 - aw["b2"]) * v[i] * v[i])
+    for i in range(len(th)):
+        if v[i] < 0.0:  # the as-written second moment goes negative with a negative gradient
+            th[i] = float("nan")
+            continue
+        th[i] = f32(th[i] - aw["lr_t"] * (m[i] / (math.sqrt(v[i]) + aw["eps"]) + aw["wd"] * th[i]))
+    return th, m, v
+
+
+tb, aswr = adamw("textbook"), adamw("as_written")
+kats["adamw_one_step_f32"] = {
+    "source": "nn/optimizers/adamw.v:78-106 (no value asserted by any reference test); fun.v:37-44 for the "
+              "operand order of napply",
+    "grad": aw_g, "theta": aw_th, "m": aw_m, "v": aw_v, "params": aw,
+    "textbook": {"theta_out": tb[0], "m_out": tb[1], "v_out": tb[2]},
+    "as_written": {"theta_out": [None if t != t else t for t in aswr[0]], "m_out": aswr[1], "v_out": aswr[2]},
+}
+
 here = os.path.dirname(os.path.abspath(__file__))
 with open(os.path.join(here, "reference_kats.json"), "w") as f:
     json.dump(kats, f, indent=1)

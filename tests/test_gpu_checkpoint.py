@@ -168,6 +168,7 @@ def test_load_weights_from_an_oracle_file(sess, tmp_path, spec):
 def test_load_weights_refuses_what_the_reference_refuses(sess, tmp_path):
     """Error cases of nn/models/serialization_test.v: layer count, layer type, missing weight,
     shape, version."""
+    from vtl_b200 import host
     from vtl_b200.capi import VtlbError
     rng = np.random.default_rng(13)
     m = build(sess, MLP)
@@ -208,6 +209,36 @@ def test_load_weights_refuses_what_the_reference_refuses(sess, tmp_path):
     json.dump(model, open(path, "w"))
     with pytest.raises(VtlbError, match="outside the base64 alphabet"):
         m.load_weights(path)
+
+    # numbers follow the JSON grammar: what strtod alone would also take is refused
+    text = json.dumps(ock.save_checkpoint(path, MLP, ps))
+    for bad in ("nan", "inf", "0x1p3", "-", "1.", "1e"):
+        open(path, "w").write(text.replace('"loss": 0.0', f'"loss": {bad}'))
+        assert f'"loss": {bad}' in open(path).read()
+        with pytest.raises(VtlbError):
+            host.load_checkpoint(path)
+    m.close()
+
+
+def test_save_replaces_the_file_only_when_complete(sess, tmp_path):
+    """The checkpoint is written beside the target and renamed over it: no temporary file stays
+    behind, and a target that cannot be written leaves the previous checkpoint as it was."""
+    from vtl_b200 import host
+    from vtl_b200.capi import VtlbError
+    rng = np.random.default_rng(14)
+    m = build(sess, MLP)
+    random_params(m, rng)
+    path = tmp_path / "m.json"
+    m.save_checkpoint(path, epoch=1, loss=0.5)
+    first = open(path, "rb").read()
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["m.json"]
+    random_params(m, rng)
+    m.save_checkpoint(path, epoch=2, loss=0.25)
+    assert host.load_checkpoint(path) == (2, 0.25) and open(path, "rb").read() != first
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["m.json"]
+    with pytest.raises(VtlbError):
+        m.save_checkpoint(tmp_path / "no_such_dir" / "m.json", epoch=3, loss=0.1)
+    assert host.load_checkpoint(path) == (2, 0.25)
     m.close()
 
 

@@ -112,3 +112,21 @@ def test_adam_reference_kat(dev):
     assert np.abs(d[1].numpy() - th2).max() < 1e-6
     assert np.abs(d[2].numpy() - m2).max() < 1e-6
     assert np.abs(d[3].numpy() - v2).max() < 1e-6
+
+
+def test_adamw_hand_derived_kat(dev):
+    """One AdamW step on the hand-derived vector of tests/golden (nn/optimizers/adamw.v:78-106
+    with the moments in the textbook operand order): theta, m and v bit for bit, and NOT the
+    values the update would give with the closures' operands as written."""
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")) as f:
+        k = json.load(f)["adamw_one_step_f32"]
+    p = k["params"]
+    d = [dev.to_device(np.array(k[n], np.float32)) for n in ("grad", "theta", "m", "v")]
+    dev.adamw_step_f32(dev.adam_table([(d[0], d[1], d[2], d[3], len(k["grad"]))]), p["b1"], p["b2"], p["lr_t"],
+                       p["eps"], p["wd"], False)
+    exp = k["textbook"]
+    for got, name in ((d[1], "theta_out"), (d[2], "m_out"), (d[3], "v_out")):
+        assert np.array_equal(got.numpy().view(np.uint32), np.array(exp[name], np.float32).view(np.uint32)), name
+    assert not np.array_equal(d[2].numpy(), np.array(k["as_written"]["m_out"], np.float32))

@@ -134,6 +134,23 @@ def test_adamw_matches_numpy_f64(orc):
     assert np.array_equal(om, m2) and np.array_equal(ov, v2) and np.array_equal(oth, th2)
 
 
+def test_adamw_kats(orc, kats):
+    """One AdamW step against the hand-derived vectors: the oracle's update (textbook operand
+    order, the deliberate deviation) and the forensic as-written variant, bit for bit."""
+    k = kats["adamw_one_step_f32"]
+    p = k["params"]
+    args = (k["grad"], k["theta"], k["m"], k["v"], p["b1"], p["b2"], p["lr_t"], p["eps"], p["wd"])
+    for name, fn in (("textbook", orc.adamw_step_f32), ("as_written", orc.adamw_step_f32_as_written)):
+        th, m, v = fn(*args)
+        exp = k[name]
+        assert np.array_equal(m, np.array(exp["m_out"], np.float32)), name
+        assert np.array_equal(v, np.array(exp["v_out"], np.float32)), name
+        want = np.array([np.nan if t is None else t for t in exp["theta_out"]], np.float32)
+        assert np.array_equal(th, want, equal_nan=True), name
+    # the two differ: the vectors really pin which one is implemented
+    assert k["textbook"]["m_out"] != k["as_written"]["m_out"]
+
+
 def test_adam_lr_t_schedule(orc):
     lr_t, b1t, b2t = orc.adam_lr_t(1e-3, 0.9, 0.999, 0.9, 0.999)
     assert abs(lr_t - 1e-3 * np.sqrt(1 - 0.999) / (1 - 0.9)) < 1e-18
@@ -186,3 +203,20 @@ def test_oracle_thread_count_can_be_raised_after_load():
     finally:
         oracle.set_threads(before)
     assert oracle.max_threads() == before
+
+
+def test_initialiser_restatement(orc):
+    """compute_fans keeps the reference's product over shape[1..] (nn/internal/init.v:21-33); the
+    counter-based fills have the moments variance_scaled asks for."""
+    assert orc.compute_fans([256, 784]) == (256 * 784, 784 * 784)
+    assert orc.compute_fans([64, 32, 3, 3]) == (64 * 32 * 9, 32 * 32 * 9)
+    std = orc.variance_scaled_std([64, 32, 3, 3], 2.0, "fan_in")
+    assert abs(std - np.sqrt(2.0 / (64 * 288))) < 1e-15
+    assert abs(orc.variance_scaled_std([4, 6], 2.0, "fan_avg") - np.sqrt(4.0 / (24 + 36))) < 1e-15
+    n = 200000
+    u = orc.init_uniform_f32(n, -1.0, 1.0, 3)
+    assert u.dtype == np.float32 and u.min() >= -1.0 and u.max() < 1.0
+    assert abs(u.mean()) < 0.01 and abs(u.std() - 1 / np.sqrt(3)) < 0.01
+    g = orc.init_normal_f32(n, 0.0, 2.0, 4)
+    assert abs(g.mean()) < 0.02 and abs(g.std() - 2.0) < 0.02
+    assert np.array_equal(orc.init_normal_f32(10, 0.0, 2.0, 4), g[:10])  # element i depends on (seed, i) only

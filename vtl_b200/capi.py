@@ -40,8 +40,10 @@ _PROTOS = {
     "vtlb_event_record": [_vp, _vp],
     "vtlb_event_elapsed_ms": [_vp, _vp, _vp, C.POINTER(C.c_float)],
     "vtlb_event_destroy": [_vp, _vp],
+    "vtlb_wait_probe": [_vp, C.c_uint64, _i],
     "vtlb_profile_gemm": [_vp, _i],
     "vtlb_profile_gemm_read": [_vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_double)],
+    "vtlb_profile_read_phase": [_vp, _i, C.POINTER(C.c_double), C.POINTER(C.c_uint64)],
     "vtlb_alloc": [_vp, _sz, C.POINTER(_vp)],
     "vtlb_free": [_vp, _vp],
     "vtlb_h2d": [_vp, _vp, _vp, _sz],
@@ -60,6 +62,8 @@ _PROTOS = {
     "vtlb_relu_bwd_f32": [_vp, _vp, _vp, _vp, _sz],
     "vtlb_add_inplace_f32": [_vp, _vp, _vp, _sz],
     "vtlb_fill_f32": [_vp, _vp, C.c_float, _sz],
+    "vtlb_init_uniform_f32": [_vp, _vp, _sz, C.c_float, C.c_float, C.c_uint64],
+    "vtlb_init_normal_f32": [_vp, _vp, _sz, C.c_double, C.c_double, C.c_uint64],
     "vtlb_ckpt_encode_f32": [_vp, _vp, _sz, _vp],
     "vtlb_linear_i8_fwd_amax": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "vtlb_copy_h2d_async": [_vp, _vp, _vp, _sz],
@@ -202,6 +206,9 @@ class Device:
         self._ck(self.lib.vtlb_check_status(self.h, C.byref(st)))
         return st.value
 
+    def wait_probe(self, limit_ns: int, arrive: bool):
+        self._ck(self.lib.vtlb_wait_probe(self.h, int(limit_ns), int(arrive)))
+
     def launch_count(self) -> int:
         return int(self.lib.vtlb_launch_count(self.h))
 
@@ -213,6 +220,17 @@ class Device:
         ms, n, ops = C.c_double(0), C.c_uint64(0), C.c_double(0)
         self._ck(self.lib.vtlb_profile_gemm_read(self.h, C.byref(ms), C.byref(n), C.byref(ops)))
         return ms.value, int(n.value), ops.value
+
+    PHASES = ("gemm", "operand_split", "optimizer", "comm_wait", "elementwise")
+
+    def profile_read_phases(self):
+        """-> {phase: (summed ms, spans)} since the last profile_gemm_read (call before it)."""
+        out = {}
+        for i, name in enumerate(self.PHASES):
+            ms, n = C.c_double(0), C.c_uint64(0)
+            self._ck(self.lib.vtlb_profile_read_phase(self.h, i, C.byref(ms), C.byref(n)))
+            out[name] = (ms.value, int(n.value))
+        return out
 
     # -- events
     def event(self) -> int:
@@ -306,6 +324,12 @@ class Device:
 
     def fill_f32(self, dst, value, n):
         self._ck(self.lib.vtlb_fill_f32(self.h, _ptr(dst), value, n))
+
+    def init_uniform_f32(self, out, n, lo, hi, seed):
+        self._ck(self.lib.vtlb_init_uniform_f32(self.h, _ptr(out), n, lo, hi, seed))
+
+    def init_normal_f32(self, out, n, mu, sigma, seed):
+        self._ck(self.lib.vtlb_init_normal_f32(self.h, _ptr(out), n, mu, sigma, seed))
 
     # -- input pipeline: copies on their own streams (host pointers as integers, pinned memory)
     COPY_IN_BEFORE_COMPUTE, COPY_OUT_BEFORE_COMPUTE, COPY_OUT_DONE = 1, 2, 4

@@ -4,8 +4,12 @@
 //
 // Adam follows adam_step_f32_cpu (nn/optimizers/adam_step_f32.v:6-21) in f32
 // with each operation rounded on its own; AdamW follows AdamWOptimizer.update
-// (nn/optimizers/adamw.v:84-104): f64 arithmetic on f32 state, m and v rounded
-// to f32 before the parameter update reads them.  SGD follows internal.sgd_optimize
+// (nn/optimizers/adamw.v:78-106): f64 arithmetic on f32 state, m and v rounded
+// to f32 before the parameter update reads them.  One deliberate deviation: the
+// moments are the textbook m = b1*m + (1-b1)*g, v = b2*v + (1-b2)*g*g, as the
+// reference's Adam computes them; adamw.v:86-93 as written hands its closures
+// the operands in the other order (napply passes the receiver first, fun.v:37-44)
+// and would evaluate m = b1*g + (1-b1)*m, v = b2*g + (1-b2)*v*v.  SGD follows internal.sgd_optimize
 // (nn/internal/optimizers.v:6-13: theta - (f32)lr * g in f32, 12 bytes per parameter) and RMSProp
 // RMSPropOptimizer.update (nn/optimizers/rmsprop.v:70-91: f64 arithmetic on f32 state, 20 bytes).
 #include "common.cuh"
@@ -121,6 +125,7 @@ int run(vtlb_ctx* ctx, const char* fn, int n_tensors, const vtlb_adam_tensor* te
         int zero_grad) {
   if (n_tensors < 0 || (n_tensors > 0 && !tensors))
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: bad tensor list", fn);
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_OPTIMIZER);
   int i = 0;
   while (i < n_tensors) {
     Table tb;

@@ -8,7 +8,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 #include "../../include/vtlb.h"
@@ -49,6 +51,12 @@ struct vtlb_ctx {
   size_t small_cached_bytes = 0;
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
+  // Byte ranges handed to collectives on the communication stream since the compute stream last
+  // waited for it.  Freeing (or recycling) a block that overlaps one of them must first order the
+  // compute stream after the communication stream; every other free needs no such wait, which is
+  // what lets a gradient all-reduce run beside the rest of backprop.
+  std::vector<std::pair<uintptr_t, uintptr_t>> comm_inflight;  // [begin, end)
+  std::unordered_map<void*, size_t> big_live;                  // blocks above kCacheBlockMax -> bytes
   uint64_t launches = 0;
   // f32 GEMMs of at most this many flops (2*M*N*K) run on the CUDA-core kernel of
   // f32_small.cu instead of the tensor-core path (vtlb_set_small_gemm_limit; 0 = never).
@@ -58,6 +66,7 @@ struct vtlb_ctx {
   bool prof_on = false;
   static constexpr int kProfSlots = 2048;
   cudaEvent_t* prof_ev = nullptr;  // 2 * kProfSlots events, created on first enable
+  uint8_t* prof_phase = nullptr;   // phase of each slot (VTLB_PHASE_*; the GEMM launch sites leave 0)
   int prof_n = 0;
   double prof_flops = 0.0;
   char err[512] = {0};
@@ -94,6 +103,40 @@ int vtlb_fail(vtlb_ctx* ctx, int code, const char* fmt, ...);
       return vtlb_fail((ctx), VTLB_ECUDA, "%s: kernel launch: %s", __func__,          \
                        cudaGetErrorString(e__));                                      \
   } while (0)
+
+// Brackets the launches of its scope with one event pair of the timing ring, filed under `phase`
+// (include/vtlb.h: VTLB_PHASE_*), while vtlb_profile_gemm is enabled; free otherwise.
+struct vtlb_prof_scope {
+  vtlb_ctx* ctx;
+  int slot;
+  vtlb_prof_scope(vtlb_ctx* c, int phase) : ctx(c), slot(-1) {
+    if (c->prof_on && c->prof_ev && c->prof_n < vtlb_ctx::kProfSlots) {
+      slot = c->prof_n++;
+      c->prof_phase[slot] = (uint8_t)phase;
+      cudaEventRecord(c->prof_ev[2 * slot], c->stream);
+    }
+  }
+  ~vtlb_prof_scope() {
+    if (slot >= 0) cudaEventRecord(ctx->prof_ev[2 * slot + 1], ctx->stream);
+  }
+  vtlb_prof_scope(const vtlb_prof_scope&) = delete;
+  vtlb_prof_scope& operator=(const vtlb_prof_scope&) = delete;
+};
+
+// Notes that a collective enqueued on the communication stream reads or writes [p, p + bytes).
+inline void vtlb_comm_track(vtlb_ctx* ctx, const void* p, size_t bytes) {
+  if (!p || !bytes) return;
+  auto& v = ctx->comm_inflight;
+  if (v.size() >= 1024) {  // a caller that never waits: fold the list into its bounding range
+    uintptr_t lo = v[0].first, hi = v[0].second;
+    for (const auto& r : v) {
+      lo = r.first < lo ? r.first : lo;
+      hi = r.second > hi ? r.second : hi;
+    }
+    v.assign(1, std::make_pair(lo, hi));
+  }
+  v.emplace_back((uintptr_t)p, (uintptr_t)p + bytes);
+}
 
 // Returns a scratch region of at least `bytes` (grown on demand; growth
 // synchronises the stream first because earlier kernels may still use the old one).

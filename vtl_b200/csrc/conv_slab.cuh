@@ -423,10 +423,10 @@ int launch(vtlb_ctx* ctx, const float* src, const Geometry& g, Tiling tl, const 
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[0], true, b_hi, g.K, N, (uint64_t)ldb * 4, 32, BN))) return rc;
   if ((rc = gemm::encode_tmap_2d(ctx, &tm.b[1], true, b_lo, g.K, N, (uint64_t)ldb * 4, 32, BN))) return rc;
   auto kern = conv_slab_kernel<Epi>;
-  static uint64_t configured = 0;
-  if (!(configured >> (ctx->device & 63) & 1)) {
+  static std::atomic<uint64_t> configured{0};
+  if (!(configured.load(std::memory_order_relaxed) >> (ctx->device & 63) & 1)) {
     VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
-    configured |= 1ull << (ctx->device & 63);
+    configured.fetch_or(1ull << (ctx->device & 63), std::memory_order_relaxed);
   }
   const int tiles = g.B * tl.tiles_per_img * ((N + BN - 1) / BN);
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;

@@ -97,6 +97,7 @@ VTLB_API int vtlb_ctx_destroy(vtlb_ctx* ctx) {
     for (int i = 0; i < 2 * vtlb_ctx::kProfSlots; ++i)
       if (ctx->prof_ev[i]) cudaEventDestroy(ctx->prof_ev[i]);
     delete[] ctx->prof_ev;
+    delete[] ctx->prof_phase;
   }
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->ksplit_buf) cudaFree(ctx->ksplit_buf);
@@ -183,12 +184,34 @@ VTLB_API int vtlb_profile_gemm(vtlb_ctx* ctx, int enable) {
   if (enable && !ctx->prof_ev) {
     ctx->prof_ev = new (std::nothrow) cudaEvent_t[2 * vtlb_ctx::kProfSlots]();
     if (!ctx->prof_ev) return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_profile_gemm: host allocation failed");
+    ctx->prof_phase = new (std::nothrow) uint8_t[vtlb_ctx::kProfSlots]();
+    if (!ctx->prof_phase) return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_profile_gemm: host allocation failed");
     for (int i = 0; i < 2 * vtlb_ctx::kProfSlots; ++i) VTLB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[i]));
   }
   ctx->prof_on = enable != 0;
   if (enable) {
     ctx->prof_n = 0;
     ctx->prof_flops = 0.0;
+    memset(ctx->prof_phase, 0, vtlb_ctx::kProfSlots);
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_profile_read_phase(vtlb_ctx* ctx, int phase, double* total_ms, uint64_t* spans) {
+  VTLB_ENTER(ctx);
+  if (!total_ms || !spans) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_profile_read_phase: null out");
+  if (phase < 0 || phase >= VTLB_PHASE_COUNT)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_profile_read_phase: unknown phase %d", phase);
+  *total_ms = 0.0;
+  *spans = 0;
+  if (!ctx->prof_ev) return VTLB_OK;
+  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int i = 0; i < ctx->prof_n; ++i) {
+    if (ctx->prof_phase[i] != phase) continue;
+    float t = 0.f;
+    VTLB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+    *total_ms += t;
+    ++*spans;
   }
   return VTLB_OK;
 }
@@ -198,16 +221,20 @@ VTLB_API int vtlb_profile_gemm_read(vtlb_ctx* ctx, double* total_ms, uint64_t* l
   if (!total_ms || !launches || !total_ops) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_profile_gemm_read: null out");
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   double ms = 0.0;
+  uint64_t n = 0;
   for (int i = 0; i < ctx->prof_n; ++i) {
+    if (ctx->prof_phase[i] != VTLB_PHASE_GEMM) continue;
     float t = 0.f;
     VTLB_CUDA(ctx, cudaEventElapsedTime(&t, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
     ms += t;
+    ++n;
   }
   *total_ms = ms;
-  *launches = (uint64_t)ctx->prof_n;
+  *launches = n;
   *total_ops = ctx->prof_flops;
   ctx->prof_n = 0;
   ctx->prof_flops = 0.0;
+  memset(ctx->prof_phase, 0, vtlb_ctx::kProfSlots);
   return VTLB_OK;
 }
 
@@ -264,20 +291,45 @@ VTLB_API int vtlb_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out) {
     cudaGetLastError();
     return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
   }
-  if (small) ctx->small_live.emplace(*d_out, bytes);
+  if (small)
+    ctx->small_live.emplace(*d_out, bytes);
+  else
+    ctx->big_live.emplace(*d_out, bytes);
   return VTLB_OK;
 }
 
 VTLB_API int vtlb_free(vtlb_ctx* ctx, void* d_ptr) {
   VTLB_ENTER(ctx);
   if (!d_ptr) return VTLB_OK;
-  // ordered after the work already enqueued on the compute stream; collectives still in
-  // flight on the communication stream are waited for first
-  if (ctx->comm) {
-    VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
-    VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
-  }
+  // The free is ordered after the work already enqueued on the compute stream.  Only a block
+  // that a collective still in flight on the communication stream reads or writes needs more:
+  // the compute stream then waits for the communication stream first.  Every other free leaves
+  // the two streams independent, so a gradient all-reduce keeps running beside backprop.
   auto it = ctx->small_live.find(d_ptr);
+  if (!ctx->comm_inflight.empty()) {
+    size_t bytes = 0;
+    bool known = false;
+    if (it != ctx->small_live.end()) {
+      bytes = it->second;
+      known = true;
+    } else {
+      auto bit = ctx->big_live.find(d_ptr);
+      if (bit != ctx->big_live.end()) {
+        bytes = bit->second;
+        known = true;
+      }
+    }
+    const uintptr_t b = (uintptr_t)d_ptr, e = b + bytes;
+    bool hit = !known;  // a pointer this context did not hand out: be conservative
+    for (size_t i = 0; i < ctx->comm_inflight.size() && !hit; ++i)
+      hit = ctx->comm_inflight[i].first < e && b < ctx->comm_inflight[i].second;
+    if (hit) {
+      VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+      VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+      ctx->comm_inflight.clear();
+    }
+  }
+  ctx->big_live.erase(d_ptr);
   if (it != ctx->small_live.end()) {
     const size_t bytes = it->second;
     ctx->small_live.erase(it);

@@ -110,6 +110,7 @@ VTLB_API int vtlb_allreduce_sum_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n) 
   if (n == 0) return VTLB_OK;
   if ((rc = comm_after_compute(ctx))) return rc;
   VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclSum, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  vtlb_comm_track(ctx, d_buf, n * sizeof(float));
   return VTLB_OK;
 }
 
@@ -120,6 +121,7 @@ VTLB_API int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n) 
   if (n == 0) return VTLB_OK;
   if ((rc = comm_after_compute(ctx))) return rc;
   VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclMax, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  vtlb_comm_track(ctx, d_buf, n * sizeof(float));
   return VTLB_OK;
 }
 
@@ -130,12 +132,16 @@ VTLB_API int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_rec
   if (bytes_per_rank == 0) return VTLB_OK;
   if ((rc = comm_after_compute(ctx))) return rc;
   VTLB_NCCL(ctx, g_nccl.AllGather(d_send, d_recv, bytes_per_rank, ncclInt8, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  vtlb_comm_track(ctx, d_send, bytes_per_rank);
+  vtlb_comm_track(ctx, d_recv, bytes_per_rank * (size_t)ctx->nranks);
   return VTLB_OK;
 }
 
 VTLB_API int vtlb_comm_wait(vtlb_ctx* ctx) {
   VTLB_ENTER(ctx);
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_COMM_WAIT);  // how long the compute stream stands idle here
   VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
   VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  ctx->comm_inflight.clear();  // the compute stream is now ordered after every collective enqueued so far
   return VTLB_OK;
 }

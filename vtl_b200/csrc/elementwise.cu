@@ -198,6 +198,7 @@ VTLB_API int vtlb_relu_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_cac
   VTLB_ENTER(ctx);
   if (n == 0) return VTLB_OK;
   if (!d_g || !d_cached_x || !d_dx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_relu_bwd_f32: null pointer");
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_ELEMENTWISE);
   const int vec = vtlb_aligned16(d_g) && vtlb_aligned16(d_cached_x) && vtlb_aligned16(d_dx);
   VTLB_CUDA(ctx, vtlb_launch_early(relu_bwd_kernel, dim3(ew_grid(ctx, n, 1024)), dim3(256), 0, ctx->stream,
                                    (const float*)d_g, (const float*)d_cached_x, (float*)d_dx, n, vec));
@@ -210,6 +211,7 @@ VTLB_API int vtlb_mse_fwd_bwd_f32(vtlb_ctx* ctx, const void* d_P, const void* d_
   VTLB_ENTER(ctx);
   if (n == 0 || n_div == 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: empty input");
   if (!d_P || !d_T || !d_loss) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_mse_fwd_bwd_f32: null pointer");
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_ELEMENTWISE);
   if (n <= 8192) {
     VTLB_CUDA(ctx, vtlb_launch_early(mse_short_kernel, dim3(1), dim3(256), 0, ctx->stream, (const float*)d_P,
                                      (const float*)d_T, n, (double)n_div, (float*)d_dP_or_null, (float*)d_loss));

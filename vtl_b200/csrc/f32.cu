@@ -150,6 +150,7 @@ __global__ void __launch_bounds__(256) reduce_splits_kernel(const float* __restr
 // operand.  `transposed` says src is stored [kdim, rows].
 int f32::split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool transposed, int ld,
                   float* hi, float* lo) {
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_SPLIT);
   if (!transposed) {
     if ((kdim & 3) == 0 && ld == kdim && vtlb_aligned16(src)) {
       const size_t n4 = (size_t)rows * kdim / 4;
@@ -190,6 +191,7 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
 }
 
 int colsum(vtlb_ctx* ctx, const float* G, int M, int N, float* out) {
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_ELEMENTWISE);
   if (M <= 1024) {
     colsum_short_kernel<<<(N + 31) / 32, 256, 0, ctx->stream>>>(G, M, N, out);
     VTLB_LAUNCHED(ctx);
@@ -295,7 +297,9 @@ static __device__ __align__(256) double g_bias_grad_scratch[(size_t)kNoAllocMaxS
 
 // In host code the array's name is only a handle; the device address has to be
 // asked for, once per device, with that device current.
-static double* g_bias_grad_scratch_addr[64] = {nullptr};
+// (Atomic: two host threads may make their first calls on different contexts at the same time;
+// both would resolve the same address, so the order of the stores does not matter.)
+static std::atomic<double*> g_bias_grad_scratch_addr[64];
 
 VTLB_API int vtlb_bias_grad_f32_noalloc(vtlb_ctx* ctx, const void* d_G, int M, int N, void* d_db) {
   VTLB_ENTER(ctx);
@@ -309,11 +313,12 @@ VTLB_API int vtlb_bias_grad_f32_noalloc(vtlb_ctx* ctx, const void* d_G, int M, i
   if (!d_G || !d_db) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_bias_grad_f32_noalloc: null pointer");
   if (ctx->device < 0 || ctx->device >= 64)
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_bias_grad_f32_noalloc: device index %d not supported", ctx->device);
-  double* scratch = g_bias_grad_scratch_addr[ctx->device];
+  double* scratch = g_bias_grad_scratch_addr[ctx->device].load(std::memory_order_relaxed);
   if (!scratch) {  // first call on this device: resolve the array's device address
     void* p = nullptr;
     VTLB_CUDA(ctx, cudaGetSymbolAddress(&p, g_bias_grad_scratch));
-    scratch = g_bias_grad_scratch_addr[ctx->device] = (double*)p;
+    scratch = (double*)p;
+    g_bias_grad_scratch_addr[ctx->device].store(scratch, std::memory_order_relaxed);
   }
   int S = (M + 63) / 64;
   if (S > kNoAllocMaxS) S = kNoAllocMaxS;

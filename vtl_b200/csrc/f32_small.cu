@@ -242,13 +242,13 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   cfg.blockDim = dim3(256);
   cfg.dynamicSmemBytes = kStageBytes;
   cfg.stream = ctx->stream;
-  static uint64_t configured = 0;  // one bit per device
-  if (!(configured >> (ctx->device & 63) & 1)) {
+  static std::atomic<uint64_t> configured{0};  // one bit per device
+  if (!(configured.load(std::memory_order_relaxed) >> (ctx->device & 63) & 1)) {
     VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
     VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
     VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
     VTLB_CUDA(ctx, cudaFuncSetAttribute(sgemm_small_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes));
-    configured |= 1ull << (ctx->device & 63);
+    configured.fetch_or(1ull << (ctx->device & 63), std::memory_order_relaxed);
   }
   static int pdl = -1;  // VTLB_SMALL_PDL=0 switches the early launch off (measurements)
   if (pdl < 0) {

@@ -366,14 +366,14 @@ int launch_s(vtlb_ctx* ctx, int tiles, const Params& p) {
 template <bool FUSED>
 int launch(vtlb_ctx* ctx, const void* Aq, const void* Wq, int M, int N, int K, Params p) {
   static int max_clusters[64][3];  // per device: clusters of 1, 2, 4 CTAs resident at a time
-  static uint64_t configured = 0;
+  static std::atomic<uint64_t> configured{0};
   const int d = ctx->device & 63;
-  if (!(configured >> d & 1)) {
+  if (!(configured.load(std::memory_order_relaxed) >> d & 1)) {
     int rc = configure<FUSED, 1>(ctx, &max_clusters[d][0]);
     if (!rc) rc = configure<FUSED, 2>(ctx, &max_clusters[d][1]);
     if (!rc) rc = configure<FUSED, 4>(ctx, &max_clusters[d][2]);
     if (rc) return rc;
-    configured |= 1ull << d;
+    configured.fetch_or(1ull << d, std::memory_order_relaxed);
   }
   const int ldk = (K + 15) / 16 * 16;
   const int MN = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;

@@ -422,11 +422,11 @@ int launch(vtlb_ctx* ctx, const TmapSet& tm, const Epi& epi, int M, int N, int K
   using S = Smem<KIND, BN, STAGES>;
   static_assert(S::TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_tc_kernel<KIND, BN, STAGES, Epi>;
-  static uint64_t configured = 0;  // one bit per device
-  if (!(configured >> (ctx->device & 63) & 1)) {
+  static std::atomic<uint64_t> configured{0};  // one bit per device
+  if (!(configured.load(std::memory_order_relaxed) >> (ctx->device & 63) & 1)) {
     VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)S::TOTAL));
-    configured |= 1ull << (ctx->device & 63);
+    configured.fetch_or(1ull << (ctx->device & 63), std::memory_order_relaxed);
   }
   {  // drop ranges that would be empty
     constexpr int BKE = ROW_BYTES / Traits<KIND>::ELEM;

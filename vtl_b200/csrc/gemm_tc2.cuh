@@ -536,10 +536,10 @@ int launch_pair(vtlb_ctx* ctx, const gemm::TmapSet& tm, const Epi& epi, int M, i
   using C = Cfg<KIND>;
   static_assert(C::SMEM_TOTAL <= 232448, "shared memory budget");
   auto kern = gemm_pair_kernel<KIND, Epi>;
-  static uint64_t configured = 0;
-  if (!(configured >> (ctx->device & 63) & 1)) {
+  static std::atomic<uint64_t> configured{0};
+  if (!(configured.load(std::memory_order_relaxed) >> (ctx->device & 63) & 1)) {
     VTLB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_TOTAL));
-    configured |= 1ull << (ctx->device & 63);
+    configured.fetch_or(1ull << (ctx->device & 63), std::memory_order_relaxed);
   }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN2 - 1) / BN2);
   int pairs = ctx->sm_count / 2;

@@ -155,10 +155,27 @@ class JParser {
     } else if (!s_.compare(p_, 4, "null")) {
       p_ += 4;
     } else {
-      char* end = nullptr;
-      v.num = std::strtod(s_.c_str() + p_, &end);
-      if (end == s_.c_str() + p_) fail("value expected");
-      p_ = (size_t)(end - s_.c_str());
+      // a JSON number and nothing else: -? int frac? exp?  (strtod alone would also take
+      // "nan", "inf" and hexadecimal floats, which a JSON decoder rejects)
+      size_t q = p_;
+      auto digits = [&] {
+        const size_t q0 = q;
+        while (q < s_.size() && s_[q] >= '0' && s_[q] <= '9') ++q;
+        return q > q0;
+      };
+      if (q < s_.size() && s_[q] == '-') ++q;
+      if (!digits()) fail("value expected");
+      if (q < s_.size() && s_[q] == '.') {
+        ++q;
+        if (!digits()) fail("digits expected after the decimal point");
+      }
+      if (q < s_.size() && (s_[q] == 'e' || s_[q] == 'E')) {
+        ++q;
+        if (q < s_.size() && (s_[q] == '+' || s_[q] == '-')) ++q;
+        if (!digits()) fail("digits expected in the exponent");
+      }
+      v.num = std::strtod(s_.substr(p_, q - p_).c_str(), nullptr);
+      p_ = q;
       v.kind = JValue::Num;
     }
     return v;
@@ -324,12 +341,26 @@ void Sequential::save_checkpoint(const std::string& path, int epoch, double loss
     optimizer += "}}";
   }
 
-  std::ofstream f(path, std::ios::binary | std::ios::trunc);
-  if (!f) throw Error(VTLB_EINVAL, "checkpoint: cannot write '" + path + "'");
-  f << "{\"version\":\"1.0\",\"layers\":" << layer_defs << ",\"layer_data\":" << layer_data
-    << ",\"optimizer\":" << optimizer << ",\"metadata\":{\"epoch\":" << epoch << ",\"loss\":" << json_number(loss)
-    << ",\"saved_at\":\"vtl_checkpoint\",\"version\":\"1.0\"}}";
-  if (!f.good()) throw Error(VTLB_EINVAL, "checkpoint: write to '" + path + "' failed");
+  // Written beside the target and renamed over it once it is complete and closed, so that a
+  // failure half way (disk full, process killed) leaves the previous checkpoint untouched.
+  const std::string tmp = path + ".tmp";
+  {
+    std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+    if (!f) throw Error(VTLB_EINVAL, "checkpoint: cannot write '" + path + "'");
+    f << "{\"version\":\"1.0\",\"layers\":" << layer_defs << ",\"layer_data\":" << layer_data
+      << ",\"optimizer\":" << optimizer << ",\"metadata\":{\"epoch\":" << epoch << ",\"loss\":" << json_number(loss)
+      << ",\"saved_at\":\"vtl_checkpoint\",\"version\":\"1.0\"}}";
+    f.flush();
+    f.close();
+    if (f.fail()) {
+      std::remove(tmp.c_str());
+      throw Error(VTLB_EINVAL, "checkpoint: write to '" + path + "' failed");
+    }
+  }
+  if (std::rename(tmp.c_str(), path.c_str()) != 0) {
+    std::remove(tmp.c_str());
+    throw Error(VTLB_EINVAL, "checkpoint: cannot replace '" + path + "'");
+  }
 }
 
 std::pair<int, double> Sequential::load_checkpoint(const std::string& path) {

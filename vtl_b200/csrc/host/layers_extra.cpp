@@ -209,7 +209,7 @@ void SgdOptimizer::update() {  // nn/optimizers/sgd.v:45-52
   if (params.empty()) return;
   Session* s = params[0]->context->device_session;
   auto tb = step_table(s, params, nullptr);
-  if (s->nranks > 1) s->check(vtlb_comm_wait(s->ctx));
+  if (s->comm_on) s->check(vtlb_comm_wait(s->ctx));
   s->check(vtlb_sgd_step_f32(s->ctx, (int)tb.size(), tb.data(), learning_rate, 0));
   clear_grads(params);
 }
@@ -225,7 +225,7 @@ void RMSPropOptimizer::update() {  // nn/optimizers/rmsprop.v:70-91
   if (params.empty()) return;
   Session* s = params[0]->context->device_session;
   auto tb = step_table(s, params, &sq_avg);
-  if (s->nranks > 1) s->check(vtlb_comm_wait(s->ctx));
+  if (s->comm_on) s->check(vtlb_comm_wait(s->ctx));
   s->check(vtlb_rmsprop_step_f32(s->ctx, (int)tb.size(), tb.data(), learning_rate, alpha, epsilon, weight_decay, 0));
   clear_grads(params);
 }

@@ -23,6 +23,7 @@ void Session::comm_init(int nranks_, int rank_, const void* id128) {
   check(vtlb_comm_init_rank(ctx, nranks_, rank_, id128));
   nranks = nranks_;
   rank = rank_;
+  comm_on = true;
 }
 
 DeviceBuf::DeviceBuf(Session* s_, size_t bytes_) : s(s_), ptr(nullptr), bytes(bytes_), owned(true) {
@@ -79,6 +80,39 @@ Tensor Tensor::reshape(std::vector<int> new_shape) const {
 }
 size_t Tensor::size() const { return numel(shape_); }
 
+// ---------------------------------------------------------------- initialisers (nn/internal/init.v)
+std::pair<long long, long long> compute_fans(const std::vector<int>& shape) {
+  if (shape.size() < 2) throw Error(VTLB_EINVAL, "compute_fans: the shape needs at least two dimensions");
+  long long product = 1;
+  for (size_t i = 1; i < shape.size(); ++i) product *= shape[i];  // shape[1..], shape[1] included
+  return {(long long)shape[0] * product, (long long)shape[1] * product};
+}
+
+Tensor variance_scaled(Session* s, const std::vector<int>& shape, double scale, FanMode mode, Distribution dist,
+                       uint64_t seed) {
+  const auto fans = compute_fans(shape);
+  double sd;
+  switch (mode) {
+    case FanMode::fan_in: sd = std::sqrt(scale / (double)fans.first); break;
+    case FanMode::fan_out: sd = std::sqrt(scale / (double)fans.second); break;
+    default: sd = std::sqrt(scale * 2.0 / (double)(fans.first + fans.second)); break;
+  }
+  Tensor t = Tensor::empty(s, shape);
+  if (dist == Distribution::uniform) {
+    const float limit = (float)(std::sqrt(3.0) * sd);  // vtl.cast[T](math.sqrt(3.0) * std)
+    s->check(vtlb_init_uniform_f32(s->ctx, t.data(), t.size(), -limit, limit, seed));
+  } else {
+    s->check(vtlb_init_normal_f32(s->ctx, t.data(), t.size(), 0.0, sd, seed));
+  }
+  return t;
+}
+Tensor kaiming_uniform(Session* s, const std::vector<int>& shape, uint64_t seed) {
+  return variance_scaled(s, shape, 2.0, FanMode::fan_in, Distribution::uniform, seed);
+}
+Tensor kaiming_normal(Session* s, const std::vector<int>& shape, uint64_t seed) {
+  return variance_scaled(s, shape, 2.0, FanMode::fan_in, Distribution::normal, seed);
+}
+
 // ---------------------------------------------------------------- autograd
 VarPtr Context::variable(const Tensor& value, bool requires_grad) {
   auto v = std::make_shared<Variable>();
@@ -133,6 +167,10 @@ void Variable::backprop() {
         p.grad = diffs[i];
         p.grad_is_zero = false;
       } else {
+        // Either operand may be a parameter gradient whose all-reduce is still running on the
+        // communication stream (a weight used twice, or two backprops before an update): the
+        // add on the compute stream has to come after it.
+        if (s->comm_on) s->check(vtlb_comm_wait(s->ctx));
         s->check(vtlb_add_inplace_f32(s->ctx, p.grad.data(), diffs[i].data(), p.grad.size()));
       }
     }
@@ -161,7 +199,7 @@ struct GradBucket {
     return g;
   }
   void allreduce(Session* s) const {
-    if (s->nranks <= 1) return;
+    if (!s->comm_on) return;
     const size_t n = db.offset() + db.size();
     s->check(vtlb_allreduce_sum_f32_async(s->ctx, dW.buffer()->ptr, n));
   }
@@ -285,10 +323,9 @@ VarPtr matmul(const VarPtr& a, const VarPtr& b) {
 // ---------------------------------------------------------------- layers
 LinearLayer::LinearLayer(Context* ctx, int in, int out) : in_features(in), out_features(out) {
   Session* s = ctx->device_session;
-  // The reference draws Kaiming-normal weights from a wall-clock-seeded RNG
-  // (nn/layers/linear.v:25, rand.v:82-89); parameters here start at zero and the caller
-  // injects the arrays it wants, identically on every side of a comparison.
-  weights = ctx->variable(Tensor::zeros(s, {out, in}));
+  // nn/layers/linear.v:25-26: Kaiming-normal weights, zero bias.  The reference's draw comes from a
+  // wall-clock-seeded generator; here from the session's seed, so it can be repeated.
+  weights = ctx->variable(kaiming_normal(s, {out, in}, s->next_init_seed()));
   bias = ctx->variable(Tensor::zeros(s, {1, out}));
 }
 
@@ -352,7 +389,7 @@ Conv2DLayer::Conv2DLayer(Context* ctx, std::vector<int> in_shape_, int out_ch_, 
                          Conv2DConfig cfg_)
     : in_ch(in_shape_[0]), out_ch(out_ch_), kh(kh_), kw(kw_), cfg(cfg_), in_shape(std::move(in_shape_)) {
   Session* s = ctx->device_session;
-  weight = ctx->variable(Tensor::zeros(s, {out_ch, in_ch, kh, kw}));
+  weight = ctx->variable(kaiming_normal(s, {out_ch, in_ch, kh, kw}, s->next_init_seed()));  // conv2d.v:49
   bias = ctx->variable(Tensor::zeros(s, {1, out_ch}));
 }
 std::vector<int> Conv2DLayer::output_shape() const {
@@ -429,6 +466,9 @@ VarPtr MSELoss::loss(const VarPtr& output, const Tensor& target, int global_rows
   Tensor l = Tensor::empty(s, {1});
   Tensor d = Tensor::empty(s, output->value.shape());
   s->check(vtlb_mse_fwd_bwd_f32(s->ctx, output->value.data(), target.data(), n, n_div, l.data(), d.data()));
+  // every rank holds its rows' share of the sum over the global divisor: the loss of the whole
+  // batch is their sum (awaited with the gradient all-reduces, before the value is read)
+  if (s->comm_on) s->check(vtlb_allreduce_sum_f32_async(s->ctx, l.data(), 1));
   VarPtr out = ctx->variable(l);
   auto g = std::make_unique<LossGate>();
   g->d_output = d;
@@ -446,6 +486,7 @@ VarPtr SoftmaxCrossEntropyLoss::loss(const VarPtr& output, const Tensor& target,
   Tensor d = Tensor::empty(s, xs);
   s->check(vtlb_softmax_ce_fwd_bwd_f32(s->ctx, output->value.data(), target.data(), xs[0], xs[1],
                                        global_rows > 0 ? global_rows : xs[0], l.data(), d.data()));
+  if (s->comm_on) s->check(vtlb_allreduce_sum_f32_async(s->ctx, l.data(), 1));  // as in MSELoss
   VarPtr out = ctx->variable(l);
   auto g = std::make_unique<LossGate>();
   g->d_output = d;
@@ -538,7 +579,7 @@ void AdamOptimizer::update() {
     tb.push_back({v.grad.data(), v.value.data(), first_moments[i].data(), second_moments[i].data(),
                   v.value.size()});
   }
-  if (s->nranks > 1) s->check(vtlb_comm_wait(s->ctx));  // gradient all-reduces started in backprop
+  if (s->comm_on) s->check(vtlb_comm_wait(s->ctx));  // gradient all-reduces started in backprop
   if (adamw)
     s->check(vtlb_adamw_step_f32(s->ctx, (int)tb.size(), tb.data(), beta1, beta2, lr_t, epsilon, weight_decay, 0));
   else

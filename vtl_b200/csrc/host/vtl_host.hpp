@@ -32,6 +32,9 @@ struct Error : std::runtime_error {
 struct Session {
   vtlb_ctx* ctx = nullptr;
   int nranks = 1, rank = 0;
+  // true once comm_init has run: gradients and loss values are then summed over the ranks.  A
+  // communicator of a single rank takes the same code path (its collectives are copies in place).
+  bool comm_on = false;
   bool owns_ctx = true;
   explicit Session(int device);
   ~Session();
@@ -39,6 +42,11 @@ struct Session {
   void comm_init(int nranks_, int rank_, const void* id128);
   void sync() const { check(vtlb_sync(ctx)); }
   std::shared_ptr<struct DeviceBuf> seed_one;  // a [1] tensor holding 1.0, filled once (Variable::backprop)
+  // Seed of the parameter initialisers.  The reference seeds V's generator from the wall clock;
+  // here layers draw their weights from (init_seed, running counter), so a model built twice
+  // with the same seed starts from the same weights, on every rank of a data-parallel job.
+  uint64_t init_seed = 0, init_counter = 0;
+  uint64_t next_init_seed() { return init_seed * 0x100000001B3ull + 0x9E3779B97F4A7C15ull * ++init_counter; }
 };
 
 struct DeviceBuf {  // one vtlb_alloc; freed (stream-ordered) when the last Tensor view dies
@@ -77,6 +85,20 @@ class Tensor {
   size_t off_ = 0;
   std::vector<int> shape_;
 };
+
+// nn/internal/init.v:7-70.  compute_fans keeps the reference's arithmetic as written:
+// f0 = shape[0] * prod(shape[1..]), f1 = shape[1] * prod(shape[1..]) (the product runs over
+// shape[1..], so shape[1] enters both), and for a 1-D shape it returns (shape[0], shape[1]) --
+// reading past the end there, which this mirror reports as an error instead.
+enum class FanMode { fan_avg, fan_in, fan_out };
+enum class Distribution { uniform, normal };
+std::pair<long long, long long> compute_fans(const std::vector<int>& shape);
+// std = sqrt(scale / fan) (fan_avg: sqrt(2*scale / (f0 + f1))); uniform draws from
+// [-sqrt(3)*std, +sqrt(3)*std), normal from N(0, std).  `seed` picks the stream.
+Tensor variance_scaled(Session* s, const std::vector<int>& shape, double scale, FanMode mode, Distribution dist,
+                       uint64_t seed);
+Tensor kaiming_uniform(Session* s, const std::vector<int>& shape, uint64_t seed);
+Tensor kaiming_normal(Session* s, const std::vector<int>& shape, uint64_t seed);
 
 struct Context;
 struct Gate;

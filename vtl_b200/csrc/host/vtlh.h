@@ -18,6 +18,13 @@ int vtlh_session_create(int device, vtlh_session** out);
 int vtlh_session_destroy(vtlh_session* s);
 void* vtlh_session_ctx(vtlh_session* s); /* the vtlb_ctx* the session owns */
 int vtlh_session_comm_init(vtlh_session* s, int nranks, int rank, const void* id128);
+/* Seed of the layers' Kaiming-normal weight draws (restarts the per-layer counter). */
+int vtlh_session_set_seed(vtlh_session* s, unsigned long long seed);
+/* nn/internal/init.v: compute_fans (as written there) and variance_scaled into a host array;
+ * fan_mode 0 = fan_avg, 1 = fan_in, 2 = fan_out; distribution 0 = uniform, 1 = normal. */
+int vtlh_compute_fans(int ndim, const int* shape, long long* f0, long long* f1);
+int vtlh_variance_scaled(vtlh_session* s, int ndim, const int* shape, double scale, int fan_mode, int distribution,
+                         unsigned long long seed, float* host_out);
 
 int vtlh_model_create(vtlh_session* s, vtlh_model** out);
 int vtlh_model_destroy(vtlh_model* m);

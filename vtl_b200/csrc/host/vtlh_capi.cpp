@@ -64,6 +64,29 @@ int vtlh_session_comm_init(vtlh_session* s, int nranks, int rank, const void* id
   return guard([&] { s->s->comm_init(nranks, rank, id128); });
 }
 
+int vtlh_session_set_seed(vtlh_session* s, unsigned long long seed) {
+  s->s->init_seed = seed;
+  s->s->init_counter = 0;
+  return VTLB_OK;
+}
+int vtlh_compute_fans(int ndim, const int* shape, long long* f0, long long* f1) {
+  return guard([&] {
+    const auto f = compute_fans(std::vector<int>(shape, shape + ndim));
+    *f0 = f.first;
+    *f1 = f.second;
+  });
+}
+int vtlh_variance_scaled(vtlh_session* s, int ndim, const int* shape, double scale, int fan_mode, int distribution,
+                         unsigned long long seed, float* host_out) {
+  return guard([&] {
+    if (fan_mode < 0 || fan_mode > 2 || distribution < 0 || distribution > 1)
+      throw Error(VTLB_EINVAL, "variance_scaled: unknown fan mode or distribution");
+    Tensor t = variance_scaled(s->s.get(), std::vector<int>(shape, shape + ndim), scale, (FanMode)fan_mode,
+                               (Distribution)distribution, seed);
+    t.to_array(host_out);
+  });
+}
+
 int vtlh_model_create(vtlh_session* s, vtlh_model** out) {
   return guard([&] {
     auto m = new vtlh_model;
@@ -250,7 +273,7 @@ int vtlh_model_train_step(vtlh_model* m, const void* d_x, int ndim, const int* x
         m->rms->update();
       else
         throw Error(VTLB_ESTATE, "train_step: no optimizer configured");
-    } else if (m->s->nranks > 1) {
+    } else if (m->s->comm_on) {
       m->s->check(vtlb_comm_wait(m->s->ctx));
     }
     if (h_loss) l->value.to_array(h_loss);

@@ -524,6 +524,7 @@ VTLB_API int vtlb_quant_rows_i8(vtlb_ctx* ctx, const void* d_A, int M, int K, vo
   if (M == 0) return VTLB_OK;
   if (!d_A || !d_Q || !d_scale) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: null pointer");
   if (!vtlb_aligned16(d_Q)) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_quant_rows_i8: Q not 16-byte aligned");
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_ELEMENTWISE);
   const int ldq = vtlb_i8_ld(K);
   if ((K & 3) == 0 && K <= 8192 && vtlb_aligned16(d_A)) {  // register-resident rows
     const float* A = (const float*)d_A;

@@ -37,6 +37,9 @@ def load() -> C.CDLL:
         protos = {
             "vtlh_session_create": [i, C.POINTER(vp)], "vtlh_session_destroy": [vp],
             "vtlh_session_comm_init": [vp, i, i, vp],
+            "vtlh_session_set_seed": [vp, C.c_ulonglong],
+            "vtlh_compute_fans": [i, ip, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)],
+            "vtlh_variance_scaled": [vp, i, ip, d, i, i, C.c_ulonglong, vp],
             "vtlh_model_create": [vp, C.POINTER(vp)], "vtlh_model_destroy": [vp],
             "vtlh_model_input": [vp, i, ip], "vtlh_model_linear": [vp, i], "vtlh_model_relu": [vp],
             "vtlh_model_flatten": [vp], "vtlh_model_conv2d": [vp] + [i] * 8,
@@ -81,6 +84,18 @@ def _shape(shape):
     return len(shape), arr
 
 
+FAN_AVG, FAN_IN, FAN_OUT = 0, 1, 2   # internal.FanMode (nn/internal/init.v:7-12)
+UNIFORM, NORMAL = 0, 1               # internal.Distribution (:14-18)
+
+
+def compute_fans(shape):
+    """internal.compute_fans as written (nn/internal/init.v:21-33): (shape[0]*prod(shape[1:]),
+    shape[1]*prod(shape[1:]))."""
+    f0, f1 = C.c_longlong(0), C.c_longlong(0)
+    _ck(load().vtlh_compute_fans(*_shape(shape), C.byref(f0), C.byref(f1)))
+    return f0.value, f1.value
+
+
 class Session:
     """autograd_cuda.DeviceSession: owns the device context of one GPU."""
 
@@ -98,6 +113,23 @@ class Session:
 
     def comm_init(self, nranks: int, rank: int, uid: bytes):
         _ck(self.lib.vtlh_session_comm_init(self.h, nranks, rank, C.c_char_p(uid)))
+
+    def set_seed(self, seed: int):
+        """Seed of the Kaiming-normal draws of the layers built after this call."""
+        _ck(self.lib.vtlh_session_set_seed(self.h, int(seed)))
+
+    def variance_scaled(self, shape, scale, fan_mode, distribution, seed):
+        """internal.variance_scaled (nn/internal/init.v:36-60) -> host array."""
+        out = np.empty(shape, np.float32)
+        _ck(self.lib.vtlh_variance_scaled(self.h, *_shape(shape), float(scale), int(fan_mode), int(distribution),
+                                          int(seed), out.ctypes.data))
+        return out
+
+    def kaiming_uniform(self, shape, seed):
+        return self.variance_scaled(shape, 2.0, FAN_IN, UNIFORM, seed)
+
+    def kaiming_normal(self, shape, seed):
+        return self.variance_scaled(shape, 2.0, FAN_IN, NORMAL, seed)
 
     def matmul_mse_backprop(self, d_A, M, K, d_B, N, d_T):
         """Variable.matmul + MSE loss + backprop on a fresh tape -> (loss, C, dA, dB) on the host."""
