@@ -617,6 +617,11 @@ def main():
         args.warmup = defaults[args.workload][1] if args.impl == "ours" else 1
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
+    # stdout carries exactly one JSON line: libraries that print to file descriptor 1 (NCCL prints its
+    # version there) are sent to stderr for the length of the run, the line goes to the real stdout
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     ranks = Ranks(args.gpus)
     if args.impl == "reference" and ranks.rank == 0:
         use_all_host_threads()
@@ -652,6 +657,8 @@ def main():
         else:
             out = bench_train.run(args, ranks, ClockSampler, peaks, cuda_sync)
     ranks.close()
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     if out is not None:
         print(json.dumps(out), flush=True)
 

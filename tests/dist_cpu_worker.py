@@ -82,6 +82,33 @@ def case_dp_gradients():
     dist.destroy_process_group()
 
 
+def case_dp_accumulate():
+    """Two backprops before an update, data-parallel: every backprop's bucket is all-reduced and the
+    reduced gradients are then added on each rank (the host mirror orders that add after the
+    collective).  Sum of reduced == reduced sum == twice the full-batch gradient, on every rank."""
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    wl = [bench_train.Workload("mlp_c1", world, r) for r in range(world)]
+    me = wl[rank]
+    X, T = me.batch()
+    _, _, dWs, dbs, _ = me.oracle_model(blas=False).grads(X, T)
+    acc = None
+    for _ in range(2):  # backprop, all-reduce, accumulate
+        red = [all_reduce_np(g.copy(), dist.ReduceOp.SUM) for g in dWs + dbs]
+        acc = red if acc is None else [a + r for a, r in zip(acc, red)]
+    order = [wl[r].batch() for r in range(world)]
+    Xf, Tf = np.concatenate([o[0] for o in order]), np.concatenate([o[1] for o in order])
+    _, _, fdWs, fdbs, _ = me.oracle_model(blas=False).grads(Xf, Tf)
+    for a, f in zip(acc, fdWs + fdbs):
+        assert np.abs(a - 2.0 * f).max() <= 2e-5 * max(1.0, float(np.abs(f).max()))
+    # and the replicas hold the same accumulated gradient bit for bit
+    for a in acc:
+        other = [None, None]
+        dist.all_gather_object(other, a.tobytes())
+        assert other[0] == other[1]
+    dist.destroy_process_group()
+
+
 def case_int8_column_shards():
     """Column-sharded INT8 layers with a max all-reduce of the row maxima and an all-gather of
     the codes give the unsharded result bit for bit."""
@@ -118,6 +145,6 @@ def case_int8_column_shards():
 
 
 if __name__ == "__main__":
-    {"plumbing": case_plumbing, "dp_gradients": case_dp_gradients,
+    {"plumbing": case_plumbing, "dp_gradients": case_dp_gradients, "dp_accumulate": case_dp_accumulate,
      "int8_column_shards": case_int8_column_shards}[sys.argv[1]]()
     print(f"rank {os.environ.get('RANK')} ok")

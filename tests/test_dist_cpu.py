@@ -8,7 +8,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("case,port", [("plumbing", 29601), ("dp_gradients", 29602),
+@pytest.mark.parametrize("case,port", [("plumbing", 29601), ("dp_gradients", 29602), ("dp_accumulate", 29604),
                                        ("int8_column_shards", 29603)])
 def test_two_cpu_ranks(case, port):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
