@@ -153,6 +153,48 @@ int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X, const v
                         void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N,
                         int K);
 
+/* ---- the same two calls, with the operand planes handed from producer to consumer -----
+ * The f32 products run as three TF32 MMAs on hi/lo planes of their operands (x = hi + lo).
+ * vtlb_linear_fwd_f32 / _bwd_f32 write those planes in a pass of their own before every
+ * product; in a deep network the same activation and gradient matrices are split again and
+ * again (each is an operand of up to three products).  Here the GEMM that PRODUCES a matrix
+ * also leaves its planes, from its epilogue, in the two layouts the consuming products read:
+ *   "rows" planes of a matrix T[R,C]:  hi, lo as [R, vtlb_plane_ld(C)]   (T as the K-major operand)
+ *   "cols" planes:                     hi, lo as [C, vtlb_plane_ld(R)]   (T transposed)
+ * Each vtlb_planes names two caller-allocated f32 arrays of that size (16-byte aligned; the
+ * padding columns are never read).  Every planes argument may be NULL: an input that is NULL is
+ * split by the call as before, an output that is NULL is not produced.  Results are the same bit
+ * for bit with or without planes.  No counterpart in the reference (its products run in f64 on
+ * the host BLAS, la/la.v:38-55).
+ *
+ * forward:  x_rows = planes of X [M,K] (in); y_rows / y_cols = planes of Y [M,N] and of Y
+ *           transposed (out; of the activated output when relu != 0).
+ * backward: g_rows / g_cols = planes of G [M,N] and G transposed, x_cols = planes of X
+ *           transposed (in).  d_relu_mask_src (the pre-activation [M,K] cached by the ReLU below
+ *           this layer, nn/gates/activation/relu.v:21-25) applies that ReLU's backward to dX on
+ *           the way out: dX = src < 0 ? 0 : dX.  dx_rows / dx_cols = planes of the (masked) dX
+ *           and its transpose (out): the G planes of the layer below.
+ * vtlb_f32_planes_worthwhile: 0 for products small enough to run on the CUDA-core route, which
+ * reads no planes (callers then skip allocating them).  vtlb_split_planes_f32 writes the planes
+ * of a matrix nobody produced through these calls (the network input, the loss gradient). */
+typedef struct vtlb_planes {
+  void* hi;
+  void* lo;
+} vtlb_planes;
+int vtlb_plane_ld(int kdim);
+int vtlb_f32_planes_worthwhile(vtlb_ctx* ctx, int M, int N, int K);
+int vtlb_split_planes_f32(vtlb_ctx* ctx, const void* d_src, int R, int C, const vtlb_planes* rows_or_null,
+                          const vtlb_planes* cols_or_null);
+int vtlb_linear_fwd_f32_planes(vtlb_ctx* ctx, const void* d_X, const void* d_W, const void* d_b_or_null,
+                               void* d_Y, int M, int N, int K, int relu, void* d_pre_or_null,
+                               const vtlb_planes* x_rows_or_null, const vtlb_planes* y_rows_or_null,
+                               const vtlb_planes* y_cols_or_null);
+int vtlb_linear_bwd_f32_planes(vtlb_ctx* ctx, const void* d_G, const void* d_X, const void* d_W,
+                               void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N,
+                               int K, const vtlb_planes* g_rows_or_null, const vtlb_planes* g_cols_or_null,
+                               const vtlb_planes* x_cols_or_null, const void* d_relu_mask_src_or_null,
+                               const vtlb_planes* dx_rows_or_null, const vtlb_planes* dx_cols_or_null);
+
 /* db[N] = column sums of G[M,N] (the bias gradient of vtlb_linear_bwd_f32) for callers
  * that cannot let the library allocate device memory: a host that has already given all of
  * HBM to its own pools, or a loop whose latency budget an allocation's implicit

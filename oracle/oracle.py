@@ -307,6 +307,21 @@ def adamw_step_f32_as_written(grad, theta, m, v, beta1, beta2, lr_t, eps, wd):
     return theta, m, v
 
 
+# ---------------------------------------------------------------- TF32 operand split of the device GEMMs
+def tf32_rna(x):
+    """cvt.rna.tf32.f32: round an f32 to 10 mantissa bits, to nearest with ties away from zero
+    (finite inputs).  Not a reference function: the device products split every operand into
+    hi = tf32(x), lo = tf32(x - hi), and the tests check the planes a product leaves for the next."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((b + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+def tf32_split(x):
+    x = np.ascontiguousarray(x, np.float32)
+    hi = tf32_rna(x)
+    return hi, tf32_rna((x - hi).astype(np.float32))
+
+
 # ---------------------------------------------------------------- initialisers (nn/internal/init.v)
 def compute_fans(shape):
     """compute_fans as written (nn/internal/init.v:21-33): the product runs over shape[1..], so

@@ -131,3 +131,38 @@ def test_config1_one_step_weights(orc):
             assert sure.mean() > 0.5  # the bound is checked on the bulk of the weights, not a remnant
         m.close()
     s.close()
+
+
+def test_plane_passing_changes_no_bit():
+    """The host mirror's large-layer path (operand planes handed from the producing product to the
+    consuming ones, ReLU backward folded into the gradient product) against the plain path in which
+    every product splits its own operands: losses, gradients, parameters and moments identical."""
+    rng = np.random.default_rng(31)
+    dims, relu_after = [128, 256, 192, 64], [True, True, False]
+    params = []
+    for i in range(3):
+        params += [kaiming_uniform(rng, dims[i + 1], dims[i]), (rng.standard_normal(dims[i + 1]) * 0.1).astype(np.float32)]
+    X = rng.standard_normal((320, 128)).astype(np.float32)
+    T = rng.standard_normal((320, 64)).astype(np.float32)
+    results = []
+    for fuse_relu in (True, False):
+        for on in (True, False):
+            s = make_session(False)
+            s.set_pass_planes(on)
+            s.dev.set_small_gemm_limit(0.0)  # all products large enough for the tensor-core path
+            m = build(s, dims, relu_after, params, "adamw")
+            m.set_fuse_relu(fuse_relu)
+            dX, dT = s.dev.to_device(X), s.dev.to_device(T)
+            loss0 = m.train_step(dX, X.shape, dT, T.shape, update=False)
+            grads = [m.get_grad(i) for i in range(6)] + [m.input_grad(X.shape)]
+            m.zero_grad()
+            losses = [loss0] + [m.train_step(dX, X.shape, dT, T.shape) for _ in range(3)]
+            results.append((losses, grads, [m.get_param(i) for i in range(6)]))
+            assert s.dev.check_status() == 0
+            m.close()
+            s.close()
+    base = results[-1]
+    for losses, grads, ps in results[:-1]:
+        assert losses == base[0]
+        for a, b in zip(grads + ps, base[1] + base[2]):
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))

@@ -98,3 +98,84 @@ def test_gemm_f32_large_against_blas(dev, orc):
     ref = orc.matmul_f32_blas(X, W, tb=True)
     err = np.abs(dY.numpy() - ref).max()
     assert err <= tol(K, X, W), f"{err} vs {tol(K, X, W)}"
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (640, 256, 1024), (200, 100, 36), (130, 102, 38)])
+def test_linear_planes_handed_from_producer_to_consumer(dev, orc, M, N, K):
+    """vtlb_linear_fwd_f32_planes / _bwd_f32_planes: the planes a product leaves are the TF32 split of
+    its stored result (rows and transposed), results are the same bit for bit with and without planes,
+    and the ReLU backward applied in the dX product equals vtlb_relu_bwd_f32 on the unmasked dX.
+    The last shape (row pitches that are no multiple of 16 bytes, so no TMA stores) takes the route
+    with separate passes."""
+    dev.set_small_gemm_limit(0.0)  # every product on the tensor-core path
+    try:
+        rng = np.random.default_rng(M + N + K)
+        X = rng.standard_normal((M, K)).astype(np.float32)
+        W = (rng.standard_normal((N, K)) * 0.1).astype(np.float32)
+        b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        G = rng.standard_normal((M, N)).astype(np.float32)
+        Pre = rng.standard_normal((M, K)).astype(np.float32)   # pre-activation of the layer below
+        dX_, dW_, db_, dG_, dPre = (dev.to_device(a) for a in (X, W, b, G, Pre))
+        # plain calls
+        Y0, pre0 = dev.zeros((M, N)), dev.zeros((M, N))
+        dev.linear_fwd_f32(dX_, dW_, db_, Y0, M, N, K, relu=True, pre=pre0)
+        gx0, gw0, gb0 = dev.zeros((M, K)), dev.zeros((N, K)), dev.zeros(N)
+        dev.linear_bwd_f32(dG_, dX_, dW_, gx0, gw0, gb0, M, N, K)
+        masked0 = dev.zeros((M, K))
+        dev.relu_bwd_f32(gx0, dPre, masked0, M * K)
+        # forward with planes in and out
+        x_rows, x_cols = dev.planes(M, K), dev.planes(K, M)
+        dev.split_planes_f32(dX_, M, K, rows=x_rows, cols=x_cols)
+        hi, lo = orc.tf32_split(X)
+        assert np.array_equal(x_rows.numpy()[0], hi) and np.array_equal(x_rows.numpy()[1], lo)
+        assert np.array_equal(x_cols.numpy()[0], hi.T) and np.array_equal(x_cols.numpy()[1], lo.T)
+        Y1, pre1 = dev.zeros((M, N)), dev.zeros((M, N))
+        y_rows, y_cols = dev.planes(M, N), dev.planes(N, M)
+        dev.linear_fwd_f32_planes(dX_, dW_, db_, Y1, M, N, K, relu=True, pre=pre1, x_rows=x_rows, y_rows=y_rows,
+                                  y_cols=y_cols)
+        assert np.array_equal(Y1.numpy().view(np.uint32), Y0.numpy().view(np.uint32))
+        assert np.array_equal(pre1.numpy().view(np.uint32), pre0.numpy().view(np.uint32))
+        hi, lo = orc.tf32_split(Y1.numpy())
+        assert np.array_equal(y_rows.numpy()[0], hi) and np.array_equal(y_rows.numpy()[1], lo)
+        assert np.array_equal(y_cols.numpy()[0], hi.T) and np.array_equal(y_cols.numpy()[1], lo.T)
+        # backward with planes in, mask and planes out
+        g_rows, g_cols = dev.planes(M, N), dev.planes(N, M)
+        dev.split_planes_f32(dG_, M, N, rows=g_rows, cols=g_cols)
+        gx1, gw1, gb1 = dev.zeros((M, K)), dev.zeros((N, K)), dev.zeros(N)
+        dx_rows, dx_cols = dev.planes(M, K), dev.planes(K, M)
+        dev.linear_bwd_f32_planes(dG_, dX_, dW_, gx1, gw1, gb1, M, N, K, g_rows=g_rows, g_cols=g_cols, x_cols=x_cols,
+                                  relu_mask_src=dPre, dx_rows=dx_rows, dx_cols=dx_cols)
+        assert dev.check_status() == 0
+        assert np.array_equal(gw1.numpy().view(np.uint32), gw0.numpy().view(np.uint32))
+        assert np.array_equal(gb1.numpy().view(np.uint32), gb0.numpy().view(np.uint32))
+        assert np.array_equal(gx1.numpy().view(np.uint32), masked0.numpy().view(np.uint32))
+        hi, lo = orc.tf32_split(gx1.numpy())
+        assert np.array_equal(dx_rows.numpy()[0], hi) and np.array_equal(dx_rows.numpy()[1], lo)
+        assert np.array_equal(dx_cols.numpy()[0], hi.T) and np.array_equal(dx_cols.numpy()[1], lo.T)
+        # mask without planes, planes without mask
+        gx2 = dev.zeros((M, K))
+        dev.linear_bwd_f32_planes(dG_, dX_, dW_, gx2, None, None, M, N, K, relu_mask_src=dPre)
+        assert np.array_equal(gx2.numpy().view(np.uint32), masked0.numpy().view(np.uint32))
+        gx3 = dev.zeros((M, K))
+        dev.linear_bwd_f32_planes(dG_, dX_, dW_, gx3, None, None, M, N, K, dx_rows=dx_rows)
+        assert np.array_equal(gx3.numpy().view(np.uint32), gx0.numpy().view(np.uint32))
+        assert np.array_equal(dx_rows.numpy()[0], orc.tf32_split(gx0.numpy())[0])
+    finally:
+        dev.set_small_gemm_limit(1.4e8)
+
+
+def test_linear_planes_argument_errors(dev):
+    from vtl_b200.capi import VtlbError, EINVAL
+    x, w, y = dev.zeros((8, 8)), dev.zeros((8, 8)), dev.zeros((8, 8))
+    pl = dev.planes(8, 8)
+    with pytest.raises(VtlbError) as e:   # a mask or dX planes make no sense without dX
+        dev.linear_bwd_f32_planes(y, x, w, None, y, None, 8, 8, 8, relu_mask_src=x)
+    assert e.value.code == EINVAL
+    with pytest.raises(VtlbError):
+        dev.linear_bwd_f32_planes(y, x, w, None, y, None, 8, 8, 8, dx_rows=pl)
+    pl.c.lo = None
+    with pytest.raises(VtlbError):
+        dev.linear_fwd_f32_planes(x, w, None, y, 8, 8, 8, x_rows=pl)
+    assert dev.plane_ld(5) == 8 and dev.plane_ld(4096) == 4096
+    dev.set_small_gemm_limit(1.4e8)  # small products run on CUDA cores, which read no planes
+    assert not dev.f32_planes_worthwhile(64, 10, 256) and dev.f32_planes_worthwhile(8192, 4096, 4096)

@@ -56,6 +56,10 @@ _PROTOS = {
     "vtlb_set_small_gemm_limit": [_vp, _d],
     "vtlb_gemm_f32": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i],
     "vtlb_linear_fwd_f32": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "vtlb_plane_ld": [_i], "vtlb_f32_planes_worthwhile": [_vp, _i, _i, _i],
+    "vtlb_split_planes_f32": [_vp, _vp, _i, _i, _vp, _vp],
+    "vtlb_linear_fwd_f32_planes": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "vtlb_linear_bwd_f32_planes": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "vtlb_linear_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i],
     "vtlb_bias_grad_f32_noalloc": [_vp, _vp, _i, _i, _vp],
     "vtlb_relu_fwd_f32": [_vp, _vp, _vp, _sz],
@@ -137,6 +141,28 @@ def device_count() -> int:
     n = C.c_int(0)
     load().vtlb_device_count(C.byref(n))
     return n.value
+
+
+class _VtlbPlanes(C.Structure):
+    _fields_ = [("hi", C.c_void_p), ("lo", C.c_void_p)]
+
+
+class Planes:
+    """TF32 hi / lo planes [rows, plane_ld(kdim)] of a matrix (vtlb_planes)."""
+
+    def __init__(self, dev: "Device", rows: int, kdim: int):
+        self.rows, self.kdim, self.ld = rows, kdim, dev.plane_ld(kdim)
+        self.hi = dev.empty((rows, self.ld))
+        self.lo = dev.empty((rows, self.ld))
+        self.c = _VtlbPlanes(self.hi.ptr, self.lo.ptr)
+
+    def numpy(self):
+        """(hi, lo) without the padding columns."""
+        return self.hi.numpy()[:, :self.kdim], self.lo.numpy()[:, :self.kdim]
+
+
+def _pl(p):
+    return C.byref(p.c) if p is not None else None
 
 
 class DBuf:
@@ -309,6 +335,30 @@ class Device:
     def linear_bwd_f32(self, G, X, W, dX, dW, db, M, N, K):
         self._ck(self.lib.vtlb_linear_bwd_f32(self.h, _ptr(G), _ptr(X), _ptr(W), _ptr(dX),
                                               _ptr(dW), _ptr(db), M, N, K))
+
+    # -- TF32 operand planes handed from producer to consumer (include/vtlb.h, vtlb_planes)
+    def plane_ld(self, kdim: int) -> int:
+        return int(self.lib.vtlb_plane_ld(int(kdim)))
+
+    def planes(self, rows: int, kdim: int) -> "Planes":
+        """Two uninitialised [rows, plane_ld(kdim)] f32 arrays (hi, lo) and their vtlb_planes struct."""
+        return Planes(self, rows, kdim)
+
+    def f32_planes_worthwhile(self, M, N, K) -> bool:
+        return bool(self.lib.vtlb_f32_planes_worthwhile(self.h, M, N, K))
+
+    def split_planes_f32(self, src, R, Ccols, rows=None, cols=None):
+        self._ck(self.lib.vtlb_split_planes_f32(self.h, _ptr(src), R, Ccols, _pl(rows), _pl(cols)))
+
+    def linear_fwd_f32_planes(self, X, W, b, Y, M, N, K, relu=False, pre=None, x_rows=None, y_rows=None, y_cols=None):
+        self._ck(self.lib.vtlb_linear_fwd_f32_planes(self.h, _ptr(X), _ptr(W), _ptr(b), _ptr(Y), M, N, K, int(relu),
+                                                     _ptr(pre), _pl(x_rows), _pl(y_rows), _pl(y_cols)))
+
+    def linear_bwd_f32_planes(self, G, X, W, dX, dW, db, M, N, K, g_rows=None, g_cols=None, x_cols=None,
+                              relu_mask_src=None, dx_rows=None, dx_cols=None):
+        self._ck(self.lib.vtlb_linear_bwd_f32_planes(self.h, _ptr(G), _ptr(X), _ptr(W), _ptr(dX), _ptr(dW), _ptr(db),
+                                                     M, N, K, _pl(g_rows), _pl(g_cols), _pl(x_cols),
+                                                     _ptr(relu_mask_src), _pl(dx_rows), _pl(dx_cols)))
 
     def bias_grad_f32_noalloc(self, G, M, N, db):
         self._ck(self.lib.vtlb_bias_grad_f32_noalloc(self.h, _ptr(G), M, N, _ptr(db)))

@@ -173,21 +173,76 @@ namespace {
 
 using f32::split_operand;
 
+// Optional extras of a product (all null / zero by default):
+//   a_planes / b_planes   the operand already split into K-major TF32 planes [rows, ld(K)] by whoever
+//                         produced it (then no split pass runs for it)
+//   mask                  ReLU backward on the result: C = mask < 0 ? 0 : C, mask laid out like C
+//   out_rows / out_cols   receive the TF32 planes of C ([M, ld(N)]) and of C transposed ([N, ld(M)])
+// The tensor-core kernels do mask and planes in their epilogue; where they cannot (CUDA-core route,
+// unaligned pointers) the same results come from separate passes over the stored C.
+struct GemmExtras {
+  const vtlb_planes* a_planes = nullptr;
+  const vtlb_planes* b_planes = nullptr;
+  const float* mask = nullptr;
+  const vtlb_planes* out_rows = nullptr;
+  const vtlb_planes* out_cols = nullptr;
+};
+
+int relu_mask_inplace(vtlb_ctx* ctx, float* C, const float* mask, size_t n) {
+  return vtlb_relu_bwd_f32(ctx, C, mask, C, n);
+}
+
 int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
-                  const float* B, float* C, const float* bias, int relu, float* pre) {
+                  const float* B, float* C, const float* bias, int relu, float* pre,
+                  const GemmExtras& ex = GemmExtras()) {
   if (!vtlb_aligned16(C) || (pre && !vtlb_aligned16(pre)) || (bias && !vtlb_aligned16(bias)))
     return vtlb_fail(ctx, VTLB_EINVAL, "f32 GEMM: output and bias pointers must be 16-byte aligned");
-  if (2.0 * M * N * K <= ctx->small_gemm_flops)  // launch-latency-bound sizes: CUDA cores, no split passes
-    return f32::sgemm_small(ctx, transA, transB, M, N, K, A, B, C, bias, relu, pre);
-  f32::Planes p;
-  int rc = f32::alloc_planes(ctx, M, N, K, 0, &p);
-  if (rc) return rc;
-  // op(A) is [M,K]: stored [K,M] when transA.  The B operand of the kernel is
-  // [N,K] K-major: B stored [K,N] (transB == 0) must be transposed.
-  if ((rc = split_operand(ctx, A, M, K, transA != 0, p.ld, p.a_hi, p.a_lo))) return rc;
-  if ((rc = split_operand(ctx, B, N, K, transB == 0, p.ld, p.b_hi, p.b_lo))) return rc;
-  f32::EpiBiasRelu epi{C, bias, pre, N, relu};
-  return f32::launch_tf32x3(ctx, p, M, N, K, epi);
+  const int ld_rows = vtlb_plane_ld(N), ld_cols = vtlb_plane_ld(M);
+  int rc, fused = 0;
+  if (2.0 * M * N * K <= ctx->small_gemm_flops) {  // launch-latency-bound sizes: CUDA cores, no split passes
+    if ((rc = f32::sgemm_small(ctx, transA, transB, M, N, K, A, B, C, bias, relu, pre))) return rc;
+  } else {
+    f32::Planes p;
+    if ((rc = f32::alloc_planes(ctx, ex.a_planes ? 0 : M, ex.b_planes ? 0 : N, K, 0, &p))) return rc;
+    // op(A) is [M,K]: stored [K,M] when transA.  The B operand of the kernel is
+    // [N,K] K-major: B stored [K,N] (transB == 0) must be transposed.
+    if (ex.a_planes) {
+      p.a_hi = (float*)ex.a_planes->hi;
+      p.a_lo = (float*)ex.a_planes->lo;
+    } else if ((rc = split_operand(ctx, A, M, K, transA != 0, p.ld, p.a_hi, p.a_lo))) {
+      return rc;
+    }
+    if (ex.b_planes) {
+      p.b_hi = (float*)ex.b_planes->hi;
+      p.b_lo = (float*)ex.b_planes->lo;
+    } else if ((rc = split_operand(ctx, B, N, K, transB == 0, p.ld, p.b_hi, p.b_lo))) {
+      return rc;
+    }
+    f32::EpiBiasRelu epi{C, bias, pre, N, relu};
+    epi.mask = ex.mask;
+    epi.planes = (ex.out_rows ? 1 : 0) | (ex.out_cols ? 2 : 0);
+    if (ex.out_rows) {
+      epi.rows_hi = (float*)ex.out_rows->hi;
+      epi.rows_lo = (float*)ex.out_rows->lo;
+      epi.ld_rows = ld_rows;
+    }
+    if (ex.out_cols) {
+      epi.cols_hi = (float*)ex.out_cols->hi;
+      epi.cols_lo = (float*)ex.out_cols->lo;
+      epi.ld_cols = ld_cols;
+    }
+    if ((rc = f32::launch_tf32x3(ctx, p, M, N, K, epi, 1, &fused))) return rc;
+  }
+  if (ex.mask && !(fused & 2) && (rc = relu_mask_inplace(ctx, C, ex.mask, (size_t)M * N))) return rc;
+  // planes written by the epilogue are those of the masked result only when it also masked
+  const bool planes_ok = (fused & 1) && (!ex.mask || (fused & 2));
+  if (!planes_ok) {
+    if (ex.out_rows && (rc = split_operand(ctx, C, M, N, false, ld_rows, (float*)ex.out_rows->hi, (float*)ex.out_rows->lo)))
+      return rc;
+    if (ex.out_cols && (rc = split_operand(ctx, C, N, M, true, ld_cols, (float*)ex.out_cols->hi, (float*)ex.out_cols->lo)))
+      return rc;
+  }
+  return VTLB_OK;
 }
 
 int colsum(vtlb_ctx* ctx, const float* G, int M, int N, float* out) {
@@ -238,48 +293,138 @@ VTLB_API int vtlb_gemm_f32(vtlb_ctx* ctx, int transA, int transB, int M, int N, 
                        (float*)d_C, (const float*)d_bias_or_null, relu, nullptr);
 }
 
+namespace {
+
+int check_planes(vtlb_ctx* ctx, const char* fn, const char* what, const vtlb_planes* p) {
+  if (p && (!p->hi || !p->lo || !vtlb_aligned16(p->hi) || !vtlb_aligned16(p->lo)))
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: %s planes need two 16-byte-aligned arrays", fn, what);
+  return VTLB_OK;
+}
+
+int linear_fwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_X, const void* d_W, const void* d_b_or_null,
+                    void* d_Y, int M, int N, int K, int relu, void* d_pre_or_null, const vtlb_planes* x_rows,
+                    const vtlb_planes* y_rows, const vtlb_planes* y_cols) {
+  int rc = check_f32(ctx, fn, M, N, K);
+  if (rc) return rc;
+  if (M == 0 || N == 0) return VTLB_OK;
+  if (!d_X || !d_W || !d_Y) return vtlb_fail(ctx, VTLB_EINVAL, "%s: null pointer", fn);
+  if ((rc = check_planes(ctx, fn, "input", x_rows)) || (rc = check_planes(ctx, fn, "output", y_rows)) ||
+      (rc = check_planes(ctx, fn, "transposed output", y_cols)))
+    return rc;
+  GemmExtras ex;
+  ex.a_planes = x_rows;
+  ex.out_rows = y_rows;
+  ex.out_cols = y_cols;
+  return gemm_f32_impl(ctx, 0, 1, M, N, K, (const float*)d_X, (const float*)d_W, (float*)d_Y,
+                       (const float*)d_b_or_null, relu, (float*)d_pre_or_null, ex);
+}
+
+int linear_bwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_G, const void* d_X, const void* d_W,
+                    void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N, int K,
+                    const vtlb_planes* g_rows, const vtlb_planes* g_cols, const vtlb_planes* x_cols,
+                    const void* d_relu_mask_src_or_null, const vtlb_planes* dx_rows, const vtlb_planes* dx_cols) {
+  if (M <= 0 || N <= 0 || K <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "%s: bad shape M=%d N=%d K=%d", fn, M, N, K);
+  if (!d_G) return vtlb_fail(ctx, VTLB_EINVAL, "%s: null gradient", fn);
+  int rc;
+  if ((rc = check_planes(ctx, fn, "gradient", g_rows)) || (rc = check_planes(ctx, fn, "transposed gradient", g_cols)) ||
+      (rc = check_planes(ctx, fn, "transposed input", x_cols)) || (rc = check_planes(ctx, fn, "dX", dx_rows)) ||
+      (rc = check_planes(ctx, fn, "transposed dX", dx_cols)))
+    return rc;
+  if (!d_dX_or_null && (d_relu_mask_src_or_null || dx_rows || dx_cols))
+    return vtlb_fail(ctx, VTLB_EINVAL, "%s: a mask or dX planes were given without a dX output", fn);
+  if (d_dX_or_null) {  // dX[M,K] = G[M,N] . W[N,K]   (then, optionally, ReLU backward of the layer below)
+    if (!d_W) return vtlb_fail(ctx, VTLB_EINVAL, "%s: dX needs W", fn);
+    GemmExtras ex;
+    ex.a_planes = g_rows;
+    ex.mask = (const float*)d_relu_mask_src_or_null;
+    ex.out_rows = dx_rows;
+    ex.out_cols = dx_cols;
+    if ((rc = gemm_f32_impl(ctx, 0, 0, M, K, N, (const float*)d_G, (const float*)d_W, (float*)d_dX_or_null, nullptr,
+                            0, nullptr, ex)))
+      return rc;
+  }
+  bool db_done = false;
+  if (d_dW_or_null) {  // dW[N,K] = G^T[N,M] . X[M,K]
+    if (!d_X) return vtlb_fail(ctx, VTLB_EINVAL, "%s: dW needs X", fn);
+    if (d_db_or_null && 2.0 * M * N * K <= ctx->small_gemm_flops && vtlb_aligned16(d_dW_or_null)) {
+      // small product: the CUDA-core kernel sums the rows of G^T (= the bias gradient) on the way
+      if ((rc = f32::sgemm_small(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X, (float*)d_dW_or_null,
+                                 nullptr, 0, nullptr, (float*)d_db_or_null, &db_done)))
+        return rc;
+    } else {
+      GemmExtras ex;
+      ex.a_planes = g_cols;
+      ex.b_planes = x_cols;
+      if ((rc = gemm_f32_impl(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X, (float*)d_dW_or_null,
+                              nullptr, 0, nullptr, ex)))
+        return rc;
+    }
+  }
+  if (d_db_or_null && !db_done) {
+    if ((rc = colsum(ctx, (const float*)d_G, M, N, (float*)d_db_or_null))) return rc;
+  }
+  return VTLB_OK;
+}
+
+}  // namespace
+
+VTLB_API int vtlb_plane_ld(int kdim) { return kdim <= 0 ? 0 : (int)vtlb_round_up((size_t)kdim, 4); }
+
+VTLB_API int vtlb_f32_planes_worthwhile(vtlb_ctx* ctx, int M, int N, int K) {
+  // products the CUDA-core route takes never read operand planes
+  return ctx && M > 0 && N > 0 && K > 0 && 2.0 * M * N * K > ctx->small_gemm_flops;
+}
+
 VTLB_API int vtlb_linear_fwd_f32(vtlb_ctx* ctx, const void* d_X, const void* d_W,
                                  const void* d_b_or_null, void* d_Y, int M, int N, int K, int relu,
                                  void* d_pre_or_null) {
   VTLB_ENTER(ctx);
-  int rc = check_f32(ctx, "vtlb_linear_fwd_f32", M, N, K);
-  if (rc) return rc;
-  if (M == 0 || N == 0) return VTLB_OK;
-  if (!d_X || !d_W || !d_Y) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_fwd_f32: null pointer");
-  return gemm_f32_impl(ctx, 0, 1, M, N, K, (const float*)d_X, (const float*)d_W, (float*)d_Y,
-                       (const float*)d_b_or_null, relu, (float*)d_pre_or_null);
+  return linear_fwd_impl(ctx, "vtlb_linear_fwd_f32", d_X, d_W, d_b_or_null, d_Y, M, N, K, relu, d_pre_or_null,
+                         nullptr, nullptr, nullptr);
+}
+
+VTLB_API int vtlb_linear_fwd_f32_planes(vtlb_ctx* ctx, const void* d_X, const void* d_W, const void* d_b_or_null,
+                                        void* d_Y, int M, int N, int K, int relu, void* d_pre_or_null,
+                                        const vtlb_planes* x_rows_or_null, const vtlb_planes* y_rows_or_null,
+                                        const vtlb_planes* y_cols_or_null) {
+  VTLB_ENTER(ctx);
+  return linear_fwd_impl(ctx, "vtlb_linear_fwd_f32_planes", d_X, d_W, d_b_or_null, d_Y, M, N, K, relu,
+                         d_pre_or_null, x_rows_or_null, y_rows_or_null, y_cols_or_null);
 }
 
 VTLB_API int vtlb_linear_bwd_f32(vtlb_ctx* ctx, const void* d_G, const void* d_X, const void* d_W,
                                  void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M,
                                  int N, int K) {
   VTLB_ENTER(ctx);
-  if (M <= 0 || N <= 0 || K <= 0)
-    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_bwd_f32: bad shape M=%d N=%d K=%d", M, N, K);
-  if (!d_G) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_bwd_f32: null gradient");
+  return linear_bwd_impl(ctx, "vtlb_linear_bwd_f32", d_G, d_X, d_W, d_dX_or_null, d_dW_or_null, d_db_or_null, M, N,
+                         K, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+}
+
+VTLB_API int vtlb_linear_bwd_f32_planes(vtlb_ctx* ctx, const void* d_G, const void* d_X, const void* d_W,
+                                        void* d_dX_or_null, void* d_dW_or_null, void* d_db_or_null, int M, int N,
+                                        int K, const vtlb_planes* g_rows_or_null, const vtlb_planes* g_cols_or_null,
+                                        const vtlb_planes* x_cols_or_null, const void* d_relu_mask_src_or_null,
+                                        const vtlb_planes* dx_rows_or_null, const vtlb_planes* dx_cols_or_null) {
+  VTLB_ENTER(ctx);
+  return linear_bwd_impl(ctx, "vtlb_linear_bwd_f32_planes", d_G, d_X, d_W, d_dX_or_null, d_dW_or_null, d_db_or_null,
+                         M, N, K, g_rows_or_null, g_cols_or_null, x_cols_or_null, d_relu_mask_src_or_null,
+                         dx_rows_or_null, dx_cols_or_null);
+}
+
+VTLB_API int vtlb_split_planes_f32(vtlb_ctx* ctx, const void* d_src, int R, int C, const vtlb_planes* rows_or_null,
+                                   const vtlb_planes* cols_or_null) {
+  VTLB_ENTER(ctx);
+  if (R <= 0 || C <= 0 || !d_src) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_split_planes_f32: bad arguments");
   int rc;
-  if (d_dX_or_null) {  // dX[M,K] = G[M,N] . W[N,K]
-    if (!d_W) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_bwd_f32: dX needs W");
-    if ((rc = gemm_f32_impl(ctx, 0, 0, M, K, N, (const float*)d_G, (const float*)d_W,
-                            (float*)d_dX_or_null, nullptr, 0, nullptr)))
-      return rc;
-  }
-  bool db_done = false;
-  if (d_dW_or_null) {  // dW[N,K] = G^T[N,M] . X[M,K]
-    if (!d_X) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_linear_bwd_f32: dW needs X");
-    if (d_db_or_null && 2.0 * M * N * K <= ctx->small_gemm_flops && vtlb_aligned16(d_dW_or_null)) {
-      // small product: the CUDA-core kernel sums the rows of G^T (= the bias gradient) on the way
-      if ((rc = f32::sgemm_small(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X, (float*)d_dW_or_null,
-                                 nullptr, 0, nullptr, (float*)d_db_or_null, &db_done)))
-        return rc;
-    } else if ((rc = gemm_f32_impl(ctx, 1, 0, N, K, M, (const float*)d_G, (const float*)d_X,
-                                   (float*)d_dW_or_null, nullptr, 0, nullptr))) {
-      return rc;
-    }
-  }
-  if (d_db_or_null && !db_done) {
-    if ((rc = colsum(ctx, (const float*)d_G, M, N, (float*)d_db_or_null))) return rc;
-  }
+  if ((rc = check_planes(ctx, "vtlb_split_planes_f32", "row", rows_or_null)) ||
+      (rc = check_planes(ctx, "vtlb_split_planes_f32", "column", cols_or_null)))
+    return rc;
+  if (rows_or_null && (rc = split_operand(ctx, (const float*)d_src, R, C, false, vtlb_plane_ld(C),
+                                          (float*)rows_or_null->hi, (float*)rows_or_null->lo)))
+    return rc;
+  if (cols_or_null && (rc = split_operand(ctx, (const float*)d_src, C, R, true, vtlb_plane_ld(R),
+                                          (float*)cols_or_null->hi, (float*)cols_or_null->lo)))
+    return rc;
   return VTLB_OK;
 }
 

@@ -65,8 +65,12 @@ inline int effective_splits(int K, int want) {
 }
 
 // D[M,N] = A[M,K] . B[N,K]^T on the planes, epilogue functor `epi`.
+// `fused` (optional) receives bit 0 = the epilogue writes the requested operand planes of the result,
+// bit 1 = it applies the ReLU-backward mask; what it does not do, the caller does in separate passes.
 template <class Epi>
-int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, int splits = 1) {
+int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, int splits = 1,
+                  int* fused = nullptr) {
+  if (fused) *fused = 0;
   gemm::TmapSet tm;
   if constexpr (Epi::kTmaCapable) {
     // outputs with a 16-byte-multiple row pitch go out through TMA stores
@@ -79,6 +83,22 @@ int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, 
       if (epi.pre &&
           (rc0 = gemm::encode_tmap_2d(ctx, &tm.out[1], true, epi.pre, N, M, (uint64_t)epi.ldy * 4, 32, 32)))
         return rc0;
+    }
+    if constexpr (gemm::EpiHasPlanes<Epi>::value) {
+      // planes of the result leave through TMA stores too; without that path the caller splits
+      // the stored result in a pass of its own
+      if (!epi.tma || N % 4 != 0 || (epi.mask && !vtlb_aligned16(epi.mask))) {
+        epi.planes = 0;
+        epi.mask_fused = 0;
+      } else {
+        epi.mask_fused = epi.mask != nullptr;
+      }
+      if (epi.planes & 1) {
+        int rc0 = gemm::encode_tmap_2d(ctx, &tm.out[2], true, epi.rows_hi, N, M, (uint64_t)epi.ld_rows * 4, 32, 32);
+        if (!rc0) rc0 = gemm::encode_tmap_2d(ctx, &tm.out[3], true, epi.rows_lo, N, M, (uint64_t)epi.ld_rows * 4, 32, 32);
+        if (rc0) return rc0;
+      }
+      if (fused) *fused = (epi.planes ? 1 : 0) | (epi.mask_fused ? 2 : 0);
     }
   }
   int bn = bn_override();
@@ -114,15 +134,57 @@ int launch_tf32x3(vtlb_ctx* ctx, const Planes& p, int M, int N, int K, Epi epi, 
 // rounded matmul result), optional store of the pre-activation, optional ReLU.
 struct EpiBiasRelu {
   static constexpr bool kTmaCapable = true;
+  static constexpr bool kPlanes = true;
   float* Y;
   const float* bias;  // may be null
   float* pre;         // may be null
   int ldy;
   int relu;
   int tma;  // store through tm.out[0] (and tm.out[1] for the pre-activation)
+  // ReLU backward on the way out (TMA path only): y = mask[row][col] < 0 ? 0 : y, mask laid out like Y
+  // (the pre-activation the layer below cached; nn/gates/activation/relu.v:21-25)
+  const float* mask;
+  int mask_fused;
+  // TF32 operand planes of the stored result (TMA path only; see gemm::epilogue_chunk):
+  // bit 0: [M, ld_rows] in Y's layout, bit 1: [N, ld_cols] of Y transposed
+  int planes;
+  float *rows_hi, *rows_lo, *cols_hi, *cols_lo;
+  int ld_rows, ld_cols;
+  // Bit j set = the mask zeroes column col0 + j of this row.  The GEMM kernels call this at the
+  // start of a tile, long before the values exist, so that the loads' latency is off the path of
+  // the stores at the tile's end; they then apply the bits and run the rest with mask_fused = 0.
+  __device__ __forceinline__ uint32_t load_mask_bits(int row, int col0, int M, int N) const {
+    uint32_t bits = 0;
+    if (mask_fused && row < M) {
+      const float* mrow = mask + (size_t)row * ldy + col0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (col0 + j < N) {
+          const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow + j));
+          bits |= (m4.x < 0.f ? 1u : 0u) << j | (m4.y < 0.f ? 2u : 0u) << j | (m4.z < 0.f ? 4u : 0u) << j |
+                  (m4.w < 0.f ? 8u : 0u) << j;
+        }
+      }
+    }
+    return bits;
+  }
   // adds the bias in registers; returns true when the pre-activation has to be stored
   // separately before activate() applies the ReLU
-  __device__ __forceinline__ bool transform(int, int col0, uint32_t (&v)[32], int, int N) const {
+  __device__ __forceinline__ bool transform(int row, int col0, uint32_t (&v)[32], int M, int N,
+                                            bool mask_applied = false) const {
+    if (mask_fused && !mask_applied && row < M) {
+      const float* mrow = mask + (size_t)row * ldy + col0;
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (col0 + j < N) {
+          const float4 m4 = __ldg(reinterpret_cast<const float4*>(mrow + j));
+          if (m4.x < 0.f) v[j] = 0u;
+          if (m4.y < 0.f) v[j + 1] = 0u;
+          if (m4.z < 0.f) v[j + 2] = 0u;
+          if (m4.w < 0.f) v[j + 3] = 0u;
+        }
+      }
+    }
     if (bias) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {

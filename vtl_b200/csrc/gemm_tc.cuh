@@ -52,7 +52,11 @@ struct Traits<KIND_TF32X3> {
 struct TmapSet {
   CUtensorMap a[2];    // [0] = A (i8) or A_hi, [1] = A_lo
   CUtensorMap b[2];
-  CUtensorMap out[2];  // output (and pre-activation output) for epilogues that store through TMA
+  // outputs of epilogues that store through TMA: [0] the result, [1] the pre-activation;
+  // [2],[3] the result's TF32 hi / lo planes in the result's own layout (epilogues that declare
+  // kPlanes: what the next product reads as an operand; the planes of the transpose are written
+  // with plain stores)
+  CUtensorMap out[4];
 };
 
 // One 32-row x 32-column staging tile (128-byte rows, 128-byte swizzle) per epilogue warp.
@@ -111,20 +115,99 @@ __device__ __forceinline__ void stage_and_store(uint32_t stg, const CUtensorMap*
   })
 }
 
+// x = hi + lo + O(2^-22 |x|), both representable in TF32 (the operand split of the 3xTF32 products).
+__device__ __forceinline__ uint32_t tf32_hi_bits(uint32_t x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(__uint_as_float(x)));
+  return r;
+}
+__device__ __forceinline__ uint32_t tf32_lo_bits(uint32_t x) {
+  const float hi = __uint_as_float(tf32_hi_bits(x));
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(__uint_as_float(x) - hi));
+  return r;
+}
+
+// The chunk's TF32 hi (LO = false) or lo plane through the staging tile and a TMA store, in the
+// chunk's own layout (box at (col0, row0) of a [rows, cols] tensor).
+template <bool LO>
+__device__ __forceinline__ void stage_and_store_plane(uint32_t stg, const CUtensorMap* tmap, int lane, int row0,
+                                                      int col0, const uint32_t (&v)[32], int M, int N) {
+  if (lane == 0) ptx::bulk_wait_read_all();
+  __syncwarp();
+  const uint32_t rowaddr = stg + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) w[e] = LO ? tf32_lo_bits(v[4 * j + e]) : tf32_hi_bits(v[4 * j + e]);
+    ptx::st_shared_v4(rowaddr + (((uint32_t)j ^ ((uint32_t)lane & 7u)) << 4), w[0], w[1], w[2], w[3]);
+  }
+  ptx::fence_proxy_async();
+  __syncwarp();
+  if (lane == 0 && row0 < M && col0 < N) {
+    ptx::tma_store_2d(tmap, col0, row0, stg);
+    ptx::bulk_commit_group();
+  }
+}
+
+// The planes of the chunk transposed, [N, ld] with the chunk's rows along the contiguous dimension:
+// lane = row, so every store instruction of the warp writes 32 consecutive words of one row of the
+// transposed plane -- whole 128-byte lines straight from the registers, no staging and no wait.
+__device__ __forceinline__ void store_planes_transposed(float* __restrict__ hi, float* __restrict__ lo, int ld,
+                                                        int row, int col0, const uint32_t (&v)[32], int M, int N) {
+  if (row >= M) return;
+  uint32_t* ph = reinterpret_cast<uint32_t*>(hi) + (size_t)col0 * ld + row;
+  uint32_t* pl = reinterpret_cast<uint32_t*>(lo) + (size_t)col0 * ld + row;
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    if (col0 + c < N) {
+      const uint32_t h = tf32_hi_bits(v[c]);
+      uint32_t l;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(__uint_as_float(v[c]) - __uint_as_float(h)));
+      ph[(size_t)c * ld] = h;
+      pl[(size_t)c * ld] = l;
+    }
+  }
+}
+
+template <class Epi>
+struct EpiHasPlanes {
+  template <class T>
+  static constexpr bool test(decltype(T::kPlanes)*) { return T::kPlanes; }
+  template <class T>
+  static constexpr bool test(...) { return false; }
+  static constexpr bool value = test<Epi>(nullptr);
+};
+
 template <class Epi>
 __device__ __forceinline__ void epilogue_chunk(const Epi& epi, const TmapSet& tm, uint32_t stg, int lane,
                                                int row0, int col0, uint32_t (&v)[32], int M, int N,
-                                               int split) {
+                                               int split, bool mask_applied = false) {
   if constexpr (Epi::kTmaCapable) {
     if (epi.tma) {
       VTLB_ETR(const long long tr_t = clock64();)
-      const bool two = epi.transform(row0 + lane, col0, v, M, N);
+      bool two;
+      if constexpr (EpiHasPlanes<Epi>::value)
+        two = epi.transform(row0 + lane, col0, v, M, N, mask_applied);
+      else
+        two = epi.transform(row0 + lane, col0, v, M, N);
       VTLB_ETR(if (threadIdx.x == 64) g_epi_trace[blockIdx.x][1] += clock64() - tr_t;)
       if (two) {  // true: v now holds the pre-activation
         stage_and_store(stg, &tm.out[1], lane, row0, col0, v, M, N);
         epi.activate(v);
       }
       stage_and_store(stg, &tm.out[0], lane, row0, col0, v, M, N);
+      if constexpr (EpiHasPlanes<Epi>::value) {
+        // operand planes of the result for the products that consume it next (what a separate
+        // split pass over the stored result would write)
+        if (epi.planes & 2)
+          store_planes_transposed(epi.cols_hi, epi.cols_lo, epi.ld_cols, row0 + lane, col0, v, M, N);
+        if (epi.planes & 1) {
+          stage_and_store_plane<false>(stg, &tm.out[2], lane, row0, col0, v, M, N);
+          stage_and_store_plane<true>(stg, &tm.out[3], lane, row0, col0, v, M, N);
+        }
+      }
       return;
     }
   }
@@ -352,6 +435,15 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
         float sum[BN / 2];
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) sum[j] = 0.0f;
+        // ReLU-backward mask of the tile's outputs, fetched now as one bit per value
+        uint32_t mask_bits[BN / 64];
+        if constexpr (EpiHasPlanes<Epi>::value) {
+#pragma unroll
+          for (int cc = 0; cc < BN / 64; ++cc) {
+            mask_bits[cc] = epi.load_mask_bits(row0 + lane, n0 + (2 * cc + half) * 32, M, N);
+            asm volatile("" ::: "memory");  // one chunk's eight loads at a time: the running sums own the registers
+          }
+        }
         for (int kb0 = kb_begin; kb0 < kb_end; kb0 += chunk_kb) {
           ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
           ok = __all_sync(0xffffffffu, ok);
@@ -380,7 +472,12 @@ gemm_tc_kernel(const __grid_constant__ TmapSet tm, const Epi epi, int M, int N, 
           uint32_t v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[cc * 32 + j]);
-          epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, split);
+          if constexpr (EpiHasPlanes<Epi>::value) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (mask_bits[cc] >> j & 1u) v[j] = 0u;
+          }
+          epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, split, true);
           __syncwarp();
         }
       }

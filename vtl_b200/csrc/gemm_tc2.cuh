@@ -472,6 +472,15 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         float sum[BN2 / 2];  // this warp's four 32-column chunks
 #pragma unroll
         for (int j = 0; j < BN2 / 2; ++j) sum[j] = 0.0f;
+        // ReLU-backward mask of the tile's outputs, fetched now as one bit per value
+        uint32_t mask_bits[BN2 / 64];
+        if constexpr (gemm::EpiHasPlanes<Epi>::value) {
+#pragma unroll
+          for (int cc = 0; cc < BN2 / 64; ++cc) {
+            mask_bits[cc] = epi.load_mask_bits(row0 + lane, n0 + (2 * cc + half) * 32, M, N);
+            asm volatile("" ::: "memory");  // one chunk's eight loads at a time: the running sums own the registers
+          }
+        }
         for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
           ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
           ok = __all_sync(0xffffffffu, ok);
@@ -497,7 +506,12 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           uint32_t v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sum[cc * 32 + j]);
-          gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, 0);
+          if constexpr (gemm::EpiHasPlanes<Epi>::value) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (mask_bits[cc] >> j & 1u) v[j] = 0u;
+          }
+          gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + (2 * cc + half) * 32, v, M, N, 0, true);
           __syncwarp();
         }
       }

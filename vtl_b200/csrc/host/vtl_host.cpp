@@ -3,12 +3,14 @@
 #include "vtl_host.hpp"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace vtl {
 
 // ---------------------------------------------------------------- session / storage
 Session::Session(int device) {
+  if (const char* e = std::getenv("VTL_PLANE_KINDS")) plane_kinds = std::atoi(e) & 3;
   int rc = vtlb_ctx_create(device, &ctx);
   if (rc != VTLB_OK) throw Error(rc, vtlb_last_error(nullptr));
 }
@@ -31,6 +33,15 @@ DeviceBuf::DeviceBuf(Session* s_, size_t bytes_) : s(s_), ptr(nullptr), bytes(by
 }
 DeviceBuf::~DeviceBuf() {
   if (ptr && owned) vtlb_free(s->ctx, ptr);
+}
+
+std::shared_ptr<PlanePair> PlanePair::make(Session* s, int rows, int kdim) {
+  auto pp = std::make_shared<PlanePair>();
+  const size_t plane = ((size_t)rows * vtlb_plane_ld(kdim) + 63) / 64 * 64;  // keeps lo 256-byte aligned
+  pp->buf = std::make_shared<DeviceBuf>(s, 2 * plane * sizeof(float));
+  pp->p.hi = pp->buf->ptr;
+  pp->p.lo = static_cast<float*>(pp->buf->ptr) + plane;
+  return pp;
 }
 
 static size_t numel(const std::vector<int>& shape) {
@@ -75,6 +86,10 @@ void Tensor::to_array(float* host) const {
 Tensor Tensor::reshape(std::vector<int> new_shape) const {
   if (numel(new_shape) != size()) throw Error(VTLB_EINVAL, "reshape: element count differs");
   Tensor t = *this;
+  if (new_shape != shape_) {  // the planes describe the 2-D layout they were written for
+    t.rows_planes.reset();
+    t.cols_planes.reset();
+  }
   t.shape_ = std::move(new_shape);
   return t;
 }
@@ -172,6 +187,10 @@ void Variable::backprop() {
         // add on the compute stream has to come after it.
         if (s->comm_on) s->check(vtlb_comm_wait(s->ctx));
         s->check(vtlb_add_inplace_f32(s->ctx, p.grad.data(), diffs[i].data(), p.grad.size()));
+        p.grad.rows_planes.reset();  // they described the first contribution alone
+        p.grad.cols_planes.reset();
+        // masked + masked stays masked; otherwise the ReLU gate masks the sum (masking twice is harmless)
+        p.grad.relu_masked = p.grad.relu_masked && diffs[i].relu_masked;
       }
     }
     node.result->grad = Tensor();  // intermediate gradients are dead once consumed
@@ -216,9 +235,29 @@ struct LinearGate : Gate {
     GradBucket b;
     const bool need_w = weight->requires_grad, need_b = bias->requires_grad;
     if (need_w || need_b) b = GradBucket::make(s, {N, K}, {1, N});
-    s->check(vtlb_linear_bwd_f32(s->ctx, g.data(), input->value.data(), weight->value.data(),
-                                 dX.defined() ? dX.data() : nullptr, need_w ? b.dW.data() : nullptr,
-                                 need_b ? b.db.data() : nullptr, M, N, K));
+    // Large products hand their operand planes from producer to consumer (include/vtlb.h): the
+    // gradient's planes come with g when the layer above produced it, the input's transposed planes
+    // with the activation; dX is masked by the ReLU below this layer in the same launch and leaves
+    // its own planes for the layer below.
+    const bool planes = s->pass_planes && vtlb_f32_planes_worthwhile(s->ctx, M, N, K) != 0;
+    const Tensor& xin = input->value;
+    const vtlb_planes* g_rows = planes && g.rows_planes ? &g.rows_planes->p : nullptr;
+    const vtlb_planes* g_cols = planes && g.cols_planes ? &g.cols_planes->p : nullptr;
+    const vtlb_planes* x_cols = planes && xin.cols_planes ? &xin.cols_planes->p : nullptr;
+    const float* mask = nullptr;
+    if (dX.defined() && planes && input->relu_cache.defined() && input->relu_cache.size() == dX.size()) {
+      mask = input->relu_cache.data();
+      dX.relu_masked = true;
+    }
+    if (dX.defined() && planes && mask) {  // somebody below will multiply with this gradient
+      if (s->plane_kinds & 1) dX.rows_planes = PlanePair::make(s, M, K);
+      if (s->plane_kinds & 2) dX.cols_planes = PlanePair::make(s, K, M);
+    }
+    s->check(vtlb_linear_bwd_f32_planes(s->ctx, g.data(), xin.data(), weight->value.data(),
+                                        dX.defined() ? dX.data() : nullptr, need_w ? b.dW.data() : nullptr,
+                                        need_b ? b.db.data() : nullptr, M, N, K, g_rows, g_cols, x_cols, mask,
+                                        dX.rows_planes ? &dX.rows_planes->p : nullptr,
+                                        dX.cols_planes ? &dX.cols_planes->p : nullptr));
     if (need_w || need_b) b.allreduce(s);
     return {dX, need_w ? b.dW : Tensor(), need_b ? b.db : Tensor()};
   }
@@ -228,6 +267,11 @@ struct LinearGate : Gate {
 struct ReLUGate : Gate {
   Tensor cache;
   std::vector<Tensor> backward(const Tensor& g) override {
+    if (g.relu_masked) {  // the GEMM that produced g applied this mask already
+      Tensor dx = g;
+      dx.relu_masked = false;  // it is now the gradient of the pre-activation
+      return {dx};
+    }
     Session* s = g.session();
     Tensor dx = Tensor::empty(s, g.shape());
     s->check(vtlb_relu_bwd_f32(s->ctx, g.data(), cache.data(), dx.data(), g.size()));
@@ -339,9 +383,20 @@ static VarPtr linear_run(LinearLayer& L, const VarPtr& input, bool relu) {
   Tensor y = Tensor::empty(s, {M, L.out_features});
   Tensor pre;
   if (relu) pre = Tensor::empty(s, {M, L.out_features});
-  s->check(vtlb_linear_fwd_f32(s->ctx, input->value.data(), L.weights->value.data(), L.bias->value.data(),
-                               y.data(), M, L.out_features, L.in_features, relu ? 1 : 0,
-                               relu ? pre.data() : nullptr));
+  // While a tape is recorded, a large layer followed by its ReLU leaves the operand planes of its
+  // output for the products that read it next: the next layer's forward (rows) and that layer's
+  // weight gradient (transposed).
+  const bool planes = s->pass_planes && relu && !ctx->no_grad && vtlb_f32_planes_worthwhile(s->ctx, M, L.out_features, L.in_features);
+  if (planes) {
+    if (s->plane_kinds & 1) y.rows_planes = PlanePair::make(s, M, L.out_features);
+    if (s->plane_kinds & 2) y.cols_planes = PlanePair::make(s, L.out_features, M);
+  }
+  const Tensor& xin = input->value;
+  s->check(vtlb_linear_fwd_f32_planes(s->ctx, xin.data(), L.weights->value.data(), L.bias->value.data(), y.data(), M,
+                                      L.out_features, L.in_features, relu ? 1 : 0, relu ? pre.data() : nullptr,
+                                      s->pass_planes && xin.rows_planes ? &xin.rows_planes->p : nullptr,
+                                      y.rows_planes ? &y.rows_planes->p : nullptr,
+                                      y.cols_planes ? &y.cols_planes->p : nullptr));
   auto gate = std::make_unique<LinearGate>();
   gate->input = input;
   gate->weight = L.weights;
@@ -354,6 +409,7 @@ static VarPtr linear_run(LinearLayer& L, const VarPtr& input, bool relu) {
   VarPtr mid = ctx->variable(pre);
   ctx->register_node("Linear", std::move(gate), mid, {input, L.weights, L.bias});
   VarPtr out = ctx->variable(y);
+  out->relu_cache = pre;
   auto rg = std::make_unique<ReLUGate>();
   rg->cache = pre;
   ctx->register_node("ReLU", std::move(rg), out, {mid});
@@ -368,6 +424,7 @@ VarPtr ReLULayer::forward(const VarPtr& input) {
   Tensor y = Tensor::empty(s, input->value.shape());
   s->check(vtlb_relu_fwd_f32(s->ctx, input->value.data(), y.data(), y.size()));
   VarPtr out = ctx->variable(y);
+  out->relu_cache = input->value;
   auto g = std::make_unique<ReLUGate>();
   g->cache = input->value;
   ctx->register_node("ReLU", std::move(g), out, {input});

@@ -45,6 +45,11 @@ struct Session {
   // Seed of the parameter initialisers.  The reference seeds V's generator from the wall clock;
   // here layers draw their weights from (init_seed, running counter), so a model built twice
   // with the same seed starts from the same weights, on every rank of a data-parallel job.
+  // Large Linear layers pass the TF32 operand planes of activations and gradients from the product
+  // that writes them to the products that read them, and fold the ReLU backward into the gradient
+  // product (off: every product splits its own operands, as a lone vtlb_linear_*_f32 call does).
+  bool pass_planes = true;
+  int plane_kinds = 3;  // which planes a large layer's product leaves: bit 0 rows, bit 1 transposed (VTL_PLANE_KINDS)
   uint64_t init_seed = 0, init_counter = 0;
   uint64_t next_init_seed() { return init_seed * 0x100000001B3ull + 0x9E3779B97F4A7C15ull * ++init_counter; }
 };
@@ -57,6 +62,15 @@ struct DeviceBuf {  // one vtlb_alloc; freed (stream-ordered) when the last Tens
   DeviceBuf(Session* s_, size_t bytes_);
   DeviceBuf(Session* s_, void* borrowed) : s(s_), ptr(borrowed), bytes(0), owned(false) {}  // caller's memory
   virtual ~DeviceBuf();
+};
+
+// TF32 hi/lo operand planes of a 2-D tensor T[R,C] (include/vtlb.h, vtlb_planes): "rows" planes are
+// [R, ld(C)], "cols" planes [C, ld(R)] (T transposed).  Written by the GEMM that produces T and read
+// by the GEMMs that consume it, so that no separate split pass runs in between.
+struct PlanePair {
+  std::shared_ptr<DeviceBuf> buf;  // hi followed by lo
+  vtlb_planes p{nullptr, nullptr};
+  static std::shared_ptr<PlanePair> make(Session* s, int rows, int kdim);
 };
 
 // vtl.Tensor[f32] (a_tensor.v): shape + storage; row-major, contiguous.  Several tensors
@@ -79,6 +93,12 @@ class Tensor {
   const std::shared_ptr<DeviceBuf>& buffer() const { return buf_; }
   size_t offset() const { return off_; }
   bool defined() const { return (bool)buf_; }
+  // Optional companions of a 2-D tensor that a tensor-core product left behind (they describe the
+  // same values; copies of the Tensor share them, reshape drops them).
+  std::shared_ptr<PlanePair> rows_planes, cols_planes;
+  // Set on a gradient that already went through the backward of the ReLU whose output it belongs
+  // to (the producing GEMM applied the mask): the ReLU gate then hands it on unchanged.
+  bool relu_masked = false;
 
  private:
   std::shared_ptr<DeviceBuf> buf_;
@@ -106,6 +126,9 @@ struct Gate;
 // autograd.Variable (autograd/variable.v:17-57)
 struct Variable {
   Tensor value, grad;
+  // for the output of a ReLU: the pre-activation that ReLU cached.  A Linear gate that computes the
+  // gradient w.r.t. this variable can apply the ReLU's backward in the same launch.
+  Tensor relu_cache;
   Context* context = nullptr;
   bool requires_grad = true;
   bool grad_is_zero = true;  // grad holds zeros_like(value): the first accumulation may alias

@@ -20,6 +20,9 @@ void* vtlh_session_ctx(vtlh_session* s); /* the vtlb_ctx* the session owns */
 int vtlh_session_comm_init(vtlh_session* s, int nranks, int rank, const void* id128);
 /* Seed of the layers' Kaiming-normal weight draws (restarts the per-layer counter). */
 int vtlh_session_set_seed(vtlh_session* s, unsigned long long seed);
+/* Whether large Linear layers hand TF32 operand planes from producer to consumer and fold the ReLU
+ * backward into the gradient product (default on; off = every product splits its own operands). */
+int vtlh_session_set_pass_planes(vtlh_session* s, int on);
 /* nn/internal/init.v: compute_fans (as written there) and variance_scaled into a host array;
  * fan_mode 0 = fan_avg, 1 = fan_in, 2 = fan_out; distribution 0 = uniform, 1 = normal. */
 int vtlh_compute_fans(int ndim, const int* shape, long long* f0, long long* f1);

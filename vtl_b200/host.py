@@ -37,7 +37,7 @@ def load() -> C.CDLL:
         protos = {
             "vtlh_session_create": [i, C.POINTER(vp)], "vtlh_session_destroy": [vp],
             "vtlh_session_comm_init": [vp, i, i, vp],
-            "vtlh_session_set_seed": [vp, C.c_ulonglong],
+            "vtlh_session_set_seed": [vp, C.c_ulonglong], "vtlh_session_set_pass_planes": [vp, i],
             "vtlh_compute_fans": [i, ip, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)],
             "vtlh_variance_scaled": [vp, i, ip, d, i, i, C.c_ulonglong, vp],
             "vtlh_model_create": [vp, C.POINTER(vp)], "vtlh_model_destroy": [vp],
@@ -117,6 +117,10 @@ class Session:
     def set_seed(self, seed: int):
         """Seed of the Kaiming-normal draws of the layers built after this call."""
         _ck(self.lib.vtlh_session_set_seed(self.h, int(seed)))
+
+    def set_pass_planes(self, on: bool):
+        """Producer-to-consumer hand-over of TF32 operand planes in large Linear layers (default on)."""
+        _ck(self.lib.vtlh_session_set_pass_planes(self.h, int(on)))
 
     def variance_scaled(self, shape, scale, fan_mode, distribution, seed):
         """internal.variance_scaled (nn/internal/init.v:36-60) -> host array."""
