@@ -68,6 +68,10 @@ def test_conv2d_reference_kat(dev):
     (2, 32, 9, 8, 40, 5, 2, 1),       # slab kernel: 25 taps, one partly filled tile per image
     (2, 32, 10, 14, 32, 3, 0, 1),     # slab kernel forward without padding (input gradient: gathered)
     (5, 32, 33, 32, 64, 3, 1, 1),     # slab kernel: 11 tiles of 3 rows per image, the last one clipped
+    (40, 3, 8, 8, 16, 3, 1, 1),       # weight gradient over pixels: CTAs start in the middle of images
+    (7, 40, 6, 5, 130, 3, 1, 1),      # ... two channel groups (the second partly filled), three output blocks
+    (9, 8, 5, 31, 9, 2, 0, 1),        # ... 2x2 window, 30-pixel rows that are no multiple of 4
+    (2, 4, 6, 40, 6, 3, 1, 1),        # output rows longer than 32 pixels: the lowered weight gradient
 ])
 def test_conv2d_fwd_bwd_vs_oracle(dev, orc, B, C, H, W, O, k, pad, stride):
     rng = np.random.default_rng(B * 100 + C * 10 + O)

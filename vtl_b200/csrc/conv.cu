@@ -13,6 +13,7 @@
 //   d_bias  : per-channel sums of g (f64 partials)
 #include "conv_igemm.cuh"
 #include "conv_slab.cuh"
+#include "conv_wgrad.cuh"
 #include "f32_common.cuh"
 
 namespace {
@@ -481,7 +482,16 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
   if (!d_g) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: null gradient");
   const int M = (int)d.M(), K = d.K(), P = d.P();
   const float* g = (const float*)d_g;
-  if (d_dw_or_null) {  // dW[oc, k] = sum_m g[m, oc] * col[m, k]
+  if (d_dw_or_null && cwgrad::usable(sh, sw, kh, kw, d.OW, 1)) {
+    // unit stride, window at most 3 x 3, output rows of at most 32 pixels: the implicit GEMM over pixels
+    if (!d_x) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_weight needs x");
+    const int parts = cwgrad::parts_for(ctx, B, C, O, d.OH);
+    void* scr = nullptr;
+    if ((rc = vtlb_scratch(ctx, (size_t)parts * O * K * sizeof(float), &scr))) return rc;
+    if ((rc = cwgrad::launch(ctx, (const float*)d_x, g, (float*)scr, (float*)d_dw_or_null, B, C, H, W, O, d.OH, d.OW,
+                             kh, kw, ph, pw)))
+      return rc;
+  } else if (d_dw_or_null) {  // dW[oc, k] = sum_m g[m, oc] * col[m, k]
     if (!d_x) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_weight needs x");
     const int mn_tiles = ((O + 127) / 128) * ((K + 63) / 64);
     int want = (2 * ctx->sm_count + mn_tiles - 1) / mn_tiles;
