@@ -11,7 +11,7 @@
 //
 // A CTA owns a run of consecutive output rows (of consecutive images) for one group of 32 source
 // channels and one block of 64 output channels, keeps the source rows of the last kh output rows in
-// a ring of kh + 1 shared-memory slots (each source row is loaded, split into TF32 hi/lo and stored
+// a ring of kh + 3 shared-memory slots (each source row is loaded, split into TF32 hi/lo and stored
 // once, although kh output rows use it), and writes its sums as one partial dW; a second launch
 // adds the partials of all CTAs in a fixed order.  Accumulators are closed every four rows and summed
 // in registers, like in the other 3xTF32 kernels (the f32 accumulate of tcgen05 truncates).
@@ -30,8 +30,8 @@ using gemm::WAIT_LIMIT_NS;
 
 constexpr int BO = 64;                 // output channels per CTA
 constexpr int MAX_KH = 3, MAX_KW = 3;
-constexpr int MAX_SLOTS = MAX_KH + 1;  // source-row window
-constexpr int GS = 3;                  // gradient stages
+constexpr int MAX_SLOTS = MAX_KH + 3;  // source-row window: the kh rows in use and three rows of lead for the fill
+constexpr int GS = 4;                  // gradient stages
 constexpr int CHUNK_ROWS = 4;          // output rows per accumulator chunk (128 pixels of the contraction)
 constexpr int NUM_WARPS = 13, NUM_THREADS = 32 * NUM_WARPS;
 constexpr int XFILL_WARPS = 4, GFILL_WARPS = 2, EPI_WARPS = 6;
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const Params
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kh = p.kh, kw = p.kw, nslots = kh + 1;
+  const int kh = p.kh, kw = p.kw, nslots = kh + 3;
   const int grp = blockIdx.y, ob = blockIdx.z;
   const int row_begin = blockIdx.x * p.rows_per_part;
   const int row_end = row_begin + p.rows_per_part < p.rows_total ? row_begin + p.rows_per_part : p.rows_total;
@@ -128,64 +128,84 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const Params
   if (warp == 0) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // One thread issues everything: no divisions (slots, stages and rows advance by counters), and the
+      // waits for the NEXT row's operands sit between the tap rows of the current one, while MMAs are
+      // queued.  (Measured: the kernel is bound by the tensor core fetching its operands from shared
+      // memory, 36 MMAs of 4 KB + 2 KB per output row at about 70 bytes per clock; issuing the commits
+      // later, behind the next row's first MMAs, changed nothing.)
       const uint64_t desc0 = ptx::umma_desc_k_sw128(base);
       uint32_t acc = 0, acc_phase = 0;
-      int xawaited = 0, xc0 = 0, xcount = 0;
+      uint32_t xs = 0, xph = 0;    // slot and parity of the next source row to wait for
+      uint32_t gs = 0, gph = 0;    // stage and parity of the next gradient row to wait for
       bool ok = true;
-      for (int i = 0; i < R && ok; ++i) {
-        int img, y;
-        row_of(i, img, y);
-        if (i == 0 || y == 0) {
-          xc0 = xcount;
-          xcount += kh;
-        } else {
-          xc0 += 1;
-          xcount += 1;
-        }
-        const bool chunk_start = (i % CHUNK_ROWS) == 0;
-        if (chunk_start) {
-          if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
-            ok = false;
-            break;
+      auto wait_operands = [&](bool first) -> bool {  // of the row that is issued next
+        const int need = first ? kh : 1;
+        for (int k = 0; k < need; ++k) {
+          if (!ptx::mbar_wait_bounded(xfull_bar((int)xs), xph, abort_flag, WAIT_LIMIT_NS)) return false;
+          if (++xs == (uint32_t)nslots) {
+            xs = 0;
+            xph ^= 1u;
           }
         }
-        while (xawaited < xc0 + kh && ok) {  // the source rows this output row adds to the window
-          ok = ptx::mbar_wait_bounded(xfull_bar(xawaited % nslots), (uint32_t)(xawaited / nslots) & 1u, abort_flag,
-                                      WAIT_LIMIT_NS);
-          ++xawaited;
+        if (!ptx::mbar_wait_bounded(gfull_bar((int)gs), gph, abort_flag, WAIT_LIMIT_NS)) return false;
+        if (++gs == (uint32_t)GS) {
+          gs = 0;
+          gph ^= 1u;
         }
-        if (!ok) break;
-        const int gs = i % GS;
-        if (!ptx::mbar_wait_bounded(gfull_bar(gs), (uint32_t)(i / GS) & 1u, abort_flag, WAIT_LIMIT_NS)) {
+        return true;
+      };
+      auto issue_tap = [&](uint32_t slot, uint32_t d, uint64_t b_hi, uint64_t b_lo, bool fresh) {
+        const uint64_t a_hi = desc0 + ((slot * SLOT) >> 4);
+        const uint64_t a_lo = a_hi + (SLOT_PLANE >> 4);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          ptx::umma_tf32(d, a_lo + 2u * kk, b_hi + 2u * kk, IDESC, (fresh && kk == 0) ? 0u : 1u);  // small terms first
+          ptx::umma_tf32(d, a_hi + 2u * kk, b_lo + 2u * kk, IDESC, 1u);
+          ptx::umma_tf32(d, a_hi + 2u * kk, b_hi + 2u * kk, IDESC, 1u);
+        }
+      };
+      auto wrap = [&](uint32_t s_) { return s_ >= (uint32_t)nslots ? s_ - (uint32_t)nslots : s_; };
+      int y = row_begin - (row_begin / p.Ho) * p.Ho;
+      uint32_t slot0 = 0, gcur = 0;  // window slot of tap row 0 and gradient stage of the current row
+      int in_chunk = 0;
+      ok = wait_operands(true);
+      for (int i = 0; i < R && ok; ++i) {
+        const bool chunk_start = in_chunk == 0;
+        if (chunk_start && !ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
           ok = false;
           break;
         }
         ptx::tc_fence_after();
-        const uint64_t b_hi = desc0 + ((G_OFF + (uint32_t)gs * G_STAGE) >> 4);
+        const uint64_t b_hi = desc0 + ((G_OFF + gcur * G_STAGE) >> 4);
         const uint64_t b_lo = b_hi + (G_PLANE >> 4);
-        for (int a = 0; a < kh; ++a) {
-          const uint32_t slot = (uint32_t)((xc0 + a) % nslots);
-          const uint64_t a_hi = desc0 + ((slot * SLOT) >> 4);
-          const uint64_t a_lo = a_hi + (SLOT_PLANE >> 4);
-          const uint32_t d = tmem_base + acc * ACC_COLS + (uint32_t)a * BO;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            ptx::umma_tf32(d, a_lo + 2u * kk, b_hi + 2u * kk, IDESC, (chunk_start && kk == 0) ? 0u : 1u);  // small terms first
-            ptx::umma_tf32(d, a_hi + 2u * kk, b_lo + 2u * kk, IDESC, 1u);
-            ptx::umma_tf32(d, a_hi + 2u * kk, b_hi + 2u * kk, IDESC, 1u);
-          }
+        const uint32_t d0 = tmem_base + acc * ACC_COLS;
+        for (int a = 0; a + 1 < kh; ++a) issue_tap(wrap(slot0 + (uint32_t)a), d0 + (uint32_t)a * BO, b_hi, b_lo, chunk_start);
+        // the next row: where its window starts, and its operands (normally long there)
+        const bool has_next = i + 1 < R;
+        const int y_next = y + 1 == p.Ho ? 0 : y + 1;
+        const bool first_next = y_next == 0;
+        const uint32_t slot0_next = first_next ? xs : wrap(slot0 + 1u);
+        const uint32_t g_next = gs;
+        if (has_next && !wait_operands(first_next)) {
+          ok = false;
+          break;
         }
-        // once these MMAs have read their operands: the gradient stage is free, and so are the window
-        // slots no later row reads -- the oldest source row, or all of them when the next output row
-        // starts a new window (first row of the next image) or there is none
-        ptx::umma_commit(gempty_bar(gs));
-        const bool last_of_window = i == R - 1 || y == p.Ho - 1;
-        for (int a = 0; a < (last_of_window ? kh : 1); ++a) ptx::umma_commit(xempty_bar((xc0 + a) % nslots));
-        if (i % CHUNK_ROWS == CHUNK_ROWS - 1 || i == R - 1) {
+        issue_tap(wrap(slot0 + (uint32_t)(kh - 1)), d0 + (uint32_t)(kh - 1) * BO, b_hi, b_lo, chunk_start);
+        // once these MMAs have read their operands the gradient stage is free, and so are the window
+        // slots no later row reads: the oldest source row, or all kh when the next output row starts a
+        // new window (first row of the next image) or there is none
+        ptx::umma_commit(gempty_bar((int)gcur));
+        const int freed = (!has_next || first_next) ? kh : 1;
+        for (int a = 0; a < freed; ++a) ptx::umma_commit(xempty_bar((int)wrap(slot0 + (uint32_t)a)));
+        if (++in_chunk == CHUNK_ROWS || !has_next) {
+          in_chunk = 0;
           ptx::umma_commit(tfull_bar(acc));
           acc ^= 1u;
           if (acc == 0) acc_phase ^= 1u;
         }
+        y = y_next;
+        slot0 = slot0_next;
+        gcur = g_next;
       }
     }
   } else if (warp == 1 || warp == 2 || warp == 3 || warp == 7) {
@@ -244,29 +264,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const Params
       }
       return true;
     };
+    // Three rows in registers: the loads of the two rows after the one being stored are in flight
+    // (a row period is about the latency of one load from HBM).  The buffers rotate by name, not by
+    // copying: a copy would wait for the newest load.
     int count = 0;
     bool ok = true;
-    float va[NV], vb[NV];
-    int img_a, r_a, img_b = 0, r_b = 0;
-    bool have_a = next_item(img_a, r_a), have_b = false;
-    if (have_a) load_row(img_a, r_a, va);
-    while (have_a && ok) {
-      have_b = next_item(img_b, r_b);
-      if (have_b) load_row(img_b, r_b, vb);  // in flight while the current row is stored
+    auto fetch = [&](float (&v)[NV]) -> bool {
+      int img, r;
+      if (!next_item(img, r)) return false;
+      load_row(img, r, v);
+      return true;
+    };
+    auto put = [&](const float (&v)[NV]) -> bool {
       const int slot = count % nslots;
-      ok = ptx::mbar_wait_bounded(xempty_bar(slot), ((uint32_t)(count / nslots) & 1u) ^ 1u, abort_flag, WAIT_LIMIT_NS);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      store_row(base + (uint32_t)slot * SLOT, va);
+      bool good = ptx::mbar_wait_bounded(xempty_bar(slot), ((uint32_t)(count / nslots) & 1u) ^ 1u, abort_flag,
+                                         WAIT_LIMIT_NS);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+      store_row(base + (uint32_t)slot * SLOT, v);
       ptx::fence_proxy_async();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(xfull_bar(slot));
       ++count;
-      have_a = have_b;
-      img_a = img_b;
-      r_a = r_b;
-#pragma unroll
-      for (int e = 0; e < NV; ++e) va[e] = vb[e];
+      return true;
+    };
+    float v0[NV], v1[NV], v2[NV];
+    bool h0 = fetch(v0), h1 = h0 && fetch(v1), h2 = false;
+    while (h0 && ok) {
+      h2 = h1 && fetch(v2);
+      ok = put(v0);
+      if (!ok || !h1) break;
+      h0 = h2 && fetch(v0);
+      ok = put(v1);
+      if (!ok || !h2) break;
+      h1 = h0 && fetch(v1);
+      ok = put(v2);
     }
   } else if (warp == 11 || warp == 12) {
     // ------------------------------------------------------------ gradient stages
@@ -309,19 +341,35 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const Params
       }
     };
     bool ok = true;
-    float va[32], vb[32];
-    load_row(0, va);
-    for (int i = 0; i < R && ok; ++i) {
-      if (i + 1 < R) load_row(i + 1, vb);
-      ok = ptx::mbar_wait_bounded(gempty_bar(i % GS), ((uint32_t)(i / GS) & 1u) ^ 1u, abort_flag, WAIT_LIMIT_NS);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      store_row(base + G_OFF + (uint32_t)(i % GS) * G_STAGE, va);
+    int loaded = 0, stored = 0;
+    auto fetch = [&](float (&v)[32]) -> bool {
+      if (loaded >= R) return false;
+      load_row(loaded++, v);
+      return true;
+    };
+    auto put = [&](const float (&v)[32]) -> bool {
+      const int i = stored;
+      bool good = ptx::mbar_wait_bounded(gempty_bar(i % GS), ((uint32_t)(i / GS) & 1u) ^ 1u, abort_flag, WAIT_LIMIT_NS);
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+      store_row(base + G_OFF + (uint32_t)(i % GS) * G_STAGE, v);
       ptx::fence_proxy_async();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(gfull_bar(i % GS));
-#pragma unroll
-      for (int e = 0; e < 32; ++e) va[e] = vb[e];
+      ++stored;
+      return true;
+    };
+    float v0[32], v1[32], v2[32];  // rotate by name, as in the window fill
+    bool h0 = fetch(v0), h1 = h0 && fetch(v1), h2 = false;
+    while (h0 && ok) {
+      h2 = h1 && fetch(v2);
+      ok = put(v0);
+      if (!ok || !h1) break;
+      h0 = h2 && fetch(v0);
+      ok = put(v1);
+      if (!ok || !h2) break;
+      h1 = h0 && fetch(v1);
+      ok = put(v2);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -392,6 +440,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) conv_wgrad_kernel(const Params
   }
 }
 
+// out[i] = sum over the parts of partial[part][i], in a fixed order.  A weight gradient has few
+// elements and many parts (one per CTA of the kernel above), so eight threads share an element:
+// thread (group, element) adds the parts = group (mod 8) in ascending order, the eight sums are then
+// added in group order.  32 elements per CTA.
+__global__ void __launch_bounds__(256) reduce_parts_kernel(const float* __restrict__ partial, int parts, size_t n,
+                                                           float* __restrict__ out) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ float part_sum[8][33];
+  const int e = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const size_t i = (size_t)blockIdx.x * 32 + e;
+  float s = 0.0f;
+  if (i < n)
+    for (int k = grp; k < parts; k += 8) s = __fadd_rn(s, partial[(size_t)k * n + i]);
+  part_sum[grp][e] = s;
+  __syncthreads();
+  if (grp == 0 && i < n) {
+    float t = part_sum[0][e];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) t = __fadd_rn(t, part_sum[k][e]);
+    out[i] = t;
+  }
+}
+
 // dW[O][C][kh][kw] of one convolution; `partial` must hold parts(...) * O*C*kh*kw floats.
 inline int parts_for(vtlb_ctx* ctx, int B, int C, int O, int Ho) {
   const int G = (C + 31) / 32, OB = (O + BO - 1) / BO;
@@ -423,7 +495,11 @@ inline int launch(vtlb_ctx* ctx, const float* x, const float* g, float* partial,
     ctx->prof_flops += 2.0 * B * Ho * Wo * (double)O * C * kh * kw;
   }
   VTLB_LAUNCHED(ctx);
-  return f32::reduce_splits(ctx, partial, parts, (size_t)O * C * kh * kw, dW);
+  const size_t n = (size_t)O * C * kh * kw;
+  VTLB_CUDA(ctx, vtlb_launch_early(reduce_parts_kernel, dim3((unsigned)((n + 31) / 32)), dim3(256), 0, ctx->stream,
+                                   (const float*)partial, parts, n, dW));
+  VTLB_LAUNCHED(ctx);
+  return VTLB_OK;
 }
 
 }  // namespace cwgrad
