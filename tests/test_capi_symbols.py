@@ -55,3 +55,26 @@ def test_product_package_does_not_touch_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower(), f"{f} mentions the oracle"
+
+
+def test_v_declarations_follow_the_header():
+    """vtl_b200/vglue/c_d_b200.v (the `fn C.vtlb_*` declarations a `-d b200` build of vtl includes)
+    is what gen_c_decls.py derives from include/vtlb.h: one line per prototype, none missing, and
+    every vtlb_* call in the hook files beside it is declared."""
+    import importlib.util
+    import re
+    vdir = os.path.join(ROOT, "vtl_b200", "vglue")
+    spec = importlib.util.spec_from_file_location("gen_c_decls", os.path.join(vdir, "gen_c_decls.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    committed = open(os.path.join(vdir, "c_d_b200.v")).read()
+    assert committed == gen.render(), "run python vtl_b200/vglue/gen_c_decls.py"
+    declared = set(re.findall(r"^fn C\.(vtlb_\w+)\(", committed, re.M))
+    header = open(os.path.join(ROOT, "include", "vtlb.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    in_header = set(re.findall(r"\b(vtlb_\w+)\s*\(", header))
+    assert declared == in_header
+    for f in os.listdir(vdir):
+        if f.endswith(".v") and f != "c_d_b200.v":
+            used = set(re.findall(r"C\.(vtlb_\w+)\(", open(os.path.join(vdir, f)).read()))
+            assert used <= declared, (f, used - declared)

@@ -104,31 +104,5 @@ def _build_host(force: bool, verbose: bool) -> str:
     return HOST_LIB
 
 
-TRACE_LIB = os.path.join(HERE, "libvtlb200_trace.so")
-
-
-def build_trace() -> str:
-    """libvtlb200_trace.so: the same library with int8.cu compiled with -DVTLB_PAIR_TRACE, which
-    makes the INT8 CTA-pair GEMM count the cycles each of its roles spends waiting and exports
-    vtlb_debug_pair_trace (see vtl_b200/pair_trace.py).  Never loaded by the product path."""
-    build()
-    obj = os.path.join(OBJ, "int8_trace.o")
-    src = os.path.join(CSRC, "int8.cu")
-    cmd = [_nvcc(), *NVCC_FLAGS, "-DVTLB_PAIR_TRACE", "-ccbin", "g++", "-I", os.path.join(HERE, "..", "include"),
-           "-c", src, "-o", obj]
-    p = subprocess.run(cmd, capture_output=True, text=True)
-    if p.returncode != 0:
-        raise RuntimeError(f"nvcc failed for the trace variant:\n{p.stdout}\n{p.stderr}")
-    objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in _sources() if not s.endswith("int8.cu")]
-    cmd = [_nvcc(), "-shared", "-o", TRACE_LIB, obj, *objs, "-ccbin", "g++", "-ldl"]
-    p = subprocess.run(cmd, capture_output=True, text=True)
-    if p.returncode != 0:
-        raise RuntimeError(f"link failed:\n{p.stdout}\n{p.stderr}")
-    return TRACE_LIB
-
-
 if __name__ == "__main__":
-    if "--trace" in sys.argv:
-        print(build_trace())
-    else:
-        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -82,21 +82,11 @@ struct Smem {
 // instead of 32 scattered 16-byte pieces per store instruction (measured: the scattered stores,
 // not the MMAs, bounded the 4096^3 INT8 GEMM).  Edges need no care: the store clips at the
 // tensor's extent.  Everything else goes through the functor's own direct stores.
-#ifdef VTLB_PAIR_TRACE
-// Tuning aid: cycles warp 2 of each CTA spent in the phases of the epilogue:
-//   0 tensor-memory load, 1 transform, 2 wait for the staging tile, 3 stage + issue the store, 4 chunks
-static __device__ long long g_epi_trace[160][8];
-#define VTLB_ETR(...) __VA_ARGS__
-#else
-#define VTLB_ETR(...)
-#endif
 
 __device__ __forceinline__ void stage_and_store(uint32_t stg, const CUtensorMap* tmap, int lane, int row0,
                                                 int col0, const uint32_t (&v)[32], int M, int N) {
-  VTLB_ETR(const bool tr_on = threadIdx.x == 64; const long long tr_a = clock64();)
   if (lane == 0) ptx::bulk_wait_read_all();  // the previous store has finished reading the tile
   __syncwarp();
-  VTLB_ETR(const long long tr_b = clock64();)
   const uint32_t rowaddr = stg + lane * 128;
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -108,11 +98,6 @@ __device__ __forceinline__ void stage_and_store(uint32_t stg, const CUtensorMap*
     ptx::tma_store_2d(tmap, col0, row0, stg);
     ptx::bulk_commit_group();
   }
-  VTLB_ETR(if (tr_on) {
-    g_epi_trace[blockIdx.x][2] += tr_b - tr_a;
-    g_epi_trace[blockIdx.x][3] += clock64() - tr_b;
-    g_epi_trace[blockIdx.x][4] += 1;
-  })
 }
 
 // x = hi + lo + O(2^-22 |x|), both representable in TF32 (the operand split of the 3xTF32 products).
@@ -186,13 +171,11 @@ __device__ __forceinline__ void epilogue_chunk(const Epi& epi, const TmapSet& tm
                                                int split, bool mask_applied = false) {
   if constexpr (Epi::kTmaCapable) {
     if (epi.tma) {
-      VTLB_ETR(const long long tr_t = clock64();)
       bool two;
       if constexpr (EpiHasPlanes<Epi>::value)
         two = epi.transform(row0 + lane, col0, v, M, N, mask_applied);
       else
         two = epi.transform(row0 + lane, col0, v, M, N);
-      VTLB_ETR(if (threadIdx.x == 64) g_epi_trace[blockIdx.x][1] += clock64() - tr_t;)
       if (two) {  // true: v now holds the pre-activation
         stage_and_store(stg, &tm.out[1], lane, row0, col0, v, M, N);
         epi.activate(v);

@@ -162,17 +162,6 @@ __device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t
   }
 }
 
-#ifdef VTLB_PAIR_TRACE
-// Tuning aid: cycles each role of a CTA spent waiting, [cta][slot]
-//   0 producer total, 1 producer waiting for empty slots, 2 MMA total, 3 MMA waiting for operands,
-//   4 MMA waiting for a free accumulator, 5 epilogue warp 2 total, 6 its wait for accumulators,
-//   7 cycle at which epilogue warp 2 finished the CTA's first unit
-//   8.. cycle (since the MMA thread started) at which its i-th unit had all MMAs issued
-static __device__ long long g_pair_trace[160][16];
-#define VTLB_TR(...) __VA_ARGS__
-#else
-#define VTLB_TR(...)
-#endif
 
 template <int KIND, class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -283,7 +272,6 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      VTLB_TR(long long tr_w = 0; const long long tr_0 = clock64();)
       for (int it = 0; ok; ++it) {
         int tmi, tni, kh, slot, kb_begin, kb_end;
         if (!decode_unit(it, tmi, tni, kh, slot)) break;
@@ -291,12 +279,10 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         const int m0 = tmi * 2 * BM + (int)rank * BM;
         const int n0 = tni * BN2 + (int)rank * (BN2 / 2);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          VTLB_TR(const long long tr_a = clock64();)
           if (!ptx::mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
-          VTLB_TR(tr_w += clock64() - tr_a;)
           const uint32_t leader_full = mapa(full_bar(stage), 0);
           if (rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::STAGE);
           const uint32_t sa = base + stage * C::STAGE;
@@ -318,35 +304,29 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           }
         }
       }
-      VTLB_TR(g_pair_trace[blockIdx.x][0] = clock64() - tr_0; g_pair_trace[blockIdx.x][1] = tr_w;)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      VTLB_TR(long long tr_f = 0, tr_e = 0; const long long tr_0 = clock64();)
       for (int it = 0; ok; ++it) {
         int tmi, tni, kh, slot, kb_begin, kb_end;
         if (!decode_unit(it, tmi, tni, kh, slot)) break;
         k_range(kh, kb_begin, kb_end);
         for (int kb0 = kb_begin; kb0 < kb_end && ok; kb0 += chunk_kb) {
           const int kb1 = kb0 + chunk_kb < kb_end ? kb0 + chunk_kb : kb_end;
-          VTLB_TR(const long long tr_a = clock64();)
           if (!ptx::mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             break;
           }
-          VTLB_TR(tr_e += clock64() - tr_a;)
           ptx::tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN2;
           for (int kb = kb0; kb < kb1; ++kb) {
-            VTLB_TR(const long long tr_b = clock64();)
             if (!ptx::mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
               ok = false;
               break;
             }
-            VTLB_TR(tr_f += clock64() - tr_b;)
             ptx::tc_fence_after();
             const uint32_t sa = base + stage * C::STAGE;
             const uint32_t sb = sa + NOP * C::A_TILE;
@@ -378,10 +358,7 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           acc ^= 1u;
           if (acc == 0) acc_phase ^= 1u;
         }
-        VTLB_TR(if (it < 8) g_pair_trace[blockIdx.x][8 + it] = clock64() - tr_0;)
       }
-      VTLB_TR(g_pair_trace[blockIdx.x][2] = clock64() - tr_0; g_pair_trace[blockIdx.x][3] = tr_f;
-              g_pair_trace[blockIdx.x][4] = tr_e;)
     }
   } else {
     // ------------------------------------------------------------ epilogue (both CTAs)
@@ -391,7 +368,6 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    VTLB_TR(long long tr_w = 0; const long long tr_0 = clock64();)
     for (int it = 0; ok; ++it) {
       int tmi, tni, kh, slot;
       if (!decode_unit(it, tmi, tni, kh, slot)) break;
@@ -405,11 +381,9 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         const bool fast = epi.tma != 0;
         typename Epi::Pre pre;
         if (fast) pre = epi.prefetch(row0 + lane, n0 + half * 32 + lane, M, N);
-        VTLB_TR(const long long tr_a = clock64();)
         ok = ptx::mbar_wait_bounded(tfull_bar(acc), acc_phase, abort_flag, WAIT_LIMIT_NS);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        VTLB_TR(tr_w += clock64() - tr_a;)
         ptx::tc_fence_after();
         // K-split tile: the unit of the first K half parks its accumulators,
         // [slot][rank][warp][chunk][value][lane], and the unit of the second half adds them to its own.
@@ -424,10 +398,8 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         auto do_chunk = [&](int cc, bool use_pre) {
           const int c = 2 * cc + half;
           uint32_t v[32];
-          VTLB_TR(const long long tr_l = clock64();)
           ptx::tmem_ld_32x32(lane_base + acc * BN2 + c * 32, v);
           ptx::tmem_wait_ld();
-          VTLB_TR(if (threadIdx.x == 64) gemm::g_epi_trace[blockIdx.x][0] += clock64() - tr_l;)
           uint32_t* pc = park + cc * 1024 + lane;
           if (kh == 0) {
 #pragma unroll
@@ -438,10 +410,8 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
               for (int j = 0; j < 32; ++j) v[j] += __ldcg(pc + j * 32);
             }
             if (use_pre) {
-              VTLB_TR(const long long tr_t = clock64();)
               epi.transform_pre(pre, cc, v);
               row_amax = fmaxf(row_amax, epi.chunk_amax(n0 + c * 32, v, N));  // one atomic per warp and tile
-              VTLB_TR(if (threadIdx.x == 64) gemm::g_epi_trace[blockIdx.x][1] += clock64() - tr_t;)
               gemm::stage_and_store(stg, &tm.out[0], lane, row0, n0 + c * 32, v, M, N);
             } else {
               gemm::epilogue_chunk(epi, tm, stg, lane, row0, n0 + c * 32, v, M, N, 0);
@@ -465,7 +435,6 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
           __syncwarp();
           if (lane == 0) flag_release(ksplit_buf + wslot, ksplit_epoch);
         }
-        VTLB_TR(if (warp == 2 && lane == 0 && it == 0) g_pair_trace[blockIdx.x][7] = clock64() - tr_0;)
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       } else {
@@ -516,10 +485,6 @@ gemm_pair_kernel(const __grid_constant__ gemm::TmapSet tm, const Epi epi, int M,
         }
       }
     }
-    VTLB_TR(if (warp == 2 && lane == 0) {
-      g_pair_trace[blockIdx.x][5] = clock64() - tr_0;
-      g_pair_trace[blockIdx.x][6] = tr_w;
-    })
   }
 
   // ------------------------------------------------------------ teardown

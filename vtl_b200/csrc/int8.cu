@@ -180,9 +180,6 @@ struct EpiStoreI32 {
   __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&v)[32], int M,
                                              int N, int /*split*/) const {
     if (row >= M) return;
-#ifdef VTLB_DEBUG_SKIP_STORES  // measurement only: how long does the GEMM take without its stores
-    if (v[0] != 0x7fffffffu) return;
-#endif
     int32_t* c = C + (size_t)row * ldc + col0;
     if (col0 + 32 <= N && (ldc & 3) == 0) {
 #pragma unroll
@@ -658,15 +655,3 @@ VTLB_API int vtlb_linear_i8_fwd_amax(vtlb_ctx* ctx, const void* d_Aq_shards, int
                             M, N, K, relu, d_row_amax);
 }
 
-#ifdef VTLB_PAIR_TRACE
-// Tuning aid (not part of the C ABI): copies the wait-cycle counters of the last INT8 pair-kernel launch.
-VTLB_API int vtlb_debug_pair_trace(vtlb_ctx* ctx, long long* out) {
-  VTLB_ENTER(ctx);
-  VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  VTLB_CUDA(ctx, cudaMemcpyFromSymbol(out, gemm2::g_pair_trace, sizeof(gemm2::g_pair_trace)));
-  VTLB_CUDA(ctx, cudaMemcpyFromSymbol(out + 160 * 16, gemm::g_epi_trace, sizeof(gemm::g_epi_trace)));
-  static long long zeros[160 * 8];
-  VTLB_CUDA(ctx, cudaMemcpyToSymbol(gemm::g_epi_trace, zeros, sizeof(zeros)));
-  return VTLB_OK;
-}
-#endif
