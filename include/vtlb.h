@@ -234,7 +234,7 @@ int vtlb_fill_f32(vtlb_ctx* ctx, void* d_dst, float value, size_t n);
 int vtlb_init_uniform_f32(vtlb_ctx* ctx, void* d_out, size_t n, float lo, float hi, uint64_t seed);
 int vtlb_init_normal_f32(vtlb_ctx* ctx, void* d_out, size_t n, double mu, double sigma, uint64_t seed);
 
-/* ---- Conv2D / max pooling (NCHW, groups = 1, dilation = 1) ------------------
+/* ---- Conv2D / max pooling (NCHW, groups = 1) ------------------------------------
  * y[B,O,OH,OW] = conv(x[B,C,H,W], w[O,C,kh,kw]) + bias[O], OH = (H+2ph-kh)/sh+1; with
  * relu != 0 the output is activated and d_pre_or_null receives the pre-activation.
  * Lowered to the 3xTF32 tcgen05 GEMM with K = C*kh*kw in (ic,kh,kw) order.
@@ -249,6 +249,16 @@ int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w, const v
 int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
                         void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
                         int W, int O, int kh, int kw, int ph, int pw, int sh, int sw);
+/* The same with a dilated window (Conv2DConfig.dilation, nn/layers/conv2d.v:15-21): taps at
+ * ih = oh*sh - ph + a*dh, iw = ow*sw - pw + b*dw, OH = (H + 2ph - dh(kh-1) - 1)/sh + 1
+ * (conv2d_forward_cpu_f32.v:26-62, conv2d_backward_cpu_f32.v:19,39,65).  dh = dw = 1 is the call
+ * above; other dilations run on the lowered route (patch matrix + GEMM). */
+int vtlb_conv2d_fwd_f32_dilated(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                                void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
+                                int sh, int sw, int dh, int dw, int relu, void* d_pre_or_null);
+int vtlb_conv2d_bwd_f32_dilated(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
+                                void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
+                                int W, int O, int kh, int kw, int ph, int pw, int sh, int sw, int dh, int dw);
 /* 2-D max pooling with the window geometry of internal.maxpool2d
  * (nn/internal/layers.v:21-66); the first maximum in scan order wins; d_idx (int32) holds
  * the flat index into the whole input.  Backward scatters g onto zeros (layers.v:69-84). */

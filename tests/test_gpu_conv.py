@@ -131,3 +131,36 @@ def test_maxpool_bit_exact(dev, orc, shape, kernel, pad, stride):
         assert np.array_equal(dgx.numpy(), ref)
     else:  # overlapping windows add in a different order
         assert np.abs(dgx.numpy() - ref).max() <= 1e-6
+
+
+@pytest.mark.parametrize("B,C,H,W,O,k,pad,stride,dil", [
+    (2, 3, 12, 11, 5, 3, (2, 2), (1, 1), (2, 2)),   # "same" output with dilation 2
+    (3, 4, 13, 9, 6, 3, (1, 0), (2, 1), (2, 3)),    # different dilation per axis, stride 2 down the rows
+    (1, 2, 7, 7, 3, 2, (0, 0), (1, 1), (3, 3)),     # 2x2 window spread over 4x4
+    (2, 3, 8, 8, 4, 3, (1, 1), (1, 1), (1, 1)),     # dilation 1 through the same entry point
+])
+def test_conv2d_dilated_vs_oracle(dev, orc, B, C, H, W, O, k, pad, stride, dil):
+    """Dilated windows (Conv2DConfig.dilation; conv2d_forward_cpu_f32.v:26-62, conv2d_backward_cpu_f32.v)."""
+    rng = np.random.default_rng(B + C + H + O + dil[0])
+    x = rng.standard_normal((B, C, H, W)).astype(np.float32)
+    w = (rng.uniform(-1, 1, (O, C, k, k)) * np.sqrt(6.0 / (C * k * k))).astype(np.float32)
+    b = (rng.standard_normal(O) * 0.1).astype(np.float32)
+    ref = orc.conv2d_fwd_f32(x, w, b, pad=pad, stride=stride, dil=dil)
+    _, _, OH, OW = ref.shape
+    dx_, dw_, db_ = dev.to_device(x), dev.to_device(w), dev.to_device(b)
+    dy, dpre = dev.zeros(ref.shape), dev.zeros(ref.shape)
+    dev.conv2d_fwd_f32(dx_, dw_, db_, dy, B, C, H, W, O, k, k, pad[0], pad[1], stride[0], stride[1], True, dpre, dil=dil)
+    assert np.abs(dpre.numpy() - ref).max() <= tol(C * k * k, x, w)
+    assert np.abs(dy.numpy() - orc.relu_f32(ref)).max() <= tol(C * k * k, x, w)
+    g = rng.standard_normal(ref.shape).astype(np.float32)
+    dg = dev.to_device(g)
+    gdx, gdw, gdb = dev.zeros(x.shape), dev.zeros(w.shape), dev.zeros(O)
+    dev.conv2d_bwd_f32(dg, dx_, dw_, gdx, gdw, gdb, B, C, H, W, O, k, k, pad[0], pad[1], stride[0], stride[1], dil=dil)
+    assert dev.check_status() == 0
+    rdx, rdw, rdb = orc.conv2d_bwd_f32(g, x, w, pad=pad, stride=stride, dil=dil)
+    assert np.abs(gdx.numpy() - rdx).max() <= tol(O * k * k, g, w)
+    assert np.abs(gdw.numpy() - rdw).max() <= tol(B * OH * OW, g, x)
+    assert np.abs(gdb.numpy() - rdb.ravel()).max() <= tol(B * OH * OW, g, np.ones(1))
+    from vtl_b200.capi import VtlbError
+    with pytest.raises(VtlbError):
+        dev.conv2d_fwd_f32(dx_, dw_, db_, dy, B, C, H, W, O, k, k, pad[0], pad[1], stride[0], stride[1], dil=(0, 1))

@@ -89,6 +89,8 @@ _PROTOS = {
     "vtlb_ckpt_decode_f32": [_vp, _vp, _sz, _vp, _sz],
     "vtlb_conv2d_fwd_f32": [_vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_vp],
     "vtlb_conv2d_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 11,
+    "vtlb_conv2d_fwd_f32_dilated": [_vp, _vp, _vp, _vp, _vp] + [_i] * 14 + [_vp],
+    "vtlb_conv2d_bwd_f32_dilated": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13,
     "vtlb_maxpool2d_fwd_f32": [_vp, _vp, _vp, _vp] + [_i] * 10,
     "vtlb_maxpool2d_bwd_f32": [_vp, _vp, _vp, _vp, _sz, _sz],
     "vtlb_mse_fwd_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp, _vp],
@@ -411,11 +413,20 @@ class Device:
     def ckpt_decode_f32(self, text, text_len, dst, n):
         self._ck(self.lib.vtlb_ckpt_decode_f32(self.h, _ptr(text), text_len, _ptr(dst), n))
 
-    def conv2d_fwd_f32(self, x, w, bias, y, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, relu=False, pre=None):
+    def conv2d_fwd_f32(self, x, w, bias, y, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, relu=False, pre=None, dil=None):
+        if dil is not None:
+            self._ck(self.lib.vtlb_conv2d_fwd_f32_dilated(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), B, Cc, H, W, O,
+                                                          kh, kw, ph, pw, sh, sw, dil[0], dil[1], int(relu), _ptr(pre)))
+            return
         self._ck(self.lib.vtlb_conv2d_fwd_f32(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), B, Cc, H, W, O,
                                               kh, kw, ph, pw, sh, sw, int(relu), _ptr(pre)))
 
-    def conv2d_bwd_f32(self, g, x, w, dx, dw, db, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw):
+    def conv2d_bwd_f32(self, g, x, w, dx, dw, db, B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, dil=None):
+        if dil is not None:
+            self._ck(self.lib.vtlb_conv2d_bwd_f32_dilated(self.h, _ptr(g), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw),
+                                                          _ptr(db), B, Cc, H, W, O, kh, kw, ph, pw, sh, sw, dil[0],
+                                                          dil[1]))
+            return
         self._ck(self.lib.vtlb_conv2d_bwd_f32(self.h, _ptr(g), _ptr(x), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db),
                                               B, Cc, H, W, O, kh, kw, ph, pw, sh, sw))
 

@@ -22,6 +22,7 @@ using f32::split1;
 
 struct ConvDims {
   int B, C, H, W, O, kh, kw, ph, pw, sh, sw, OH, OW;
+  int dh = 1, dw = 1;  // dilation (conv2d_forward_cpu_f32.v:26-62: ih = oh*s - p + kh*d)
   __host__ __device__ int P() const { return OH * OW; }
   __host__ __device__ int K() const { return C * kh * kw; }
   __host__ __device__ long long M() const { return (long long)B * OH * OW; }
@@ -49,7 +50,7 @@ __global__ void __launch_bounds__(256) im2colT_split_kernel(const float* __restr
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float v = 0.0f;
-        const int ih = oh * d.sh - d.ph + kh, iw = ow * d.sw - d.pw + kw;
+        const int ih = oh * d.sh - d.ph + kh * d.dh, iw = ow * d.sw - d.pw + kw * d.dw;
         if (m4 + j < M && ih >= 0 && ih < d.H && iw >= 0 && iw < d.W)
           v = __ldg(x + (((size_t)b * d.C + ic) * d.H + ih) * d.W + iw);
         split1(v, h[j], l[j]);
@@ -92,9 +93,9 @@ __global__ void __launch_bounds__(256) im2col_split_kernel(const float* __restri
       if (k < K) {
         const int ic = k / khw, r = k - ic * khw;
         const int kh = r / d.kw, kw = r - kh * d.kw;
-        k_off[threadIdx.x] = (ic * d.H + kh) * d.W + kw;
-        k_h[threadIdx.x] = kh;
-        k_w[threadIdx.x] = kw;
+        k_off[threadIdx.x] = (ic * d.H + kh * d.dh) * d.W + kw * d.dw;
+        k_h[threadIdx.x] = kh * d.dh;
+        k_w[threadIdx.x] = kw * d.dw;
       } else {
         k_off[threadIdx.x] = -1;
         k_h[threadIdx.x] = 0;
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restr
       const int ih = i / d.W, iw = i - ih * d.W;
       float s = 0.0f;
       for (int kh = 0; kh < d.kh; ++kh) {
-        const int th = ih + d.ph - kh;
+        const int th = ih + d.ph - kh * d.dh;
         if (th < 0) continue;
         int oh = th;
         if (!unit_stride) {
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(256) col2im_gather_kernel(const float* __restr
         }
         if (oh >= d.OH) continue;
         for (int kw = 0; kw < d.kw; ++kw) {
-          const int tw = iw + d.pw - kw;
+          const int tw = iw + d.pw - kw * d.dw;
           if (tw < 0) continue;
           int ow = tw;
           if (!unit_stride) {
@@ -424,10 +425,10 @@ bool igemm_taps_ok(int kh, int kw) { return kh * kw <= 32; }  // one validity bi
 
 int check_conv(vtlb_ctx* ctx, const char* fn, ConvDims& d) {
   if (d.B <= 0 || d.C <= 0 || d.H <= 0 || d.W <= 0 || d.O <= 0 || d.kh <= 0 || d.kw <= 0 || d.ph < 0 ||
-      d.pw < 0 || d.sh <= 0 || d.sw <= 0)
+      d.pw < 0 || d.sh <= 0 || d.sw <= 0 || d.dh <= 0 || d.dw <= 0)
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: bad convolution geometry", fn);
-  d.OH = (d.H + 2 * d.ph - (d.kh - 1) - 1) / d.sh + 1;
-  d.OW = (d.W + 2 * d.pw - (d.kw - 1) - 1) / d.sw + 1;
+  d.OH = (d.H + 2 * d.ph - d.dh * (d.kh - 1) - 1) / d.sh + 1;
+  d.OW = (d.W + 2 * d.pw - d.dw * (d.kw - 1) - 1) / d.sw + 1;
   if (d.OH <= 0 || d.OW <= 0) return vtlb_fail(ctx, VTLB_EINVAL, "%s: empty output", fn);
   if (d.M() > 0x7fffffffLL || d.M() * d.K() > (1LL << 40) || (long long)d.B * d.O > 0x7fffffffLL ||
       (long long)d.B * d.C * d.H * d.W > 0x7fffffffLL)
@@ -437,17 +438,20 @@ int check_conv(vtlb_ctx* ctx, const char* fn, ConvDims& d) {
 
 }  // namespace
 
-VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
-                                 void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
-                                 int sh, int sw, int relu, void* d_pre_or_null) {
-  VTLB_ENTER(ctx);
+namespace {
+
+int conv2d_fwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                    void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw, int sh, int sw,
+                    int dh, int dw, int relu, void* d_pre_or_null) {
   ConvDims d{B, C, H, W, O, kh, kw, ph, pw, sh, sw, 0, 0};
-  int rc = check_conv(ctx, "vtlb_conv2d_fwd_f32", d);
+  d.dh = dh;
+  d.dw = dw;
+  int rc = check_conv(ctx, fn, d);
   if (rc) return rc;
-  if (!d_x || !d_w || !d_y) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_fwd_f32: null pointer");
+  if (!d_x || !d_w || !d_y) return vtlb_fail(ctx, VTLB_EINVAL, "%s: null pointer", fn);
   const int M = (int)d.M(), K = d.K();
   f32::Planes p;
-  if (use_igemm(K) && igemm_taps_ok(kh, kw)) {
+  if (dh == 1 && dw == 1 && use_igemm(K) && igemm_taps_ok(kh, kw)) {  // dilated windows take the lowered route
     if ((rc = f32::alloc_planes(ctx, 0, O, K, 0, &p))) return rc;
     VTLB_CUDA(ctx, vtlb_launch_early(regroup_weights_split_kernel, dim3(f32::grid_for(ctx, (size_t)O * K, 256)), dim3(256),
                                      0, ctx->stream, (const float*)d_w, O, C, kh * kw, 0, p.ld, p.b_hi, p.b_lo));
@@ -472,17 +476,19 @@ VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w
   return f32::launch_tf32x3(ctx, p, M, O, K, epi);
 }
 
-VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
-                                 void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
-                                 int W, int O, int kh, int kw, int ph, int pw, int sh, int sw) {
-  VTLB_ENTER(ctx);
+int conv2d_bwd_impl(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w, void* d_dx_or_null,
+                    void* d_dw_or_null, void* d_db_or_null, int B, int C, int H, int W, int O, int kh, int kw, int ph,
+                    int pw, int sh, int sw, int dh, int dw) {
   ConvDims d{B, C, H, W, O, kh, kw, ph, pw, sh, sw, 0, 0};
+  d.dh = dh;
+  d.dw = dw;
+  const bool dilated = dh != 1 || dw != 1;
   int rc = check_conv(ctx, "vtlb_conv2d_bwd_f32", d);
   if (rc) return rc;
   if (!d_g) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: null gradient");
   const int M = (int)d.M(), K = d.K(), P = d.P();
   const float* g = (const float*)d_g;
-  if (d_dw_or_null && cwgrad::usable(sh, sw, kh, kw, d.OW, 1)) {
+  if (d_dw_or_null && cwgrad::usable(sh, sw, kh, kw, d.OW, dilated ? 2 : 1)) {
     // unit stride, window at most 3 x 3, output rows of at most 32 pixels: the implicit GEMM over pixels
     if (!d_x) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_weight needs x");
     const int parts = cwgrad::parts_for(ctx, B, C, O, d.OH);
@@ -526,7 +532,7 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
       if ((rc = f32::reduce_splits(ctx, (const float*)p.extra, S, (size_t)O * K, (float*)d_dw_or_null))) return rc;
     }
   }
-  if (d_dx_or_null && sh == 1 && sw == 1 && use_igemm(O * kh * kw) && igemm_taps_ok(kh, kw) &&
+  if (d_dx_or_null && !dilated && sh == 1 && sw == 1 && use_igemm(O * kh * kw) && igemm_taps_ok(kh, kw) &&
       (long long)B * O * d.OH * d.OW <= 0x7fffffffLL) {
     // dx[(b, ih, iw), ic] = sum over (oc, a, b) of g[b][oc][ih + ph - a][iw + pw - b] * W[oc][ic][a][b]
     if (!d_w) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_conv2d_bwd_f32: d_input needs the weights");
@@ -576,6 +582,41 @@ VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x
     VTLB_LAUNCHED(ctx);
   }
   return VTLB_OK;
+}
+
+}  // namespace
+
+VTLB_API int vtlb_conv2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                                 void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph, int pw,
+                                 int sh, int sw, int relu, void* d_pre_or_null) {
+  VTLB_ENTER(ctx);
+  return conv2d_fwd_impl(ctx, "vtlb_conv2d_fwd_f32", d_x, d_w, d_bias_or_null, d_y, B, C, H, W, O, kh, kw, ph, pw, sh,
+                         sw, 1, 1, relu, d_pre_or_null);
+}
+
+VTLB_API int vtlb_conv2d_fwd_f32_dilated(vtlb_ctx* ctx, const void* d_x, const void* d_w, const void* d_bias_or_null,
+                                         void* d_y, int B, int C, int H, int W, int O, int kh, int kw, int ph,
+                                         int pw, int sh, int sw, int dh, int dw, int relu, void* d_pre_or_null) {
+  VTLB_ENTER(ctx);
+  return conv2d_fwd_impl(ctx, "vtlb_conv2d_fwd_f32_dilated", d_x, d_w, d_bias_or_null, d_y, B, C, H, W, O, kh, kw, ph,
+                         pw, sh, sw, dh, dw, relu, d_pre_or_null);
+}
+
+VTLB_API int vtlb_conv2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
+                                 void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C, int H,
+                                 int W, int O, int kh, int kw, int ph, int pw, int sh, int sw) {
+  VTLB_ENTER(ctx);
+  return conv2d_bwd_impl(ctx, d_g, d_x, d_w, d_dx_or_null, d_dw_or_null, d_db_or_null, B, C, H, W, O, kh, kw, ph, pw,
+                         sh, sw, 1, 1);
+}
+
+VTLB_API int vtlb_conv2d_bwd_f32_dilated(vtlb_ctx* ctx, const void* d_g, const void* d_x, const void* d_w,
+                                         void* d_dx_or_null, void* d_dw_or_null, void* d_db_or_null, int B, int C,
+                                         int H, int W, int O, int kh, int kw, int ph, int pw, int sh, int sw, int dh,
+                                         int dw) {
+  VTLB_ENTER(ctx);
+  return conv2d_bwd_impl(ctx, d_g, d_x, d_w, d_dx_or_null, d_dw_or_null, d_db_or_null, B, C, H, W, O, kh, kw, ph, pw,
+                         sh, sw, dh, dw);
 }
 
 VTLB_API int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, void* d_idx, int B, int C, int H,

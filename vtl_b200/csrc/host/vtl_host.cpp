@@ -296,9 +296,10 @@ struct Conv2DGate : Gate {
     Tensor dX;
     if (input->requires_grad) dX = Tensor::empty(s, xs);
     GradBucket b = GradBucket::make(s, weight->value.shape(), {1, O});
-    s->check(vtlb_conv2d_bwd_f32(s->ctx, g.data(), input->value.data(), weight->value.data(),
-                                 dX.defined() ? dX.data() : nullptr, b.dW.data(), b.db.data(), B, C, H,
-                                 W, O, kh, kw, cfg.pad_h, cfg.pad_w, cfg.stride_h, cfg.stride_w));
+    s->check(vtlb_conv2d_bwd_f32_dilated(s->ctx, g.data(), input->value.data(), weight->value.data(),
+                                         dX.defined() ? dX.data() : nullptr, b.dW.data(), b.db.data(), B, C, H, W, O,
+                                         kh, kw, cfg.pad_h, cfg.pad_w, cfg.stride_h, cfg.stride_w, cfg.dilation_h,
+                                         cfg.dilation_w));
     b.allreduce(s);
     return {dX, b.dW, b.db};
   }
@@ -450,8 +451,8 @@ Conv2DLayer::Conv2DLayer(Context* ctx, std::vector<int> in_shape_, int out_ch_, 
   bias = ctx->variable(Tensor::zeros(s, {1, out_ch}));
 }
 std::vector<int> Conv2DLayer::output_shape() const {
-  const int oh = (in_shape[1] + 2 * cfg.pad_h - (kh - 1) - 1) / cfg.stride_h + 1;
-  const int ow = (in_shape[2] + 2 * cfg.pad_w - (kw - 1) - 1) / cfg.stride_w + 1;
+  const int oh = (in_shape[1] + 2 * cfg.pad_h - cfg.dilation_h * (kh - 1) - 1) / cfg.stride_h + 1;
+  const int ow = (in_shape[2] + 2 * cfg.pad_w - cfg.dilation_w * (kw - 1) - 1) / cfg.stride_w + 1;
   return {out_ch, oh, ow};
 }
 VarPtr Conv2DLayer::run(const VarPtr& input, bool relu) {
@@ -464,9 +465,10 @@ VarPtr Conv2DLayer::run(const VarPtr& input, bool relu) {
   Tensor y = Tensor::empty(s, {B, os[0], os[1], os[2]});
   Tensor pre;
   if (relu) pre = Tensor::empty(s, y.shape());
-  s->check(vtlb_conv2d_fwd_f32(s->ctx, input->value.data(), weight->value.data(), bias->value.data(),
-                               y.data(), B, in_ch, xs[2], xs[3], out_ch, kh, kw, cfg.pad_h, cfg.pad_w,
-                               cfg.stride_h, cfg.stride_w, relu ? 1 : 0, relu ? pre.data() : nullptr));
+  s->check(vtlb_conv2d_fwd_f32_dilated(s->ctx, input->value.data(), weight->value.data(), bias->value.data(),
+                                       y.data(), B, in_ch, xs[2], xs[3], out_ch, kh, kw, cfg.pad_h, cfg.pad_w,
+                                       cfg.stride_h, cfg.stride_w, cfg.dilation_h, cfg.dilation_w, relu ? 1 : 0,
+                                       relu ? pre.data() : nullptr));
   auto gate = std::make_unique<Conv2DGate>();
   gate->input = input;
   gate->weight = weight;

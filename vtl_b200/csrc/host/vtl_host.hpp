@@ -232,9 +232,9 @@ struct FlattenLayer : Layer {
   const char* type_name() const override { return "FlattenLayer"; }
 };
 
-// nn/layers/conv2d.v:15-105 -- weight [oc, ic, kh, kw], bias [1, oc]; groups = 1, dilation = 1
+// nn/layers/conv2d.v:15-105 -- weight [oc, ic, kh, kw], bias [1, oc]; groups = 1
 struct Conv2DConfig {
-  int pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1;
+  int pad_h = 0, pad_w = 0, stride_h = 1, stride_w = 1, dilation_h = 1, dilation_w = 1;
 };
 struct Conv2DLayer : Layer {
   VarPtr weight, bias;
@@ -251,8 +251,8 @@ struct Conv2DLayer : Layer {
   std::vector<std::pair<std::string, int>> config() const override {
     return {{"in_channels", in_ch},        {"out_channels", out_ch},      {"kernel_h", kh},
             {"kernel_w", kw},              {"padding_h", cfg.pad_h},      {"padding_w", cfg.pad_w},
-            {"stride_h", cfg.stride_h},    {"stride_w", cfg.stride_w},    {"dilation_h", 1},
-            {"dilation_w", 1},             {"groups", 1}};
+            {"stride_h", cfg.stride_h},    {"stride_w", cfg.stride_w},    {"dilation_h", cfg.dilation_h},
+            {"dilation_w", cfg.dilation_w}, {"groups", 1}};
   }
 
  private:

@@ -36,6 +36,8 @@ int vtlh_model_linear(vtlh_model* m, int output_size);
 int vtlh_model_relu(vtlh_model* m);
 int vtlh_model_flatten(vtlh_model* m);
 int vtlh_model_conv2d(vtlh_model* m, int in_ch, int out_ch, int kh, int kw, int ph, int pw, int sh, int sw);
+int vtlh_model_conv2d_dilated(vtlh_model* m, int in_ch, int out_ch, int kh, int kw, int ph, int pw, int sh, int sw,
+                              int dh, int dw);
 int vtlh_model_maxpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw);
 int vtlh_model_mse_loss(vtlh_model* m);
 int vtlh_model_softmax_cross_entropy_loss(vtlh_model* m);

@@ -112,6 +112,10 @@ int vtlh_model_flatten(vtlh_model* m) { return guard([&] { m->seq->flatten(); })
 int vtlh_model_conv2d(vtlh_model* m, int ic, int oc, int kh, int kw, int ph, int pw, int sh, int sw) {
   return guard([&] { m->seq->conv2d(ic, oc, kh, kw, Conv2DConfig{ph, pw, sh, sw}); });
 }
+int vtlh_model_conv2d_dilated(vtlh_model* m, int ic, int oc, int kh, int kw, int ph, int pw, int sh, int sw, int dh,
+                              int dw) {
+  return guard([&] { m->seq->conv2d(ic, oc, kh, kw, Conv2DConfig{ph, pw, sh, sw, dh, dw}); });
+}
 int vtlh_model_maxpool2d(vtlh_model* m, int kh, int kw, int ph, int pw, int sh, int sw) {
   return guard([&] { m->seq->maxpool2d(kh, kw, ph, pw, sh, sw); });
 }

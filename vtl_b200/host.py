@@ -43,6 +43,7 @@ def load() -> C.CDLL:
             "vtlh_model_create": [vp, C.POINTER(vp)], "vtlh_model_destroy": [vp],
             "vtlh_model_input": [vp, i, ip], "vtlh_model_linear": [vp, i], "vtlh_model_relu": [vp],
             "vtlh_model_flatten": [vp], "vtlh_model_conv2d": [vp] + [i] * 8,
+            "vtlh_model_conv2d_dilated": [vp] + [i] * 10,
             "vtlh_model_maxpool2d": [vp] + [i] * 6, "vtlh_model_mse_loss": [vp],
             "vtlh_model_softmax_cross_entropy_loss": [vp], "vtlh_model_set_fuse_relu": [vp, i],
             "vtlh_model_adam": [vp, d, d, d, d], "vtlh_model_adamw": [vp, d, d, d, d, d],
@@ -177,9 +178,9 @@ class Model:
     def flatten(self):
         _ck(self.lib.vtlh_model_flatten(self.h))
 
-    def conv2d(self, in_ch, out_ch, kernel, padding=(0, 0), stride=(1, 1)):
-        _ck(self.lib.vtlh_model_conv2d(self.h, in_ch, out_ch, kernel[0], kernel[1], padding[0], padding[1],
-                                       stride[0], stride[1]))
+    def conv2d(self, in_ch, out_ch, kernel, padding=(0, 0), stride=(1, 1), dilation=(1, 1)):
+        _ck(self.lib.vtlh_model_conv2d_dilated(self.h, in_ch, out_ch, kernel[0], kernel[1], padding[0], padding[1],
+                                               stride[0], stride[1], dilation[0], dilation[1]))
 
     def maxpool2d(self, kernel, padding, stride):
         _ck(self.lib.vtlh_model_maxpool2d(self.h, kernel[0], kernel[1], padding[0], padding[1], stride[0],
