@@ -67,15 +67,16 @@ class ShardedInt8MLP:
         aq = [self.q_in.ptr + c * Mc * self.dims[0] for c in range(C)]
         sa = [self.sa_in.ptr + 4 * c * Mc for c in range(C)]
         shards = 1
-        issued = waited = 0          # collectives enqueued / covered by a comm_wait so far
-        gathered_at = [0] * C        # sequence number of the block's last all-gather
+        # Every wait is for one collective, not for the communication stream as a whole: mark c follows
+        # the all-gather of row block c (bulk lane), mark 32 + c its max all-reduce (small lane).
+        gathered = [False] * C       # an all-gather of the block is in flight
         for li, L in enumerate(self.layers):
             last = li + 1 == len(self.layers)
             n, K = L["n"], L["K"]
             for c in range(C):
-                if gathered_at[c] > waited:  # the block's codes must have arrived
-                    dev.comm_wait()
-                    waited = issued
+                if gathered[c]:      # the block's codes must have arrived
+                    dev.comm_wait_mark(c)
+                    gathered[c] = False
                 y = (y_out.ptr if (last and y_out is not None) else L["Y"].ptr) + 4 * c * Mc * n
                 if last:
                     dev.linear_i8_fwd_sharded_a(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K,
@@ -89,19 +90,18 @@ class ShardedInt8MLP:
                 if R > 1:
                     q_loc = L["q_local"].ptr + c * Mc * n
                     dev.allreduce_max_f32_async(amax, Mc)
-                    issued += 1
-                    dev.comm_wait()
-                    waited = issued
+                    dev.comm_mark(dev.LANE_SMALL, 32 + c)
+                    dev.comm_wait_mark(32 + c)
                     dev.quant_rows_i8(y, Mc, n, q_loc, sa_out, amax)
                     dev.allgather_async(q_loc, q_all, Mc * n)
-                    issued += 1
-                    gathered_at[c] = issued
+                    dev.comm_mark(dev.LANE_BULK, c)
+                    gathered[c] = True
                 else:
                     dev.quant_rows_i8(y, Mc, n, q_all, sa_out, amax)
                 aq[c], sa[c] = q_all, sa_out
             shards = R
-        if issued > waited:
-            dev.comm_wait()
+        if R > 1:
+            dev.comm_wait()  # nothing of this pass is left in flight (and the library forgets the operands it tracks)
         return y_out if y_out is not None else self.layers[-1]["Y"]
 
 

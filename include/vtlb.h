@@ -449,6 +449,16 @@ int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
 int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_recv, size_t bytes_per_rank);
 /* Makes the compute stream wait for every collective enqueued so far. */
 int vtlb_comm_wait(vtlb_ctx* ctx);
+/* Waiting for ONE collective instead of all of them.  Collectives run on two lanes: the bulk lane
+ * (all-gather, sum all-reduce) and the small lane (max all-reduce), which has a communicator and
+ * a stream of its own where the NCCL at hand can split communicators, so that a few kilobytes of
+ * row maxima do not queue behind hundreds of megabytes of codes.  vtlb_comm_mark records mark
+ * `slot` (0..63) behind the collectives enqueued so far on `lane`; vtlb_comm_wait_mark makes the
+ * compute stream wait for that mark only.  A slot may be marked again once its wait is enqueued. */
+#define VTLB_COMM_LANE_BULK 0
+#define VTLB_COMM_LANE_SMALL 1
+int vtlb_comm_mark(vtlb_ctx* ctx, int lane, int slot);
+int vtlb_comm_wait_mark(vtlb_ctx* ctx, int slot);
 
 #ifdef __cplusplus
 }

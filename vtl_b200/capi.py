@@ -109,7 +109,7 @@ _PROTOS = {
     "vtlb_allreduce_sum_f32_async": [_vp, _vp, _sz],
     "vtlb_allreduce_max_f32_async": [_vp, _vp, _sz],
     "vtlb_allgather_async": [_vp, _vp, _vp, _sz],
-    "vtlb_comm_wait": [_vp],
+    "vtlb_comm_wait": [_vp], "vtlb_comm_mark": [_vp, _i, _i], "vtlb_comm_wait_mark": [_vp, _i],
 }
 
 _lib = None
@@ -543,6 +543,14 @@ class Device:
 
     def allgather_async(self, send, recv, bytes_per_rank):
         self._ck(self.lib.vtlb_allgather_async(self.h, _ptr(send), _ptr(recv), bytes_per_rank))
+
+    LANE_BULK, LANE_SMALL = 0, 1
+
+    def comm_mark(self, lane: int, slot: int):
+        self._ck(self.lib.vtlb_comm_mark(self.h, lane, slot))
+
+    def comm_wait_mark(self, slot: int):
+        self._ck(self.lib.vtlb_comm_wait_mark(self.h, slot))
 
     def comm_wait(self):
         self._ck(self.lib.vtlb_comm_wait(self.h))

@@ -51,6 +51,16 @@ struct vtlb_ctx {
   size_t small_cached_bytes = 0;
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
+  // A second communicator (split off the first) on a stream of its own carries the small,
+  // latency-critical collectives (the max all-reduce of row maxima), so that they do not queue
+  // behind a bulk all-gather or gradient all-reduce still running on the first.  Null when the
+  // NCCL at hand cannot split communicators: both lanes then share the first.
+  void* comm_small = nullptr;
+  cudaStream_t comm_small_stream = nullptr;
+  // Marks: events recorded behind the collectives enqueued so far on one lane, for which the compute
+  // stream can wait individually (vtlb_comm_mark / vtlb_comm_wait_mark).
+  static constexpr int kCommMarks = 64;
+  cudaEvent_t comm_marks[kCommMarks] = {};
   // Byte ranges handed to collectives on the communication stream since the compute stream last
   // waited for it.  Freeing (or recycling) a block that overlaps one of them must first order the
   // compute stream after the communication stream; every other free needs no such wait, which is

@@ -117,6 +117,7 @@ VTLB_API int vtlb_sync(vtlb_ctx* ctx) {
   VTLB_ENTER(ctx);
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_in));
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->comm_stream));
+  if (ctx->comm_small_stream) VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->comm_small_stream));
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   VTLB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_out));
   return VTLB_OK;
@@ -324,6 +325,10 @@ VTLB_API int vtlb_free(vtlb_ctx* ctx, void* d_ptr) {
     for (size_t i = 0; i < ctx->comm_inflight.size() && !hit; ++i)
       hit = ctx->comm_inflight[i].first < e && b < ctx->comm_inflight[i].second;
     if (hit) {
+      if (ctx->comm_small) {
+        VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_small_stream));
+        VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+      }
       VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
       VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
       ctx->comm_inflight.clear();

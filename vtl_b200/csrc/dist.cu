@@ -15,6 +15,7 @@ struct NcclApi {
   ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommSplit)(ncclComm_t, int, int, ncclComm_t*, void*) = nullptr;  // optional (NCCL >= 2.18)
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                             cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t,
@@ -38,6 +39,7 @@ int load_nccl(vtlb_ctx* ctx) {
   VTLB_SYM(AllGather, "ncclAllGather");
   VTLB_SYM(GetErrorString, "ncclGetErrorString");
 #undef VTLB_SYM
+  *(void**)(&g_nccl.CommSplit) = dlsym(h, "ncclCommSplit");
   g_nccl.handle = h;
   return VTLB_OK;
 }
@@ -50,12 +52,13 @@ int load_nccl(vtlb_ctx* ctx) {
                        g_nccl.GetErrorString(r__));                               \
   } while (0)
 
-// Orders the communication stream after everything enqueued on the compute stream.
-int comm_after_compute(vtlb_ctx* ctx) {
+// Orders a communication stream after everything enqueued on the compute stream.
+int comm_after_compute(vtlb_ctx* ctx, cudaStream_t lane) {
   VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_compute, ctx->stream));
-  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_compute, 0));
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(lane, ctx->ev_compute, 0));
   return VTLB_OK;
 }
+int comm_after_compute(vtlb_ctx* ctx) { return comm_after_compute(ctx, ctx->comm_stream); }
 
 int need_comm(vtlb_ctx* ctx, const char* fn) {
   if (!ctx->comm) return vtlb_fail(ctx, VTLB_ESTATE, "%s: vtlb_comm_init_rank has not been called", fn);
@@ -89,6 +92,23 @@ VTLB_API int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void
   ctx->comm = comm;
   ctx->nranks = nranks;
   ctx->rank = rank;
+  // the lane for small collectives: a communicator of its own, so that NCCL may run both at once
+  static int two_lanes = -1;
+  if (two_lanes < 0) {
+    const char* e = getenv("VTLB_COMM_TWO_LANES");
+    two_lanes = e ? atoi(e) != 0 : 1;
+  }
+  if (two_lanes && g_nccl.CommSplit && nranks > 1) {
+    ncclComm_t small = nullptr;
+    if (g_nccl.CommSplit(comm, 0, rank, &small, nullptr) == ncclSuccess && small) {
+      if (cudaStreamCreateWithFlags(&ctx->comm_small_stream, cudaStreamNonBlocking) == cudaSuccess) {
+        ctx->comm_small = small;
+      } else {
+        cudaGetLastError();
+        g_nccl.CommDestroy(small);
+      }
+    }
+  }
   return VTLB_OK;
 }
 
@@ -96,6 +116,18 @@ VTLB_API int vtlb_comm_destroy(vtlb_ctx* ctx) {
   if (!ctx || !ctx->comm) return VTLB_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->comm_stream);
+  if (ctx->comm_small) {
+    cudaStreamSynchronize(ctx->comm_small_stream);
+    g_nccl.CommDestroy((ncclComm_t)ctx->comm_small);
+    cudaStreamDestroy(ctx->comm_small_stream);
+    ctx->comm_small = nullptr;
+    ctx->comm_small_stream = nullptr;
+  }
+  for (auto& ev : ctx->comm_marks)
+    if (ev) {
+      cudaEventDestroy(ev);
+      ev = nullptr;
+    }
   g_nccl.CommDestroy((ncclComm_t)ctx->comm);
   ctx->comm = nullptr;
   ctx->nranks = 1;
@@ -119,8 +151,11 @@ VTLB_API int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n) 
   int rc = need_comm(ctx, __func__);
   if (rc) return rc;
   if (n == 0) return VTLB_OK;
-  if ((rc = comm_after_compute(ctx))) return rc;
-  VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclMax, (ncclComm_t)ctx->comm, ctx->comm_stream));
+  const bool small = ctx->comm_small != nullptr;
+  cudaStream_t lane = small ? ctx->comm_small_stream : ctx->comm_stream;
+  if ((rc = comm_after_compute(ctx, lane))) return rc;
+  VTLB_NCCL(ctx, g_nccl.AllReduce(d_buf, d_buf, n, ncclFloat32, ncclMax,
+                                  (ncclComm_t)(small ? ctx->comm_small : ctx->comm), lane));
   vtlb_comm_track(ctx, d_buf, n * sizeof(float));
   return VTLB_OK;
 }
@@ -137,9 +172,32 @@ VTLB_API int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_rec
   return VTLB_OK;
 }
 
+VTLB_API int vtlb_comm_mark(vtlb_ctx* ctx, int lane, int slot) {
+  VTLB_ENTER(ctx);
+  if (slot < 0 || slot >= vtlb_ctx::kCommMarks || lane < 0 || lane > 1)
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_comm_mark: lane %d / slot %d out of range", lane, slot);
+  if (!ctx->comm_marks[slot]) VTLB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->comm_marks[slot], cudaEventDisableTiming));
+  cudaStream_t s = (lane == VTLB_COMM_LANE_SMALL && ctx->comm_small) ? ctx->comm_small_stream : ctx->comm_stream;
+  VTLB_CUDA(ctx, cudaEventRecord(ctx->comm_marks[slot], s));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_comm_wait_mark(vtlb_ctx* ctx, int slot) {
+  VTLB_ENTER(ctx);
+  if (slot < 0 || slot >= vtlb_ctx::kCommMarks || !ctx->comm_marks[slot])
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_comm_wait_mark: slot %d was never marked", slot);
+  vtlb_prof_scope prof(ctx, VTLB_PHASE_COMM_WAIT);
+  VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->comm_marks[slot], 0));
+  return VTLB_OK;
+}
+
 VTLB_API int vtlb_comm_wait(vtlb_ctx* ctx) {
   VTLB_ENTER(ctx);
   vtlb_prof_scope prof(ctx, VTLB_PHASE_COMM_WAIT);  // how long the compute stream stands idle here
+  if (ctx->comm_small) {
+    VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_small_stream));
+    VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  }
   VTLB_CUDA(ctx, cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
   VTLB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
   ctx->comm_inflight.clear();  // the compute stream is now ordered after every collective enqueued so far
