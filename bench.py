@@ -422,6 +422,8 @@ def run_int8(args, ranks):
     # milliseconds of launches, timed in isolation (the burst regime of the clocks)
     gemm_ms = case.gemm_kernel_ms(min(max(args.steps, 20), 200))
     kernel_clocks = sampler.snapshot() if ranks.rank == 0 else None
+    # what the tensor cores do with INT8 MMAs when nothing has to be loaded (same clocks regime)
+    yard_burst = dev.int8_issue_yardstick(20000)
     # whole steps: repeats of K-step regions, each behind a barrier + sync, one event pair per region;
     # seconds of back-to-back steps, so these run under the power cap
     l0 = dev.launch_count()
@@ -429,6 +431,7 @@ def run_int8(args, ranks):
     launches = dev.launch_count() - l0
     ms_step = statistics.median(per_step)
     step_clocks = sampler.snapshot() if ranks.rank == 0 else None
+    yard_loaded = dev.int8_issue_yardstick(20000)  # again, straight after seconds of load (power-capped clocks)
     assert dev.check_status() == 0
 
     # end to end through the C ABI with host buffers (pinned), copies inside the timed region: every
@@ -523,7 +526,13 @@ def run_int8(args, ranks):
             "clocks": dict(step_clocks, whole_run=clocks,
                            note="sampled through NVML during the timed repeats of whole steps; whole_run covers "
                                 "every pass of this process (kernel-alone pass, repeats, end-to-end, sweep)"),
-            "roofline": dict(roof, clocks=kernel_clocks),
+            "roofline": dict(roof, clocks=kernel_clocks,
+                             int8_issue_yardstick={
+                                 "tops_after_warmup": yard_burst, "tops_after_sustained_load": yard_loaded,
+                                 "frac_of_yardstick": (roof["achieved"] / yard_burst) if roof["bound"] == "tensor" else None,
+                                 "what": "this library's own kernel issuing tcgen05.mma.kind::i8 (cta_group::2, 256x256x32) "
+                                         "back to back on operands resident in shared memory, no loads: the INT8 "
+                                         "ceiling measured on this GPU, beside the 2 x bf16 proxy used as peak"}),
         }
         if sweep is not None:
             out["sweep"] = sweep

@@ -435,6 +435,12 @@ size_t vtlb_ckpt_text_len(size_t n);
 int vtlb_ckpt_encode_f32(vtlb_ctx* ctx, const void* d_src, size_t n, void* d_text);
 int vtlb_ckpt_decode_f32(vtlb_ctx* ctx, const void* d_text, size_t text_len, void* d_dst, size_t n);
 
+/* Measurement helper (no counterpart in the reference): the rate at which this GPU's tensor cores
+ * execute INT8 MMAs when nothing has to be loaded -- every CTA pair issues 4 * mma_groups
+ * tcgen05.mma.kind::i8 instructions (256 x 256 x 32) on operands resident in shared memory.  The
+ * ceiling of any INT8 GEMM at the clocks of the moment, in TOPS; launches two kernels and blocks. */
+int vtlb_int8_issue_yardstick(vtlb_ctx* ctx, int mma_groups, double* tops_out);
+
 /* ---- collectives (NCCL over NVLink) ---------------------------------------
  * No counterpart in the reference (single device).  One ctx per rank/process.
  * vtlb_comm_unique_id fills a 128-byte id on one rank; the caller ships it to

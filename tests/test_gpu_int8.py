@@ -182,3 +182,14 @@ def test_linear_i8_fwd_amax_returns_the_row_maxima_of_its_output(dev, orc, M, N,
     assert np.array_equal(dmax.numpy().view(np.uint32), np.abs(ref).max(axis=1).view(np.uint32))
     for buf in (dQw, dSw, dQa, dSa, db, dY, dmax):
         buf.free()
+
+
+def test_int8_issue_yardstick(dev):
+    """The no-load INT8 MMA loop runs, leaves the status clean and reports a rate of the order of the
+    device's INT8 tensor throughput (nominally 4.5 POPS dense; well above any real GEMM here)."""
+    tops = dev.int8_issue_yardstick(4000)
+    assert dev.check_status() == 0
+    assert 1500.0 < tops < 6000.0, tops
+    from vtl_b200.capi import VtlbError
+    with pytest.raises(VtlbError):
+        dev.int8_issue_yardstick(0)

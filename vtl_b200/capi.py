@@ -109,6 +109,7 @@ _PROTOS = {
     "vtlb_allreduce_sum_f32_async": [_vp, _vp, _sz],
     "vtlb_allreduce_max_f32_async": [_vp, _vp, _sz],
     "vtlb_allgather_async": [_vp, _vp, _vp, _sz],
+    "vtlb_int8_issue_yardstick": [_vp, _i, C.POINTER(C.c_double)],
     "vtlb_comm_wait": [_vp], "vtlb_comm_mark": [_vp, _i, _i], "vtlb_comm_wait_mark": [_vp, _i],
 }
 
@@ -523,6 +524,12 @@ class Device:
     def linear_i8_fwd_amax(self, Aq_shards, shards, sa, Wq, sw, bias, Y, M, N, K, relu, row_amax):
         self._ck(self.lib.vtlb_linear_i8_fwd_amax(self.h, _ptr(Aq_shards), shards, _ptr(sa), _ptr(Wq), _ptr(sw),
                                                   _ptr(bias), _ptr(Y), M, N, K, int(relu), _ptr(row_amax)))
+
+    def int8_issue_yardstick(self, mma_groups: int = 20000) -> float:
+        """TOPS of back-to-back INT8 MMAs on shared-memory-resident operands (no loads)."""
+        t = C.c_double(0)
+        self._ck(self.lib.vtlb_int8_issue_yardstick(self.h, mma_groups, C.byref(t)))
+        return t.value
 
     # -- collectives
     def comm_unique_id(self) -> bytes:

@@ -655,3 +655,91 @@ VTLB_API int vtlb_linear_i8_fwd_amax(vtlb_ctx* ctx, const void* d_Aq_shards, int
                             M, N, K, relu, d_row_amax);
 }
 
+
+// ---------------------------------------------------------------- INT8 issue-rate yardstick
+// What the tensor cores deliver when nothing has to be loaded: every CTA pair issues
+// tcgen05.mma.cta_group::2.kind::i8 (M = 256, N = 256, K = 32) back to back on operands that sit in
+// shared memory for the whole launch, into one accumulator.  The result is meaningless; the rate is the
+// ceiling of any INT8 GEMM on this device at the clocks it runs at, measured instead of derived from a
+// bf16 figure.  No global memory is read or written apart from the status word.
+namespace {
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+i8_issue_yardstick_kernel(int mma_groups, uint32_t* status) {
+  constexpr uint32_t TILE = 128 * 128;  // 128 rows of 128 bytes: this CTA's half of A, and of B
+  constexpr uint32_t IDESC = ptx::umma_idesc(ptx::kCfmtS32, ptx::kFmtS8, 256, 256);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t bar = base + 2 * TILE;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bar - raw) + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = gemm2::cluster_ctarank();
+  for (uint32_t i = threadIdx.x; i < 2 * TILE / 16; i += blockDim.x)  // defined operands (zeros)
+    ptx::st_shared_v4(base + i * 16, 0u, 0u, 0u, 0u);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  ptx::fence_proxy_async();
+  if (warp == 1) {
+    gemm2::tmem_alloc2(ptx::smem_u32(tmem_slot), 256);
+    gemm2::tmem_relinquish2();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  gemm2::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (warp == 0 && lane == 0 && rank == 0) {
+    const uint64_t da = ptx::umma_desc_k_sw128(base), db = ptx::umma_desc_k_sw128(base + TILE);
+    for (int g = 0; g < mma_groups; ++g) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) gemm2::umma_i8_pair(tmem_base, da + 2u * kk, db + 2u * kk, IDESC, (g | kk) ? 1u : 0u);
+    }
+    gemm2::umma_commit_pair(bar);  // arrives in both CTAs once every MMA has completed
+  }
+  if (warp == 0) {
+    // both CTAs stay until the MMAs have stopped reading their shared memory
+    bool ok = ptx::mbar_wait_bounded(bar, 0, abort_flag, gemm::WAIT_LIMIT_NS, 200);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && lane == 0) atomicOr(status, VTLB_ST_GEMM_TIMEOUT);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  gemm2::cluster_sync_all();
+  ptx::tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    gemm2::tmem_dealloc2(tmem_base, 256);
+  }
+}
+
+}  // namespace
+
+VTLB_API int vtlb_int8_issue_yardstick(vtlb_ctx* ctx, int mma_groups, double* tops_out) {
+  VTLB_ENTER(ctx);
+  if (!tops_out || mma_groups < 1 || mma_groups > (1 << 20))
+    return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_int8_issue_yardstick: bad arguments");
+  constexpr int SMEM = 2 * 128 * 128 + 64 + 1024;
+  const int pairs = ctx->sm_count / 2;
+  cudaEvent_t e0, e1;
+  VTLB_CUDA(ctx, cudaEventCreate(&e0));
+  VTLB_CUDA(ctx, cudaEventCreate(&e1));
+  i8_issue_yardstick_kernel<<<2 * pairs, 128, SMEM, ctx->stream>>>(mma_groups, ctx->d_status);  // warm-up
+  VTLB_CUDA(ctx, cudaEventRecord(e0, ctx->stream));
+  i8_issue_yardstick_kernel<<<2 * pairs, 128, SMEM, ctx->stream>>>(mma_groups, ctx->d_status);
+  VTLB_CUDA(ctx, cudaEventRecord(e1, ctx->stream));
+  ctx->launches += 2;
+  cudaError_t e = cudaGetLastError();
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventSynchronize(e1);
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (e != cudaSuccess) return vtlb_fail(ctx, VTLB_ECUDA, "vtlb_int8_issue_yardstick: %s", cudaGetErrorString(e));
+  *tops_out = 2.0 * 256 * 256 * 32 * 4.0 * mma_groups * pairs / (ms * 1e-3) / 1e12;
+  return VTLB_OK;
+}
