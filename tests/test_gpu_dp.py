@@ -149,6 +149,7 @@ def test_plane_passing_changes_no_bit():
         for on in (True, False):
             s = make_session(False)
             s.set_pass_planes(on)
+            s.set_plane_min_flops(0.0)       # hand planes on at this size too
             s.dev.set_small_gemm_limit(0.0)  # all products large enough for the tensor-core path
             m = build(s, dims, relu_after, params, "adamw")
             m.set_fuse_relu(fuse_relu)

@@ -96,7 +96,7 @@ VTLB_API int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void
   static int two_lanes = -1;
   if (two_lanes < 0) {
     const char* e = getenv("VTLB_COMM_TWO_LANES");
-    two_lanes = e ? atoi(e) != 0 : 1;
+    two_lanes = e ? atoi(e) != 0 : 0;  // off by default: on 2 GPUs two NCCL kernels at once cost the GEMMs more than the queueing
   }
   if (two_lanes && g_nccl.CommSplit && nranks > 1) {
     ncclComm_t small = nullptr;

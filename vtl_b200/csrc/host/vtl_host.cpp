@@ -239,13 +239,14 @@ struct LinearGate : Gate {
     // gradient's planes come with g when the layer above produced it, the input's transposed planes
     // with the activation; dX is masked by the ReLU below this layer in the same launch and leaves
     // its own planes for the layer below.
-    const bool planes = s->pass_planes && vtlb_f32_planes_worthwhile(s->ctx, M, N, K) != 0;
+    const bool tc = s->pass_planes && vtlb_f32_planes_worthwhile(s->ctx, M, N, K) != 0;  // tensor-core route
+    const bool planes = tc && 2.0 * M * N * K >= s->plane_min_flops;
     const Tensor& xin = input->value;
-    const vtlb_planes* g_rows = planes && g.rows_planes ? &g.rows_planes->p : nullptr;
-    const vtlb_planes* g_cols = planes && g.cols_planes ? &g.cols_planes->p : nullptr;
-    const vtlb_planes* x_cols = planes && xin.cols_planes ? &xin.cols_planes->p : nullptr;
+    const vtlb_planes* g_rows = tc && g.rows_planes ? &g.rows_planes->p : nullptr;
+    const vtlb_planes* g_cols = tc && g.cols_planes ? &g.cols_planes->p : nullptr;
+    const vtlb_planes* x_cols = tc && xin.cols_planes ? &xin.cols_planes->p : nullptr;
     const float* mask = nullptr;
-    if (dX.defined() && planes && input->relu_cache.defined() && input->relu_cache.size() == dX.size()) {
+    if (dX.defined() && tc && input->relu_cache.defined() && input->relu_cache.size() == dX.size()) {
       mask = input->relu_cache.data();
       dX.relu_masked = true;
     }
@@ -387,7 +388,9 @@ static VarPtr linear_run(LinearLayer& L, const VarPtr& input, bool relu) {
   // While a tape is recorded, a large layer followed by its ReLU leaves the operand planes of its
   // output for the products that read it next: the next layer's forward (rows) and that layer's
   // weight gradient (transposed).
-  const bool planes = s->pass_planes && relu && !ctx->no_grad && vtlb_f32_planes_worthwhile(s->ctx, M, L.out_features, L.in_features);
+  const bool planes = s->pass_planes && relu && !ctx->no_grad &&
+                      vtlb_f32_planes_worthwhile(s->ctx, M, L.out_features, L.in_features) &&
+                      2.0 * M * L.out_features * L.in_features >= s->plane_min_flops;
   if (planes) {
     if (s->plane_kinds & 1) y.rows_planes = PlanePair::make(s, M, L.out_features);
     if (s->plane_kinds & 2) y.cols_planes = PlanePair::make(s, L.out_features, M);

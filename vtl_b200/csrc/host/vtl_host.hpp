@@ -49,6 +49,12 @@ struct Session {
   // that writes them to the products that read them, and fold the ReLU backward into the gradient
   // product (off: every product splits its own operands, as a lone vtlb_linear_*_f32 call does).
   bool pass_planes = true;
+  // Planes are handed on only by products of at least this many flops (2*M*N*K).  Measured on config 4:
+  // at 65536 rows per GPU (2.2 TFLOP per product, the GPU under its power cap for seconds) the step is
+  // 2 % shorter with the hand-over; at 8192 rows (0.27 TFLOP, the shard of an 8-GPU job) the epilogue's
+  // extra stores cost the GEMMs more than the split passes they replace and the step is 3.6 % longer.
+  // The ReLU backward is folded into the gradient product at every size (neutral to slightly faster).
+  double plane_min_flops = 1.0e12;
   int plane_kinds = 3;  // which planes a large layer's product leaves: bit 0 rows, bit 1 transposed (VTL_PLANE_KINDS)
   uint64_t init_seed = 0, init_counter = 0;
   uint64_t next_init_seed() { return init_seed * 0x100000001B3ull + 0x9E3779B97F4A7C15ull * ++init_counter; }

@@ -23,6 +23,8 @@ int vtlh_session_set_seed(vtlh_session* s, unsigned long long seed);
 /* Whether large Linear layers hand TF32 operand planes from producer to consumer and fold the ReLU
  * backward into the gradient product (default on; off = every product splits its own operands). */
 int vtlh_session_set_pass_planes(vtlh_session* s, int on);
+/* Smallest product (2*M*N*K flops) that hands its planes on; default 1e12 (see vtl_host.hpp). */
+int vtlh_session_set_plane_min_flops(vtlh_session* s, double flops);
 /* nn/internal/init.v: compute_fans (as written there) and variance_scaled into a host array;
  * fan_mode 0 = fan_avg, 1 = fan_in, 2 = fan_out; distribution 0 = uniform, 1 = normal. */
 int vtlh_compute_fans(int ndim, const int* shape, long long* f0, long long* f1);

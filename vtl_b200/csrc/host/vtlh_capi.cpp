@@ -73,6 +73,10 @@ int vtlh_session_set_pass_planes(vtlh_session* s, int on) {
   s->s->pass_planes = on != 0;
   return VTLB_OK;
 }
+int vtlh_session_set_plane_min_flops(vtlh_session* s, double flops) {
+  s->s->plane_min_flops = flops;
+  return VTLB_OK;
+}
 int vtlh_compute_fans(int ndim, const int* shape, long long* f0, long long* f1) {
   return guard([&] {
     const auto f = compute_fans(std::vector<int>(shape, shape + ndim));

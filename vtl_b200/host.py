@@ -38,6 +38,7 @@ def load() -> C.CDLL:
             "vtlh_session_create": [i, C.POINTER(vp)], "vtlh_session_destroy": [vp],
             "vtlh_session_comm_init": [vp, i, i, vp],
             "vtlh_session_set_seed": [vp, C.c_ulonglong], "vtlh_session_set_pass_planes": [vp, i],
+            "vtlh_session_set_plane_min_flops": [vp, d],
             "vtlh_compute_fans": [i, ip, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)],
             "vtlh_variance_scaled": [vp, i, ip, d, i, i, C.c_ulonglong, vp],
             "vtlh_model_create": [vp, C.POINTER(vp)], "vtlh_model_destroy": [vp],
@@ -122,6 +123,10 @@ class Session:
     def set_pass_planes(self, on: bool):
         """Producer-to-consumer hand-over of TF32 operand planes in large Linear layers (default on)."""
         _ck(self.lib.vtlh_session_set_pass_planes(self.h, int(on)))
+
+    def set_plane_min_flops(self, flops: float):
+        """Smallest product (2*M*N*K) whose planes are handed on (default 1e12)."""
+        _ck(self.lib.vtlh_session_set_plane_min_flops(self.h, float(flops)))
 
     def variance_scaled(self, shape, scale, fan_mode, distribution, seed):
         """internal.variance_scaled (nn/internal/init.v:36-60) -> host array."""
