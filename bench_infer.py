@@ -6,7 +6,8 @@ tokens ~N(0,1), ReLU between layers.
 With N ranks every layer is sharded by output columns (rank r owns N_l/N channels and their
 scales) and the activations are exchanged between layers:
     local f32 slab [M, N_l/N]  ->  row max-abs  ->  NCCL all-reduce(max) over ranks
-    ->  quantise the slab with the global row scale  ->  NCCL all-gather of the int8 codes
+    ->  quantise the slab with the global row scale  ->  all-gather of the int8 codes (each rank
+        copies its codes into the peers' buffers with the copy engines; NCCL's kernel on request)
 The next layer's GEMM reads the gathered shards in place (vtlb_linear_i8_fwd_sharded_a).
 The last layer's output stays sharded.  Strong scaling: the total work is fixed."""
 from __future__ import annotations
@@ -32,10 +33,18 @@ class ShardedInt8MLP:
     With more than one rank the tokens are processed as `chunks` independent row blocks (rows
     are quantised independently, so a block can run ahead through the layers): while the codes
     of one block are all-gathered on the communication stream, the GEMM of the next block runs
-    on the compute stream."""
+    on the compute stream.
 
-    def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5, chunks=None):
+    `exchange` (obj -> [obj of every rank], a host channel) switches the all-gathers from NCCL's
+    kernel to the copy engines: each rank exports its receive buffers to the others, and a
+    gather is every rank copying its codes straight into the peers' buffers, so the SMs stay
+    with the GEMMs (VTLB_C5_GATHER=nccl keeps NCCL's all-gather)."""
+
+    def __init__(self, dev, world, rank, tokens=TOKENS, dims=DIMS, seed=5, chunks=None, exchange=None):
         self.dev, self.R, self.rank, self.M, self.dims = dev, world, rank, tokens, dims
+        self.push = bool(world > 1 and exchange is not None
+                         and os.environ.get("VTLB_C5_GATHER", "push") != "nccl")
+        self._shared, self._opened = [], []
         self.C = chunks if chunks else (int(os.environ.get("VTLB_C5_ROW_BLOCKS", "2")) if world > 1 else 1)
         assert tokens % self.C == 0
         self.Mc = tokens // self.C
@@ -52,12 +61,37 @@ class ShardedInt8MLP:
             dev.quant_rows_i8(dW, n, K, dQ, dS)
             dev.sync()
             dW.free()
-            self.layers.append(dict(K=K, N=N, n=n, Wq=dQ, sw=dS, bias=dev.to_device(b),
-                                    Y=dev.zeros((tokens, n)), amax=dev.zeros(tokens),
-                                    q_local=dev.zeros((tokens, n), np.int8),
-                                    # per row block: the gathered shards [world][Mc][n]
-                                    q_all=dev.zeros((self.C, world, self.Mc, n), np.int8), sa=dev.zeros(tokens)))
+            L = dict(K=K, N=N, n=n, Wq=dQ, sw=dS, bias=dev.to_device(b),
+                     Y=dev.zeros((tokens, n)), amax=dev.zeros(tokens), sa=dev.zeros(tokens))
+            # per row block: the gathered shards [world][Mc][n]
+            if self.push and li + 1 < len(dims) - 1:
+                ptr, handle = dev.shared_alloc(self.C * world * self.Mc * n)
+                self._shared.append(ptr)
+                L["q_all_ptr"], L["handle"] = ptr, handle
+            else:
+                L["q_local"] = dev.zeros((tokens, n), np.int8)
+                L["q_all"] = dev.zeros((self.C, world, self.Mc, n), np.int8)
+                L["q_all_ptr"] = L["q_all"].ptr
+            self.layers.append(L)
+        if self.push:
+            # every rank's handles -> the address of each peer's buffer in this process
+            table = exchange([L.get("handle") for L in self.layers])
+            for li, L in enumerate(self.layers):
+                if "handle" not in L:
+                    continue
+                L["peers"] = [None if r == rank else dev.shared_open(table[r][li]) for r in range(world)]
+                self._opened += [p for p in L["peers"] if p]
+            exchange(0)  # all handles are open before any rank can start pushing
         self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's (after the device has gone idle)."""
+        for p in self._opened:
+            self.dev.shared_close(p)
+        self._opened = []
+        for p in self._shared:
+            self.dev.shared_free(p)
+        self._shared = []
 
     def forward(self, dX, y_out=None):
         """`y_out`: an alternative buffer for the last layer's output (for double buffering)."""
@@ -84,16 +118,24 @@ class ShardedInt8MLP:
                     continue
                 amax = L["amax"].ptr + 4 * c * Mc
                 sa_out = L["sa"].ptr + 4 * c * Mc
-                q_all = L["q_all"].ptr + c * R * Mc * n
+                q_all = L["q_all_ptr"] + c * R * Mc * n
                 # the GEMM's epilogue also leaves the row maxima of its output slab (no second pass over Y)
                 dev.linear_i8_fwd_amax(aq[c], shards, sa[c], L["Wq"], L["sw"], L["bias"], y, Mc, n, K, True, amax)
                 if R > 1:
-                    q_loc = L["q_local"].ptr + c * Mc * n
                     dev.allreduce_max_f32_async(amax, Mc)
                     dev.comm_mark(dev.LANE_SMALL, 32 + c)
                     dev.comm_wait_mark(32 + c)
-                    dev.quant_rows_i8(y, Mc, n, q_loc, sa_out, amax)
-                    dev.allgather_async(q_loc, q_all, Mc * n)
+                    if self.push:
+                        # quantise into this rank's own part of the gathered block, then copy it
+                        # into the same part of every peer's block
+                        mine = (c * R + self.rank) * Mc * n
+                        dev.quant_rows_i8(y, Mc, n, q_all + self.rank * Mc * n, sa_out, amax)
+                        dev.allgather_push_async(q_all + self.rank * Mc * n,
+                                                 [p + mine if p else None for p in L["peers"]], Mc * n)
+                    else:
+                        q_loc = L["q_local"].ptr + c * Mc * n
+                        dev.quant_rows_i8(y, Mc, n, q_loc, sa_out, amax)
+                        dev.allgather_async(q_loc, q_all, Mc * n)
                     dev.comm_mark(dev.LANE_BULK, c)
                     gathered[c] = True
                 else:
@@ -152,7 +194,7 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
     from vtl_b200 import capi
     dev = capi.Device(ranks.local_rank)
     ranks.attach(dev)
-    model = ShardedInt8MLP(dev, ranks.world, ranks.rank)
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank, exchange=ranks.gather_objects)
     X = np.random.default_rng(5).standard_normal((TOKENS, DIMS[0]), dtype=np.float32)
     dX = dev.to_device(X)
     cuda_sync(dev)
@@ -232,7 +274,8 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
                                       "layers (baseline config 5)",
                           "tokens": TOKENS, "tokens_per_s": TOKENS / (ms_step * 1e-3),
                           "parallelism": f"output columns sharded x{ranks.world}; per layer all-reduce(max) of row "
-                                         "maxima and all-gather of int8 codes over NCCL" if ranks.world > 1
+                                         "maxima (NCCL) and all-gather of int8 codes (copy engines into "
+                                         "the peers' buffers)" if ranks.world > 1
                           else "single GPU",
                           "l2": "weights (4 x 235 MB int8) and activations exceed the 126 MB L2"},
                "e2e": {"value": total_ops() / (e2e_ms / esteps * 1e-3) / 1e12, "unit": "TOPS",
@@ -247,6 +290,9 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
         if ranks.world == 1:
             cb, _ = cpu_sample()
             out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    dev.sync()
+    ranks.barrier()  # no rank is still copying into a peer's buffer
+    model.close()
     dev.close()
     return out
 
@@ -257,12 +303,14 @@ def sharded_parity(ranks, dev, dims=(1024, 4096, 1024, 4096, 1024), tokens=512, 
     rank's output slab collected on rank 0 and compared with the UNSHARDED CPU oracle: the int32
     GEMM is exact, max is associative and quantisation is element-wise, so the result must be the
     same bit for bit however many ranks share the columns.  Rank 0 returns the report."""
-    model = ShardedInt8MLP(dev, ranks.world, ranks.rank, tokens=tokens, dims=list(dims), seed=55, chunks=chunks)
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank, tokens=tokens, dims=list(dims), seed=55, chunks=chunks,
+                           exchange=ranks.gather_objects)
     X = np.random.default_rng(56).standard_normal((tokens, dims[0]), dtype=np.float32)
     dX = dev.to_device(X)
     y = model.forward(dX)
     dev.sync()
-    slabs = ranks.gather_objects(y.numpy())
+    slabs = ranks.gather_objects(y.numpy())  # every rank is past its last copy into a peer's buffer
+    model.close()
     if ranks.rank != 0:
         return None
     from oracle import oracle
@@ -292,7 +340,7 @@ def run_tp(ranks, tools, steps=10, warmup=3):
     dev = capi.Device(ranks.local_rank)
     ranks.attach(dev)
     parity = sharded_parity(ranks, dev)
-    model = ShardedInt8MLP(dev, ranks.world, ranks.rank)
+    model = ShardedInt8MLP(dev, ranks.world, ranks.rank, exchange=ranks.gather_objects)
     dX = dev.to_device(np.random.default_rng(5).standard_normal((TOKENS, DIMS[0]), dtype=np.float32))
 
     def run_steps(n):
@@ -313,6 +361,10 @@ def run_tp(ranks, tools, steps=10, warmup=3):
     gemm_ms, gemm_n, gemm_ops = dev.profile_gemm_read()
     dev.profile_gemm(False)
     assert dev.check_status() == 0
+    dev.sync()
+    ranks.barrier()  # no rank is still copying into a peer's buffer
+    push = model.push
+    model.close()
     dev.close()
     if ranks.rank != 0:
         return None
@@ -334,6 +386,8 @@ def run_tp(ranks, tools, steps=10, warmup=3):
                                              "time the compute stream stood idle until an all-reduce(max) or "
                                              "all-gather had finished (CUDA-event brackets, profiled passes)"},
             "parallelism": (f"output columns sharded x{ranks.world}; per layer and row block: all-reduce(max) of row "
-                            "maxima, quantise, all-gather of int8 codes over NCCL; the next GEMM reads the gathered "
+                            "maxima (NCCL), quantise, all-gather of int8 codes ("
+                            + ("copy engines into the peers' buffers" if push else "NCCL")
+                            + "); the next GEMM reads the gathered "
                             "shards in place") if ranks.world > 1 else "single GPU",
             "parity": parity}

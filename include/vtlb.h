@@ -453,6 +453,22 @@ int vtlb_comm_destroy(vtlb_ctx* ctx);
 int vtlb_allreduce_sum_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
 int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
 int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_recv, size_t bytes_per_rank);
+/* All-gather by the copy engines instead of an NCCL kernel (which occupies 16-32 SMs and slows a
+ * persistent GEMM running beside it far more than its share).  Every rank allocates its receive
+ * buffer with vtlb_shared_alloc (a plain device allocation plus its 64-byte CUDA IPC handle), ships
+ * the handle to the other ranks' processes over any host channel, and opens theirs with
+ * vtlb_shared_open.  vtlb_allgather_push_async then copies `bytes` from d_src into every non-null
+ * d_peer_dst[r] (the address of this rank's part inside rank r's buffer) on the bulk lane, after the
+ * compute work enqueued so far, and appends an all-reduce of one word: once that has completed on a
+ * rank (vtlb_comm_mark / vtlb_comm_wait_mark / vtlb_comm_wait) every rank's part has landed in its
+ * buffer.  The caller writes its own part itself.  A part may be pushed into a peer's buffer again
+ * only after a later collective of this communicator has completed behind the peer's last read of
+ * it (the one-word all-reduce of any later push does).  No counterpart in the reference. */
+int vtlb_shared_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out, void* h_handle64);
+int vtlb_shared_free(vtlb_ctx* ctx, void* d_ptr);
+int vtlb_shared_open(vtlb_ctx* ctx, const void* h_handle64, void** d_peer_out);
+int vtlb_shared_close(vtlb_ctx* ctx, void* d_peer);
+int vtlb_allgather_push_async(vtlb_ctx* ctx, const void* d_src, void* const* d_peer_dst, int npeers, size_t bytes);
 /* Makes the compute stream wait for every collective enqueued so far. */
 int vtlb_comm_wait(vtlb_ctx* ctx);
 /* Waiting for ONE collective instead of all of them.  Collectives run on two lanes: the bulk lane

@@ -41,9 +41,14 @@ def main():
     from vtl_b200 import capi
     dev = capi.Device(ranks.local_rank)
     ranks.attach(dev)
-    par = bench_infer.sharded_parity(ranks, dev, dims=(512, 1024, 512), tokens=256, chunks=2)
-    if ranks.rank == 0:
-        assert par["bit_exact"], par
+    # the codes all-gathered by the copy engines (each rank copies into the peers' buffers), then
+    # by NCCL's kernel; three layers make a buffer that is pushed into again within one pass
+    for gather in ("push", "nccl"):
+        os.environ["VTLB_C5_GATHER"] = gather
+        for dims, chunks in (((512, 1024, 512), 2), ((256, 512, 256, 512, 256), 4)):
+            par = bench_infer.sharded_parity(ranks, dev, dims=dims, tokens=256, chunks=chunks)
+            if ranks.rank == 0:
+                assert par["bit_exact"], (gather, par)
     assert dev.check_status() == 0
     dev.close()
     ranks.close()

@@ -59,7 +59,10 @@ def test_linear_kat_from_reference_session_test(dev, orc):
 
 
 @pytest.mark.parametrize("M,N,K,relu", [(64, 256, 784, True), (64, 10, 256, False),
-                                        (300, 130, 90, True), (1024, 512, 512, True)])
+                                        (300, 130, 90, True), (1024, 512, 512, True),
+                                        # few output features, many inputs: the streaming kernels of linear_narrow.cu
+                                        (256, 10, 16384, False), (37, 16, 2048, True), (5, 1, 4100, False),
+                                        (130, 3, 6148, True)])
 def test_linear_fwd_bwd(dev, orc, M, N, K, relu):
     rng = np.random.default_rng(M + N + K)
     X = rng.random((M, K), dtype=np.float32)

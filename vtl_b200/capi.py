@@ -110,6 +110,9 @@ _PROTOS = {
     "vtlb_allreduce_max_f32_async": [_vp, _vp, _sz],
     "vtlb_allgather_async": [_vp, _vp, _vp, _sz],
     "vtlb_int8_issue_yardstick": [_vp, _i, C.POINTER(C.c_double)],
+    "vtlb_shared_alloc": [_vp, _sz, C.POINTER(_vp), _vp], "vtlb_shared_free": [_vp, _vp],
+    "vtlb_shared_open": [_vp, _vp, C.POINTER(_vp)], "vtlb_shared_close": [_vp, _vp],
+    "vtlb_allgather_push_async": [_vp, _vp, C.POINTER(_vp), _i, _sz],
     "vtlb_comm_wait": [_vp], "vtlb_comm_mark": [_vp, _i, _i], "vtlb_comm_wait_mark": [_vp, _i],
 }
 
@@ -552,6 +555,29 @@ class Device:
         self._ck(self.lib.vtlb_allgather_async(self.h, _ptr(send), _ptr(recv), bytes_per_rank))
 
     LANE_BULK, LANE_SMALL = 0, 1
+
+    # -- all-gather by copy engines: buffers that the other ranks' processes can write
+    def shared_alloc(self, nbytes: int):
+        """-> (device pointer, 64-byte IPC handle) of a zeroed buffer the peers may open."""
+        p, h = _vp(), C.create_string_buffer(64)
+        self._ck(self.lib.vtlb_shared_alloc(self.h, nbytes, C.byref(p), h))
+        return p.value, h.raw
+
+    def shared_free(self, ptr: int):
+        self._ck(self.lib.vtlb_shared_free(self.h, ptr))
+
+    def shared_open(self, handle: bytes) -> int:
+        p = _vp()
+        self._ck(self.lib.vtlb_shared_open(self.h, C.c_char_p(handle), C.byref(p)))
+        return p.value
+
+    def shared_close(self, ptr: int):
+        self._ck(self.lib.vtlb_shared_close(self.h, ptr))
+
+    def allgather_push_async(self, src, peer_dst, nbytes: int):
+        """peer_dst: one device address per rank (None / 0 = skip, e.g. this rank itself)."""
+        arr = (_vp * len(peer_dst))(*[_vp(p) if p else _vp(None) for p in peer_dst])
+        self._ck(self.lib.vtlb_allgather_push_async(self.h, _ptr(src), arr, len(peer_dst), nbytes))
 
     def comm_mark(self, lane: int, slot: int):
         self._ck(self.lib.vtlb_comm_mark(self.h, lane, slot))

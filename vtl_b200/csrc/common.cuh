@@ -59,6 +59,7 @@ struct vtlb_ctx {
   cudaStream_t comm_small_stream = nullptr;
   // Marks: events recorded behind the collectives enqueued so far on one lane, for which the compute
   // stream can wait individually (vtlb_comm_mark / vtlb_comm_wait_mark).
+  float* comm_barrier_word = nullptr;  // one word all-reduced behind pushed copies (vtlb_allgather_push_async)
   static constexpr int kCommMarks = 64;
   cudaEvent_t comm_marks[kCommMarks] = {};
   // Byte ranges handed to collectives on the communication stream since the compute stream last

@@ -123,6 +123,10 @@ VTLB_API int vtlb_comm_destroy(vtlb_ctx* ctx) {
     ctx->comm_small = nullptr;
     ctx->comm_small_stream = nullptr;
   }
+  if (ctx->comm_barrier_word) {
+    cudaFree(ctx->comm_barrier_word);
+    ctx->comm_barrier_word = nullptr;
+  }
   for (auto& ev : ctx->comm_marks)
     if (ev) {
       cudaEventDestroy(ev);
@@ -169,6 +173,93 @@ VTLB_API int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_rec
   VTLB_NCCL(ctx, g_nccl.AllGather(d_send, d_recv, bytes_per_rank, ncclInt8, (ncclComm_t)ctx->comm, ctx->comm_stream));
   vtlb_comm_track(ctx, d_send, bytes_per_rank);
   vtlb_comm_track(ctx, d_recv, bytes_per_rank * (size_t)ctx->nranks);
+  return VTLB_OK;
+}
+
+// ---------------------------------------------------------------- all-gather by copy engines
+// NCCL's all-gather runs as a kernel on 16 to 32 SMs.  Beside a persistent GEMM that wants every SM
+// (one CTA pair per TPC, tiles assigned statically) that costs far more than its share: pairs that
+// start late finish late, and the column-sharded inference pipeline measured its GEMMs 50 % slower
+// while an all-gather was in flight.  Here the copy engines move the data: every rank exports its
+// receive buffer to the other processes (CUDA IPC), and an all-gather is each rank copying its part
+// straight into every peer's buffer over NVLink, followed by an all-reduce of one word -- when that
+// completes on a rank, every rank has entered it, which it does only after its own copies: all parts
+// have landed everywhere.  No SM is used except by that one-word collective.
+VTLB_API int vtlb_shared_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out, void* h_handle64) {
+  VTLB_ENTER(ctx);
+  if (!d_out || !h_handle64 || bytes == 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_shared_alloc: bad arguments");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  *d_out = nullptr;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return vtlb_fail(ctx, VTLB_ENOMEM, "vtlb_shared_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+  }
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(p);
+    return vtlb_fail(ctx, VTLB_ECUDA, "vtlb_shared_alloc: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  VTLB_CUDA(ctx, cudaMemset(p, 0, bytes));
+  memcpy(h_handle64, &h, sizeof h);
+  *d_out = p;
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_shared_free(vtlb_ctx* ctx, void* d_ptr) {
+  VTLB_ENTER(ctx);
+  if (!d_ptr) return VTLB_OK;
+  VTLB_CUDA(ctx, cudaDeviceSynchronize());
+  VTLB_CUDA(ctx, cudaFree(d_ptr));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_shared_open(vtlb_ctx* ctx, const void* h_handle64, void** d_peer_out) {
+  VTLB_ENTER(ctx);
+  if (!h_handle64 || !d_peer_out) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_shared_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, h_handle64, sizeof h);
+  *d_peer_out = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(d_peer_out, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return vtlb_fail(ctx, VTLB_ECUDA, "vtlb_shared_open: cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+  }
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_shared_close(vtlb_ctx* ctx, void* d_peer) {
+  VTLB_ENTER(ctx);
+  if (!d_peer) return VTLB_OK;
+  VTLB_CUDA(ctx, cudaDeviceSynchronize());
+  VTLB_CUDA(ctx, cudaIpcCloseMemHandle(d_peer));
+  return VTLB_OK;
+}
+
+VTLB_API int vtlb_allgather_push_async(vtlb_ctx* ctx, const void* d_src, void* const* d_peer_dst, int npeers,
+                                       size_t bytes) {
+  VTLB_ENTER(ctx);
+  int rc = need_comm(ctx, __func__);
+  if (rc) return rc;
+  if (!d_src || !d_peer_dst || npeers < 0) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_allgather_push_async: bad arguments");
+  if (!ctx->comm_barrier_word) {
+    VTLB_CUDA(ctx, cudaMalloc(&ctx->comm_barrier_word, 256));
+    VTLB_CUDA(ctx, cudaMemset(ctx->comm_barrier_word, 0, 256));
+  }
+  if ((rc = comm_after_compute(ctx))) return rc;
+  // rank r starts with peer r + 1: at every moment the ranks write to different receivers, so no
+  // receiver's link carries more than one copy at a time
+  for (int i = 1; i <= npeers; ++i) {
+    const int r = (ctx->rank + i) % npeers;
+    if (d_peer_dst[r] && bytes)
+      VTLB_CUDA(ctx, cudaMemcpyAsync(d_peer_dst[r], d_src, bytes, cudaMemcpyDeviceToDevice, ctx->comm_stream));
+  }
+  VTLB_NCCL(ctx, g_nccl.AllReduce(ctx->comm_barrier_word, ctx->comm_barrier_word, 1, ncclFloat32, ncclSum,
+                                  (ncclComm_t)ctx->comm, ctx->comm_stream));
+  vtlb_comm_track(ctx, d_src, bytes);
   return VTLB_OK;
 }
 

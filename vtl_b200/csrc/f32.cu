@@ -311,6 +311,10 @@ int linear_fwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_X, const void* 
   if ((rc = check_planes(ctx, fn, "input", x_rows)) || (rc = check_planes(ctx, fn, "output", y_rows)) ||
       (rc = check_planes(ctx, fn, "transposed output", y_cols)))
     return rc;
+  if (!x_rows && !y_rows && !y_cols && 2.0 * M * N * K <= ctx->small_gemm_flops &&
+      f32::narrow_linear_ok(M, N, K, d_X, d_W, d_X))
+    return f32::narrow_linear_fwd(ctx, (const float*)d_X, (const float*)d_W, (const float*)d_b_or_null, (float*)d_Y, M, N,
+                                  K, relu, (float*)d_pre_or_null);
   GemmExtras ex;
   ex.a_planes = x_rows;
   ex.out_rows = y_rows;
@@ -332,6 +336,20 @@ int linear_bwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_G, const void* 
     return rc;
   if (!d_dX_or_null && (d_relu_mask_src_or_null || dx_rows || dx_cols))
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: a mask or dX planes were given without a dX output", fn);
+  // a layer with few output features and many inputs: memory-bound kernels that stream X / dX once
+  const bool any_planes = g_rows || g_cols || x_cols || dx_rows || dx_cols || d_relu_mask_src_or_null;
+  const bool narrow = !any_planes && 2.0 * M * N * K <= ctx->small_gemm_flops;
+  if (narrow && d_dX_or_null && d_W && f32::narrow_linear_ok(M, N, K, d_dX_or_null, d_W, d_W)) {
+    if ((rc = f32::narrow_linear_dx(ctx, (const float*)d_G, (const float*)d_W, (float*)d_dX_or_null, M, N, K))) return rc;
+    d_dX_or_null = nullptr;
+  }
+  if (narrow && d_dW_or_null && d_X && f32::narrow_linear_ok(M, N, K, d_X, d_dW_or_null, d_X)) {
+    if ((rc = f32::narrow_linear_dw(ctx, (const float*)d_G, (const float*)d_X, (float*)d_dW_or_null,
+                                    (float*)d_db_or_null, M, N, K)))
+      return rc;
+    d_dW_or_null = nullptr;
+    d_db_or_null = nullptr;
+  }
   if (d_dX_or_null) {  // dX[M,K] = G[M,N] . W[N,K]   (then, optionally, ReLU backward of the layer below)
     if (!d_W) return vtlb_fail(ctx, VTLB_EINVAL, "%s: dX needs W", fn);
     GemmExtras ex;

@@ -276,6 +276,15 @@ int sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, cons
                 const float* B, float* C, const float* bias, int relu, float* pre,
                 float* a_rowsum = nullptr, bool* rowsum_done = nullptr);
 
+// Linear layers with at most 16 output features and at least 2048 inputs (linear_narrow.cu): Y = X.W^T + b,
+// dX = G.W, dW = G^T.X with db = column sums of G (either of dW / db may be null), each streaming its
+// long operand once.  narrow_linear_ok checks shape and the alignment of the three long operands.
+bool narrow_linear_ok(int M, int N, int K, const void* a, const void* b, const void* c);
+int narrow_linear_fwd(vtlb_ctx* ctx, const float* X, const float* W, const float* bias, float* Y, int M, int N, int K,
+                      int relu, float* pre);
+int narrow_linear_dx(vtlb_ctx* ctx, const float* G, const float* W, float* dX, int M, int N, int K);
+int narrow_linear_dw(vtlb_ctx* ctx, const float* G, const float* X, float* dW, float* db, int M, int N, int K);
+
 // out[i] = sum_s partial[s][i] (fixed order, f32 round-to-nearest), n elements.
 int reduce_splits(vtlb_ctx* ctx, const float* partial, int splits, size_t n, float* out);
 
