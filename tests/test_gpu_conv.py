@@ -107,6 +107,36 @@ def test_conv2d_split_k_path(dev, orc):
     assert np.abs(db - rdb.ravel()).max() <= tol(B * H * W, g, np.ones(1))
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 6, 8), (4, 64, 32, 32), (1, 1, 2, 4), (3, 5, 10, 12)])
+def test_maxpool2x2_backward_direct_and_with_relu(dev, orc, shape):
+    """The tiling 2x2 window: dX written directly equals the scatter onto zeros bit for bit; with the
+    pooled output handed in it equals scatter followed by the backward of a ReLU in front of the pool."""
+    rng = np.random.default_rng(sum(shape) + 1)
+    pre = rng.standard_normal(shape).astype(np.float32)
+    pre[0, 0, 0, :2] = -1.0
+    pre[0, 0, 1, :2] = [-0.5, -2.0]  # a window that is negative throughout: its gradient must vanish
+    x = orc.relu_f32(pre)
+    ry, ridx = orc.maxpool2d_fwd_f32(x, (2, 2), (0, 0), (2, 2))
+    B, C, H, W = shape
+    dx = dev.to_device(x)
+    dy, didx = dev.zeros(ry.shape), dev.zeros(ry.shape, np.int32)
+    dev.maxpool2d_fwd_f32(dx, dy, didx, B, C, H, W, 2, 2, 0, 0, 2, 2)
+    g = rng.standard_normal(ry.shape).astype(np.float32)
+    dg = dev.to_device(g)
+    out = dev.to_device(np.full(shape, 9.0, np.float32))  # stale contents must not survive
+    dev.maxpool2x2_bwd_f32(dg, didx, None, out, B, C, H, W)
+    scat = orc.maxpool2d_bwd_f32(g, ridx, shape)
+    assert np.array_equal(out.numpy().view(np.uint32), scat.view(np.uint32))
+    dev.maxpool2x2_bwd_f32(dg, didx, dy, out, B, C, H, W)
+    ref = orc.relu_bwd_f32(scat, pre)
+    assert np.array_equal(out.numpy(), ref)
+    assert out.numpy()[0, 0, :2, :2].any() == False  # noqa: E712
+    from vtl_b200 import capi
+    with pytest.raises(capi.VtlbError):
+        dev.maxpool2x2_bwd_f32(dg, didx, None, out, B, C, H, W + 2)
+    assert dev.check_status() == 0
+
+
 @pytest.mark.parametrize("shape,kernel,pad,stride", [((2, 3, 6, 8), (2, 2), (0, 0), (2, 2)),
                                                       ((4, 64, 32, 32), (2, 2), (0, 0), (2, 2)),
                                                       ((2, 3, 5, 6), (2, 2), (0, 0), (2, 2)),   # general kernel

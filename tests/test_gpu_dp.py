@@ -167,3 +167,29 @@ def test_plane_passing_changes_no_bit():
         assert losses == base[0]
         for a, b in zip(grads + ps, base[1] + base[2]):
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_shared_buffer_and_push_without_peers():
+    """A buffer for the copy-engine all-gather comes back zeroed with a 64-byte handle; a push with
+    no peer to write to is just the one-word all-reduce behind the compute stream; argument errors."""
+    from vtl_b200 import capi
+    dev = capi.Device(0)
+    dev.comm_init_rank(1, 0, dev.comm_unique_id())
+    ptr, handle = dev.shared_alloc(1 << 20)
+    assert ptr and len(handle) == 64 and any(handle)
+    back = np.empty(1 << 20, np.uint8)
+    dev.d2h_raw(back.ctypes.data, ptr, back.nbytes)
+    dev.sync()
+    assert not back.any()
+    src = dev.to_device(np.arange(4096, dtype=np.float32))
+    dev.allgather_push_async(src, [None], 4096 * 4)
+    dev.comm_mark(dev.LANE_BULK, 3)
+    dev.comm_wait_mark(3)
+    dev.comm_wait()
+    dev.sync()
+    assert np.array_equal(src.numpy(), np.arange(4096, dtype=np.float32))
+    with pytest.raises(capi.VtlbError):
+        dev.shared_alloc(0)
+    assert dev.check_status() == 0
+    dev.shared_free(ptr)
+    dev.close()

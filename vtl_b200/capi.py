@@ -93,6 +93,7 @@ _PROTOS = {
     "vtlb_conv2d_bwd_f32_dilated": [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13,
     "vtlb_maxpool2d_fwd_f32": [_vp, _vp, _vp, _vp] + [_i] * 10,
     "vtlb_maxpool2d_bwd_f32": [_vp, _vp, _vp, _vp, _sz, _sz],
+    "vtlb_maxpool2x2_bwd_f32": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i],
     "vtlb_mse_fwd_bwd_f32": [_vp, _vp, _vp, _sz, _sz, _vp, _vp],
     "vtlb_softmax_ce_fwd_bwd_f32": [_vp, _vp, _vp, _i, _i, _i, _vp, _vp],
     "vtlb_adam_step_f32": [_vp, _i, C.POINTER(AdamTensor), _d, _d, _d, _d, _i],
@@ -437,6 +438,10 @@ class Device:
     def maxpool2d_fwd_f32(self, x, y, idx, B, Cc, H, W, kh, kw, ph, pw, sh, sw):
         self._ck(self.lib.vtlb_maxpool2d_fwd_f32(self.h, _ptr(x), _ptr(y), _ptr(idx), B, Cc, H, W, kh, kw,
                                                  ph, pw, sh, sw))
+
+    def maxpool2x2_bwd_f32(self, g, idx, y, dx, B, Cc, H, W):
+        """y (the pooled output) or None; with y the backward of a ReLU in front of the pool is fused."""
+        self._ck(self.lib.vtlb_maxpool2x2_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(y), _ptr(dx), B, Cc, H, W))
 
     def maxpool2d_bwd_f32(self, g, idx, dx, n_out, n_in):
         self._ck(self.lib.vtlb_maxpool2d_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(dx), n_out, n_in))

@@ -309,10 +309,19 @@ struct Conv2DGate : Gate {
 struct MaxPool2DGate : Gate {
   std::shared_ptr<DeviceBuf> indices;
   std::vector<int> in_shape;
+  bool tiles_2x2 = false;  // 2x2 window, stride 2, no padding, H % 2 = 0, W % 4 = 0: the direct kernel applies
+  bool after_relu = false; // the input is a ReLU's output: its backward is fused (needs `pooled`)
+  Tensor pooled;
   std::vector<Tensor> backward(const Tensor& g) override {
     Session* s = g.session();
     Tensor dx = Tensor::empty(s, in_shape);
-    s->check(vtlb_maxpool2d_bwd_f32(s->ctx, g.data(), indices->ptr, dx.data(), g.size(), dx.size()));
+    if (tiles_2x2) {
+      s->check(vtlb_maxpool2x2_bwd_f32(s->ctx, g.data(), indices->ptr, after_relu ? pooled.data() : nullptr, dx.data(),
+                                       in_shape[0], in_shape[1], in_shape[2], in_shape[3]));
+      dx.relu_masked = after_relu;  // the ReLU gate in front hands it through
+    } else {
+      s->check(vtlb_maxpool2d_bwd_f32(s->ctx, g.data(), indices->ptr, dx.data(), g.size(), dx.size()));
+    }
     return {dx};
   }
 };
@@ -487,6 +496,7 @@ VarPtr Conv2DLayer::run(const VarPtr& input, bool relu) {
   VarPtr mid = ctx->variable(pre);
   ctx->register_node("Conv2D", std::move(gate), mid, {input, weight, bias});
   VarPtr out = ctx->variable(y);
+  out->relu_cache = pre;
   auto rg = std::make_unique<ReLUGate>();
   rg->cache = pre;
   ctx->register_node("ReLU", std::move(rg), out, {mid});
@@ -513,6 +523,11 @@ VarPtr MaxPool2DLayer::forward(const VarPtr& input) {
   auto g = std::make_unique<MaxPool2DGate>();
   g->indices = idx;
   g->in_shape = xs;
+  g->tiles_2x2 = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && xs[2] % 2 == 0 && xs[3] % 4 == 0 &&
+                 input->value.size() < 0x7fffffffu;
+  // only a ReLU that feeds nothing but this pool may be skipped: its gate sees exactly this gradient
+  g->after_relu = g->tiles_2x2 && input->relu_cache.defined() && input->relu_cache.size() == input->value.size();
+  if (g->after_relu) g->pooled = y;
   ctx->register_node("MaxPool2D", std::move(g), out, {input});
   return out;
 }
