@@ -268,11 +268,11 @@ int vtlb_maxpool2d_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, vo
                            size_t n_in);
 /* The same backward for the 2x2 window with stride 2 and no padding (H % 2 = 0, W % 4 = 0, 16-byte
  * aligned pointers): the windows tile the input, so dX is written directly, without the zero fill
- * and the scatter.  d_y_or_null = the pooled output of the forward pass: when given, the gradient
- * of a window whose maximum is not positive is dropped, which is the backward of a ReLU standing
- * directly in front of the pool (nn/gates/activation/relu.v:21-25: max(x,0) > 0 at the winning
- * position iff x > 0 there); the result is then the gradient of that ReLU's input. */
-int vtlb_maxpool2x2_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, const void* d_y_or_null,
+ * and the scatter.  d_relu_cache_or_null = the pre-activation cached by a ReLU whose output the pool
+ * read (shaped like dX): when given, that ReLU's backward (nn/internal/activation.v:78-87: zero
+ * where the cached value is < 0) is applied in the same pass, and the result is the gradient of the
+ * ReLU's input. */
+int vtlb_maxpool2x2_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, const void* d_relu_cache_or_null,
                             void* d_dx, int B, int C, int H, int W);
 
 /* ---- losses ---------------------------------------------------------------

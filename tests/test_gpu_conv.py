@@ -110,11 +110,14 @@ def test_conv2d_split_k_path(dev, orc):
 @pytest.mark.parametrize("shape", [(2, 3, 6, 8), (4, 64, 32, 32), (1, 1, 2, 4), (3, 5, 10, 12)])
 def test_maxpool2x2_backward_direct_and_with_relu(dev, orc, shape):
     """The tiling 2x2 window: dX written directly equals the scatter onto zeros bit for bit; with the
-    pooled output handed in it equals scatter followed by the backward of a ReLU in front of the pool."""
+    cache of a ReLU in front of the pool it equals scatter followed by that ReLU's backward -- which
+    zeroes where the cache is negative and lets the gradient pass where it is exactly zero."""
     rng = np.random.default_rng(sum(shape) + 1)
     pre = rng.standard_normal(shape).astype(np.float32)
     pre[0, 0, 0, :2] = -1.0
     pre[0, 0, 1, :2] = [-0.5, -2.0]  # a window that is negative throughout: its gradient must vanish
+    pre[0, 0, 0, 2:4] = [0.0, -1.0]
+    pre[0, 0, 1, 2:4] = [-3.0, -0.25]  # the winner of this window is an exact zero: the gradient passes
     x = orc.relu_f32(pre)
     ry, ridx = orc.maxpool2d_fwd_f32(x, (2, 2), (0, 0), (2, 2))
     B, C, H, W = shape
@@ -127,10 +130,13 @@ def test_maxpool2x2_backward_direct_and_with_relu(dev, orc, shape):
     dev.maxpool2x2_bwd_f32(dg, didx, None, out, B, C, H, W)
     scat = orc.maxpool2d_bwd_f32(g, ridx, shape)
     assert np.array_equal(out.numpy().view(np.uint32), scat.view(np.uint32))
-    dev.maxpool2x2_bwd_f32(dg, didx, dy, out, B, C, H, W)
+    dpre = dev.to_device(pre)
+    dev.maxpool2x2_bwd_f32(dg, didx, dpre, out, B, C, H, W)
     ref = orc.relu_bwd_f32(scat, pre)
     assert np.array_equal(out.numpy(), ref)
-    assert out.numpy()[0, 0, :2, :2].any() == False  # noqa: E712
+    assert not out.numpy()[0, 0, :2, :2].any()
+    # relu(window) = [0, 0; 0, 0]: the first position wins, and its pre-activation is 0, not negative
+    assert ridx[0, 0, 0, 1] == 2 and out.numpy()[0, 0, 0, 2] == g[0, 0, 0, 1] != 0.0
     from vtl_b200 import capi
     with pytest.raises(capi.VtlbError):
         dev.maxpool2x2_bwd_f32(dg, didx, None, out, B, C, H, W + 2)

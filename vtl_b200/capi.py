@@ -439,9 +439,9 @@ class Device:
         self._ck(self.lib.vtlb_maxpool2d_fwd_f32(self.h, _ptr(x), _ptr(y), _ptr(idx), B, Cc, H, W, kh, kw,
                                                  ph, pw, sh, sw))
 
-    def maxpool2x2_bwd_f32(self, g, idx, y, dx, B, Cc, H, W):
-        """y (the pooled output) or None; with y the backward of a ReLU in front of the pool is fused."""
-        self._ck(self.lib.vtlb_maxpool2x2_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(y), _ptr(dx), B, Cc, H, W))
+    def maxpool2x2_bwd_f32(self, g, idx, relu_cache, dx, B, Cc, H, W):
+        """relu_cache: the pre-activation of a ReLU in front of the pool (its backward is fused) or None."""
+        self._ck(self.lib.vtlb_maxpool2x2_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(relu_cache), _ptr(dx), B, Cc, H, W))
 
     def maxpool2d_bwd_f32(self, g, idx, dx, n_out, n_in):
         self._ck(self.lib.vtlb_maxpool2d_bwd_f32(self.h, _ptr(g), _ptr(idx), _ptr(dx), n_out, n_in))

@@ -394,11 +394,12 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
 
 // Backward of the 2x2 / stride 2 / no padding window.  The windows tile the input, so every input
 // element has exactly one window: dX is written directly (no zero fill, no scatter), items as in
-// the forward kernel.  With `y` (the pooled output) the gradient of a window whose maximum is not
-// positive is dropped: when a ReLU feeds the pool, max(pre, 0) > 0 at the winning position is
-// pre > 0 there, which is that ReLU's backward -- fused, it saves a pass over the full-size tensor.
+// the forward kernel.  With `c` (the pre-activation cached by a ReLU whose output the pool read)
+// that ReLU's backward is applied as well: only the winning position of a window carries a
+// gradient, and it is dropped where c there is negative (the reference's comparison: zero and NaN
+// pass) -- one gathered read instead of another pass over the full-size tensor.
 __global__ void __launch_bounds__(256) maxpool2x2_bwd_kernel(const float* __restrict__ g, const int32_t* __restrict__ idx,
-                                                             const float* __restrict__ y, float* __restrict__ dx,
+                                                             const float* __restrict__ c, float* __restrict__ dx,
                                                              int planes, int H, int W) {
   asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done from here on
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -413,10 +414,9 @@ __global__ void __launch_bounds__(256) maxpool2x2_bwd_kernel(const float* __rest
     const int o = (nc * OH + h) * OW + 2 * j;
     float2 gv = __ldg(reinterpret_cast<const float2*>(g + o));
     const int2 t = __ldg(reinterpret_cast<const int2*>(idx + o));
-    if (y) {
-      const float2 yv = __ldg(reinterpret_cast<const float2*>(y + o));
-      if (!(yv.x > 0.0f)) gv.x = 0.0f;
-      if (!(yv.y > 0.0f)) gv.y = 0.0f;
+    if (c) {
+      if (__ldg(c + t.x) < 0.0f) gv.x = 0.0f;
+      if (__ldg(c + t.y) < 0.0f) gv.y = 0.0f;
     }
     const int p0 = t.x - f0, p1 = t.y - f0;
     float4 a, b;
@@ -684,19 +684,19 @@ VTLB_API int vtlb_maxpool2d_fwd_f32(vtlb_ctx* ctx, const void* d_x, void* d_y, v
   return VTLB_OK;
 }
 
-VTLB_API int vtlb_maxpool2x2_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, const void* d_y_or_null,
+VTLB_API int vtlb_maxpool2x2_bwd_f32(vtlb_ctx* ctx, const void* d_g, const void* d_idx, const void* d_relu_cache_or_null,
                                      void* d_dx, int B, int C, int H, int W) {
   VTLB_ENTER(ctx);
   if (!d_g || !d_idx || !d_dx) return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2x2_bwd_f32: null pointer");
   if (B < 0 || C <= 0 || H <= 0 || W <= 0 || (W & 3) || (H & 1) || (size_t)B * C * H * W > 0x7fffffffu)
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2x2_bwd_f32: needs H %% 2 = 0, W %% 4 = 0, < 2^31 elements (got %dx%dx%dx%d)",
                      B, C, H, W);
-  if (!vtlb_aligned16(d_g) || !vtlb_aligned16(d_idx) || !vtlb_aligned16(d_dx) || (d_y_or_null && !vtlb_aligned16(d_y_or_null)))
+  if (!vtlb_aligned16(d_g) || !vtlb_aligned16(d_idx) || !vtlb_aligned16(d_dx))
     return vtlb_fail(ctx, VTLB_EINVAL, "vtlb_maxpool2x2_bwd_f32: pointers must be 16-byte aligned");
   const size_t n = (size_t)B * C * (H / 2) * (W / 4);
   if (n == 0) return VTLB_OK;
   VTLB_CUDA(ctx, vtlb_launch_early(maxpool2x2_bwd_kernel, dim3(f32::grid_for(ctx, n, 1024)), dim3(256), 0, ctx->stream,
-                                   (const float*)d_g, (const int32_t*)d_idx, (const float*)d_y_or_null, (float*)d_dx,
+                                   (const float*)d_g, (const int32_t*)d_idx, (const float*)d_relu_cache_or_null, (float*)d_dx,
                                    B * C, H, W));
   VTLB_LAUNCHED(ctx);
   return VTLB_OK;

@@ -310,15 +310,15 @@ struct MaxPool2DGate : Gate {
   std::shared_ptr<DeviceBuf> indices;
   std::vector<int> in_shape;
   bool tiles_2x2 = false;  // 2x2 window, stride 2, no padding, H % 2 = 0, W % 4 = 0: the direct kernel applies
-  bool after_relu = false; // the input is a ReLU's output: its backward is fused (needs `pooled`)
-  Tensor pooled;
+  Tensor relu_cache;       // the input is a ReLU's output: its backward is fused (its cached pre-activation)
   std::vector<Tensor> backward(const Tensor& g) override {
     Session* s = g.session();
     Tensor dx = Tensor::empty(s, in_shape);
     if (tiles_2x2) {
-      s->check(vtlb_maxpool2x2_bwd_f32(s->ctx, g.data(), indices->ptr, after_relu ? pooled.data() : nullptr, dx.data(),
-                                       in_shape[0], in_shape[1], in_shape[2], in_shape[3]));
-      dx.relu_masked = after_relu;  // the ReLU gate in front hands it through
+      s->check(vtlb_maxpool2x2_bwd_f32(s->ctx, g.data(), indices->ptr,
+                                       relu_cache.defined() ? relu_cache.data() : nullptr, dx.data(), in_shape[0],
+                                       in_shape[1], in_shape[2], in_shape[3]));
+      dx.relu_masked = relu_cache.defined();  // the ReLU gate in front hands it through
     } else {
       s->check(vtlb_maxpool2d_bwd_f32(s->ctx, g.data(), indices->ptr, dx.data(), g.size(), dx.size()));
     }
@@ -525,9 +525,8 @@ VarPtr MaxPool2DLayer::forward(const VarPtr& input) {
   g->in_shape = xs;
   g->tiles_2x2 = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && xs[2] % 2 == 0 && xs[3] % 4 == 0 &&
                  input->value.size() < 0x7fffffffu;
-  // only a ReLU that feeds nothing but this pool may be skipped: its gate sees exactly this gradient
-  g->after_relu = g->tiles_2x2 && input->relu_cache.defined() && input->relu_cache.size() == input->value.size();
-  if (g->after_relu) g->pooled = y;
+  if (g->tiles_2x2 && input->relu_cache.defined() && input->relu_cache.size() == input->value.size())
+    g->relu_cache = input->relu_cache;
   ctx->register_node("MaxPool2D", std::move(g), out, {input});
   return out;
 }
