@@ -74,6 +74,9 @@ class ShardedInt8MLP:
                 L["q_all_ptr"] = L["q_all"].ptr
             self.layers.append(L)
         if self.push:
+            # row maxima are all-reduced beside the copies, not queued behind them
+            if os.environ.get("VTLB_C5_SMALL_LANE", "1") != "0":
+                dev.comm_small_lane()
             # every rank's handles -> the address of each peer's buffer in this process
             table = exchange([L.get("handle") for L in self.layers])
             for li, L in enumerate(self.layers):

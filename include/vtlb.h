@@ -461,6 +461,10 @@ int vtlb_comm_destroy(vtlb_ctx* ctx);
 int vtlb_allreduce_sum_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
 int vtlb_allreduce_max_f32_async(vtlb_ctx* ctx, void* d_buf, size_t n);
 int vtlb_allgather_async(vtlb_ctx* ctx, const void* d_send, void* d_recv, size_t bytes_per_rank);
+/* Gives the small collectives of this communicator (vtlb_allreduce_max_f32_async) a communicator and
+ * stream of their own, VTLB_COMM_LANE_SMALL; collective, every rank calls it once after
+ * vtlb_comm_init_rank.  Without it both lanes are the same stream.  No counterpart in the reference. */
+int vtlb_comm_small_lane(vtlb_ctx* ctx);
 /* All-gather by the copy engines instead of an NCCL kernel (which occupies 16-32 SMs and slows a
  * persistent GEMM running beside it far more than its share).  Every rank allocates its receive
  * buffer with vtlb_shared_alloc (a plain device allocation plus its 64-byte CUDA IPC handle), ships

@@ -111,6 +111,7 @@ _PROTOS = {
     "vtlb_allreduce_max_f32_async": [_vp, _vp, _sz],
     "vtlb_allgather_async": [_vp, _vp, _vp, _sz],
     "vtlb_int8_issue_yardstick": [_vp, _i, C.POINTER(C.c_double)],
+    "vtlb_comm_small_lane": [_vp],
     "vtlb_shared_alloc": [_vp, _sz, C.POINTER(_vp), _vp], "vtlb_shared_free": [_vp, _vp],
     "vtlb_shared_open": [_vp, _vp, C.POINTER(_vp)], "vtlb_shared_close": [_vp, _vp],
     "vtlb_allgather_push_async": [_vp, _vp, C.POINTER(_vp), _i, _sz],
@@ -560,6 +561,10 @@ class Device:
         self._ck(self.lib.vtlb_allgather_async(self.h, _ptr(send), _ptr(recv), bytes_per_rank))
 
     LANE_BULK, LANE_SMALL = 0, 1
+
+    def comm_small_lane(self):
+        """A communicator and stream of their own for the small collectives (every rank calls it)."""
+        self._ck(self.lib.vtlb_comm_small_lane(self.h))
 
     # -- all-gather by copy engines: buffers that the other ranks' processes can write
     def shared_alloc(self, nbytes: int):

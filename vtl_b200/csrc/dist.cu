@@ -78,6 +78,22 @@ VTLB_API int vtlb_comm_unique_id(void* h_id128) {
   return VTLB_OK;
 }
 
+namespace {
+bool open_small_lane(vtlb_ctx* ctx) {
+  if (ctx->comm_small) return true;
+  if (!g_nccl.CommSplit || ctx->nranks < 2) return false;
+  ncclComm_t small = nullptr;
+  if (g_nccl.CommSplit((ncclComm_t)ctx->comm, 0, ctx->rank, &small, nullptr) != ncclSuccess || !small) return false;
+  if (cudaStreamCreateWithFlags(&ctx->comm_small_stream, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    g_nccl.CommDestroy(small);
+    return false;
+  }
+  ctx->comm_small = small;
+  return true;
+}
+}  // namespace
+
 VTLB_API int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void* h_id128) {
   VTLB_ENTER(ctx);
   if (nranks < 1 || rank < 0 || rank >= nranks || !h_id128)
@@ -98,17 +114,21 @@ VTLB_API int vtlb_comm_init_rank(vtlb_ctx* ctx, int nranks, int rank, const void
     const char* e = getenv("VTLB_COMM_TWO_LANES");
     two_lanes = e ? atoi(e) != 0 : 0;  // off by default: on 2 GPUs two NCCL kernels at once cost the GEMMs more than the queueing
   }
-  if (two_lanes && g_nccl.CommSplit && nranks > 1) {
-    ncclComm_t small = nullptr;
-    if (g_nccl.CommSplit(comm, 0, rank, &small, nullptr) == ncclSuccess && small) {
-      if (cudaStreamCreateWithFlags(&ctx->comm_small_stream, cudaStreamNonBlocking) == cudaSuccess) {
-        ctx->comm_small = small;
-      } else {
-        cudaGetLastError();
-        g_nccl.CommDestroy(small);
-      }
-    }
-  }
+  if (two_lanes) open_small_lane(ctx);
+  return VTLB_OK;
+}
+
+// A lane of its own for the small collectives of this communicator (collective: every rank calls it).
+// Worth it when the bulk lane carries copy-engine transfers (vtlb_allgather_push_async): a 32 KB
+// all-reduce then runs beside them instead of queueing behind 200 MB of copies.  Beside NCCL's own
+// bulk kernels it measured no gain (two NCCL kernels at once cost the GEMMs as much as the queueing).
+VTLB_API int vtlb_comm_small_lane(vtlb_ctx* ctx) {
+  VTLB_ENTER(ctx);
+  int rc = need_comm(ctx, __func__);
+  if (rc) return rc;
+  if (ctx->comm_small || ctx->nranks < 2) return VTLB_OK;
+  if (!g_nccl.CommSplit) return vtlb_fail(ctx, VTLB_ESTATE, "vtlb_comm_small_lane: this NCCL has no ncclCommSplit");
+  if (!open_small_lane(ctx)) return vtlb_fail(ctx, VTLB_ECUDA, "vtlb_comm_small_lane: could not split the communicator");
   return VTLB_OK;
 }
 
@@ -251,7 +271,9 @@ VTLB_API int vtlb_allgather_push_async(vtlb_ctx* ctx, const void* d_src, void* c
   }
   if ((rc = comm_after_compute(ctx))) return rc;
   // rank r starts with peer r + 1: at every moment the ranks write to different receivers, so no
-  // receiver's link carries more than one copy at a time
+  // receiver's link carries more than one copy at a time.  (Dealing the seven copies of a push to two
+  // or four streams, so that they overlap, breaks exactly that: 2.39 -> 3.11 / 3.25 ms per forward
+  // of the column-sharded MLP on 8 GPUs.)
   for (int i = 1; i <= npeers; ++i) {
     const int r = (ctx->rank + i) % npeers;
     if (d_peer_dst[r] && bytes)
