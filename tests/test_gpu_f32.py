@@ -167,6 +167,32 @@ def test_linear_planes_handed_from_producer_to_consumer(dev, orc, M, N, K):
         dev.set_small_gemm_limit(1.4e8)
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 10, 256), (33, 7, 100), (256, 10, 16384), (48, 256, 784), (32, 1024, 64)])
+def test_relu_mask_on_the_cuda_core_routes(dev, M, N, K):
+    """The ReLU backward handed to a small dX product (in the CUDA-core kernel's epilogue, cluster
+    exchange and partial-buffer variants alike) and to a narrow layer (a pass behind the streaming
+    kernel) equals vtlb_relu_bwd_f32 on the unmasked dX, bit for bit; zeros in the cache pass."""
+    dev.set_small_gemm_limit(1.4e8)
+    rng = np.random.default_rng(M * 7 + N + K)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) * 0.1).astype(np.float32)
+    G = rng.standard_normal((M, N)).astype(np.float32)
+    Pre = rng.standard_normal((M, K)).astype(np.float32)
+    Pre[0, :3] = [0.0, -0.0, -1.0]
+    dX_, dW_, dG_, dPre = (dev.to_device(a) for a in (X, W, G, Pre))
+    gx0, gw0, gb0 = dev.zeros((M, K)), dev.zeros((N, K)), dev.zeros(N)
+    dev.linear_bwd_f32(dG_, dX_, dW_, gx0, gw0, gb0, M, N, K)
+    want = dev.zeros((M, K))
+    dev.relu_bwd_f32(gx0, dPre, want, M * K)
+    gx1, gw1, gb1 = dev.to_device(np.full((M, K), 3.0, np.float32)), dev.zeros((N, K)), dev.zeros(N)
+    dev.linear_bwd_f32_planes(dG_, dX_, dW_, gx1, gw1, gb1, M, N, K, relu_mask_src=dPre)
+    assert dev.check_status() == 0
+    assert np.array_equal(gx1.numpy().view(np.uint32), want.numpy().view(np.uint32))
+    assert np.array_equal(gw1.numpy().view(np.uint32), gw0.numpy().view(np.uint32))
+    assert np.array_equal(gb1.numpy().view(np.uint32), gb0.numpy().view(np.uint32))
+    assert gx1.numpy()[0, 2] == 0.0 and gx1.numpy()[0, 0] == gx0.numpy()[0, 0]
+
+
 def test_linear_planes_argument_errors(dev):
     from vtl_b200.capi import VtlbError, EINVAL
     x, w, y = dev.zeros((8, 8)), dev.zeros((8, 8)), dev.zeros((8, 8))

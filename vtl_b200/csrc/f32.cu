@@ -200,7 +200,9 @@ int gemm_f32_impl(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, co
   const int ld_rows = vtlb_plane_ld(N), ld_cols = vtlb_plane_ld(M);
   int rc, fused = 0;
   if (2.0 * M * N * K <= ctx->small_gemm_flops) {  // launch-latency-bound sizes: CUDA cores, no split passes
-    if ((rc = f32::sgemm_small(ctx, transA, transB, M, N, K, A, B, C, bias, relu, pre))) return rc;
+    if ((rc = f32::sgemm_small(ctx, transA, transB, M, N, K, A, B, C, bias, relu, pre, nullptr, nullptr, ex.mask)))
+      return rc;
+    if (ex.mask) fused |= 2;  // the mask is part of that kernel's epilogue
   } else {
     f32::Planes p;
     if ((rc = f32::alloc_planes(ctx, ex.a_planes ? 0 : M, ex.b_planes ? 0 : N, K, 0, &p))) return rc;
@@ -337,10 +339,13 @@ int linear_bwd_impl(vtlb_ctx* ctx, const char* fn, const void* d_G, const void* 
   if (!d_dX_or_null && (d_relu_mask_src_or_null || dx_rows || dx_cols))
     return vtlb_fail(ctx, VTLB_EINVAL, "%s: a mask or dX planes were given without a dX output", fn);
   // a layer with few output features and many inputs: memory-bound kernels that stream X / dX once
-  const bool any_planes = g_rows || g_cols || x_cols || dx_rows || dx_cols || d_relu_mask_src_or_null;
+  const bool any_planes = g_rows || g_cols || x_cols || dx_rows || dx_cols;
   const bool narrow = !any_planes && 2.0 * M * N * K <= ctx->small_gemm_flops;
   if (narrow && d_dX_or_null && d_W && f32::narrow_linear_ok(M, N, K, d_dX_or_null, d_W, d_W)) {
     if ((rc = f32::narrow_linear_dx(ctx, (const float*)d_G, (const float*)d_W, (float*)d_dX_or_null, M, N, K))) return rc;
+    if (d_relu_mask_src_or_null &&
+        (rc = relu_mask_inplace(ctx, (float*)d_dX_or_null, (const float*)d_relu_mask_src_or_null, (size_t)M * K)))
+      return rc;
     d_dX_or_null = nullptr;
   }
   if (narrow && d_dW_or_null && d_X && f32::narrow_linear_ok(M, N, K, d_X, d_dW_or_null, d_X)) {

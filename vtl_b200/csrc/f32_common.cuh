@@ -271,10 +271,11 @@ int split_operand(vtlb_ctx* ctx, const float* src, int rows, int kdim, bool tran
 
 // C[M,N] = op(A).op(B) (+bias, pre-activation copy, ReLU) on CUDA cores, for small products.
 // With `a_rowsum` the launch also writes a_rowsum[m] = sum over k of op(A)(m, k) (f64 sums, rounded
-// once) when it can (K not cut into ranges); *rowsum_done says whether it did.
+// once) when it can (K not cut into ranges); *rowsum_done says whether it did.  With `mask` (shaped
+// like C) the result is zeroed where mask < 0: a ReLU backward on the way out.
 int sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
                 const float* B, float* C, const float* bias, int relu, float* pre,
-                float* a_rowsum = nullptr, bool* rowsum_done = nullptr);
+                float* a_rowsum = nullptr, bool* rowsum_done = nullptr, const float* mask = nullptr);
 
 // Linear layers with at most 16 output features and at least 2048 inputs (linear_narrow.cu): Y = X.W^T + b,
 // dX = G.W, dW = G^T.X with db = column sums of G (either of dW / db may be null), each streaming its

@@ -20,11 +20,14 @@ namespace {
 
 constexpr int TM = 32, TN = 64, TK = 32;
 
+// `mask` (shaped like C): the result is zeroed where mask is negative -- the backward of the ReLU
+// whose cached input mask is, applied to a dX product on its way out (nn/internal/activation.v:78-87).
 __device__ __forceinline__ void small_epilogue(float o, int m, int n, int N, const float* bias, float* pre,
-                                               int relu, float* C) {
+                                               int relu, float* C, const float* mask) {
   if (bias) o = __fadd_rn(o, bias[n]);
   if (pre) pre[(size_t)m * N + n] = o;
   if (relu && o < 0.f) o = 0.f;
+  if (mask && __ldg(mask + (size_t)m * N + n) < 0.f) o = 0.f;
   C[(size_t)m * N + n] = o;
 }
 
@@ -65,7 +68,8 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
                                                           float* __restrict__ pre, int M, int N, int K,
                                                           int k_per_split, int relu,
                                                           float* __restrict__ partial, int cluster,
-                                                          float* __restrict__ a_rowsum) {
+                                                          float* __restrict__ a_rowsum,
+                                                          const float* __restrict__ mask) {
   // NST stages of (A tile [TK][TM+1], B tile [TK][TN+4]) in dynamic shared memory, filled by
   // cp.async: the loads of up to NST K steps (a whole K range) are in flight at once, so
   // a CTA pays one global-memory latency, not one per step
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
       if (ml >= TM || m >= M || n >= N) continue;
       float s0 = Land[slot][nl];
       for (int r = 1; r < S; ++r) s0 = __fadd_rn(s0, Land[r * rows_per + slot][nl]);
-      small_epilogue(s0, m, n, N, bias, pre, relu, C);
+      small_epilogue(s0, m, n, N, bias, pre, relu, C, mask);
     }
     return;
   }
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
       if (partial)
         partial[((size_t)blockIdx.z * M + m) * N + n] = acc[r][j];
       else
-        small_epilogue(acc[r][j], m, n, N, bias, pre, relu, C);
+        small_epilogue(acc[r][j], m, n, N, bias, pre, relu, C, mask);
     }
   }
 }
@@ -196,21 +200,21 @@ __global__ void __launch_bounds__(256) sgemm_small_kernel(const float* __restric
 __global__ void __launch_bounds__(256) small_reduce_kernel(const float* __restrict__ partial, int splits,
                                                            int M, int N, const float* __restrict__ bias,
                                                            float* __restrict__ pre, int relu,
-                                                           float* __restrict__ C) {
+                                                           float* __restrict__ C, const float* __restrict__ mask) {
   asm volatile("griddepcontrol.wait;" ::: "memory");  // launched early (vtlb_launch_early): the kernel in front is done
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // a small GEMM behind this one may start early
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= M * N) return;
   float s = partial[i];
   for (int z = 1; z < splits; ++z) s = __fadd_rn(s, partial[(size_t)z * M * N + i]);
-  small_epilogue(s, i / N, i % N, N, bias, pre, relu, C);
+  small_epilogue(s, i / N, i % N, N, bias, pre, relu, C, mask);
 }
 
 }  // namespace
 
 int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K, const float* A,
                      const float* B, float* C, const float* bias, int relu, float* pre, float* a_rowsum,
-                     bool* rowsum_done) {
+                     bool* rowsum_done, const float* mask) {
   const int tiles = ((N + TN - 1) / TN) * ((M + TM - 1) / TM);
   // K ranges of `kps_want` (VTLB_SMALL_KPS overrides): the product is spread over as many SMs as
   // the cluster limit of 8 ranges allows, since a CTA that walks a long K alone is bound by its own
@@ -266,7 +270,7 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   cfg.numAttrs = pdl ? 2 : 1;
 #define VTLB_SMALL(TA, TB)                                                                               \
   VTLB_CUDA(ctx, cudaLaunchKernelEx(&cfg, sgemm_small_kernel<TA, TB>, A, B, C, bias, pre, M, N, K, kps, relu, \
-                                    partial, (int)cluster, a_rowsum))
+                                    partial, (int)cluster, a_rowsum, mask))
   if (transA && transB) VTLB_SMALL(true, true);
   else if (transA) VTLB_SMALL(true, false);
   else if (transB) VTLB_SMALL(false, true);
@@ -275,7 +279,7 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   VTLB_LAUNCHED(ctx);
   if (splits > 1 && !cluster) {
     VTLB_CUDA(ctx, vtlb_launch_early(small_reduce_kernel, dim3((M * N + 255) / 256), dim3(256), 0, ctx->stream,
-                                     (const float*)partial, splits, M, N, bias, pre, relu, C));
+                                     (const float*)partial, splits, M, N, bias, pre, relu, C, mask));
     VTLB_LAUNCHED(ctx);
   }
   return VTLB_OK;

@@ -246,7 +246,9 @@ struct LinearGate : Gate {
     const vtlb_planes* g_cols = tc && g.cols_planes ? &g.cols_planes->p : nullptr;
     const vtlb_planes* x_cols = tc && xin.cols_planes ? &xin.cols_planes->p : nullptr;
     const float* mask = nullptr;
-    if (dX.defined() && tc && input->relu_cache.defined() && input->relu_cache.size() == dX.size()) {
+    // (every route of the library applies the mask: in the epilogue of the tensor-core and the small
+    // CUDA-core product, as a pass of its own behind the streaming kernel for narrow layers)
+    if (dX.defined() && s->pass_planes && input->relu_cache.defined() && input->relu_cache.size() == dX.size()) {
       mask = input->relu_cache.data();
       dX.relu_masked = true;
     }
