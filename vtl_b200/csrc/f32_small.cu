@@ -230,6 +230,19 @@ int f32::sgemm_small(vtlb_ctx* ctx, int transA, int transB, int M, int N, int K,
   int kps = (K + splits - 1) / splits;
   kps = (kps + TK - 1) / TK * TK;
   splits = (K + kps - 1) / kps;
+  // A few ranges more than a cluster holds (config 1's first layer: K = 784 = 13 ranges of 64) go
+  // through the partial buffer and a second launch.  VTLB_SMALL_CLUSTER_CAP=1 makes the ranges long
+  // enough to fit one cluster instead, which saves that launch and measured slower (config 1: 46.6
+  // against 46.1 us per step -- the longer K walk costs more than the early-launched reduction).
+  static int cap = -1;
+  if (cap < 0) {
+    const char* e = getenv("VTLB_SMALL_CLUSTER_CAP");
+    cap = e ? atoi(e) != 0 : 0;
+  }
+  if (cap && splits > kMaxClusterSplits && splits <= 2 * kMaxClusterSplits) {
+    kps = ((K + kMaxClusterSplits - 1) / kMaxClusterSplits + TK - 1) / TK * TK;
+    splits = (K + kps - 1) / kps;
+  }
   const bool cluster = splits > 1 && splits <= kMaxClusterSplits;
   if (splits > 1) a_rowsum = nullptr;  // the by-product needs the whole K in one CTA
   if (rowsum_done) *rowsum_done = a_rowsum != nullptr;
