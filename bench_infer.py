@@ -87,11 +87,15 @@ class ShardedInt8MLP:
             exchange(0)  # all handles are open before any rank can start pushing
         self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
 
-    def close(self):
-        """Unmaps the peers' buffers and frees this rank's (after the device has gone idle)."""
+    def close(self, barrier=None):
+        """Unmaps the peers' buffers, then frees this rank's.  Call it on every rank once no rank is
+        still copying; `barrier` (a host barrier over the ranks) separates the two halves, because an
+        exported buffer must not be freed while another process still has it mapped."""
         for p in self._opened:
             self.dev.shared_close(p)
         self._opened = []
+        if barrier is not None and self._shared:
+            barrier()
         for p in self._shared:
             self.dev.shared_free(p)
         self._shared = []
@@ -295,7 +299,7 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
             out["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     dev.sync()
     ranks.barrier()  # no rank is still copying into a peer's buffer
-    model.close()
+    model.close(ranks.barrier)
     dev.close()
     return out
 
@@ -313,7 +317,7 @@ def sharded_parity(ranks, dev, dims=(1024, 4096, 1024, 4096, 1024), tokens=512, 
     y = model.forward(dX)
     dev.sync()
     slabs = ranks.gather_objects(y.numpy())  # every rank is past its last copy into a peer's buffer
-    model.close()
+    model.close(ranks.barrier)
     if ranks.rank != 0:
         return None
     from oracle import oracle
@@ -367,7 +371,7 @@ def run_tp(ranks, tools, steps=10, warmup=3):
     dev.sync()
     ranks.barrier()  # no rank is still copying into a peer's buffer
     push = model.push
-    model.close()
+    model.close(ranks.barrier)
     dev.close()
     if ranks.rank != 0:
         return None

@@ -475,7 +475,10 @@ int vtlb_comm_small_lane(vtlb_ctx* ctx);
  * rank (vtlb_comm_mark / vtlb_comm_wait_mark / vtlb_comm_wait) every rank's part has landed in its
  * buffer.  The caller writes its own part itself.  A part may be pushed into a peer's buffer again
  * only after a later collective of this communicator has completed behind the peer's last read of
- * it (the one-word all-reduce of any later push does).  No counterpart in the reference. */
+ * it (the one-word all-reduce of any later push does).  At the end every process closes the buffers
+ * it opened (vtlb_shared_close), and only when all have done so does the owner free its own
+ * (vtlb_shared_free): an exported buffer must not be freed while another process has it mapped.
+ * No counterpart in the reference. */
 int vtlb_shared_alloc(vtlb_ctx* ctx, size_t bytes, void** d_out, void* h_handle64);
 int vtlb_shared_free(vtlb_ctx* ctx, void* d_ptr);
 int vtlb_shared_open(vtlb_ctx* ctx, const void* h_handle64, void** d_peer_out);
