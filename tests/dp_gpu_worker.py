@@ -45,7 +45,8 @@ def main():
     # by NCCL's kernel; three layers make a buffer that is pushed into again within one pass
     for gather in ("push", "nccl"):
         os.environ["VTLB_C5_GATHER"] = gather
-        for dims, chunks in (((512, 1024, 512), 2), ((256, 512, 256, 512, 256), 4)):
+        W = ranks.world  # every shard must be a multiple of 128 columns wide
+        for dims, chunks in (((256 * W, 512 * W, 256 * W), 2), ((128 * W, 256 * W, 128 * W, 256 * W, 128 * W), 4)):
             par = bench_infer.sharded_parity(ranks, dev, dims=dims, tokens=256, chunks=chunks)
             if ranks.rank == 0:
                 assert par["bit_exact"], (gather, par)
