@@ -643,10 +643,15 @@ def main():
             import bench_infer
             import bench_train
             me = sys.modules[__name__]
-            dp = bench_train.run_dp(ranks, me)
-            tp = bench_infer.run_tp(ranks, me)
+            extra = {}
+            for key, fn in (("dp_train", bench_train.run_dp), ("tp_infer", bench_infer.run_tp)):
+                try:
+                    extra[key] = fn(ranks, me)
+                except Exception as e:  # the headline above stands; the failure is reported in its place
+                    extra[key] = {"error": f"{type(e).__name__}: {e}"}
+                    print(f"bench: {key} failed on rank {ranks.rank}: {e}", file=sys.stderr)
             if out is not None:
-                out["dp_train"], out["tp_infer"] = dp, tp
+                out.update(extra)
     elif args.workload == "int8_mlp_c5":
         import bench_infer
         if args.impl == "reference":

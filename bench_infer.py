@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes as C
 import os
 import statistics
+import sys
 import time
 
 import numpy as np
@@ -63,29 +64,63 @@ class ShardedInt8MLP:
             dW.free()
             L = dict(K=K, N=N, n=n, Wq=dQ, sw=dS, bias=dev.to_device(b),
                      Y=dev.zeros((tokens, n)), amax=dev.zeros(tokens), sa=dev.zeros(tokens))
-            # per row block: the gathered shards [world][Mc][n]
-            if self.push and li + 1 < len(dims) - 1:
-                ptr, handle = dev.shared_alloc(self.C * world * self.Mc * n)
+            self.layers.append(L)
+        hidden = self.layers[:-1]  # the layers whose output is exchanged
+        if self.push and not self._open_shared(hidden, exchange):
+            self.push = False      # every rank took the same decision: NCCL's all-gather instead
+            print("bench_infer: gather buffers could not be shared between the ranks' processes; "
+                  "using NCCL's all-gather", file=sys.stderr)
+        for L in self.layers:
+            if "q_all_ptr" not in L:
+                # per row block: the gathered shards [world][Mc][n]
+                L["q_local"] = dev.zeros((tokens, L["n"]), np.int8)
+                L["q_all"] = dev.zeros((self.C, world, self.Mc, L["n"]), np.int8)
+                L["q_all_ptr"] = L["q_all"].ptr
+        self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
+
+    def _open_shared(self, hidden, exchange) -> bool:
+        """Allocates this rank's gather buffers, ships their handles and opens the peers'.  After
+        each of the two steps the ranks tell each other whether it worked, so that either all of
+        them use the copy-engine route or none does; on failure everything is undone."""
+        from vtl_b200.capi import VtlbError
+        dev, R = self.dev, self.R
+        inject = os.environ.get("VTLB_C5_FAIL_SHARING") == str(self.rank)  # failure made on the host, for tests
+        ok = True
+        try:
+            if inject:
+                raise VtlbError(-1, "injected")
+            for L in hidden:
+                ptr, handle = dev.shared_alloc(self.C * R * self.Mc * L["n"])
                 self._shared.append(ptr)
                 L["q_all_ptr"], L["handle"] = ptr, handle
-            else:
-                L["q_local"] = dev.zeros((tokens, n), np.int8)
-                L["q_all"] = dev.zeros((self.C, world, self.Mc, n), np.int8)
-                L["q_all_ptr"] = L["q_all"].ptr
-            self.layers.append(L)
-        if self.push:
-            # row maxima are all-reduced beside the copies, not queued behind them
-            if os.environ.get("VTLB_C5_SMALL_LANE", "1") != "0":
-                dev.comm_small_lane()
-            # every rank's handles -> the address of each peer's buffer in this process
-            table = exchange([L.get("handle") for L in self.layers])
-            for li, L in enumerate(self.layers):
-                if "handle" not in L:
-                    continue
-                L["peers"] = [None if r == rank else dev.shared_open(table[r][li]) for r in range(world)]
-                self._opened += [p for p in L["peers"] if p]
-            exchange(0)  # all handles are open before any rank can start pushing
-        self.q_in, self.sa_in = dev.zeros((tokens, dims[0]), np.int8), dev.zeros(tokens)
+        except VtlbError:
+            ok = False
+        if all(exchange(ok)):
+            table = exchange([L["handle"] for L in hidden])
+            try:
+                for li, L in enumerate(hidden):
+                    L["peers"] = []
+                    for r in range(R):
+                        L["peers"].append(None if r == self.rank else dev.shared_open(table[r][li]))
+                        if L["peers"][-1]:
+                            self._opened.append(L["peers"][-1])
+            except VtlbError:
+                ok = False
+            if all(exchange(ok)):  # also: all handles are open before any rank can start pushing
+                # row maxima are all-reduced beside the copies, not queued behind them
+                if os.environ.get("VTLB_C5_SMALL_LANE", "1") != "0":
+                    dev.comm_small_lane()
+                return True
+        for p in self._opened:
+            dev.shared_close(p)
+        exchange(0)  # nobody has a peer's buffer mapped any more (every rank gets here, with or without buffers)
+        for p in self._shared:
+            dev.shared_free(p)
+        self._opened, self._shared = [], []
+        for L in hidden:
+            for k in ("q_all_ptr", "handle", "peers"):
+                L.pop(k, None)
+        return False
 
     def close(self, barrier=None):
         """Unmaps the peers' buffers, then frees this rank's.  Call it on every rank once no rank is
@@ -280,10 +315,10 @@ def run(args, ranks, ClockSampler, peaks, cuda_sync):
                                       "16384 tokens ~N(0,1), per-row dynamic activation quantisation, ReLU between "
                                       "layers (baseline config 5)",
                           "tokens": TOKENS, "tokens_per_s": TOKENS / (ms_step * 1e-3),
-                          "parallelism": f"output columns sharded x{ranks.world}; per layer all-reduce(max) of row "
-                                         "maxima (NCCL) and all-gather of int8 codes (copy engines into "
-                                         "the peers' buffers)" if ranks.world > 1
-                          else "single GPU",
+                          "parallelism": (f"output columns sharded x{ranks.world}; per layer all-reduce(max) of row "
+                                          "maxima (NCCL) and all-gather of int8 codes ("
+                                          + ("copy engines into the peers' buffers" if model.push else "NCCL") + ")")
+                          if ranks.world > 1 else "single GPU",
                           "l2": "weights (4 x 235 MB int8) and activations exceed the 126 MB L2"},
                "e2e": {"value": total_ops() / (e2e_ms / esteps * 1e-3) / 1e12, "unit": "TOPS",
                        "h2d_bytes_per_step": int(X.nbytes), "d2h_bytes_per_step": int(out_bytes),
