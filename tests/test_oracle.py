@@ -220,3 +220,20 @@ def test_initialiser_restatement(orc):
     g = orc.init_normal_f32(n, 0.0, 2.0, 4)
     assert abs(g.mean()) < 0.02 and abs(g.std() - 2.0) < 0.02
     assert np.array_equal(orc.init_normal_f32(10, 0.0, 2.0, 4), g[:10])  # element i depends on (seed, i) only
+
+
+def test_reference_optimizer_tests_hold_for_the_oracle(orc):
+    """The assertions of the reference's own optimizer tests, on the oracle: SGD 5.0 - 0.1 * 1.0 = 4.9
+    (nn/optimizers/optimizer_test.v:16-27) and the Adam f32 / f64 steps from zero moments moving theta
+    down and the first moment up (optimizer_test.v:39-67: grad [1, 2], theta [5, 5], beta 0.9 / 0.999,
+    lr_t 0.001, eps 1e-8)."""
+    theta = orc.sgd_step_f32(np.array([1.0], np.float32), np.array([5.0], np.float32), 0.1)
+    assert abs(float(theta[0]) - 4.9) < 1e-6
+    g = [1.0, 2.0]
+    for step, dt in ((orc.adam_step_f32, np.float32), (orc.adam_step_f64, np.float64)):
+        th, m, v = step(np.array(g, dt), np.array([5.0, 5.0], dt), np.zeros(2, dt), np.zeros(2, dt),
+                        0.9, 0.999, 0.001, 1e-8)
+        assert th[0] < 5.0 and th[1] < 5.0 and m[0] > 0.0
+        # first step from zero moments: m = 0.1 g, v = 0.001 g^2, so theta moves by lr_t * 0.1 / sqrt(0.001)
+        want = 5.0 - 0.001 * (0.1 * np.array(g)) / (np.sqrt(0.001 * np.array(g) ** 2) + 1e-8)
+        assert np.allclose(th, want, rtol=0, atol=2e-6 if dt == np.float32 else 1e-12)
