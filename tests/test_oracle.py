@@ -237,3 +237,32 @@ def test_reference_optimizer_tests_hold_for_the_oracle(orc):
         # first step from zero moments: m = 0.1 g, v = 0.001 g^2, so theta moves by lr_t * 0.1 / sqrt(0.001)
         want = 5.0 - 0.001 * (0.1 * np.array(g)) / (np.sqrt(0.001 * np.array(g) ** 2) + 1e-8)
         assert np.allclose(th, want, rtol=0, atol=2e-6 if dt == np.float32 else 1e-12)
+
+
+def test_inputs_of_the_reference_device_comparison_tests(orc):
+    """The reference compares its GPU paths with its CPU functions on a few fixed inputs.  The inputs
+    are simple enough for the CPU side to be worked out by hand, which pins the oracle:
+    ReLU of [[2, -1], [0.5, -3]] (nn/layers/activation_vulkan_relu_f32_d_vulkan_test.v:12-14);
+    all-ones 1x2x8x8 input and 4x2x3x3 weights, zero bias, padding 1 and 0
+    (nn/internal/conv2d_vulkan_forward_f32_d_vulkan_test.v:19-23, conv2d_vulkan_backward_f32_d_vulkan_test.v:12-34):
+    an output is 2 x (taps inside the image), a weight gradient under all-ones upstream is the number
+    of output positions whose tap falls inside the image."""
+    assert np.array_equal(orc.relu_f32(np.array([[2, -1], [0.5, -3]], np.float32)),
+                          np.array([[2, 0], [0.5, 0]], np.float32))
+    x, w, b = np.ones((1, 2, 8, 8), np.float32), np.ones((4, 2, 3, 3), np.float32), np.zeros((1, 4), np.float32)
+    y = orc.conv2d_fwd_f32(x, w, b, pad=(1, 1), stride=(1, 1))
+    assert y.shape == (1, 4, 8, 8)
+    inside = np.array([2] + [3] * 6 + [2])  # taps of a 3-wide window that fall inside an 8-long axis
+    assert np.array_equal(y[0, 0], 2.0 * np.outer(inside, inside)) and (y == y[:, :1]).all()
+    y0 = orc.conv2d_fwd_f32(x, w, b, pad=(0, 0), stride=(1, 1))
+    assert y0.shape == (1, 4, 6, 6) and (y0 == 18.0).all()
+    for pad, out in ((0, 6), (1, 8)):
+        g = np.ones((1, 4, out, out), np.float32)
+        dx, dw, db = orc.conv2d_bwd_f32(g, x, w, pad=(pad, pad), stride=(1, 1))
+        # tap (a, b) meets the image at out - |a - 1| * pad positions per axis
+        per_axis = np.array([out - pad, out, out - pad]) if pad else np.array([out] * 3)
+        assert np.array_equal(dw[0, 0], np.outer(per_axis, per_axis).astype(np.float32)) and (dw == dw[:1, :1]).all()
+        assert (db.ravel() == out * out).all()
+        # every input pixel feeds 4 channels x (windows that cover it)
+        cover = np.array([1, 2] + [3] * 4 + [2, 1]) if pad == 0 else inside
+        assert np.array_equal(dx[0, 0], 4.0 * np.outer(cover, cover)) and (dx == dx[:, :1]).all()
